@@ -1,0 +1,229 @@
+"""Generate the golden fixtures in this folder by running the REFERENCE's own code.
+
+Run where the reference checkout is available (it is not needed to run the tests):
+
+    python tests/golden/make_golden.py --reference /path/to/OmniKV
+
+It imports ``modeling.omnikv.select_tokens_by_attn_universal`` and
+``modeling.spec_cache.{OmniKVMultiStageCache, WOPackCache}`` unchanged, feeds them
+seeded inputs, and stores their outputs as small ``.npz`` / ``.json`` files.
+Nothing of the reference is copied; the import needs a few shims because the
+reference targets transformers 4.41.2:
+
+* its logger wants a git work tree with a ``debug_logs/`` folder as the current
+  directory (tiny_tools/get_code_id.py:5-28, tiny_tools/log.py:46-49) -> a scratch
+  repository under the temp dir is used as cwd while importing;
+* ``from transformers.models.llama.modeling_llama import *`` is expected to leak
+  ``torch, math, nn, F, Cache, DynamicCache, ...`` -> those names are set on that
+  module and its ``__all__`` widened before the import;
+* the 5.x ``DynamicCache`` has no ``key_cache`` list -> caches are built through
+  ``from_dynamic_cache`` on a namespace carrying the three attributes it copies;
+* ``Tensor.cuda`` is made the identity on this GPU-less host
+  (modeling/spec_cache.py:298-303 calls it on the gathered rows).
+
+Only the reference's OUTPUTS are stored; the inputs are rebuilt from the seeded
+functions of ``inputs.py`` (a checksum of them is stored beside each fixture).
+What the restatement in ``oracle/`` returns is not stored either: the tests
+recompute it, so a fixture can only come from the reference.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+import types
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+sys.path.insert(0, str(HERE))
+from inputs import (CACHE_FLOW, OPERATOR, cache_flow_inputs, checksum, operator_inputs,  # noqa: E402
+                    selector_case_list, selector_inputs)
+
+
+def import_reference(ref_root: str):
+    scratch = tempfile.mkdtemp(prefix="omnikv_ref_cwd_")
+    os.makedirs(os.path.join(scratch, "debug_logs"))
+    env = dict(os.environ, GIT_AUTHOR_NAME="g", GIT_AUTHOR_EMAIL="g@g", GIT_COMMITTER_NAME="g", GIT_COMMITTER_EMAIL="g@g")
+    subprocess.check_call(["git", "init", "-q"], cwd=scratch)
+    subprocess.check_call(["git", "commit", "-q", "--allow-empty", "-m", "scratch"], cwd=scratch, env=env)
+    os.chdir(scratch)
+    sys.path.insert(0, ref_root)
+
+    import transformers  # noqa: F401
+    import transformers.models.llama.modeling_llama as ml
+    from typing import List, Optional, Tuple, Union
+    from transformers.cache_utils import Cache, DynamicCache
+    from transformers.modeling_outputs import CausalLMOutputWithPast
+    from transformers.models.llama.configuration_llama import LlamaConfig
+
+    leak = dict(
+        LlamaConfig=LlamaConfig, math=math, F=torch.nn.functional, nn=torch.nn, torch=torch, Cache=Cache,
+        DynamicCache=DynamicCache, CausalLMOutputWithPast=CausalLMOutputWithPast, Optional=Optional,
+        Tuple=Tuple, Union=Union, List=List, CrossEntropyLoss=torch.nn.CrossEntropyLoss,
+        LLAMA_ATTENTION_CLASSES={},
+    )
+    for k, v in leak.items():
+        setattr(ml, k, v)
+    ml.__all__ = [n for n in dir(ml) if not n.startswith("_")]
+    torch.Tensor.cuda = lambda self, *a, **k: self  # GPU-less host
+
+    import modeling.omnikv as ref_omnikv
+    import modeling.spec_cache as ref_cache
+
+    return ref_omnikv, ref_cache
+
+
+class _Cfg:
+    def get(self, key, default=None):
+        return default
+
+
+class DuckAttn:
+    """The attributes select_tokens_by_attn_universal reads from ``self_attn``."""
+
+    def __init__(self, wq, wk, num_heads, num_kv_heads, head_dim, theta, layer_idx=0, identity_rope=False):
+        self.num_heads = num_heads
+        self.num_key_value_heads = num_kv_heads
+        self.num_key_value_groups = num_heads // num_kv_heads
+        self.head_dim = head_dim
+        self.layer_idx = layer_idx
+        self.config = _Cfg()
+        self._wq, self._wk, self._theta, self._id = wq, wk, theta, identity_rope
+
+    def q_proj(self, x):
+        return x @ self._wq.T
+
+    def k_proj(self, x):
+        return x @ self._wk.T
+
+    def rotary_emb(self, x, position_ids):
+        if self._id:
+            shape = (position_ids.shape[0], position_ids.shape[1], self.head_dim)
+            return torch.ones(shape), torch.zeros(shape)
+        inv_freq = 1.0 / (self._theta ** (torch.arange(0, self.head_dim, 2, dtype=torch.float32) / self.head_dim))
+        freqs = position_ids.float()[:, :, None] * inv_freq[None, None, :]
+        emb = torch.cat((freqs, freqs), dim=-1)
+        return emb.cos(), emb.sin()
+
+
+def make_selector_fixture(ref_omnikv):
+    arrays, meta = {}, []
+    for case in selector_case_list():
+        x = selector_inputs(case)
+        wq, wk, hs, kc = (torch.from_numpy(x[n]) for n in ("wq", "wk", "hs", "kc"))
+        pos = torch.full((case["B"], 1), case["pos"], dtype=torch.long)
+        attn = DuckAttn(wq, wk, case["H"], case["KVH"], case["d"], case["theta"])
+        cache = types.SimpleNamespace(key_cache=[kc])
+        for k in case["ks"]:
+            idx = ref_omnikv.select_tokens_by_attn_universal(attn, hs, pos, cache, k, case["L"], 0, case["selector"])
+            arrays[f"{case['name']}/k{k}"] = idx.numpy().astype(np.int32)
+        meta.append(dict(case, input_checksum=checksum(x.values())))
+    np.savez_compressed(HERE / "selector_small.npz", **arrays)
+    (HERE / "selector_small.json").write_text(json.dumps(meta, indent=1))
+    print("selector groups:", len(meta), "idx lists:", len(arrays))
+
+
+def make_plan_fixture(ref_cache):
+    rows = []
+    grid = [
+        (32, [2, 8, 18], 1), (32, [2, 8, 18], 2), (32, [2, 8, 18], 0), (80, [5, 20, 45], 1), (80, [5, 20, 45], 2),
+        (6, [1, 3], 1), (4, [0], 0), (4, [0], 5), (8, [7], 1), (12, [3, 4, 5], 1), (16, [0, 15], 3),
+    ]
+    for n, sel, wait in grid:
+        full = list(range(0, sel[0])) + sel + [n]
+        for cls in (ref_cache.OmniKVMultiStageCache, ref_cache.WOPackCache):
+            c = cls(full, n, wait, False)
+            rows.append(dict(cls=cls.__name__, num_layers=n, do_select=sel, wait=wait, full_attn_layers=full,
+                             layer_state={str(k): list(v) for k, v in sorted(c.layer_state.items())}))
+    (HERE / "layer_plan.json").write_text(json.dumps(rows))
+    print("plan rows:", len(rows))
+
+
+def make_cache_flow_fixture(ref_cache):
+    """Prefill -> set_idx_on_gpu -> three decode updates on a 6-layer plan, both cache classes."""
+    c = CACHE_FLOW
+    x = cache_flow_inputs()
+    n_layers, sel, wait, steps = c["n_layers"], c["sel"], c["wait"], c["steps"]
+    full = list(range(0, sel[0])) + sel + [n_layers]
+    t = lambda a: torch.from_numpy(a)  # noqa: E731
+    arrays = {}
+    for cls in (ref_cache.OmniKVMultiStageCache, ref_cache.WOPackCache):
+        dyn = types.SimpleNamespace(key_cache=[], value_cache=[], _seen_tokens=0)
+        cache = cls.from_dynamic_cache(dyn, full, n_layers, wait, False)
+        cache.stage = "prefill"
+        for i in range(n_layers):
+            cache.update(t(x["k_pre"][i]), t(x["v_pre"][i]), i)
+        for s in range(steps):
+            cache.stage = "decoding"
+            for i in range(n_layers):
+                if i in sel:
+                    cache.set_idx_on_gpu(t(x["idx"][(s, i)]), i)
+                kk, vv = cache.update(t(x["k_new"][s][i]), t(x["v_new"][s][i]), i)
+                arrays[f"{cls.__name__}/ret_k/{s}/{i}"] = kk.numpy().copy()
+                arrays[f"{cls.__name__}/ret_v/{s}/{i}"] = vv.numpy().copy()
+        arrays[f"{cls.__name__}/seen"] = np.array([cache._seen_tokens])
+    np.savez_compressed(HERE / "cache_flow.npz", **arrays)
+    flat = x["k_pre"] + x["v_pre"] + [a for r in x["k_new"] for a in r] + [a for r in x["v_new"] for a in r]
+    (HERE / "cache_flow.json").write_text(json.dumps(dict(c, full=full, input_checksum=checksum(flat))))
+    print("cache flow arrays:", len(arrays))
+
+
+def make_operator_fixture(ref_omnikv, ref_cache):
+    """The single-layer operator case through the reference: selector ``last`` (k = 1098), gather of the
+    second layer's rows by OmniKVMultiStageCache, then fp32 attention over what ``update`` returns."""
+    o = OPERATOR
+    H, KVH, d, L, W, k = o["H"], o["KVH"], o["d"], o["L"], o["W"], o["k"]
+    x = operator_inputs()
+    q = torch.from_numpy(x["q"])
+    # q_proj = identity on a [1, W, H*d] layout and an identity rotation reproduce Q exactly.
+    hs = q.transpose(1, 2).reshape(1, W, H * d)
+    attn = DuckAttn(torch.eye(H * d), torch.zeros(KVH * d, H * d), H, KVH, d, 1.0, identity_rope=True)
+    dyn = types.SimpleNamespace(key_cache=[], value_cache=[], _seen_tokens=0)
+    cache = ref_cache.OmniKVMultiStageCache.from_dynamic_cache(dyn, [0, 2], 2, 0, False)
+    cache.stage = "prefill"
+    kf = torch.from_numpy(x["k"])
+    cache.update(kf, torch.zeros_like(kf), 0)
+    cache.update(torch.from_numpy(x["k2"]), torch.from_numpy(x["v2"]), 1)
+    cache.stage = "decoding"
+    view = types.SimpleNamespace(key_cache=cache.key_cache)
+    idx = ref_omnikv.select_tokens_by_attn_universal(attn, hs[:, -1:], torch.tensor([[L]]), view, k, L, 0, "last")
+    cache.set_idx_on_gpu(idx, 0)
+    kk, vv = cache.update(torch.from_numpy(x["k_new"]), torch.from_numpy(x["v_new"]), 1)
+    assert kk.shape == (1, KVH, k + 1, d)
+    qq = q[:, :, -1, :]
+    kk = kk[:, :, None].expand(1, KVH, H // KVH, k + 1, d).reshape(1, H, k + 1, d)
+    vv = vv[:, :, None].expand(1, KVH, H // KVH, k + 1, d).reshape(1, H, k + 1, d)
+    s = torch.matmul(qq[:, :, None, :], kk.transpose(2, 3)) / math.sqrt(d)
+    out = torch.matmul(torch.softmax(s, dim=-1), vv)[:, :, 0, :]
+    # window selectors on the same inputs (all 16 window queries), k = 1098 as well
+    extra = {}
+    for sel in ("uniform", "exp"):
+        extra[f"idx_{sel}"] = ref_omnikv.select_tokens_by_attn_universal(
+            attn, hs, torch.tensor([[L]]), view, k, L, 0, sel).numpy().astype(np.int32)
+    np.savez_compressed(HERE / "operator_cfg1.npz", idx=idx.numpy().astype(np.int32), out=out.numpy(), **extra)
+    names = ("q", "k", "k2", "v2", "k_new", "v_new")
+    (HERE / "operator_cfg1.json").write_text(json.dumps(dict(o, input_checksum=checksum([x[n] for n in names]))))
+    print("operator: |idx & hot| =", len(set(idx[0].tolist()) & set(x["hot"].tolist())), "of", len(x["hot"]))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", required=True, help="path of the OmniKV checkout")
+    args = ap.parse_args()
+    ref_omnikv, ref_cache = import_reference(os.path.abspath(args.reference))
+    torch.set_num_threads(8)
+    make_selector_fixture(ref_omnikv)
+    make_plan_fixture(ref_cache)
+    make_cache_flow_fixture(ref_cache)
+    make_operator_fixture(ref_omnikv, ref_cache)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,127 @@
+"""The CPU oracle against the fixtures produced by the reference's own code."""
+import json
+import types
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import inputs as gi
+import oracle
+
+G = Path(__file__).resolve().parent / "golden"
+
+
+class _Attn:
+    def __init__(self, wq, h, kvh, d, theta):
+        self.num_heads, self.num_key_value_heads, self.head_dim, self.layer_idx = h, kvh, d, 0
+        self._wq, self._theta = wq, theta
+
+    def q_proj(self, x):
+        return x @ self._wq.T
+
+    def rotary_emb(self, x, position_ids):
+        return oracle.rope_cos_sin(position_ids, self.head_dim, self._theta)
+
+
+SEL_META = json.loads((G / "selector_small.json").read_text())
+SEL = np.load(G / "selector_small.npz")
+
+
+def _sets_match_up_to_ties(scores, got, want, k):
+    """Equal, or differing only on positions whose score ties the k-th one (torch.topk leaves ties open)."""
+    if np.array_equal(got, want):
+        return True
+    for b in range(scores.shape[0]):
+        s = scores[b]
+        kth = np.sort(s)[::-1][min(k, len(s)) - 1]
+        diff = set(got[b].tolist()) ^ set(want[b].tolist())
+        if any(abs(s[i] - kth) > 1e-6 for i in diff):
+            return False
+    return True
+
+
+@pytest.mark.parametrize("case", SEL_META, ids=[c["name"] for c in SEL_META])
+def test_selector_matches_reference(case):
+    x = gi.selector_inputs(case)
+    assert gi.checksum(x.values()) == pytest.approx(case["input_checksum"], rel=1e-12)
+    attn = _Attn(torch.from_numpy(x["wq"]), case["H"], case["KVH"], case["d"], case["theta"])
+    cache = types.SimpleNamespace(key_cache=[torch.from_numpy(x["kc"])])
+    hs = torch.from_numpy(x["hs"])
+    pos = torch.full((case["B"], 1), case["pos"], dtype=torch.long)
+    for k in case["ks"]:
+        want = SEL[f"{case['name']}/k{k}"]
+        got = oracle.select_tokens_by_attn_universal(attn, hs, pos, cache, k, case["L"], 0, case["selector"]).numpy()
+        assert got.shape == want.shape and got.dtype == np.int64
+        assert np.all(np.diff(got, axis=1) > 0)
+        if not np.array_equal(got, want):
+            # recompute the score to allow exact ties at the threshold only
+            q = attn.q_proj(hs).view(case["B"], case["W"], case["H"], case["d"]).transpose(1, 2)
+            q = oracle.apply_rope(q, *attn.rotary_emb(q, pos))
+            kc = cache.key_cache[0]
+            s = (oracle.score_last(q[:, :, -1], kc, case["L"]) if case["selector"] == "last"
+                 else oracle.score_window(q, kc, case["L"], case["selector"])).numpy()
+            assert _sets_match_up_to_ties(s, got, want, k), (case["name"], k)
+
+
+def test_layer_plan_matches_reference():
+    for row in json.loads((G / "layer_plan.json").read_text()):
+        assert oracle.omnikv_oracle.full_attn_layers_of(row["do_select"], row["num_layers"]) == row["full_attn_layers"]
+        got = oracle.layer_plan(row["full_attn_layers"], row["num_layers"], row["wait"])
+        want = {int(k): (bool(v[0]), v[1], v[2]) for k, v in row["layer_state"].items()}
+        assert got == want, row
+
+
+@pytest.mark.parametrize("cls_name", ["OmniKVMultiStageCache", "WOPackCache"])
+def test_cache_flow_matches_reference(cls_name):
+    c = json.loads((G / "cache_flow.json").read_text())
+    gold = np.load(G / "cache_flow.npz")
+    x = gi.cache_flow_inputs()
+    t = torch.from_numpy
+    cls = oracle.OracleMultiStageCache if cls_name == "OmniKVMultiStageCache" else oracle.OracleWOPackCache
+    cache = cls(c["full"], c["n_layers"], c["wait"], False)
+    for i in range(c["n_layers"]):
+        cache.update(t(x["k_pre"][i]), t(x["v_pre"][i]), i)
+    for s in range(c["steps"]):
+        cache.stage = "decoding"
+        for i in range(c["n_layers"]):
+            if i in c["sel"]:
+                cache.set_idx_on_gpu(t(x["idx"][(s, i)]), i)
+            kk, vv = cache.update(t(x["k_new"][s][i]), t(x["v_new"][s][i]), i)
+            np.testing.assert_array_equal(kk.numpy(), gold[f"{cls_name}/ret_k/{s}/{i}"])
+            np.testing.assert_array_equal(vv.numpy(), gold[f"{cls_name}/ret_v/{s}/{i}"])
+    assert cache._seen_tokens == int(gold[f"{cls_name}/seen"][0])
+
+
+def test_operator_case_matches_reference():
+    o = json.loads((G / "operator_cfg1.json").read_text())
+    gold = np.load(G / "operator_cfg1.npz")
+    x = gi.operator_inputs()
+    assert gi.checksum([x[n] for n in ("q", "k", "k2", "v2", "k_new", "v_new")]) == pytest.approx(o["input_checksum"], rel=1e-12)
+    q = torch.from_numpy(x["q"])
+    kf = torch.from_numpy(x["k"])
+    s = oracle.score_last(q[:, :, -1], kf, o["L"])
+    idx = oracle.topk_ascending(s, o["k"])
+    assert _sets_match_up_to_ties(s.numpy(), idx.numpy(), gold["idx"].astype(np.int64), o["k"])
+    out = oracle.sparse_attention(q[:, :, -1], torch.from_numpy(x["k2"]), torch.from_numpy(x["v2"]),
+                                  torch.from_numpy(gold["idx"].astype(np.int64)),
+                                  torch.from_numpy(x["k_new"]), torch.from_numpy(x["v_new"]))
+    np.testing.assert_allclose(out.numpy(), gold["out"], atol=1e-5, rtol=0)
+    for sel in ("uniform", "exp"):
+        sw = oracle.score_window(q, kf, o["L"], sel)
+        got = oracle.topk_ascending(sw, o["k"]).numpy()
+        want = gold[f"idx_{sel}"].astype(np.int64)
+        # fp32 summation order may differ: positions may differ only inside a 1e-7 band around the threshold
+        diff = set(got[0].tolist()) ^ set(want[0].tolist())
+        kth = np.sort(sw.numpy()[0])[::-1][o["k"] - 1]
+        assert all(abs(sw.numpy()[0, i] - kth) < 1e-7 for i in diff)
+
+
+def test_k_rule():
+    # int() truncation of the fractional k (the reference's rule), window bookkeeping
+    assert oracle.selector_k_rule(0.067, 16384, "last", 16, 1) == (1097, 16384, 0)
+    assert oracle.selector_k_rule(0.067, 131072, "last", 16, 5) == (8781, 131072, 0)
+    assert oracle.selector_k_rule(2048, 20000, "exp", 16, 1) == (2033, 19985, 15)
+    assert oracle.selector_k_rule(2048, 20000, "exp", 16, 40) == (2048, 20000, 0)
+    assert oracle.selector_k_rule(3, 100, "uniform", 16, 2) == (1, 86, 14)
