@@ -1,0 +1,195 @@
+/*
+ * omnikv_b200 -- C ABI of the B200 (sm_100a) kernels behind OmniKV's decode-time
+ * context selection.
+ *
+ * The reference (antgroup/OmniKV) has no native boundary: its "plugin API" is
+ * Python (modeling/omnikv.py, modeling/spec_cache.py).  Each entry point below
+ * names the reference lines whose GPU work it replaces; the Python classes in
+ * omnikv_b200/modeling keep the reference's names and call these through ctypes.
+ *
+ * Conventions
+ *   - raw device pointers (tensor.data_ptr()), explicit sizes and ELEMENT strides;
+ *   - the caller owns every buffer, workspaces included: nothing here allocates,
+ *     frees or synchronises, so every call may be captured in a CUDA graph;
+ *   - per-sequence lengths are DEVICE arrays of int32 so that a captured graph can
+ *     be replayed while the context grows;
+ *   - the last argument is the cudaStream_t to launch on (passed as void*);
+ *   - return value: 0 or a negative omnikv_status after host-side validation;
+ *     nothing throws or aborts across the boundary;
+ *   - head_dim is 128 (Llama-3 8B / 70B); other values return OMNIKV_E_UNSUPPORTED.
+ */
+#ifndef OMNIKV_B200_H_
+#define OMNIKV_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OMNIKV_ABI_VERSION 1
+
+typedef enum {
+  OMNIKV_OK = 0,
+  OMNIKV_E_BADARG = -1,      /* null pointer, non-positive size, bad stride or alignment */
+  OMNIKV_E_UNSUPPORTED = -2, /* shape or dtype outside what the kernels are built for   */
+  OMNIKV_E_WORKSPACE = -3,   /* workspace missing or smaller than omnikv_*_workspace_bytes */
+  OMNIKV_E_CUDA = -4         /* a CUDA runtime call failed; see omnikv_last_cuda_error()  */
+} omnikv_status;
+
+typedef enum { OMNIKV_F32 = 0, OMNIKV_BF16 = 1, OMNIKV_F16 = 2 } omnikv_dtype;
+
+/* Window selectors of modeling/omnikv.py:49-105. */
+typedef enum {
+  OMNIKV_SEL_SOFTMAX_LAST = 0, /* "softmax_before_last" :49-58  */
+  OMNIKV_SEL_UNIFORM = 1,      /* "uniform"             :59-80  */
+  OMNIKV_SEL_EXP = 2           /* "exp"                 :81-105 */
+} omnikv_window_selector;
+
+int omnikv_abi_version(void);
+const char* omnikv_strerror(int status);
+/* Text of the last CUDA error seen by this library on the calling thread ("" if none). */
+const char* omnikv_last_cuda_error(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Decode attention over a list of KV rows, with optional selection-score output.
+ *
+ * One query token per sequence.  The rows a sequence attends to are the concatenation of
+ *   segment A: lenA[b] rows of (kA, vA); row j is cache position idxA[b][j] when idxA is
+ *              given, else position j;
+ *   segment B: lenB[b] consecutive rows of (kB, vB) starting at position startB[b].
+ * out[b,h,:] = softmax_j(q[b,h,:] . K_j * scale) V_j with query head h reading KV head
+ * h / (H / KVH).
+ *
+ *   dense layer  (modeling/spec_cache.py:358-369 + the attention call modeling/omnikv.py:219-227):
+ *       A = the whole cache, idxA = NULL, lenA = prompt + decoded tokens; lenB = NULL.
+ *   sparse layer (modeling/spec_cache.py:337-356: cat([part_key, tail_k])):
+ *       A = prompt rows at the selected indices (replaces the index_select of :297-303 and
+ *       the torch.cat of :349-356: no gathered copy is materialised), B = the decode-time tail.
+ *   offloaded sparse layer: A = the staged rows written by omnikv_offload_gather (idxA = NULL).
+ *
+ * score_out (optional, dense only): the filter layer's selection score of selector "last"
+ * (modeling/omnikv.py:40-46) for free while K streams through: for every position
+ * p < score_len[b], score_out[kvh][b][p] = max over the query heads of KV head kvh of the
+ * scaled raw logit.  The max over KV heads is taken by omnikv_topk (n_planes = KVH), or by a
+ * MAX all-reduce of the planes when KV heads are sharded over GPUs.
+ *
+ * out == NULL with score_out != NULL computes scores only (V is never read).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+  int32_t dtype;    /* omnikv_dtype of q, k, v, out */
+  int32_t B, H, KVH, head_dim;
+  float scale;      /* 1/sqrt(head_dim) */
+  const void* q;    /* [B, H, d] */
+  int64_t q_stride_b, q_stride_h;
+  void* out;        /* [B, H, d], same strides as q; may be NULL (scores only) */
+  /* segment A */
+  const void* kA;
+  const void* vA;
+  int64_t a_stride_b, a_stride_h, a_stride_row; /* elements; a row is head_dim contiguous elements */
+  const int32_t* idxA; /* device [B, idx_stride] or NULL */
+  int64_t idx_stride;
+  const int32_t* lenA; /* device [B] */
+  /* segment B (all NULL / 0 when unused) */
+  const void* kB;
+  const void* vB;
+  int64_t b_stride_b, b_stride_h, b_stride_row;
+  const int32_t* startB; /* device [B] */
+  const int32_t* lenB;   /* device [B] */
+  /* optional score output */
+  float* score_out;           /* device [KVH, B, score_stride] or NULL */
+  int64_t score_stride;
+  const int32_t* score_len;   /* device [B]: positions >= score_len[b] are not written */
+  /* split-K */
+  int32_t n_splits;           /* >= 1; rows of a sequence are cut into n_splits contiguous chunks */
+  void* workspace;            /* omnikv_decode_attn_workspace_bytes(B, H, n_splits) bytes */
+  size_t workspace_bytes;
+} omnikv_attn_params;
+
+size_t omnikv_decode_attn_workspace_bytes(int B, int H, int n_splits);
+int omnikv_decode_attn(const omnikv_attn_params* p, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Window-selector scores (modeling/omnikv.py:49-105), replaces the per-window-query Python
+ * loop of matmul + softmax + max + sum and the repeat_kv copy of :38.
+ *
+ * qw [B, H, W, d]: rotated queries of the observation window, slot W-1 = current token.
+ * For every position p < consider_len[b]:
+ *   A[h,w,p] = softmax over p' < consider_len[b] of (qw[b,h,w,:] . K[b,h/G,p',:] * scale)
+ *   score_out[b][p] = sum_w weight_w * max_h A[h,w,p]
+ * with weight_w = 1 (uniform), 2^-(W-1-w) (exp), or only slot W-1 (softmax_before_last).
+ * When planes_out is given instead (KV heads sharded over GPUs), planes_out[b][w][p] holds
+ * max over the LOCAL heads, to be MAX-all-reduced and folded by omnikv_window_fold.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+  int32_t dtype;
+  int32_t B, H, KVH, head_dim, W;
+  int32_t selector; /* omnikv_window_selector */
+  float scale;
+  const void* qw; /* [B, H, W, d] contiguous */
+  const void* k;  /* [B, KVH, *, d] */
+  int64_t k_stride_b, k_stride_h, k_stride_row;
+  const int32_t* consider_len; /* device [B] */
+  int32_t max_len;             /* host upper bound of consider_len, sizes the grid */
+  float* score_out;            /* device [B, score_stride] or NULL */
+  float* planes_out;           /* device [B, W, score_stride] or NULL */
+  int64_t score_stride;
+  void* workspace;
+  size_t workspace_bytes;
+} omnikv_window_params;
+
+size_t omnikv_score_window_workspace_bytes(int B, int H, int W, int max_len);
+int omnikv_score_window(const omnikv_window_params* p, void* stream);
+/* score_out[b][p] = sum_w weight_w * planes[b][w][p] (after the MAX all-reduce of the planes). */
+int omnikv_window_fold(const float* planes, float* score_out, int B, int W, int64_t score_stride,
+                       const int32_t* consider_len, int max_len, int selector, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Top-k selector: replaces torch.topk(sorted=True) + torch.sort of the indices,
+ * modeling/omnikv.py:47-48, :79, :105, :109.
+ *
+ * score[b][p] = max over planes pl < n_planes of scores[pl*plane_stride + b*batch_stride + p].
+ * For every sequence: kk = min(k[b], len[b]); the kk positions with the largest score are
+ * written to idx_out[b][0..kk) in ASCENDING position order (int32); among equal scores the
+ * lowest position wins; NaN ranks above +inf (as torch.topk).  Then append_n[b] consecutive
+ * positions len[b], len[b]+1, ... are appended (the prompt tokens still inside the observation
+ * window, modeling/omnikv.py:199-210); count_out[b] = kk + append_n[b].
+ * One thread-block cluster per sequence; radix select with shared-memory histograms.
+ * ------------------------------------------------------------------------------------------ */
+size_t omnikv_topk_workspace_bytes(int B, int max_len);
+int omnikv_topk(const float* scores, int n_planes, int64_t plane_stride, int64_t batch_stride,
+                const int32_t* len, const int32_t* k, const int32_t* append_n /* may be NULL */,
+                int B, int max_len, int32_t* idx_out, int64_t idx_stride, int32_t* count_out,
+                void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Offload gather: replaces the CPU index_select + .cuda(non_blocking=True) of
+ * modeling/spec_cache.py:293-303 (real_offload).  The prompt KV of the sparse layers of one
+ * group lives in PINNED, device-mapped host memory, token-major:
+ *     host_kv[token][layer_in_group][K|V][KVH][d]
+ * so that one selected token is one contiguous chunk.  The kernel reads the selected chunks
+ * straight over the host link with 16-byte loads and writes, per layer, the compact rows
+ *     staged[layer_in_group][K|V][KVH][n_idx_capacity][d]
+ * that omnikv_decode_attn then reads as segment A with idxA = NULL.
+ * host_kv must be a device-visible address of the pinned buffer (cudaHostGetDevicePointer).
+ * ------------------------------------------------------------------------------------------ */
+int omnikv_offload_gather(const void* host_kv, int64_t token_stride_bytes, int n_layers_in_group,
+                          int KVH, int head_dim, int elem_bytes, const int32_t* idx,
+                          const int32_t* n_idx /* device [1] */, int n_idx_capacity, void* staged,
+                          int n_ctas, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Append the current token's K/V rows: replaces the torch.cat re-copy of the whole cache,
+ * modeling/spec_cache.py:363-369 (dense) and :343-347 (tail of sparse layers).
+ * k_new, v_new [B, KVH, d] are written at row pos[b] of k_cache, v_cache [B, KVH, *, d].
+ * ------------------------------------------------------------------------------------------ */
+int omnikv_kv_append(int dtype, const void* k_new, const void* v_new, void* k_cache, void* v_cache,
+                     int B, int KVH, int head_dim, int64_t new_stride_b, int64_t new_stride_h,
+                     int64_t cache_stride_b, int64_t cache_stride_h, int64_t cache_stride_row,
+                     const int32_t* pos, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OMNIKV_B200_H_ */

@@ -1,0 +1,111 @@
+"""ctypes binding of ``libomnikv_b200.so`` (the C ABI declared in ``include/omnikv_b200.h``).
+
+There is no fallback: if the library is missing, ``lib()`` raises with the build command.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libomnikv_b200.so"
+_lib = None
+
+ABI_VERSION = 1
+F32, BF16, F16 = 0, 1, 2
+SEL_SOFTMAX_LAST, SEL_UNIFORM, SEL_EXP = 0, 1, 2
+
+c_i32p = C.POINTER(C.c_int32)
+c_f32p = C.POINTER(C.c_float)
+
+
+class AttnParams(C.Structure):
+    """Mirror of ``omnikv_attn_params``."""
+
+    _fields_ = [
+        ("dtype", C.c_int32), ("B", C.c_int32), ("H", C.c_int32), ("KVH", C.c_int32), ("head_dim", C.c_int32),
+        ("scale", C.c_float),
+        ("q", C.c_void_p), ("q_stride_b", C.c_int64), ("q_stride_h", C.c_int64),
+        ("out", C.c_void_p),
+        ("kA", C.c_void_p), ("vA", C.c_void_p),
+        ("a_stride_b", C.c_int64), ("a_stride_h", C.c_int64), ("a_stride_row", C.c_int64),
+        ("idxA", C.c_void_p), ("idx_stride", C.c_int64), ("lenA", C.c_void_p),
+        ("kB", C.c_void_p), ("vB", C.c_void_p),
+        ("b_stride_b", C.c_int64), ("b_stride_h", C.c_int64), ("b_stride_row", C.c_int64),
+        ("startB", C.c_void_p), ("lenB", C.c_void_p),
+        ("score_out", C.c_void_p), ("score_stride", C.c_int64), ("score_len", C.c_void_p),
+        ("n_splits", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class WindowParams(C.Structure):
+    """Mirror of ``omnikv_window_params``."""
+
+    _fields_ = [
+        ("dtype", C.c_int32), ("B", C.c_int32), ("H", C.c_int32), ("KVH", C.c_int32), ("head_dim", C.c_int32),
+        ("W", C.c_int32), ("selector", C.c_int32), ("scale", C.c_float),
+        ("qw", C.c_void_p), ("k", C.c_void_p),
+        ("k_stride_b", C.c_int64), ("k_stride_h", C.c_int64), ("k_stride_row", C.c_int64),
+        ("consider_len", C.c_void_p), ("max_len", C.c_int32),
+        ("score_out", C.c_void_p), ("planes_out", C.c_void_p), ("score_stride", C.c_int64),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+# name -> (restype, argtypes); every symbol the header declares
+SIGNATURES = {
+    "omnikv_abi_version": (C.c_int, []),
+    "omnikv_strerror": (C.c_char_p, [C.c_int]),
+    "omnikv_last_cuda_error": (C.c_char_p, []),
+    "omnikv_decode_attn_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "omnikv_decode_attn": (C.c_int, [C.POINTER(AttnParams), C.c_void_p]),
+    "omnikv_score_window_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int]),
+    "omnikv_score_window": (C.c_int, [C.POINTER(WindowParams), C.c_void_p]),
+    "omnikv_window_fold": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_void_p, C.c_int,
+                                     C.c_int, C.c_void_p]),
+    "omnikv_topk_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int]),
+    "omnikv_topk": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,
+                              C.c_int, C.c_int, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_size_t,
+                              C.c_void_p]),
+    "omnikv_offload_gather": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                        C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
+    "omnikv_kv_append": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                   C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
+                                   C.c_void_p]),
+}
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def lib():
+    """The loaded library.  Raises when it has not been built: there is no other code path."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise RuntimeError(
+                f"{_LIB_PATH} is missing: build it with `python -m omnikv_b200.build` (needs nvcc). "
+                "omnikv_b200 has no CPU or PyTorch fallback for its kernels."
+            )
+        handle = C.CDLL(str(_LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)  # AttributeError if the symbol is not exported
+            fn.restype, fn.argtypes = res, args
+        got = handle.omnikv_abi_version()
+        if got != ABI_VERSION:
+            raise RuntimeError(f"libomnikv_b200 ABI {got} != binding ABI {ABI_VERSION}: rebuild the library")
+        _lib = handle
+    return _lib
+
+
+class OmniKVError(RuntimeError):
+    pass
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        l = lib()
+        msg = l.omnikv_strerror(status).decode()
+        extra = l.omnikv_last_cuda_error().decode() if status == -4 else ""
+        raise OmniKVError(f"{what}: {msg}{(' -- ' + extra) if extra else ''}")

@@ -1,0 +1,551 @@
+// Decode attention over a row list (dense cache / selected rows + tail), split-K flash-decode,
+// with the filter layer's selection score emitted while K streams through.
+//
+// bf16 / fp16: K and V rows (256 B each) are staged through a 3-deep shared-memory ring with
+// 16-byte cp.async copies (rows padded to 272 B so that ldmatrix is bank-conflict free), and the
+// GQA group's queries meet them in m16n8k16 tensor-core MMAs: HBM-bound streaming where the MMA
+// only keeps the issue slots free; every K/V byte is read once for all query heads of its KV head.
+// fp32: CUDA-core kernel (tensor cores would have to round the operands to tf32).
+//
+// Grid (n_splits, KVH, B).  Every CTA owns one contiguous chunk of the sequence's row list and
+// writes one un-normalised partial (o, m, l) per query head; a second kernel merges the splits.
+#include "common.cuh"
+
+namespace omnikv {
+
+struct AttnArgs {
+  const void* q;
+  int64_t q_sb, q_sh;
+  void* out;
+  const void* kA;
+  const void* vA;
+  int64_t a_sb, a_sh, a_sr;
+  const int* idxA;
+  int64_t idx_stride;
+  const int* lenA;
+  const void* kB;
+  const void* vB;
+  int64_t b_sb, b_sh, b_sr;
+  const int* startB;
+  const int* lenB;
+  float* score_out;
+  int64_t score_stride;
+  const int* score_len;
+  float* ws_o;
+  float* ws_ml;
+  int B, H, KVH, G, S;
+  float scale;
+};
+
+namespace {
+
+constexpr int TILE = 64;       // rows per pipeline stage
+constexpr int NWARPS = 4;      // each warp owns 16 rows of every tile
+constexpr int NTHREADS = NWARPS * 32;
+constexpr int STAGES = 3;
+constexpr int PITCH = 272;     // bytes per staged row: 256 + 16 pad
+constexpr int TILE_BYTES = TILE * PITCH;
+constexpr int Q_BYTES = 16 * PITCH;
+
+template <bool WITH_V>
+constexpr int mma_smem_bytes() {
+  return STAGES * (WITH_V ? 2 : 1) * TILE_BYTES + Q_BYTES;
+}
+
+// Row range [r0, r1) of split `split` out of S for a list of n rows (chunks are TILE-aligned).
+__device__ __forceinline__ void split_range(int n, int S, int split, int& r0, int& r1) {
+  int chunk = ceil_div(ceil_div(n, S), TILE) * TILE;
+  r0 = split * chunk;
+  r1 = min(n, r0 + chunk);
+}
+
+template <typename T, bool WITH_V, bool WITH_SCORE>
+__global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const AttnArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int STAGE_BYTES = (WITH_V ? 2 : 1) * TILE_BYTES;
+  unsigned char* q_s = smem + STAGES * STAGE_BYTES;
+
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int G = a.G;
+  const int nA = a.lenA[b];
+  const int nB = a.lenB ? a.lenB[b] : 0;
+  const int n = nA + nB;
+  int r0, r1;
+  split_range(n, a.S, split, r0, r1);
+  const int ntiles = r1 > r0 ? ceil_div(r1 - r0, TILE) : 0;
+
+  float* ws_o = a.ws_o;
+  float* ws_ml = a.ws_ml;
+  if (ntiles == 0) {  // empty split: neutral partial
+    if (WITH_V) {
+      for (int r = 0; r < G; ++r) {
+        size_t base = ((size_t)(b * a.H + kvh * G + r) * a.S + split);
+        ws_o[base * kHeadDim + tid] = 0.f;
+        if (tid == 0) {
+          ws_ml[base * 2 + 0] = -INFINITY;
+          ws_ml[base * 2 + 1] = 0.f;
+        }
+      }
+    }
+    return;
+  }
+
+  const T* kA = static_cast<const T*>(a.kA) + (size_t)b * a.a_sb + (size_t)kvh * a.a_sh;
+  const T* vA = WITH_V ? static_cast<const T*>(a.vA) + (size_t)b * a.a_sb + (size_t)kvh * a.a_sh : nullptr;
+  const T* kB = a.kB ? static_cast<const T*>(a.kB) + (size_t)b * a.b_sb + (size_t)kvh * a.b_sh : nullptr;
+  const T* vB = (WITH_V && a.vB) ? static_cast<const T*>(a.vB) + (size_t)b * a.b_sb + (size_t)kvh * a.b_sh : nullptr;
+  const int* idx = a.idxA ? a.idxA + (size_t)b * a.idx_stride : nullptr;
+  const int startB = a.startB ? a.startB[b] : 0;
+
+  auto issue_tile = [&](int tile, int slot) {
+    unsigned char* ks = smem + slot * STAGE_BYTES;
+    unsigned char* vs = ks + TILE_BYTES;
+    const int cc = tid & 15, rowi = tid >> 4;
+#pragma unroll
+    for (int i = 0; i < TILE / 8; ++i) {
+      const int row = rowi + 8 * i;
+      const int R = r0 + tile * TILE + row;
+      const bool valid = R < r1;
+      const T* ksrc = kA;
+      const T* vsrc = vA;
+      if (valid) {
+        if (R < nA) {
+          const size_t pos = idx ? (size_t)idx[R] : (size_t)R;
+          ksrc = kA + pos * a.a_sr;
+          if (WITH_V) vsrc = vA + pos * a.a_sr;
+        } else {
+          const size_t pos = (size_t)(startB + (R - nA));
+          ksrc = kB + pos * a.b_sr;
+          if (WITH_V) vsrc = vB + pos * a.b_sr;
+        }
+      }
+      cp_async16(ks + row * PITCH + cc * 16, ksrc + cc * 8, valid);
+      if (WITH_V) cp_async16(vs + row * PITCH + cc * 16, vsrc + cc * 8, valid);
+    }
+  };
+
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < ntiles) issue_tile(s, s);
+    cp_async_commit();
+  }
+
+  // Q tile: 16 rows x 128, rows >= G are zero.
+  for (int i = tid; i < 16 * 16; i += NTHREADS) {
+    const int r = i >> 4, c = i & 15;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < G) {
+      const T* qp = static_cast<const T*>(a.q) + (size_t)b * a.q_sb + (size_t)(kvh * G + r) * a.q_sh;
+      v = *reinterpret_cast<const uint4*>(qp + c * 8);
+    }
+    *reinterpret_cast<uint4*>(q_s + r * PITCH + c * 16) = v;
+  }
+  __syncthreads();
+  unsigned qf[8][4];
+#pragma unroll
+  for (int kk = 0; kk < 8; ++kk) {
+    const int row = (lane & 7) + 8 * ((lane >> 3) & 1);
+    const int col = kk * 16 + 8 * (lane >> 4);
+    ldmatrix_x4(qf[kk], q_s + row * PITCH + col * 2);
+  }
+
+  float m_row[2] = {-INFINITY, -INFINITY};
+  float l_row[2] = {0.f, 0.f};
+  float o[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  const int mi = lane >> 3;  // which 8x8 matrix this lane addresses in ldmatrix.x4
+  int score_lim = 0;
+  if (WITH_SCORE) score_lim = min(a.score_len[b], nA);
+  float* score_row = WITH_SCORE ? a.score_out + ((size_t)kvh * a.B + b) * a.score_stride : nullptr;
+
+  for (int tile = 0; tile < ntiles; ++tile) {
+    cp_async_wait<STAGES - 2>();
+    __syncthreads();
+    {
+      const int nt = tile + STAGES - 1;
+      if (nt < ntiles) issue_tile(nt, nt % STAGES);
+      cp_async_commit();
+    }
+    const unsigned char* ks = smem + (tile % STAGES) * STAGE_BYTES;
+    const unsigned char* vs = ks + TILE_BYTES;
+
+    // S = Q K^T for this warp's 16 rows: two n-tiles of 8 rows
+    float s[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      unsigned kf[4];
+      const int row = warp * 16 + 8 * (mi >> 1) + (lane & 7);
+      const int col = kk * 16 + 8 * (mi & 1);
+      ldmatrix_x4(kf, ks + row * PITCH + col * 2);
+      mma_16816<T>(s[0], qf[kk], kf[0], kf[1]);
+      mma_16816<T>(s[1], qf[kk], kf[2], kf[3]);
+    }
+    const int tile_base = r0 + tile * TILE + warp * 16;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int R = tile_base + 8 * j + 2 * t + (e & 1);
+        s[j][e] = (R < r1) ? s[j][e] * a.scale : -INFINITY;
+      }
+
+    if (WITH_SCORE) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          float v = -INFINITY;
+          if (g < G) v = s[j][e];
+          if (g + 8 < G) v = fmaxf(v, s[j][2 + e]);
+          v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+          v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+          v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+          const int R = tile_base + 8 * j + 2 * t + e;
+          if (g == 0 && R < score_lim) score_row[R] = v;
+        }
+    }
+
+    if (WITH_V) {
+      unsigned pa[4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float mx = fmaxf(fmaxf(s[0][2 * h], s[0][2 * h + 1]), fmaxf(s[1][2 * h], s[1][2 * h + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_row[h], mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float corr = exp2f((m_row[h] - m_use) * kLog2e);
+        m_row[h] = m_new;
+        const float ml2 = m_use * kLog2e;
+        const float p0 = exp2f(fmaf(s[0][2 * h], kLog2e, -ml2));
+        const float p1 = exp2f(fmaf(s[0][2 * h + 1], kLog2e, -ml2));
+        const float p2 = exp2f(fmaf(s[1][2 * h], kLog2e, -ml2));
+        const float p3 = exp2f(fmaf(s[1][2 * h + 1], kLog2e, -ml2));
+        l_row[h] = l_row[h] * corr + ((p0 + p1) + (p2 + p3));
+        pa[h] = pack2<T>(p0, p1);
+        pa[2 + h] = pack2<T>(p2, p3);
+#pragma unroll
+        for (int nn = 0; nn < 16; ++nn) {
+          o[nn][2 * h] *= corr;
+          o[nn][2 * h + 1] *= corr;
+        }
+      }
+      // O += P V : 8 steps of 16 output dims
+#pragma unroll
+      for (int nn = 0; nn < 8; ++nn) {
+        unsigned vf[4];
+        const int row = warp * 16 + 8 * (mi & 1) + (lane & 7);
+        const int col = nn * 16 + 8 * (mi >> 1);
+        ldmatrix_x4_trans(vf, vs + row * PITCH + col * 2);
+        mma_16816<T>(o[2 * nn], pa, vf[0], vf[1]);
+        mma_16816<T>(o[2 * nn + 1], pa, vf[2], vf[3]);
+      }
+    }
+  }
+  cp_async_wait<0>();
+  if (!WITH_V) return;
+  __syncthreads();  // every warp is done with the ring: reuse it for the cross-warp merge
+
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_row[h] += __shfl_xor_sync(0xffffffffu, l_row[h], 1);
+    l_row[h] += __shfl_xor_sync(0xffffffffu, l_row[h], 2);
+  }
+  float* o_s = reinterpret_cast<float*>(smem);                  // [NWARPS][16][128]
+  float* ml_s = o_s + NWARPS * 16 * kHeadDim;                   // [NWARPS][16][2]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = g + 8 * h;
+    if (r < G) {
+      float* dst = o_s + ((size_t)warp * 16 + r) * kHeadDim;
+#pragma unroll
+      for (int nn = 0; nn < 16; ++nn) {
+        *reinterpret_cast<float2*>(dst + nn * 8 + 2 * t) = make_float2(o[nn][2 * h], o[nn][2 * h + 1]);
+      }
+      if (t == 0) {
+        ml_s[(warp * 16 + r) * 2 + 0] = m_row[h];
+        ml_s[(warp * 16 + r) * 2 + 1] = l_row[h];
+      }
+    }
+  }
+  __syncthreads();
+  for (int r = 0; r < G; ++r) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, ml_s[(w * 16 + r) * 2]);
+    const float Mu = (M == -INFINITY) ? 0.f : M;
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) {
+      const float wgt = exp2f((ml_s[(w * 16 + r) * 2] - Mu) * kLog2e);
+      acc += o_s[((size_t)w * 16 + r) * kHeadDim + tid] * wgt;
+      l += ml_s[(w * 16 + r) * 2 + 1] * wgt;
+    }
+    const size_t base = ((size_t)(b * a.H + kvh * G + r) * a.S + split);
+    ws_o[base * kHeadDim + tid] = acc;
+    if (tid == 0) {
+      ws_ml[base * 2 + 0] = M;
+      ws_ml[base * 2 + 1] = l;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// fp32 CUDA-core kernel.  One warp per row at a time (a 512-byte row is one coalesced request,
+// lane L holds dims 4L..4L+3), four rows in flight per warp.
+// ---------------------------------------------------------------------------------------------
+template <int G>
+__global__ void __launch_bounds__(NTHREADS) decode_attn_f32_kernel(const AttnArgs a, const bool with_v,
+                                                                    const bool with_score) {
+  __shared__ float o_s[NWARPS][G][kHeadDim];
+  __shared__ float ml_s[NWARPS][G][2];
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nA = a.lenA[b];
+  const int nB = a.lenB ? a.lenB[b] : 0;
+  const int n = nA + nB;
+  int r0, r1;
+  split_range(n, a.S, split, r0, r1);
+
+  const float* kA = static_cast<const float*>(a.kA) + (size_t)b * a.a_sb + (size_t)kvh * a.a_sh;
+  const float* vA = with_v ? static_cast<const float*>(a.vA) + (size_t)b * a.a_sb + (size_t)kvh * a.a_sh : nullptr;
+  const float* kB = a.kB ? static_cast<const float*>(a.kB) + (size_t)b * a.b_sb + (size_t)kvh * a.b_sh : nullptr;
+  const float* vB = (with_v && a.vB) ? static_cast<const float*>(a.vB) + (size_t)b * a.b_sb + (size_t)kvh * a.b_sh : nullptr;
+  const int* idx = a.idxA ? a.idxA + (size_t)b * a.idx_stride : nullptr;
+  const int startB = a.startB ? a.startB[b] : 0;
+  const int score_lim = with_score ? min(a.score_len[b], nA) : 0;
+  float* score_row = with_score ? a.score_out + ((size_t)kvh * a.B + b) * a.score_stride : nullptr;
+
+  float4 qv[G];
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    const float* qp = static_cast<const float*>(a.q) + (size_t)b * a.q_sb + (size_t)(kvh * G + h) * a.q_sh;
+    qv[h] = *reinterpret_cast<const float4*>(qp + lane * 4);
+  }
+  float m[G], l[G];
+  float4 acc[G];
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    m[h] = -INFINITY;
+    l[h] = 0.f;
+    acc[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+
+  constexpr int U = 4;
+  for (int base = r0 + warp * U; base < r1; base += NWARPS * U) {
+    float4 kx[U], vx[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int R = base + u;
+      kx[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      vx[u] = kx[u];
+      if (R < r1) {
+        const float* kp;
+        const float* vp = nullptr;
+        if (R < nA) {
+          const size_t pos = idx ? (size_t)idx[R] : (size_t)R;
+          kp = kA + pos * a.a_sr;
+          if (with_v) vp = vA + pos * a.a_sr;
+        } else {
+          const size_t pos = (size_t)(startB + (R - nA));
+          kp = kB + pos * a.b_sr;
+          if (with_v) vp = vB + pos * a.b_sr;
+        }
+        kx[u] = __ldg(reinterpret_cast<const float4*>(kp) + lane);
+        if (with_v) vx[u] = __ldg(reinterpret_cast<const float4*>(vp) + lane);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int R = base + u;
+      if (R >= r1) break;  // warp-uniform
+      float sc[G];
+      float best = -INFINITY;
+#pragma unroll
+      for (int h = 0; h < G; ++h) {
+        float d = qv[h].x * kx[u].x;
+        d = fmaf(qv[h].y, kx[u].y, d);
+        d = fmaf(qv[h].z, kx[u].z, d);
+        d = fmaf(qv[h].w, kx[u].w, d);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+        sc[h] = d * a.scale;
+        best = fmaxf(best, sc[h]);
+      }
+      if (with_score && lane == 0 && R < score_lim) score_row[R] = best;
+      if (with_v) {
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+          const float m_new = fmaxf(m[h], sc[h]);  // finite: sc is a finite dot product
+          const float corr = exp2f((m[h] - m_new) * kLog2e);
+          const float p = exp2f((sc[h] - m_new) * kLog2e);
+          m[h] = m_new;
+          l[h] = l[h] * corr + p;
+          acc[h].x = fmaf(p, vx[u].x, acc[h].x * corr);
+          acc[h].y = fmaf(p, vx[u].y, acc[h].y * corr);
+          acc[h].z = fmaf(p, vx[u].z, acc[h].z * corr);
+          acc[h].w = fmaf(p, vx[u].w, acc[h].w * corr);
+        }
+      }
+    }
+  }
+  if (!with_v) return;
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    *reinterpret_cast<float4*>(&o_s[warp][h][lane * 4]) = acc[h];
+    if (lane == 0) {
+      ml_s[warp][h][0] = m[h];
+      ml_s[warp][h][1] = l[h];
+    }
+  }
+  __syncthreads();
+  for (int h = 0; h < G; ++h) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, ml_s[w][h][0]);
+    const float Mu = (M == -INFINITY) ? 0.f : M;
+    float accv = 0.f, lv = 0.f;
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) {
+      const float mw = ml_s[w][h][0];
+      const float wgt = (mw == -INFINITY) ? 0.f : exp2f((mw - Mu) * kLog2e);
+      accv += o_s[w][h][tid] * wgt;
+      lv += ml_s[w][h][1] * wgt;
+    }
+    const size_t base = ((size_t)(b * a.H + kvh * G + h) * a.S + split);
+    a.ws_o[base * kHeadDim + tid] = accv;
+    if (tid == 0) {
+      a.ws_ml[base * 2 + 0] = M;
+      a.ws_ml[base * 2 + 1] = lv;
+    }
+  }
+}
+
+// Merge of the split-K partials: grid (H, B), one thread per output dim.
+template <typename T>
+__global__ void __launch_bounds__(kHeadDim) splitk_merge_kernel(const float* __restrict__ ws_o,
+                                                                const float* __restrict__ ws_ml, T* out,
+                                                                int64_t out_sb, int64_t out_sh, int H, int S) {
+  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+  const size_t base = (size_t)(b * H + h) * S;
+  float M = -INFINITY;
+  for (int s = 0; s < S; ++s) M = fmaxf(M, ws_ml[(base + s) * 2]);
+  const float Mu = (M == -INFINITY) ? 0.f : M;
+  float acc = 0.f, l = 0.f;
+  for (int s = 0; s < S; ++s) {
+    const float ms = ws_ml[(base + s) * 2];
+    const float w = (ms == -INFINITY) ? 0.f : exp2f((ms - Mu) * kLog2e);
+    acc = fmaf(ws_o[(base + s) * kHeadDim + tid], w, acc);
+    l = fmaf(ws_ml[(base + s) * 2 + 1], w, l);
+  }
+  out[(size_t)b * out_sb + (size_t)h * out_sh + tid] = from_float<T>(l > 0.f ? acc / l : 0.f);
+}
+
+template <typename T>
+int launch_mma(const AttnArgs& a, bool with_v, bool with_score, cudaStream_t st) {
+  dim3 grid(a.S, a.KVH, a.B), block(NTHREADS);
+  if (with_v && with_score) {
+    auto kern = decode_attn_mma_kernel<T, true, true>;
+    OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, mma_smem_bytes<true>()));
+    kern<<<grid, block, mma_smem_bytes<true>(), st>>>(a);
+  } else if (with_v) {
+    auto kern = decode_attn_mma_kernel<T, true, false>;
+    OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, mma_smem_bytes<true>()));
+    kern<<<grid, block, mma_smem_bytes<true>(), st>>>(a);
+  } else {
+    auto kern = decode_attn_mma_kernel<T, false, true>;
+    OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, mma_smem_bytes<false>()));
+    kern<<<grid, block, mma_smem_bytes<false>(), st>>>(a);
+  }
+  OMNIKV_CUDA_OK(cudaGetLastError());
+  if (with_v) {
+    splitk_merge_kernel<T><<<dim3(a.H, a.B), kHeadDim, 0, st>>>(a.ws_o, a.ws_ml, static_cast<T*>(a.out), a.q_sb,
+                                                                  a.q_sh, a.H, a.S);
+    OMNIKV_CUDA_OK(cudaGetLastError());
+  }
+  return OMNIKV_OK;
+}
+
+int launch_f32(const AttnArgs& a, bool with_v, bool with_score, cudaStream_t st) {
+  dim3 grid(a.S, a.KVH, a.B), block(NTHREADS);
+  switch (a.G) {
+    case 1: decode_attn_f32_kernel<1><<<grid, block, 0, st>>>(a, with_v, with_score); break;
+    case 2: decode_attn_f32_kernel<2><<<grid, block, 0, st>>>(a, with_v, with_score); break;
+    case 4: decode_attn_f32_kernel<4><<<grid, block, 0, st>>>(a, with_v, with_score); break;
+    case 8: decode_attn_f32_kernel<8><<<grid, block, 0, st>>>(a, with_v, with_score); break;
+    default: return OMNIKV_E_UNSUPPORTED;
+  }
+  OMNIKV_CUDA_OK(cudaGetLastError());
+  if (with_v) {
+    splitk_merge_kernel<float><<<dim3(a.H, a.B), kHeadDim, 0, st>>>(a.ws_o, a.ws_ml, static_cast<float*>(a.out),
+                                                                      a.q_sb, a.q_sh, a.H, a.S);
+    OMNIKV_CUDA_OK(cudaGetLastError());
+  }
+  return OMNIKV_OK;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+}  // namespace omnikv
+
+extern "C" size_t omnikv_decode_attn_workspace_bytes(int B, int H, int n_splits) {
+  if (B <= 0 || H <= 0 || n_splits <= 0) return 0;
+  return (omnikv::attn_ws_o_floats(B, H, n_splits) + omnikv::attn_ws_ml_floats(B, H, n_splits)) * sizeof(float);
+}
+
+extern "C" int omnikv_decode_attn(const omnikv_attn_params* p, void* stream) {
+  using namespace omnikv;
+  if (!p || !p->q || !p->kA || !p->lenA) return OMNIKV_E_BADARG;
+  if (p->B <= 0 || p->H <= 0 || p->KVH <= 0 || p->n_splits <= 0) return OMNIKV_E_BADARG;
+  if (p->head_dim != kHeadDim) return OMNIKV_E_UNSUPPORTED;
+  if (p->H % p->KVH != 0) return OMNIKV_E_BADARG;
+  const int G = p->H / p->KVH;
+  const bool with_v = p->out != nullptr;
+  const bool with_score = p->score_out != nullptr;
+  if (!with_v && !with_score) return OMNIKV_E_BADARG;
+  if (with_v && !p->vA) return OMNIKV_E_BADARG;
+  if (with_score && (p->idxA || !p->score_len || p->score_stride <= 0)) return OMNIKV_E_BADARG;
+  if (p->lenB && (!p->kB || !p->startB || (with_v && !p->vB))) return OMNIKV_E_BADARG;
+  const int esz = p->dtype == OMNIKV_F32 ? 4 : 2;
+  const int vec = 16 / esz;  // elements per 16-byte vector
+  if (p->dtype != OMNIKV_F32 && p->dtype != OMNIKV_BF16 && p->dtype != OMNIKV_F16) return OMNIKV_E_UNSUPPORTED;
+  if (!aligned16(p->q) || !aligned16(p->kA) || (p->vA && !aligned16(p->vA)) || (p->kB && !aligned16(p->kB)) ||
+      (p->vB && !aligned16(p->vB)))
+    return OMNIKV_E_BADARG;
+  if (p->q_stride_b % vec || p->q_stride_h % vec || p->a_stride_b % vec || p->a_stride_h % vec ||
+      p->a_stride_row % vec || p->a_stride_row < kHeadDim)
+    return OMNIKV_E_BADARG;
+  if (p->lenB && (p->b_stride_b % vec || p->b_stride_h % vec || p->b_stride_row % vec || p->b_stride_row < kHeadDim))
+    return OMNIKV_E_BADARG;
+  if (p->dtype == OMNIKV_F32 ? (G != 1 && G != 2 && G != 4 && G != 8) : (G > 16)) return OMNIKV_E_UNSUPPORTED;
+  if (with_v) {
+    if (!p->workspace || p->workspace_bytes < omnikv_decode_attn_workspace_bytes(p->B, p->H, p->n_splits))
+      return OMNIKV_E_WORKSPACE;
+    if (!aligned16(p->workspace)) return OMNIKV_E_BADARG;
+  }
+  AttnArgs a;
+  a.q = p->q; a.q_sb = p->q_stride_b; a.q_sh = p->q_stride_h; a.out = p->out;
+  a.kA = p->kA; a.vA = p->vA; a.a_sb = p->a_stride_b; a.a_sh = p->a_stride_h; a.a_sr = p->a_stride_row;
+  a.idxA = p->idxA; a.idx_stride = p->idx_stride; a.lenA = p->lenA;
+  a.kB = p->lenB ? p->kB : nullptr; a.vB = p->lenB ? p->vB : nullptr;
+  a.b_sb = p->b_stride_b; a.b_sh = p->b_stride_h; a.b_sr = p->b_stride_row;
+  a.startB = p->startB; a.lenB = p->lenB;
+  a.score_out = p->score_out; a.score_stride = p->score_stride; a.score_len = p->score_len;
+  a.ws_o = static_cast<float*>(p->workspace);
+  a.ws_ml = with_v ? a.ws_o + attn_ws_o_floats(p->B, p->H, p->n_splits) : nullptr;
+  a.B = p->B; a.H = p->H; a.KVH = p->KVH; a.G = G; a.S = p->n_splits;
+  a.scale = p->scale;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (p->dtype) {
+    case OMNIKV_BF16: return launch_mma<__nv_bfloat16>(a, with_v, with_score, st);
+    case OMNIKV_F16: return launch_mma<__half>(a, with_v, with_score, st);
+    default: return launch_f32(a, with_v, with_score, st);
+  }
+}

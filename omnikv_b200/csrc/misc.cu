@@ -1,0 +1,169 @@
+// ABI bookkeeping, the KV append, the offload gather and the window-plane fold.
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace omnikv {
+
+static thread_local char g_last_error[256] = "";
+
+int record_cuda_error(cudaError_t e, const char* where) {
+  snprintf(g_last_error, sizeof(g_last_error), "%s: %s (%s)", where, cudaGetErrorName(e), cudaGetErrorString(e));
+  (void)cudaGetLastError();  // clear the sticky-less error state
+  return OMNIKV_E_CUDA;
+}
+
+namespace {
+
+// k_new/v_new [B, KVH, d] -> row pos[b] of the caches.  One 16-byte vector per thread.
+template <int ESZ>
+__global__ void kv_append_kernel(const unsigned char* k_new, const unsigned char* v_new, unsigned char* k_cache,
+                                 unsigned char* v_cache, int KVH, int64_t new_sb, int64_t new_sh, int64_t c_sb,
+                                 int64_t c_sh, int64_t c_sr, const int* pos) {
+  constexpr int VECS = kHeadDim * ESZ / 16;  // 16-byte vectors per row
+  const int b = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= KVH * VECS) return;
+  const int h = i / VECS, c = i % VECS;
+  const int64_t p = pos[b];
+  if (p < 0) return;
+  const size_t src = ((size_t)b * new_sb + (size_t)h * new_sh) * ESZ + (size_t)c * 16;
+  const size_t dst = ((size_t)b * c_sb + (size_t)h * c_sh + (size_t)p * c_sr) * ESZ + (size_t)c * 16;
+  *reinterpret_cast<uint4*>(k_cache + dst) = *reinterpret_cast<const uint4*>(k_new + src);
+  *reinterpret_cast<uint4*>(v_cache + dst) = *reinterpret_cast<const uint4*>(v_new + src);
+}
+
+// Host-link gather.  One selected token is one contiguous chunk of n_layers*2*KVH rows in pinned
+// host memory; row r of the chunk (layer l, K|V c, head h) goes to staged[l][c][h][j][:].
+// A warp copies rows with one 16-byte load per lane per step, several rows in flight.
+__global__ void __launch_bounds__(256) offload_gather_kernel(const unsigned char* __restrict__ host_kv,
+                                                             int64_t token_stride, int rows_per_token,
+                                                             int row_bytes, const int* __restrict__ idx,
+                                                             const int* __restrict__ n_idx, int cap,
+                                                             unsigned char* __restrict__ staged) {
+  const int n = min(*n_idx, cap);
+  const int vec_per_row = row_bytes / 16;
+  const long long total = (long long)n * rows_per_token * vec_per_row;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  constexpr int U = 4;
+  for (long long v0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; v0 < total; v0 += stride * U) {
+    uint4 buf[U];
+    long long dst[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + u * stride;
+      dst[u] = -1;
+      if (v < total) {
+        const int c = (int)(v % vec_per_row);
+        const long long rr = v / vec_per_row;
+        const int r = (int)(rr % rows_per_token);
+        const int j = (int)(rr / rows_per_token);
+        const unsigned char* src = host_kv + (size_t)idx[j] * token_stride + (size_t)r * row_bytes + (size_t)c * 16;
+        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(buf[u].x), "=r"(buf[u].y), "=r"(buf[u].z), "=r"(buf[u].w)
+                     : "l"(src));
+        dst[u] = ((long long)r * cap + j) * row_bytes + (long long)c * 16;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (dst[u] >= 0) *reinterpret_cast<uint4*>(staged + dst[u]) = buf[u];
+  }
+}
+
+__global__ void window_fold_kernel(const float* __restrict__ planes, float* __restrict__ score_out, int W,
+                                   int64_t score_stride, const int* __restrict__ consider_len, int selector) {
+  const int b = blockIdx.y;
+  const int n = consider_len[b];
+  for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < n; p += gridDim.x * blockDim.x) {
+    const float* pl = planes + (size_t)b * W * score_stride + p;
+    float acc = 0.f;
+    if (selector == OMNIKV_SEL_SOFTMAX_LAST) {
+      acc = pl[(size_t)(W - 1) * score_stride];
+    } else {
+      for (int w = 0; w < W; ++w) {
+        const float v = pl[(size_t)w * score_stride];
+        acc = (selector == OMNIKV_SEL_EXP) ? fmaf(acc, 0.5f, v) : acc + v;
+      }
+    }
+    score_out[(size_t)b * score_stride + p] = acc;
+  }
+}
+
+}  // namespace
+}  // namespace omnikv
+
+extern "C" int omnikv_abi_version(void) { return OMNIKV_ABI_VERSION; }
+
+extern "C" const char* omnikv_strerror(int status) {
+  switch (status) {
+    case OMNIKV_OK: return "ok";
+    case OMNIKV_E_BADARG: return "bad argument (null pointer, non-positive size, stride or alignment)";
+    case OMNIKV_E_UNSUPPORTED: return "unsupported shape or dtype";
+    case OMNIKV_E_WORKSPACE: return "workspace missing or too small";
+    case OMNIKV_E_CUDA: return "CUDA runtime error (see omnikv_last_cuda_error)";
+    default: return "unknown status";
+  }
+}
+
+extern "C" const char* omnikv_last_cuda_error(void) { return omnikv::g_last_error; }
+
+extern "C" int omnikv_kv_append(int dtype, const void* k_new, const void* v_new, void* k_cache, void* v_cache, int B,
+                                int KVH, int head_dim, int64_t new_stride_b, int64_t new_stride_h,
+                                int64_t cache_stride_b, int64_t cache_stride_h, int64_t cache_stride_row,
+                                const int32_t* pos, void* stream) {
+  using namespace omnikv;
+  if (!k_new || !v_new || !k_cache || !v_cache || !pos || B <= 0 || KVH <= 0) return OMNIKV_E_BADARG;
+  if (head_dim != kHeadDim) return OMNIKV_E_UNSUPPORTED;
+  const int esz = dtype == OMNIKV_F32 ? 4 : 2;
+  const int vec = 16 / esz;
+  if (new_stride_b % vec || new_stride_h % vec || cache_stride_b % vec || cache_stride_h % vec || cache_stride_row % vec)
+    return OMNIKV_E_BADARG;
+  const int threads = 128;
+  const int work = KVH * kHeadDim * esz / 16;
+  dim3 grid((work + threads - 1) / threads, B);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto kn = static_cast<const unsigned char*>(k_new);
+  auto vn = static_cast<const unsigned char*>(v_new);
+  auto kc = static_cast<unsigned char*>(k_cache);
+  auto vc = static_cast<unsigned char*>(v_cache);
+  if (esz == 4)
+    kv_append_kernel<4><<<grid, threads, 0, st>>>(kn, vn, kc, vc, KVH, new_stride_b, new_stride_h, cache_stride_b,
+                                                  cache_stride_h, cache_stride_row, pos);
+  else
+    kv_append_kernel<2><<<grid, threads, 0, st>>>(kn, vn, kc, vc, KVH, new_stride_b, new_stride_h, cache_stride_b,
+                                                  cache_stride_h, cache_stride_row, pos);
+  OMNIKV_CUDA_OK(cudaGetLastError());
+  return OMNIKV_OK;
+}
+
+extern "C" int omnikv_offload_gather(const void* host_kv, int64_t token_stride_bytes, int n_layers_in_group, int KVH,
+                                     int head_dim, int elem_bytes, const int32_t* idx, const int32_t* n_idx,
+                                     int n_idx_capacity, void* staged, int n_ctas, void* stream) {
+  using namespace omnikv;
+  if (!host_kv || !idx || !n_idx || !staged || n_layers_in_group <= 0 || KVH <= 0 || n_idx_capacity <= 0 || n_ctas <= 0)
+    return OMNIKV_E_BADARG;
+  if (head_dim != kHeadDim || (elem_bytes != 2 && elem_bytes != 4)) return OMNIKV_E_UNSUPPORTED;
+  const int row_bytes = head_dim * elem_bytes;
+  const int rows_per_token = n_layers_in_group * 2 * KVH;
+  if (token_stride_bytes < (int64_t)rows_per_token * row_bytes || token_stride_bytes % 16) return OMNIKV_E_BADARG;
+  offload_gather_kernel<<<n_ctas, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned char*>(host_kv), token_stride_bytes, rows_per_token, row_bytes, idx, n_idx,
+      n_idx_capacity, static_cast<unsigned char*>(staged));
+  OMNIKV_CUDA_OK(cudaGetLastError());
+  return OMNIKV_OK;
+}
+
+extern "C" int omnikv_window_fold(const float* planes, float* score_out, int B, int W, int64_t score_stride,
+                                  const int32_t* consider_len, int max_len, int selector, void* stream) {
+  using namespace omnikv;
+  if (!planes || !score_out || !consider_len || B <= 0 || W <= 0 || max_len <= 0 || score_stride < max_len)
+    return OMNIKV_E_BADARG;
+  if (selector < OMNIKV_SEL_SOFTMAX_LAST || selector > OMNIKV_SEL_EXP) return OMNIKV_E_BADARG;
+  dim3 grid(min(1184, (max_len + 255) / 256), B);
+  window_fold_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(planes, score_out, W, score_stride,
+                                                                         consider_len, selector);
+  OMNIKV_CUDA_OK(cudaGetLastError());
+  return OMNIKV_OK;
+}

@@ -1,0 +1,268 @@
+"""Tensor-level wrappers over the C ABI: they take ``torch`` CUDA tensors, pass raw pointers,
+sizes and element strides to ``libomnikv_b200.so`` and launch on the current CUDA stream.
+
+PyTorch is used here for device memory and streams only.  Nothing in this module computes a
+result on its own: if the library is missing, every call raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import abi
+
+_DT = {torch.float32: abi.F32, torch.bfloat16: abi.BF16, torch.float16: abi.F16}
+_SEL = {"softmax_before_last": abi.SEL_SOFTMAX_LAST, "uniform": abi.SEL_UNIFORM, "exp": abi.SEL_EXP}
+
+_sm_count = {}
+_workspaces = {}
+
+
+def sm_count(device) -> int:
+    idx = torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    if idx not in _sm_count:
+        _sm_count[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _sm_count[idx]
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise abi.OmniKVError("omnikv_b200 kernels need CUDA tensors; there is no CPU path")
+
+
+def workspace(device, nbytes: int, tag: str = "default") -> torch.Tensor:
+    """A cached per-device scratch tensor of at least ``nbytes`` bytes (the caller of the C ABI
+    owns the workspace; this cache is that caller).  Grows on demand; never call it with a larger
+    size for the first time while a CUDA graph is being captured."""
+    key = (torch.device(device).index, tag)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def default_splits(B: int, KVH: int, max_rows: int, device) -> int:
+    """Split count that fills the GPU with about two CTAs per SM, at least 128 rows per split."""
+    s = (2 * sm_count(device)) // max(1, B * KVH)
+    return max(1, min(s, (max_rows + 127) // 128))
+
+
+def _kv_strides(t: torch.Tensor) -> Tuple[int, int, int]:
+    if t.dim() != 4 or t.stride(3) != 1:
+        raise abi.OmniKVError("KV tensors must be [B, KVH, rows, d] with contiguous rows")
+    return t.stride(0), t.stride(1), t.stride(2)
+
+
+def decode_attn(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: Optional[torch.Tensor],
+    len_a: torch.Tensor,
+    *,
+    idx: Optional[torch.Tensor] = None,
+    k_tail: Optional[torch.Tensor] = None,
+    v_tail: Optional[torch.Tensor] = None,
+    tail_start: Optional[torch.Tensor] = None,
+    tail_len: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+    score_out: Optional[torch.Tensor] = None,
+    score_len: Optional[torch.Tensor] = None,
+    n_splits: Optional[int] = None,
+    max_rows: Optional[int] = None,
+    scale: Optional[float] = None,
+    ws: Optional[torch.Tensor] = None,
+    scores_only: bool = False,
+) -> Optional[torch.Tensor]:
+    """``omnikv_decode_attn``.  q ``[B,H,d]``; k, v ``[B,KVH,rows,d]``; ``len_a`` int32 ``[B]`` on
+    the device; ``idx`` int32 ``[B, >=len_a]`` selects rows of (k, v); the tail is
+    ``tail_len[b]`` rows of (k_tail, v_tail) from ``tail_start[b]``.  ``score_out``
+    ``[KVH,B,stride]`` fp32 receives the per-KV-head selector-``last`` scores of positions
+    ``< score_len[b]``.  Returns ``out`` ``[B,H,d]`` (None when ``scores_only``)."""
+    _need_cuda(q, k, v, len_a, idx, k_tail, v_tail, out, score_out)
+    B, H, d = q.shape
+    KVH = k.shape[1]
+    if q.stride(2) != 1:
+        raise abi.OmniKVError("q must have contiguous head vectors")
+    p = abi.AttnParams()
+    p.dtype = _DT[q.dtype]
+    p.B, p.H, p.KVH, p.head_dim = B, H, KVH, d
+    p.scale = float(scale if scale is not None else 1.0 / math.sqrt(d))
+    p.q, p.q_stride_b, p.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1)
+    if not scores_only:
+        if out is None:
+            out = torch.empty_like(q)
+        if out.stride() != q.stride():
+            raise abi.OmniKVError("out must have the strides of q")
+        p.out = out.data_ptr()
+    p.kA, p.vA = k.data_ptr(), _ptr(v)
+    p.a_stride_b, p.a_stride_h, p.a_stride_row = _kv_strides(k)
+    if v is not None and _kv_strides(v) != _kv_strides(k):
+        raise abi.OmniKVError("k and v must share strides")
+    if idx is not None:
+        if idx.dtype != torch.int32 or idx.stride(-1) != 1:
+            raise abi.OmniKVError("idx must be contiguous int32")
+        p.idxA, p.idx_stride = idx.data_ptr(), idx.stride(0) if idx.dim() == 2 else 0
+    if len_a.dtype != torch.int32:
+        raise abi.OmniKVError("len_a must be int32")
+    p.lenA = len_a.data_ptr()
+    if tail_len is not None:
+        p.kB, p.vB = k_tail.data_ptr(), _ptr(v_tail)
+        p.b_stride_b, p.b_stride_h, p.b_stride_row = _kv_strides(k_tail)
+        p.startB, p.lenB = tail_start.data_ptr(), tail_len.data_ptr()
+    if score_out is not None:
+        if score_out.dtype != torch.float32 or score_out.dim() != 3 or score_out.shape[0] != KVH or not score_out.is_contiguous():
+            raise abi.OmniKVError("score_out must be contiguous fp32 [KVH, B, stride]")
+        p.score_out, p.score_stride, p.score_len = score_out.data_ptr(), score_out.stride(1), score_len.data_ptr()
+    if max_rows is None:
+        max_rows = k.shape[2] + (k_tail.shape[2] if k_tail is not None else 0)
+    p.n_splits = int(n_splits or default_splits(B, KVH, max_rows, q.device))
+    if not scores_only:
+        need = abi.lib().omnikv_decode_attn_workspace_bytes(B, H, p.n_splits)
+        if ws is None:
+            ws = workspace(q.device, need, "attn")
+        p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
+    abi.check(abi.lib().omnikv_decode_attn(C.byref(p), _stream()), "omnikv_decode_attn")
+    return out
+
+
+def score_last(q: torch.Tensor, k: torch.Tensor, score_len: torch.Tensor, *, score_out: Optional[torch.Tensor] = None,
+               n_splits: Optional[int] = None, scale: Optional[float] = None) -> torch.Tensor:
+    """Selector-``last`` score planes ``[KVH, B, rows]`` (max over a KV head's query heads of the scaled
+    raw logits) without the attention output: the score-only mode of ``omnikv_decode_attn``."""
+    B, KVH, rows = q.shape[0], k.shape[1], k.shape[2]
+    if score_out is None:
+        score_out = torch.empty(KVH, B, rows, dtype=torch.float32, device=q.device)
+    decode_attn(q, k, None, score_len, score_out=score_out, score_len=score_len, n_splits=n_splits, scale=scale,
+                scores_only=True)
+    return score_out
+
+
+def topk(scores: torch.Tensor, length: torch.Tensor, k: torch.Tensor, *, append_n: Optional[torch.Tensor] = None,
+         idx_out: Optional[torch.Tensor] = None, count_out: Optional[torch.Tensor] = None,
+         max_len: Optional[int] = None, ws: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``omnikv_topk``.  scores fp32 ``[B, n]`` or planes ``[P, B, n]`` (max over P is taken);
+    ``length``, ``k`` (and ``append_n``) int32 ``[B]`` on the device.  Returns (idx int32 ``[B, cap]``
+    ascending, count int32 ``[B]``)."""
+    _need_cuda(scores, length, k, append_n, idx_out, count_out)
+    if scores.dtype != torch.float32 or scores.stride(-1) != 1:
+        raise abi.OmniKVError("scores must be fp32 with contiguous rows")
+    if scores.dim() == 2:
+        n_planes, plane_stride, B, batch_stride = 1, 0, scores.shape[0], scores.stride(0)
+    else:
+        n_planes, plane_stride, B, batch_stride = scores.shape[0], scores.stride(0), scores.shape[1], scores.stride(1)
+    if max_len is None:
+        max_len = scores.shape[-1]
+    if idx_out is None:
+        idx_out = torch.empty(B, max_len, dtype=torch.int32, device=scores.device)
+    if count_out is None:
+        count_out = torch.empty(B, dtype=torch.int32, device=scores.device)
+    need = abi.lib().omnikv_topk_workspace_bytes(B, max_len)
+    if ws is None and max_len > 8 * 49152:
+        ws = workspace(scores.device, need, "topk")
+    abi.check(
+        abi.lib().omnikv_topk(scores.data_ptr(), n_planes, plane_stride, batch_stride, length.data_ptr(), k.data_ptr(),
+                              _ptr(append_n), B, int(max_len), idx_out.data_ptr(), idx_out.stride(0),
+                              count_out.data_ptr(), _ptr(ws), 0 if ws is None else ws.numel() * ws.element_size(),
+                              _stream()),
+        "omnikv_topk")
+    return idx_out, count_out
+
+
+def score_window(qw: torch.Tensor, k: torch.Tensor, consider_len: torch.Tensor, selector: str, *, max_len: int,
+                 score_out: Optional[torch.Tensor] = None, planes_out: Optional[torch.Tensor] = None,
+                 scale: Optional[float] = None, ws: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``omnikv_score_window``.  qw ``[B,H,W,d]`` contiguous; k ``[B,KVH,rows,d]``.  Returns fp32 scores
+    ``[B, stride]`` (positions ``>= consider_len[b]`` are left untouched), or fills ``planes_out``
+    ``[B,W,stride]`` with the max over the local heads when given."""
+    _need_cuda(qw, k, consider_len, score_out, planes_out)
+    B, H, W, d = qw.shape
+    if not qw.is_contiguous():
+        raise abi.OmniKVError("qw must be contiguous [B,H,W,d]")
+    p = abi.WindowParams()
+    p.dtype = _DT[qw.dtype]
+    p.B, p.H, p.KVH, p.head_dim, p.W = B, H, k.shape[1], d, W
+    p.selector = _SEL[selector]
+    p.scale = float(scale if scale is not None else 1.0 / math.sqrt(d))
+    p.qw, p.k = qw.data_ptr(), k.data_ptr()
+    p.k_stride_b, p.k_stride_h, p.k_stride_row = _kv_strides(k)
+    p.consider_len, p.max_len = consider_len.data_ptr(), int(max_len)
+    if planes_out is None and score_out is None:
+        score_out = torch.empty(B, max_len, dtype=torch.float32, device=qw.device)
+    if score_out is not None:
+        p.score_out, p.score_stride = score_out.data_ptr(), score_out.stride(0)
+    if planes_out is not None:
+        p.planes_out, p.score_stride = planes_out.data_ptr(), planes_out.stride(1)
+    need = abi.lib().omnikv_score_window_workspace_bytes(B, H, W, int(max_len))
+    if ws is None:
+        ws = workspace(qw.device, need, "window")
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
+    abi.check(abi.lib().omnikv_score_window(C.byref(p), _stream()), "omnikv_score_window")
+    return score_out if planes_out is None else planes_out
+
+
+def window_fold(planes: torch.Tensor, consider_len: torch.Tensor, selector: str, *, max_len: int,
+                score_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need_cuda(planes, consider_len, score_out)
+    B, W, stride = planes.shape
+    if score_out is None:
+        score_out = torch.empty(B, stride, dtype=torch.float32, device=planes.device)
+    abi.check(abi.lib().omnikv_window_fold(planes.data_ptr(), score_out.data_ptr(), B, W, planes.stride(1),
+                                           consider_len.data_ptr(), int(max_len), _SEL[selector], _stream()),
+              "omnikv_window_fold")
+    return score_out
+
+
+def kv_append(k_new: torch.Tensor, v_new: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+              pos: torch.Tensor) -> None:
+    """Write k_new, v_new ``[B,KVH,d]`` at row ``pos[b]`` (int32, device) of the caches ``[B,KVH,rows,d]``."""
+    _need_cuda(k_new, v_new, k_cache, v_cache, pos)
+    B, KVH, d = k_new.shape
+    if k_new.stride() != v_new.stride() or k_new.stride(2) != 1 or _kv_strides(k_cache) != _kv_strides(v_cache):
+        raise abi.OmniKVError("kv_append: k/v layouts must match")
+    sb, sh, sr = _kv_strides(k_cache)
+    abi.check(abi.lib().omnikv_kv_append(_DT[k_new.dtype], k_new.data_ptr(), v_new.data_ptr(), k_cache.data_ptr(),
+                                         v_cache.data_ptr(), B, KVH, d, k_new.stride(0), k_new.stride(1), sb, sh, sr,
+                                         pos.data_ptr(), _stream()), "omnikv_kv_append")
+
+
+def offload_gather(host_kv: torch.Tensor, idx: torch.Tensor, n_idx: torch.Tensor, staged: torch.Tensor,
+                   *, n_ctas: Optional[int] = None) -> None:
+    """``omnikv_offload_gather``.  host_kv: PINNED CPU tensor ``[tokens, layers, 2, KVH, d]``;
+    idx int32 device ``[>= n]``; n_idx int32 device ``[1]``; staged device ``[layers, 2, KVH, cap, d]``."""
+    if host_kv.is_cuda or not host_kv.is_pinned():
+        raise abi.OmniKVError("host_kv must be a pinned CPU tensor")
+    _need_cuda(idx, n_idx, staged)
+    tokens, layers, two, KVH, d = host_kv.shape
+    if two != 2 or not host_kv.is_contiguous() or not staged.is_contiguous():
+        raise abi.OmniKVError("offload_gather: bad layout")
+    cap = staged.shape[3]
+    dev_ptr = host_device_pointer(host_kv)
+    if n_ctas is None:
+        n_ctas = 2 * sm_count(staged.device)
+    abi.check(abi.lib().omnikv_offload_gather(dev_ptr, host_kv.stride(0) * host_kv.element_size(), layers, KVH, d,
+                                              host_kv.element_size(), idx.data_ptr(), n_idx.data_ptr(), cap,
+                                              staged.data_ptr(), int(n_ctas), _stream()), "omnikv_offload_gather")
+
+
+def host_device_pointer(t: torch.Tensor) -> int:
+    """Device-visible address of a pinned host tensor.  With unified virtual addressing (every
+    64-bit Linux CUDA process) a page-locked allocation made by the CUDA runtime is mapped into
+    the device address space at the same address, so the host pointer is the device pointer."""
+    if t.is_cuda or not t.is_pinned():
+        raise abi.OmniKVError("expected a pinned CPU tensor")
+    return t.data_ptr()

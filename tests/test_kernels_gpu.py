@@ -1,0 +1,345 @@
+"""Parity of the CUDA kernels (called through the C ABI) against the CPU oracle.
+
+Tolerances (from the task's acceptance rules): top-k indices bit-exact on an identical fp32
+score tensor; selected sets equal wherever the k-th score gap exceeds 1e-4; attention outputs
+within 2e-2 absolute for bf16/fp16 and 1e-4 for fp32.
+"""
+import json
+import math
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import inputs as gi
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+G = Path(__file__).resolve().parent / "golden"
+ATOL = {torch.float32: 1e-4, torch.bfloat16: 2e-2, torch.float16: 2e-2}
+
+
+def ops():
+    from omnikv_b200 import ops as _ops
+    return _ops
+
+
+def dev_i32(x):
+    return torch.tensor(x, dtype=torch.int32, device="cuda")
+
+
+def make_kv(B, KVH, L, d, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    k = torch.randn(B, KVH, L, d, generator=g).to(dtype)
+    v = torch.randn(B, KVH, L, d, generator=g).to(dtype)
+    return k, v
+
+
+def make_q(B, H, d, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(B, H, d, generator=g) * scale).to(dtype)
+
+
+# ------------------------------------------------------------------------------------------
+# dense decode attention (+ fused score planes)
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("B,H,KVH,lens,splits", [
+    (1, 32, 8, [1], 1), (1, 32, 8, [63], 3), (1, 32, 8, [64], 1), (1, 32, 8, [65], 2), (1, 32, 8, [1000], 5),
+    (3, 32, 8, [4097, 17, 2500], 7), (2, 16, 2, [777, 1], 4), (2, 8, 8, [300, 299], 3), (1, 32, 8, [20000], 37),
+])
+def test_dense_attention_and_scores(dtype, B, H, KVH, lens, splits):
+    d, L = 128, max(lens) + 5
+    k, v = make_kv(B, KVH, L, d, dtype, 1)
+    q = make_q(B, H, d, dtype, 2, 1.5)
+    len_a = dev_i32(lens)
+    score_len = dev_i32([max(0, n - 2) for n in lens])  # e.g. the prompt is 2 tokens shorter
+    planes = torch.full((KVH, B, L), float("nan"), dtype=torch.float32, device="cuda")
+    out = ops().decode_attn(q.cuda(), k.cuda(), v.cuda(), len_a, score_out=planes, score_len=score_len,
+                            n_splits=splits)
+    out2 = ops().decode_attn(q.cuda(), k.cuda(), v.cuda(), len_a, n_splits=splits)
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2)  # the score output does not change the attention result
+    for b, n in enumerate(lens):
+        want = oracle.dense_attention(q[b:b + 1], k[b:b + 1, :, :n], v[b:b + 1, :, :n])
+        err = (out[b:b + 1].float().cpu() - want).abs().max().item()
+        assert err <= ATOL[dtype], (b, n, err)
+        sl = max(0, n - 2)
+        if sl:
+            s_want = oracle.score_last(q[b:b + 1], k[b:b + 1], sl)[0]
+            s_got = planes[:, b, :sl].max(dim=0).values.cpu()
+            assert (s_got - s_want).abs().max().item() <= 2e-5 * max(1.0, s_want.abs().max().item())
+        assert torch.isnan(planes[:, b, sl:]).all()  # nothing is written past score_len
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_score_only_mode_matches_fused(dtype):
+    B, H, KVH, d, L = 2, 32, 8, 128, 3000
+    k, v = make_kv(B, KVH, L, d, dtype, 3)
+    q = make_q(B, H, d, dtype, 4)
+    lens = dev_i32([3000, 1234])
+    fused = torch.zeros(KVH, B, L, dtype=torch.float32, device="cuda")
+    ops().decode_attn(q.cuda(), k.cuda(), v.cuda(), lens, score_out=fused, score_len=lens, n_splits=6)
+    only = torch.zeros(KVH, B, L, dtype=torch.float32, device="cuda")
+    ops().score_last(q.cuda(), k.cuda(), lens, score_out=only, n_splits=9)
+    torch.cuda.synchronize()
+    assert torch.equal(fused, only)
+
+
+# ------------------------------------------------------------------------------------------
+# sparse decode attention: selected rows + tail
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("B,P,ks,tails,splits", [
+    (1, 5000, [335], [1], 4), (1, 5000, [1], [0], 1), (2, 3000, [200, 64], [7, 130], 3), (1, 70000, [4690], [128], 37),
+    (3, 1000, [1000, 0, 999], [3, 5, 0], 5),
+])
+def test_sparse_attention(dtype, B, P, ks, tails, splits):
+    H, KVH, d = 32, 8, 128
+    cap = P + 256
+    k, v = make_kv(B, KVH, cap, d, dtype, 5)
+    q = make_q(B, H, d, dtype, 6, 1.5)
+    g = torch.Generator().manual_seed(7)
+    kmax = max(max(ks), 1)
+    idx = torch.zeros(B, kmax, dtype=torch.int64)
+    for b in range(B):
+        idx[b, :ks[b]] = torch.sort(torch.randperm(P, generator=g)[:ks[b]]).values
+    out = ops().decode_attn(q.cuda(), k.cuda(), v.cuda(), dev_i32(ks), idx=idx.to(torch.int32).cuda(),
+                            k_tail=k.cuda(), v_tail=v.cuda(), tail_start=dev_i32([P] * B), tail_len=dev_i32(tails),
+                            n_splits=splits)
+    torch.cuda.synchronize()
+    for b in range(B):
+        if ks[b] + tails[b] == 0:
+            assert out[b].float().abs().max().item() == 0.0
+            continue
+        want = oracle.sparse_attention(q[b:b + 1], k[b:b + 1, :, :P], v[b:b + 1, :, :P], idx[b:b + 1, :ks[b]],
+                                       k[b:b + 1, :, P:P + tails[b]], v[b:b + 1, :, P:P + tails[b]])
+        err = (out[b:b + 1].float().cpu() - want).abs().max().item()
+        assert err <= ATOL[dtype], (b, err)
+
+
+# ------------------------------------------------------------------------------------------
+# top-k
+# ------------------------------------------------------------------------------------------
+def _check_topk(scores, lens, ks, idx, count, append=None):
+    """Bit-exact against the oracle's rule (stable: lowest position wins among equal scores)."""
+    idx, count = idx.cpu(), count.cpu()
+    for b in range(scores.shape[0]):
+        n = lens[b]
+        kk = min(ks[b], n)
+        app = append[b] if append else 0
+        assert count[b].item() == kk + app
+        want = oracle.topk_ascending(scores[b:b + 1, :n], kk)[0] if kk else torch.zeros(0, dtype=torch.int64)
+        got = idx[b, :kk].long()
+        assert torch.equal(got, want), (b, n, kk)
+        if app:
+            assert torch.equal(idx[b, kk:kk + app].long(), torch.arange(n, n + app))
+
+
+@pytest.mark.parametrize("L", [1, 2, 17, 255, 4096, 8193, 40000, 131072])
+def test_topk_random(L):
+    g = torch.Generator().manual_seed(L)
+    B = 3
+    s = torch.randn(B, L, generator=g)
+    lens = [L, max(1, L // 2), max(1, L - 1)]
+    for ks in ([1, 1, 1], [L, L, L], [L + 5, 3, max(1, L - 1)], [max(1, int(0.067 * L))] * 3, [0, 1, 2]):
+        idx, cnt = ops().topk(s.cuda(), dev_i32(lens), dev_i32(ks))
+        torch.cuda.synchronize()
+        _check_topk(s, lens, ks, idx, cnt)
+
+
+def test_topk_ties_planes_append_and_specials():
+    g = torch.Generator().manual_seed(11)
+    B, L, P = 4, 20000, 8
+    planes = (torch.randn(P, B, L, generator=g) * 3).round() / 4  # heavy ties
+    planes[0, 1, 5] = float("inf")
+    planes[3, 1, 7] = float("-inf")
+    planes[:, 2, :] = 1.25  # all equal: the first k positions win
+    s = planes.max(dim=0).values
+    lens, ks, app = [L, L - 3, 777, 19999], [1340, 5, 100, 19999], [0, 15, 3, 1]
+    idx = torch.full((B, L + 32), -1, dtype=torch.int32, device="cuda")
+    idx, cnt = ops().topk(planes.cuda(), dev_i32(lens), dev_i32(ks), append_n=dev_i32(app), idx_out=idx, max_len=L)
+    torch.cuda.synchronize()
+    _check_topk(s, lens, ks, idx, cnt, app)
+    assert torch.equal(idx[2, :100].cpu().long(), torch.arange(100))
+
+
+def test_topk_nan_ranks_first():
+    s = torch.randn(1, 1000)
+    s[0, 123] = float("nan")
+    idx, cnt = ops().topk(s.cuda(), dev_i32([1000]), dev_i32([1]))
+    assert idx[0, 0].item() == 123
+
+
+def test_topk_long_context_not_resident():
+    # 450 000 keys: the slice of a CTA no longer fits shared memory, keys go through the workspace
+    L = 450000
+    g = torch.Generator().manual_seed(5)
+    s = torch.randn(1, L, generator=g)
+    k = int(0.067 * L)
+    idx, cnt = ops().topk(s.cuda(), dev_i32([L]), dev_i32([k]))
+    torch.cuda.synchronize()
+    _check_topk(s, [L], [k], idx, cnt)
+
+
+def test_topk_batch16_ragged():
+    g = torch.Generator().manual_seed(6)
+    B = 16
+    lens = torch.randint(16384, 32769, (B,), generator=g).tolist()
+    s = torch.randn(B, 32768, generator=g)
+    ks = [2048] * B
+    idx, cnt = ops().topk(s.cuda(), dev_i32(lens), dev_i32(ks))
+    torch.cuda.synchronize()
+    _check_topk(s, lens, ks, idx, cnt)
+
+
+# ------------------------------------------------------------------------------------------
+# window selectors
+# ------------------------------------------------------------------------------------------
+def _band_check(s_ref, got_idx, k, band):
+    """Sets equal, or differing only on positions whose reference score lies within `band` of the k-th."""
+    want = oracle.topk_ascending(s_ref[None], k)[0]
+    diff = set(got_idx.tolist()) ^ set(want.tolist())
+    kth = torch.sort(s_ref, descending=True).values[k - 1].item()
+    assert all(abs(s_ref[i].item() - kth) <= band for i in diff), len(diff)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("selector", ["uniform", "exp", "softmax_before_last"])
+@pytest.mark.parametrize("B,H,KVH,W,lens", [(1, 32, 8, 16, [3000]), (2, 32, 8, 5, [777, 64]), (1, 8, 2, 1, [130]),
+                                             (2, 16, 2, 16, [1, 4100])])
+def test_score_window(dtype, selector, B, H, KVH, W, lens):
+    d, L = 128, max(lens) + 3
+    g = torch.Generator().manual_seed(13)
+    k = torch.randn(B, KVH, L, d, generator=g).to(dtype)
+    qw = (torch.randn(B, H, W, d, generator=g) * 1.2).to(dtype)
+    got = ops().score_window(qw.cuda(), k.cuda(), dev_i32(lens), selector, max_len=max(lens))
+    planes = torch.zeros(B, W, max(lens), dtype=torch.float32, device="cuda")
+    ops().score_window(qw.cuda(), k.cuda(), dev_i32(lens), selector, max_len=max(lens), planes_out=planes)
+    folded = ops().window_fold(planes, dev_i32(lens), selector, max_len=max(lens))
+    torch.cuda.synchronize()
+    for b, n in enumerate(lens):
+        want = oracle.score_window(qw[b:b + 1], k[b:b + 1], n, selector)[0]
+        tol = 1e-5 * max(1.0, want.max().item()) + 1e-6
+        assert (got[b, :n].cpu() - want).abs().max().item() <= tol
+        assert (folded[b, :n].cpu() - want).abs().max().item() <= tol
+
+
+# ------------------------------------------------------------------------------------------
+# the single-layer operator case against the fixture produced by the reference itself
+# ------------------------------------------------------------------------------------------
+def test_operator_case_against_reference_fixture():
+    o = json.loads((G / "operator_cfg1.json").read_text())
+    gold = np.load(G / "operator_cfg1.npz")
+    x = gi.operator_inputs()
+    assert gi.checksum([x[n] for n in ("q", "k", "k2", "v2", "k_new", "v_new")]) == pytest.approx(o["input_checksum"], rel=1e-12)
+    L, k = o["L"], o["k"]
+    q = torch.from_numpy(x["q"]).cuda()
+    kf = torch.from_numpy(x["k"]).cuda()
+    q_last = q[:, :, -1, :].contiguous()
+    n = dev_i32([L])
+    planes = ops().score_last(q_last, kf, n)
+    idx, cnt = ops().topk(planes, n, dev_i32([k]))
+    torch.cuda.synchronize()
+    assert cnt.item() == k
+    s_ref = oracle.score_last(torch.from_numpy(x["q"])[:, :, -1], torch.from_numpy(x["k"]), L)[0]
+    got = idx[0, :k].cpu().long()
+    if not np.array_equal(got.numpy(), gold["idx"][0].astype(np.int64)):
+        _band_check(s_ref, got, k, 1e-4)
+    # second layer: prompt rows of (k2, v2) at the REFERENCE's indices + the current token's row
+    cap = L + 8
+    k2 = torch.zeros(1, 8, cap, 128)
+    v2 = torch.zeros(1, 8, cap, 128)
+    k2[:, :, :L], v2[:, :, :L] = torch.from_numpy(x["k2"]), torch.from_numpy(x["v2"])
+    k2, v2 = k2.cuda(), v2.cuda()
+    ops().kv_append(torch.from_numpy(x["k_new"])[:, :, 0].cuda(), torch.from_numpy(x["v_new"])[:, :, 0].cuda(), k2, v2, n)
+    ref_idx = torch.from_numpy(gold["idx"].astype(np.int32)).cuda()
+    out = ops().decode_attn(q_last, k2, v2, dev_i32([k]), idx=ref_idx, k_tail=k2, v_tail=v2, tail_start=n,
+                            tail_len=dev_i32([1]))
+    torch.cuda.synchronize()
+    assert np.abs(out.cpu().numpy() - gold["out"]).max() <= 1e-4
+    # window selectors on the same inputs
+    for sel in ("uniform", "exp"):
+        s = ops().score_window(q.contiguous(), kf, n, sel, max_len=L)
+        idx_w, _ = ops().topk(s, n, dev_i32([k]))
+        torch.cuda.synchronize()
+        s_ref = oracle.score_window(torch.from_numpy(x["q"]), torch.from_numpy(x["k"]), L, sel)[0]
+        got = idx_w[0, :k].cpu().long()
+        if not np.array_equal(got.numpy(), gold[f"idx_{sel}"][0].astype(np.int64)):
+            _band_check(s_ref, got, k, 1e-6)
+
+
+# ------------------------------------------------------------------------------------------
+# full-size (128K, bf16) run: oracle comparison + size-independent properties
+# ------------------------------------------------------------------------------------------
+def test_full_size_128k_bf16():
+    B, H, KVH, d, L, k = 1, 32, 8, 128, 131072, 8781
+    g = torch.Generator().manual_seed(21)
+    kc = torch.randn(B, KVH, L + 128, d, generator=g).to(torch.bfloat16)
+    vc = torch.randn(B, KVH, L + 128, d, generator=g).to(torch.bfloat16)
+    q = (torch.randn(B, H, d, generator=g) * 1.5).to(torch.bfloat16)
+    kg, vg, qg = kc.cuda(), vc.cuda(), q.cuda()
+    n_prompt, n_all = dev_i32([L]), dev_i32([L + 1])
+    planes = torch.empty(KVH, B, L, dtype=torch.float32, device="cuda")
+    out = ops().decode_attn(qg, kg, vg, n_all, score_out=planes, score_len=n_prompt)
+    idx, cnt = ops().topk(planes, n_prompt, dev_i32([k]))
+    out_sparse = ops().decode_attn(qg, kg, vg, cnt, idx=idx, k_tail=kg, v_tail=vg, tail_start=n_prompt,
+                                   tail_len=dev_i32([1]))
+    torch.cuda.synchronize()
+    assert cnt.item() == k
+    sel = idx[0, :k].cpu().long()
+    assert torch.all(sel[1:] > sel[:-1]) and sel[0] >= 0 and sel[-1] < L  # ascending, in range, unique
+    # oracle
+    want = oracle.dense_attention(q, kc[:, :, :L + 1], vc[:, :, :L + 1])
+    assert (out.float().cpu() - want).abs().max().item() <= 2e-2
+    s_ref = oracle.score_last(q, kc, L)[0]
+    assert (planes.max(dim=0).values[0].cpu() - s_ref).abs().max().item() <= 1e-4
+    _band_check(s_ref, sel, k, 1e-4)
+    want_sparse = oracle.sparse_attention(q, kc[:, :, :L], vc[:, :, :L], sel[None], kc[:, :, L:L + 1], vc[:, :, L:L + 1])
+    assert (out_sparse.float().cpu() - want_sparse).abs().max().item() <= 2e-2
+    # property: selecting every row (k = L) reproduces the dense result
+    idx_all, cnt_all = ops().topk(planes, n_prompt, dev_i32([L]))
+    out_all = ops().decode_attn(qg, kg, vg, cnt_all, idx=idx_all, k_tail=kg, v_tail=vg, tail_start=n_prompt,
+                                tail_len=dev_i32([1]))
+    torch.cuda.synchronize()
+    assert torch.equal(idx_all[0].cpu().long(), torch.arange(L))
+    assert (out_all.float() - out.float()).abs().max().item() <= 4e-3
+    # property: the result does not depend on the split count beyond rounding
+    out_s3 = ops().decode_attn(qg, kg, vg, n_all, n_splits=3)
+    assert (out_s3.float() - out.float()).abs().max().item() <= 4e-3
+
+
+# ------------------------------------------------------------------------------------------
+# KV append and the host-link gather
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_kv_append(dtype):
+    B, KVH, d, cap = 3, 8, 128, 50
+    kc = torch.zeros(B, KVH, cap, d, dtype=dtype, device="cuda")
+    vc = torch.zeros_like(kc)
+    kn = torch.randn(B, KVH, d, device="cuda").to(dtype)
+    vn = torch.randn(B, KVH, d, device="cuda").to(dtype)
+    pos = [0, 49, 17]
+    ops().kv_append(kn, vn, kc, vc, dev_i32(pos))
+    torch.cuda.synchronize()
+    for b, p in enumerate(pos):
+        assert torch.equal(kc[b, :, p], kn[b]) and torch.equal(vc[b, :, p], vn[b])
+    assert kc.float().abs().sum().item() == pytest.approx(kn.float().abs().sum().item(), rel=1e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_offload_gather(dtype):
+    tokens, layers, KVH, d, cap, n = 5000, 3, 8, 128, 400, 335
+    g = torch.Generator().manual_seed(3)
+    host = torch.randn(tokens, layers, 2, KVH, d, generator=g).to(dtype).pin_memory()
+    idx = torch.sort(torch.randperm(tokens, generator=g)[:n]).values
+    staged = torch.zeros(layers, 2, KVH, cap, d, dtype=dtype, device="cuda")
+    idx_dev = torch.zeros(cap, dtype=torch.int32, device="cuda")
+    idx_dev[:n] = idx.to(torch.int32).cuda()
+    ops().offload_gather(host, idx_dev, dev_i32([n]), staged)
+    torch.cuda.synchronize()
+    want = host[idx].permute(1, 2, 3, 0, 4)  # [layers, 2, KVH, n, d]
+    assert torch.equal(staged[:, :, :, :n].cpu(), want)
+    assert staged[:, :, :, n:].float().abs().sum().item() == 0.0
