@@ -1,0 +1,660 @@
+"""OmniKV's decode-time context selection on B200: the reference's ``modeling/omnikv.py`` API
+(``select_tokens_by_attn_universal``, ``OmniKVMulLayer``, ``OmniKVMulModel``, ``OmniKVMulLM``) over
+the sm_100a kernels of this package.
+
+What is different from the reference, and why the results are the same:
+
+* the filter layer's selector-``last`` scores are emitted by the layer's OWN decode attention
+  kernel while K streams through (same q, same prompt keys as modeling/omnikv.py:24-46, which
+  re-projects q and re-reads K in a separate matmul over a ``repeat_kv`` copy);
+* top-k + ascending order come from one kernel (``omnikv_topk``) instead of ``topk`` + ``sort``;
+* sparse layers read the selected rows through the index list (no gathered copy, no ``cat``);
+* lengths, k, and the window bookkeeping live in int32 device arrays, so a decode step has no
+  host synchronisation and can be captured in a CUDA graph (``OmniKVMulLM.generate_greedy``).
+
+The Llama decoder itself (embedding, RMSNorm, projections, SwiGLU, lm_head) is plain PyTorch here:
+in the reference it is third-party code (transformers' ``LlamaDecoderLayer``), not part of the path.
+"""
+from __future__ import annotations
+
+import math
+import time
+from types import SimpleNamespace
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from .. import ops
+from .omnikv_config import logger
+from .spec_cache import OmniKVMultiStageCache, WOPackCache, full_attn_layers_of, get_cache_cls  # noqa: F401
+
+_last_call_t = time.time()
+
+
+def time_analyze() -> float:
+    """Seconds since the previous call (modeling/offload_select_once.py:15-19)."""
+    global _last_call_t
+    now = time.time()
+    out = round(now - _last_call_t, 4)
+    _last_call_t = now
+    return out
+
+
+# ----------------------------------------------------------------------------------------------
+# rotary embedding (cos/sin generation is the boundary to the HF Llama patch,
+# modeling/patch_of_llama3_1.py: default, linear, dynamic-NTK and llama3 frequency rules)
+# ----------------------------------------------------------------------------------------------
+def _inv_freq(config, seq_len: Optional[int] = None) -> Tuple[torch.Tensor, float]:
+    d = config.head_dim
+    base = float(config.rope_theta)
+    scaling = getattr(config, "rope_scaling", None) or {}
+    kind = scaling.get("rope_type", scaling.get("type", "default"))
+    factor = float(scaling.get("factor", 1.0))
+    if kind == "dynamic" and seq_len is not None and seq_len > config.max_position_embeddings:
+        base = base * ((factor * seq_len / config.max_position_embeddings) - (factor - 1)) ** (d / (d - 2))
+    inv = 1.0 / (base ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    if kind == "linear":
+        inv = inv / factor
+    elif kind == "llama3":
+        lo, hi = float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
+        old = float(scaling["original_max_position_embeddings"])
+        wavelen = 2 * math.pi / inv
+        smooth = ((old / wavelen) - lo) / (hi - lo)
+        mid = (1 - smooth) * inv / factor + smooth * inv
+        inv = torch.where(wavelen > old / lo, inv / factor, torch.where(wavelen < old / hi, inv, mid))
+    elif kind not in ("default", "dynamic"):
+        raise NotImplementedError(f"rope_scaling type {kind!r}")
+    return inv, 1.0
+
+
+class OmniKVRotaryEmbedding(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        inv, _ = _inv_freq(config)
+        self.register_buffer("inv_freq", inv, persistent=False)
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor, position_ids: torch.Tensor):
+        """cos, sin ``[B, q, d]`` in x's dtype for integer positions ``[B, q]`` (computed in fp32)."""
+        freqs = position_ids.to(torch.float32)[:, :, None] * self.inv_freq.to(x.device)[None, None, :]
+        emb = torch.cat((freqs, freqs), dim=-1)
+        return emb.cos().to(x.dtype), emb.sin().to(x.dtype)
+
+
+def rotate_half(x):
+    h = x.shape[-1] // 2
+    return torch.cat((-x[..., h:], x[..., :h]), dim=-1)
+
+
+def apply_rotary(x, cos, sin):
+    """x ``[B, heads, q, d]``; cos/sin ``[B, q', d]`` with q' == q or 1 (broadcast)."""
+    return x * cos.unsqueeze(1) + rotate_half(x) * sin.unsqueeze(1)
+
+
+# ----------------------------------------------------------------------------------------------
+# the selector, reference signature
+# ----------------------------------------------------------------------------------------------
+def select_tokens_by_attn_universal(raw_attn, hidden_states, position_ids, past_key_value, num_selected_tokens,
+                                    consider_len, layer_idx=None, selector_cls="last"):
+    """Drop-in for modeling/omnikv.py:8-110: returns the ascending positions ``[B, k]`` (int64) of the
+    ``k = min(num_selected_tokens, consider_len)`` prompt tokens with the largest selector score.
+
+    ``raw_attn`` is read exactly as the reference reads it (``q_proj``, ``num_heads``, ``head_dim``,
+    ``num_key_value_heads``, ``rotary_emb(x, position_ids)``, ``layer_idx``); ``hidden_states`` is
+    ``[B, W, hidden]`` (W = 1 for ``last``) and, as in the reference, every window query is rotated
+    with the cos/sin of ``position_ids [B, 1]``.  Scores (fp32) and the top-k run in the CUDA kernels.
+    """
+    bsz, q_len, _ = hidden_states.shape
+    if not past_key_value:
+        raise AssertionError("select_tokens_by_attn_universal needs the KV cache")
+    if raw_attn.config.get("pretraining_tp", -1) > 1:
+        raise NotImplementedError
+    q = raw_attn.q_proj(hidden_states).view(bsz, q_len, raw_attn.num_heads, raw_attn.head_dim).transpose(1, 2)
+    cos, sin = raw_attn.rotary_emb(q, position_ids)
+    q = apply_rotary(q, cos, sin)
+    k_cache = past_key_value.key_cache[raw_attn.layer_idx]
+    if not k_cache.is_cuda:
+        raise ValueError("the filter layer's keys must be on the GPU (filter layers are never offloaded)")
+    q = q.to(k_cache.dtype)
+    dev = k_cache.device
+    n_dev = torch.full((bsz,), int(consider_len), dtype=torch.int32, device=dev)
+    k_dev = torch.full((bsz,), int(num_selected_tokens), dtype=torch.int32, device=dev)
+    if selector_cls == "last":
+        scores = ops.score_last(q[:, :, -1].contiguous(), k_cache, n_dev)
+    elif selector_cls in ("softmax_before_last", "uniform", "exp"):
+        scores = ops.score_window(q.contiguous(), k_cache, n_dev, selector_cls, max_len=int(consider_len))
+    else:
+        raise NotImplementedError
+    idx, _ = ops.topk(scores, n_dev, k_dev, max_len=int(consider_len))
+    return idx[:, : min(int(num_selected_tokens), int(consider_len))].long()
+
+
+# ----------------------------------------------------------------------------------------------
+# modules
+# ----------------------------------------------------------------------------------------------
+class RMSNorm(nn.Module):
+    def __init__(self, hidden_size, eps):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(hidden_size))
+        self.variance_epsilon = eps
+
+    def forward(self, x):
+        return F.rms_norm(x, (x.shape[-1],), self.weight, self.variance_epsilon)
+
+
+class _ProjView:
+    """``q_proj`` / ``k_proj`` / ... as views of a fused weight: callable and with ``.weight``."""
+
+    def __init__(self, owner, name, lo, hi):
+        self._owner, self._name, self._lo, self._hi = owner, name, lo, hi
+
+    @property
+    def weight(self):
+        return getattr(self._owner, self._name)[self._lo:self._hi]
+
+    def __call__(self, x):
+        return F.linear(x, self.weight)
+
+
+class OmniKVAttention(nn.Module):
+    """The ``self_attn`` object of a layer: Llama attention with fused QKV weights whose decode path
+    runs in ``omnikv_decode_attn`` through the cache."""
+
+    def __init__(self, config, layer_idx: int, tp=None):
+        super().__init__()
+        self.config = config
+        self.layer_idx = layer_idx
+        self.tp = tp
+        world = tp.world if tp is not None else 1
+        self.hidden_size = config.hidden_size
+        # with tensor parallelism these are the LOCAL head counts (KV heads are sharded, query heads follow)
+        self.num_heads = config.num_attention_heads // world
+        self.head_dim = config.head_dim
+        self.num_key_value_heads = config.num_key_value_heads // world
+        if self.num_key_value_heads * world != config.num_key_value_heads:
+            raise ValueError("the tensor-parallel size must divide the number of KV heads")
+        self.num_key_value_groups = self.num_heads // self.num_key_value_heads
+        nq, nkv = self.num_heads * self.head_dim, self.num_key_value_heads * self.head_dim
+        self.qkv_weight = nn.Parameter(torch.empty(nq + 2 * nkv, self.hidden_size))
+        self.o_weight = nn.Parameter(torch.empty(self.hidden_size, nq))
+        self.q_proj = _ProjView(self, "qkv_weight", 0, nq)
+        self.k_proj = _ProjView(self, "qkv_weight", nq, nq + nkv)
+        self.v_proj = _ProjView(self, "qkv_weight", nq + nkv, nq + 2 * nkv)
+        self.o_proj = _ProjView(self, "o_weight", 0, self.hidden_size)
+        self.rotary_emb = OmniKVRotaryEmbedding(config)
+
+    def qkv(self, x, cos, sin):
+        """x ``[B, n, hidden]`` -> rotated q ``[B,H,n,d]``, rotated k and v ``[B,KVH,n,d]``."""
+        B, n, _ = x.shape
+        nq, nkv = self.num_heads * self.head_dim, self.num_key_value_heads * self.head_dim
+        qkv = F.linear(x, self.qkv_weight)
+        q = qkv[..., :nq].view(B, n, self.num_heads, self.head_dim).transpose(1, 2)
+        k = qkv[..., nq:nq + nkv].view(B, n, self.num_key_value_heads, self.head_dim).transpose(1, 2)
+        v = qkv[..., nq + nkv:].view(B, n, self.num_key_value_heads, self.head_dim).transpose(1, 2)
+        return apply_rotary(q, cos, sin), apply_rotary(k, cos, sin), v
+
+    def forward(self, hidden_states, position_embeddings, past_key_value, score_out=None, score_len=None):
+        B, n, _ = hidden_states.shape
+        cos, sin = position_embeddings
+        q, k, v = self.qkv(hidden_states, cos, sin)
+        if n > 1:  # prefill: full causal attention over the fresh keys (what cache.update returns)
+            k, v = past_key_value.update(k, v, self.layer_idx)
+            o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.num_key_value_groups > 1)
+            o = o.transpose(1, 2).reshape(B, n, self.num_heads * self.head_dim)
+        else:
+            past_key_value.append_kv(k[:, :, 0].contiguous(), v[:, :, 0].contiguous(), self.layer_idx)
+            o = past_key_value.attend(q[:, :, 0].contiguous(), self.layer_idx, score_out=score_out,
+                                      score_len=score_len)
+            o = o.view(B, 1, self.num_heads * self.head_dim)
+        o = F.linear(o, self.o_weight)
+        return self.tp.all_reduce_sum(o) if self.tp is not None else o
+
+
+class OmniKVMLP(nn.Module):
+    def __init__(self, config, tp=None):
+        super().__init__()
+        self.tp = tp
+        self.intermediate_size = config.intermediate_size // (tp.world if tp is not None else 1)  # local slice
+        self.gate_up_weight = nn.Parameter(torch.empty(2 * self.intermediate_size, config.hidden_size))
+        self.down_weight = nn.Parameter(torch.empty(config.hidden_size, self.intermediate_size))
+        self.gate_proj = _ProjView(self, "gate_up_weight", 0, self.intermediate_size)
+        self.up_proj = _ProjView(self, "gate_up_weight", self.intermediate_size, 2 * self.intermediate_size)
+        self.down_proj = _ProjView(self, "down_weight", 0, config.hidden_size)
+
+    def forward(self, x):
+        gu = F.linear(x, self.gate_up_weight)
+        g, u = gu[..., : self.intermediate_size], gu[..., self.intermediate_size:]
+        o = F.linear(F.silu(g) * u, self.down_weight)
+        return self.tp.all_reduce_sum(o) if self.tp is not None else o
+
+
+class OmniKVMulLayer(nn.Module):
+    """Decoder layer with the filter-layer hook of modeling/omnikv.py:113-246."""
+
+    def __init__(self, config, layer_idx, tp=None):
+        super().__init__()
+        self.config = config
+        self.layer_idx = layer_idx
+        self.tp = tp
+        self.self_attn = OmniKVAttention(config, layer_idx, tp)
+        self.mlp = OmniKVMLP(config, tp)
+        self.input_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps)
+        self.post_attention_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps)
+        self.prefill_len = None
+        self.cache_cls = get_cache_cls(config)
+        self.sparse_in_prefill = config.get("sparse_in_prefill", False)
+        self.max_len_can_hold = config.get("max_len_can_hold", 32_000)
+        self.attn_seg_sz = config.get("attn_seg_sz", 8000)
+        self.do_select_layers = [int(i) for i in config.get("do_select_layers").split(",")]
+        self.hidden_state_window = None
+        self.selector_cls = config.get("selector_cls", "softmax_before_last")
+        self.window_size = config.get("window_size", 16)
+        self.decode_step = 0
+        self.is_filter = layer_idx in self.do_select_layers
+
+    # -- selection state -------------------------------------------------------------------------
+    def _init_selection_state(self, cache: OmniKVMultiStageCache, device) -> None:
+        """k, candidate range and window bookkeeping as int32 device arrays, per sequence, following
+        modeling/omnikv.py:167-188: ``k0 = int(frac * prefill_len)`` (truncation) or the integer;
+        for the window selectors ``nptw = max(0, window_size - decode_step)`` newest prompt positions
+        are outside the candidate range and are appended after the selection."""
+        P = cache.prefill_len_dev
+        B = P.shape[0]
+        nsel = self.config.get("num_of_selected_tokens", 4096)
+        if isinstance(nsel, float):
+            # int() truncation of the fraction, per sequence; computed on the host from exact integers
+            k0 = torch.tensor([int(nsel * p) for p in P.tolist()], dtype=torch.int32, device=device)
+        else:
+            k0 = torch.full((B,), int(nsel), dtype=torch.int32, device=device)
+        kcap = int(k0.max().item()) if B else 0
+        kcap = max(1, min(kcap, int(P.max().item()))) + self.window_size
+        st = SimpleNamespace()
+        st.k0 = k0
+        st.nptw = torch.full((B,), 0 if "last" in self.selector_cls else max(0, self.window_size - 1),
+                             dtype=torch.int32, device=device)
+        st.k = k0.clone()
+        st.consider = P.clone()
+        st.idx = torch.zeros(B, kcap, dtype=torch.int32, device=device)
+        st.count = torch.zeros(B, dtype=torch.int32, device=device)
+        st.max_len = int(P.max().item())
+        st.planes = None
+        cache.sel_state[self.layer_idx] = st
+        return st
+
+    def _select(self, hidden_states, position_embeddings, cache: OmniKVMultiStageCache) -> None:
+        """Window selectors: scores from ``omnikv_score_window`` on the observation window's queries."""
+        st, attn = cache.sel_state[self.layer_idx], self.self_attn
+        B = hidden_states.shape[0]
+        if "last" in self.selector_cls:  # "softmax_before_last": the current token only, no window bookkeeping
+            window_hs = hidden_states
+        else:
+            win = torch.cat([self.hidden_state_window, hidden_states], dim=1)[:, -self.window_size:]
+            if win.shape == self.hidden_state_window.shape:
+                self.hidden_state_window.copy_(win)  # same buffer every step: replayable in a CUDA graph
+            else:
+                self.hidden_state_window = win.contiguous()
+            window_hs = self.hidden_state_window
+        W = window_hs.shape[1]
+        cos, sin = position_embeddings
+        q = F.linear(window_hs, attn.q_proj.weight).view(B, W, attn.num_heads, attn.head_dim).transpose(1, 2)
+        q = apply_rotary(q, cos, sin).contiguous()
+        torch.sub(cache.prefill_len_dev, st.nptw, out=st.consider)
+        torch.clamp(st.k0 - st.nptw, min=1, out=st.k)
+        if st.planes is None:
+            st.planes = torch.zeros(B, st.max_len, dtype=torch.float32, device=q.device)
+        if self.tp is None:
+            ops.score_window(q, cache._k[self.layer_idx], st.consider, self.selector_cls, max_len=st.max_len,
+                             score_out=st.planes)
+        else:  # max over the local heads per window slot -> MAX over ranks -> weighted window sum
+            if getattr(st, "wplanes", None) is None:
+                st.wplanes = torch.zeros(B, W, st.max_len, dtype=torch.float32, device=q.device)
+            ops.score_window(q, cache._k[self.layer_idx], st.consider, self.selector_cls, max_len=st.max_len,
+                             planes_out=st.wplanes)
+            self.tp.all_reduce_max(st.wplanes)
+            ops.window_fold(st.wplanes, st.consider, self.selector_cls, max_len=st.max_len, score_out=st.planes)
+        ops.topk(st.planes, st.consider, st.k, append_n=st.nptw, idx_out=st.idx, count_out=st.count,
+                 max_len=st.max_len)
+        torch.clamp(st.nptw - 1, min=0, out=st.nptw)
+        cache.set_idx_device(st.idx, st.count, self.layer_idx)
+
+    def forward(self, hidden_states, attention_mask=None, position_ids=None, past_key_value=None,
+                output_attentions=False, use_cache=False, cache_position=None, position_embeddings=None):
+        residual = hidden_states
+        hidden_states = self.input_layernorm(hidden_states)
+        n = hidden_states.shape[1]
+        if n > 1:
+            self.prefill_len = n
+            if "last" not in self.selector_cls and self.is_filter:
+                self.hidden_state_window = hidden_states[:, -self.window_size:].clone()
+                self.decode_step = 1
+        if past_key_value is not None and not isinstance(past_key_value, self.cache_cls):
+            raise AssertionError(f"expected a {self.cache_cls.__name__}")
+        if position_embeddings is None:
+            position_embeddings = self.self_attn.rotary_emb(hidden_states, position_ids)
+
+        selecting = n == 1 and past_key_value is not None and self.is_filter
+        score_out = score_len = None
+        if selecting:
+            if not self.config.get("dense_more", False):
+                raise ValueError("dense_more=False is not supported")  # as modeling/omnikv.py:211-214
+            st = past_key_value.sel_state.get(self.layer_idx)
+            if st is None:  # first decode step on this cache (host reads of the lengths happen once, here)
+                st = self._init_selection_state(past_key_value, hidden_states.device)
+            if self.selector_cls == "last":
+                if st.planes is None:
+                    st.planes = torch.zeros(self.self_attn.num_key_value_heads, hidden_states.shape[0], st.max_len,
+                                            dtype=torch.float32, device=hidden_states.device)
+                score_out, score_len = st.planes, past_key_value.prefill_len_dev
+            else:
+                self._select(hidden_states, position_embeddings, past_key_value)
+
+        hidden_states = self.self_attn(hidden_states, position_embeddings, past_key_value, score_out=score_out,
+                                       score_len=score_len)
+        if selecting:
+            if score_out is not None:  # selector "last": the scores came out of the attention kernel
+                if self.tp is not None:  # plane j <- max over ranks of their j-th local KV head: order independent
+                    self.tp.all_reduce_max(st.planes)
+                ops.topk(st.planes, past_key_value.prefill_len_dev, st.k0, idx_out=st.idx, count_out=st.count,
+                         max_len=st.max_len)
+                past_key_value.set_idx_device(st.idx, st.count, self.layer_idx)
+            past_key_value.stage = "decoding"
+            self.decode_step += 1
+        hidden_states = residual + hidden_states
+
+        residual = hidden_states
+        hidden_states = self.post_attention_layernorm(hidden_states)
+        if n > 4000:  # prefill: MLP in 4000-token chunks (modeling/omnikv.py:233-235)
+            hidden_states = torch.cat([self.mlp(hs) for hs in torch.split(hidden_states, 4000, dim=1)], dim=1)
+        else:
+            hidden_states = self.mlp(hidden_states)
+        hidden_states = residual + hidden_states
+        outputs = (hidden_states,)
+        if output_attentions:
+            outputs += (None,)
+        if use_cache:
+            outputs += (past_key_value,)
+        return outputs
+
+
+class OmniKVMulModel(nn.Module):
+    def __init__(self, config, tp=None):
+        super().__init__()
+        self.config = config
+        self.tp = tp
+        self.padding_idx = config.pad_token_id
+        self.vocab_size = config.vocab_size
+        self.embed_tokens = nn.Embedding(config.vocab_size, config.hidden_size, self.padding_idx)
+        self.layers = nn.ModuleList([OmniKVMulLayer(config, i, tp) for i in range(config.num_hidden_layers)])
+        self.norm = RMSNorm(config.hidden_size, config.rms_norm_eps)
+        self.rotary_emb = OmniKVRotaryEmbedding(config)
+
+    def forward(self, input_ids=None, attention_mask=None, position_ids=None, past_key_values=None,
+                inputs_embeds=None, use_cache=None, output_attentions=None, output_hidden_states=None,
+                return_dict=None, cache_position=None):
+        h = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
+        B, n, _ = h.shape
+        cache = past_key_values
+        if n == 1:
+            cache.begin_decode_step()
+            if position_ids is None:
+                position_ids = cache.pos_dev[:, None]
+        elif position_ids is None:
+            position_ids = torch.arange(n, device=h.device)[None, :].expand(B, n)
+        pos_emb = self.rotary_emb(h, position_ids)
+        for layer in self.layers:
+            h = layer(h, attention_mask=attention_mask, position_ids=position_ids, past_key_value=cache,
+                      use_cache=use_cache, cache_position=cache_position, position_embeddings=pos_emb)[0]
+            if n > 1:
+                h = h.contiguous()
+        h = self.norm(h)
+        return SimpleNamespace(last_hidden_state=h, past_key_values=cache, hidden_states=None, attentions=None)
+
+
+class CausalLMOutputWithPast(SimpleNamespace):
+    def __getitem__(self, i):
+        return (self.logits, self.past_key_values)[i]
+
+
+class OmniKVMulLM(nn.Module):
+    """``model_cls = "multi"`` (modeling/omnikv.py:271-394)."""
+
+    def __init__(self, config, tp=None):
+        super().__init__()
+        if (fac := config.get("rope_factor", -1)) > 0:
+            config.rope_scaling = {"type": "dynamic", "factor": fac}
+        config.rope_scaling_ = config.rope_scaling
+        self.config = config
+        self.tp = tp
+        self.model = OmniKVMulModel(config, tp)
+        self.vocab_size = config.vocab_size
+        vocab_local = config.vocab_size // (tp.world if tp is not None else 1)  # vocabulary-sharded head
+        self.lm_head = nn.Linear(config.hidden_size, vocab_local, bias=False)
+        self.max_context_len = config.get("max_context_len", 50_000)
+        self.cache_cls = get_cache_cls(config)
+        self._graph = None
+
+    # -- construction ----------------------------------------------------------------------------
+    @torch.no_grad()
+    def init_random_(self, seed: int = 0, std: float = 0.02):
+        """Seeded N(0, std) weights, norm weights 1 (benchmarks run on random-init weights)."""
+        dev = self.lm_head.weight.device
+        rank = self.tp.rank if self.tp is not None else 0
+        g_shared = torch.Generator(device=dev).manual_seed(seed)             # replicated tensors
+        g_shard = torch.Generator(device=dev).manual_seed(seed + 1000 * (rank + 1))  # this rank's shards
+        for name, p in self.named_parameters():
+            g = g_shared if "embed_tokens" in name else g_shard
+            if p.dim() == 1:
+                p.fill_(1.0)
+            else:
+                step = max(1, (1 << 28) // max(1, p.shape[1]))
+                for s in range(0, p.shape[0], step):
+                    blk = p[s:s + step]
+                    blk.copy_(torch.randn(blk.shape, generator=g, device=p.device, dtype=torch.float32) * std)
+        return self
+
+    @classmethod
+    def from_config(cls, config, dtype=torch.bfloat16, device="cuda", seed: Optional[int] = 0, tp=None):
+        prev = torch.get_default_dtype()
+        torch.set_default_dtype(dtype)
+        try:
+            with torch.device(device):
+                m = cls(config, tp)
+        finally:
+            torch.set_default_dtype(prev)
+        m.eval()
+        if seed is not None:
+            m.init_random_(seed)
+        return m
+
+    @classmethod
+    def from_pretrained(cls, path, config=None, torch_dtype=torch.float16, device="cuda", **_unused):
+        """Load a Hugging Face Llama checkpoint directory (``*.safetensors``) into the fused layout."""
+        import glob
+        import os
+        from safetensors import safe_open  # optional dependency, only for real checkpoints
+
+        from .omnikv_config import LlamaCompressorConfig
+        config = config or LlamaCompressorConfig.from_pretrained(path)
+        m = cls.from_config(config, dtype=torch_dtype, device=device, seed=None)
+        sd = {}
+        for fn in sorted(glob.glob(os.path.join(path, "*.safetensors"))):
+            with safe_open(fn, framework="pt", device="cpu") as f:
+                for k in f.keys():
+                    sd[k] = f.get_tensor(k)
+        m.load_hf_state_dict(sd)
+        return m
+
+    @torch.no_grad()
+    def load_hf_state_dict(self, sd):
+        tp = self.tp
+
+        def put(dst, src, dim=None):
+            """Copy the full tensor, or this rank's slice of dimension ``dim`` when sharded."""
+            if tp is not None and dim is not None:
+                lo, hi = tp.shard(src.shape[dim])
+                src = src.narrow(dim, lo, hi - lo)
+            dst.copy_(src.to(dst.dtype))
+        put(self.model.embed_tokens.weight, sd["model.embed_tokens.weight"])
+        put(self.model.norm.weight, sd["model.norm.weight"])
+        put(self.lm_head.weight, sd.get("lm_head.weight", sd["model.embed_tokens.weight"]), 0)
+        for i, layer in enumerate(self.model.layers):
+            p = f"model.layers.{i}."
+            a, mlp = layer.self_attn, layer.mlp
+            for name in ("q_proj", "k_proj", "v_proj"):
+                put(getattr(a, name).weight, sd[p + f"self_attn.{name}.weight"], 0)
+            put(a.o_proj.weight, sd[p + "self_attn.o_proj.weight"], 1)
+            put(mlp.gate_proj.weight, sd[p + "mlp.gate_proj.weight"], 0)
+            put(mlp.up_proj.weight, sd[p + "mlp.up_proj.weight"], 0)
+            put(mlp.down_proj.weight, sd[p + "mlp.down_proj.weight"], 1)
+            put(layer.input_layernorm.weight, sd[p + "input_layernorm.weight"])
+            put(layer.post_attention_layernorm.weight, sd[p + "post_attention_layernorm.weight"])
+
+    def hf_state_dict(self):
+        """Weights under their Hugging Face Llama names (views of the fused tensors)."""
+        sd = {"model.embed_tokens.weight": self.model.embed_tokens.weight, "model.norm.weight": self.model.norm.weight,
+              "lm_head.weight": self.lm_head.weight}
+        for i, layer in enumerate(self.model.layers):
+            p = f"model.layers.{i}."
+            for name in ("q_proj", "k_proj", "v_proj", "o_proj"):
+                sd[p + f"self_attn.{name}.weight"] = getattr(layer.self_attn, name).weight
+            for name in ("gate_proj", "up_proj", "down_proj"):
+                sd[p + f"mlp.{name}.weight"] = getattr(layer.mlp, name).weight
+            sd[p + "input_layernorm.weight"] = layer.input_layernorm.weight
+            sd[p + "post_attention_layernorm.weight"] = layer.post_attention_layernorm.weight
+        return sd
+
+    # -- cache -----------------------------------------------------------------------------------
+    def new_cache(self, past_key_values=None):
+        """The cache wrap of modeling/omnikv.py:315-341."""
+        cache_cls_name = self.config.get("cache_cls", "default")
+        if cache_cls_name not in ("multi", "without_pack"):
+            raise NotImplementedError
+        do_sel_layers = [int(i) for i in self.config.get("do_select_layers").split(",")]
+        return self.cache_cls.from_dynamic_cache(
+            past_key_values,
+            full_attn_layers=full_attn_layers_of(do_sel_layers, self.config.num_hidden_layers),
+            num_hidden_layers=self.config.num_hidden_layers,
+            num_wait_load_layers=self.config.get("num_wait_load_layers", 2),
+            real_offload=self.config.get("real_offload", True),
+        )
+
+    # -- reference forward -----------------------------------------------------------------------
+    @torch.no_grad()
+    def forward(self, input_ids=None, attention_mask=None, position_ids=None, past_key_values=None,
+                inputs_embeds=None, labels=None, use_cache=None, output_attentions=None,
+                output_hidden_states=None, return_dict=None, cache_position=None):
+        n = input_ids.shape[1]
+        if not isinstance(past_key_values, self.cache_cls):
+            past_key_values = self.new_cache(past_key_values)
+        past_key_values.stage = "decoding" if n == 1 else "prefill"
+        outputs = self.model(input_ids=input_ids, attention_mask=attention_mask, position_ids=position_ids,
+                             past_key_values=past_key_values, inputs_embeds=inputs_embeds, use_cache=use_cache,
+                             cache_position=cache_position)
+        hidden_states = outputs.last_hidden_state[:, -1:]
+        logits = self._gather_logits(self.lm_head(hidden_states)).float()
+        if labels is not None:
+            raise NotImplementedError
+        if n > 1:
+            logger.info(f"---prefill time {round(time_analyze(), 3)}s")
+        else:
+            logger.info(f"---decoding time {round(time_analyze(), 3)}s")
+        return CausalLMOutputWithPast(loss=None, logits=logits, past_key_values=past_key_values,
+                                      hidden_states=None, attentions=None)
+
+    # -- decode engine ---------------------------------------------------------------------------
+    def _decode_step(self, tokens: torch.Tensor, cache) -> torch.Tensor:
+        """One decode step for tokens ``[B, 1]`` (device): fp32 logits ``[B, vocab]``.  No host sync."""
+        out = self.model(input_ids=tokens, past_key_values=cache)
+        return self._gather_logits(self.lm_head(out.last_hidden_state[:, -1])).float()
+
+    def _gather_logits(self, local):
+        return self.tp.all_gather_last(local) if self.tp is not None else local
+
+    @torch.no_grad()
+    def generate_greedy(self, input_ids: Optional[torch.Tensor], max_new_tokens: int, cache=None,
+                        first_token: Optional[torch.Tensor] = None, use_cuda_graph: bool = True,
+                        warmup_steps: int = 2) -> torch.Tensor:
+        """Greedy decoding.  Prefills ``input_ids`` (or continues from a filled ``cache`` with
+        ``first_token`` ``[B, 1]``), then runs ``max_new_tokens - 1`` decode steps on the device
+        without host synchronisation; with ``use_cuda_graph`` one step is captured and replayed.
+        Returns the generated ids ``[B, max_new_tokens]``."""
+        runner = DecodeRunner(self, input_ids, cache=cache, first_token=first_token, max_new_tokens=max_new_tokens,
+                              use_cuda_graph=use_cuda_graph, warmup_steps=warmup_steps)
+        runner.run(max_new_tokens - 1 - runner.steps_done)
+        return runner.tokens()
+
+
+class DecodeRunner:
+    """Greedy decode loop whose state lives on the device: the last token, the output buffer and the
+    step counter are device tensors, so steps chain without the host; ``use_cuda_graph`` captures one
+    step (all kernels of this package launch on the capturing stream) and replays it."""
+
+    def __init__(self, lm: OmniKVMulLM, input_ids, cache=None, first_token=None, max_new_tokens=128,
+                 use_cuda_graph=True, warmup_steps=2):
+        self.lm = lm
+        if cache is None:
+            out = lm(input_ids=input_ids)
+            cache = out.past_key_values
+            first_token = out.logits[:, -1].argmax(-1, keepdim=True)
+        self.cache = cache
+        cache.stage = "decoding"
+        B = first_token.shape[0]
+        dev = first_token.device
+        self.token = first_token.clone().to(torch.int64)              # [B,1] the token to feed next
+        self.out = torch.zeros(B, max_new_tokens, dtype=torch.int64, device=dev)
+        self.out[:, 0:1] = self.token
+        self.step_dev = torch.ones(1, 1, dtype=torch.int64, device=dev).expand(B, 1).contiguous()
+        self.logits = None
+        self.steps_done = 0
+        self.max_new_tokens = max_new_tokens
+        self.graph = None
+        self.launches_per_step = 0
+        if use_cuda_graph:
+            for _ in range(min(warmup_steps, max_new_tokens - 1)):
+                self._step()
+                self.steps_done += 1
+            if self.steps_done < max_new_tokens - 1:
+                self._capture()
+
+    def _step(self):
+        n0 = ops.launch_count()
+        logits = self.lm._decode_step(self.token, self.cache)
+        self.launches_per_step = ops.launch_count() - n0  # kernels of this package launched by one step
+        nxt = logits.argmax(-1, keepdim=True)
+        self.token.copy_(nxt)
+        self.out.scatter_(1, self.step_dev, nxt)
+        self.step_dev.add_(1)
+        if self.logits is None:
+            self.logits = torch.empty_like(logits)
+        self.logits.copy_(logits)
+
+    def _capture(self):
+        torch.cuda.synchronize()
+        seen = self.cache._seen_tokens
+        steps = [layer.decode_step for layer in self.lm.model.layers]
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._step()
+        # capture ran the host side of one step without executing it on the device
+        self.cache._seen_tokens = seen
+        for layer, s in zip(self.lm.model.layers, steps):
+            layer.decode_step = s
+
+    def run(self, n_steps: int) -> None:
+        n_steps = max(0, min(n_steps, self.max_new_tokens - 1 - self.steps_done))
+        for _ in range(n_steps):
+            if self.graph is not None:
+                self.graph.replay()
+                self.cache._seen_tokens += 1
+                for layer in self.lm.model.layers:
+                    if layer.is_filter:
+                        layer.decode_step += 1
+            else:
+                self._step()
+        self.steps_done += n_steps
+
+    def tokens(self) -> torch.Tensor:
+        return self.out[:, : self.steps_done + 1]

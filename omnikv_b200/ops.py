@@ -19,6 +19,17 @@ _SEL = {"softmax_before_last": abi.SEL_SOFTMAX_LAST, "uniform": abi.SEL_UNIFORM,
 
 _sm_count = {}
 _workspaces = {}
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far by this process (each ABI call adds what it launches)."""
+    return _launches
+
+
+def _count(n: int) -> None:
+    global _launches
+    _launches += n
 
 
 def sm_count(device) -> int:
@@ -137,6 +148,7 @@ def decode_attn(
             ws = workspace(q.device, need, "attn")
         p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
     abi.check(abi.lib().omnikv_decode_attn(C.byref(p), _stream()), "omnikv_decode_attn")
+    _count(1 if scores_only else 2)  # the attention kernel + the split merge
     return out
 
 
@@ -180,6 +192,7 @@ def topk(scores: torch.Tensor, length: torch.Tensor, k: torch.Tensor, *, append_
                               count_out.data_ptr(), _ptr(ws), 0 if ws is None else ws.numel() * ws.element_size(),
                               _stream()),
         "omnikv_topk")
+    _count(1)
     return idx_out, count_out
 
 
@@ -212,6 +225,7 @@ def score_window(qw: torch.Tensor, k: torch.Tensor, consider_len: torch.Tensor, 
         ws = workspace(qw.device, need, "window")
     p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
     abi.check(abi.lib().omnikv_score_window(C.byref(p), _stream()), "omnikv_score_window")
+    _count(3)  # pass 1, statistics merge, pass 2
     return score_out if planes_out is None else planes_out
 
 
@@ -224,6 +238,7 @@ def window_fold(planes: torch.Tensor, consider_len: torch.Tensor, selector: str,
     abi.check(abi.lib().omnikv_window_fold(planes.data_ptr(), score_out.data_ptr(), B, W, planes.stride(1),
                                            consider_len.data_ptr(), int(max_len), _SEL[selector], _stream()),
               "omnikv_window_fold")
+    _count(1)
     return score_out
 
 
@@ -238,6 +253,7 @@ def kv_append(k_new: torch.Tensor, v_new: torch.Tensor, k_cache: torch.Tensor, v
     abi.check(abi.lib().omnikv_kv_append(_DT[k_new.dtype], k_new.data_ptr(), v_new.data_ptr(), k_cache.data_ptr(),
                                          v_cache.data_ptr(), B, KVH, d, k_new.stride(0), k_new.stride(1), sb, sh, sr,
                                          pos.data_ptr(), _stream()), "omnikv_kv_append")
+    _count(1)
 
 
 def offload_gather(host_kv: torch.Tensor, idx: torch.Tensor, n_idx: torch.Tensor, staged: torch.Tensor,
@@ -257,6 +273,7 @@ def offload_gather(host_kv: torch.Tensor, idx: torch.Tensor, n_idx: torch.Tensor
     abi.check(abi.lib().omnikv_offload_gather(dev_ptr, host_kv.stride(0) * host_kv.element_size(), layers, KVH, d,
                                               host_kv.element_size(), idx.data_ptr(), n_idx.data_ptr(), cap,
                                               staged.data_ptr(), int(n_ctas), _stream()), "omnikv_offload_gather")
+    _count(1)
 
 
 def host_device_pointer(t: torch.Tensor) -> int:

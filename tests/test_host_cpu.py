@@ -1,0 +1,107 @@
+"""Host-side logic that needs no GPU: config semantics, layer plan, the C ABI's symbols."""
+import ctypes
+import json
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+G = ROOT / "tests" / "golden"
+
+
+def test_config_get_writes_default_back():
+    from omnikv_b200.modeling import LlamaCompressorConfig
+    c = LlamaCompressorConfig()
+    assert not hasattr(c, "window_size")
+    assert c.get("window_size", 16) == 16
+    assert c.window_size == 16            # written back, as modeling/omnikv_config.py:15-19
+    assert c.get("window_size", 99) == 16
+    c.set_config_of_compressor(**json.loads((ROOT / "tests" / "golden" / "example_config.json").read_text()))
+    assert c.get("do_select_layers") == "2,8,18" and c.get("num_of_selected_tokens") == 0.067
+    assert c.get("selector_cls", "softmax_before_last") == "last" and c.get("real_offload", True) is False
+
+
+@pytest.mark.parametrize("cls_name", ["OmniKVMultiStageCache", "WOPackCache"])
+def test_layer_plan_matches_reference_fixture(cls_name):
+    from omnikv_b200.modeling import spec_cache
+    cls = getattr(spec_cache, cls_name)
+    rows = [r for r in json.loads((G / "layer_plan.json").read_text()) if r["cls"] == cls_name]
+    assert rows
+    for row in rows:
+        assert spec_cache.full_attn_layers_of(row["do_select"], row["num_layers"]) == row["full_attn_layers"]
+        c = cls.from_dynamic_cache(None, row["full_attn_layers"], row["num_layers"], row["wait"], False)
+        want = {int(k): (bool(v[0]), v[1], v[2]) for k, v in row["layer_state"].items()}
+        assert c.layer_state == want, row
+        assert c.stage == "prefill" and c.device is None
+    c = cls([0, 2], 2, 0, True)
+    assert c.device == "cpu"
+
+
+def test_llama3_8b_plan_counts():
+    from omnikv_b200.modeling import spec_cache
+    c = spec_cache.OmniKVMultiStageCache(spec_cache.full_attn_layers_of([2, 8, 18], 32), 32, 1, False)
+    dense = sorted(i for i, s in c.layer_state.items() if not s[0])
+    assert dense == [0, 1, 2, 3, 8, 9, 18, 19]
+    assert c.groups == {2: [4, 5, 6, 7], 8: list(range(10, 18)), 18: list(range(20, 32))}
+
+
+def test_get_cache_cls():
+    from omnikv_b200.modeling import LlamaCompressorConfig, OmniKVMultiStageCache, WOPackCache, get_cache_cls
+    c = LlamaCompressorConfig()
+    c.set_config_of_compressor(cache_cls="multi")
+    assert get_cache_cls(c) is OmniKVMultiStageCache
+    c.cache_cls = "without_pack"
+    assert get_cache_cls(c) is WOPackCache
+    c.cache_cls = "eff"
+    with pytest.raises(NotImplementedError):
+        get_cache_cls(c)
+
+
+def test_library_exports_every_declared_symbol():
+    from omnikv_b200 import abi
+    header = (ROOT / "include" / "omnikv_b200.h").read_text()
+    declared = set(re.findall(r"\b(omnikv_[a-z0-9_]+)\s*\(", header))
+    assert declared == set(abi.SIGNATURES), declared ^ set(abi.SIGNATURES)
+    lib = abi.lib()
+    for name in declared:
+        assert getattr(lib, name) is not None
+    assert lib.omnikv_abi_version() == abi.ABI_VERSION == int(re.search(r"OMNIKV_ABI_VERSION (\d+)", header).group(1))
+    assert b"workspace" in lib.omnikv_strerror(-3)
+    assert lib.omnikv_decode_attn_workspace_bytes(1, 32, 37) == (32 * 37 * 128 + 32 * 37 * 2) * 4
+    assert lib.omnikv_topk_workspace_bytes(2, 1000) == 2 * 1000 * 4
+
+
+def test_bad_arguments_are_rejected_on_the_host():
+    """Validation happens before any launch, so it can be exercised without a GPU."""
+    from omnikv_b200 import abi
+    lib = abi.lib()
+    p = abi.AttnParams()
+    assert lib.omnikv_decode_attn(ctypes.byref(p), None) == -1          # null pointers
+    p.q = p.kA = p.vA = p.lenA = p.out = 256
+    p.B, p.H, p.KVH, p.head_dim, p.n_splits = 1, 32, 8, 64, 4
+    assert lib.omnikv_decode_attn(ctypes.byref(p), None) == -2          # head_dim 64 unsupported
+    p.head_dim = 128
+    p.q_stride_b, p.q_stride_h, p.a_stride_b, p.a_stride_h, p.a_stride_row = 4096, 128, 1 << 20, 1 << 17, 128
+    p.dtype = abi.BF16
+    assert lib.omnikv_decode_attn(ctypes.byref(p), None) == -3          # no workspace
+    p.H = 30
+    assert lib.omnikv_decode_attn(ctypes.byref(p), None) == -1          # H % KVH != 0
+    assert lib.omnikv_topk(None, 1, 0, 0, None, None, None, 1, 10, None, 10, None, None, 0, None) == -1
+    with pytest.raises(abi.OmniKVError):
+        abi.check(-2, "x")
+
+
+def test_ops_refuse_cpu_tensors():
+    from omnikv_b200 import abi, ops
+    q = torch.zeros(1, 32, 128)
+    k = torch.zeros(1, 8, 16, 128)
+    with pytest.raises(abi.OmniKVError):
+        ops.decode_attn(q, k, k, torch.zeros(1, dtype=torch.int32))
+
+
+def test_product_package_does_not_import_the_oracle():
+    for f in (ROOT / "omnikv_b200").rglob("*.py"):
+        text = f.read_text()
+        assert "import oracle" not in text and "from oracle" not in text, f
