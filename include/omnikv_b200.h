@@ -189,6 +189,36 @@ int omnikv_kv_append(int dtype, const void* k_new, const void* v_new, void* k_ca
                      int64_t cache_stride_b, int64_t cache_stride_h, int64_t cache_stride_row,
                      const int32_t* pos, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Batch-1 decode step: weight-streaming kernels with the element-wise work of the decoder layer
+ * fused in.  In the reference these are third-party transformers modules called around the hot
+ * path (LlamaRMSNorm, q/k/v/o_proj, apply_rotary_pos_emb, LlamaMLP, lm_head: the calls at
+ * modeling/omnikv.py:156, :219-236, :361-373) plus the cache append of modeling/spec_cache.py:363-369;
+ * at batch 1 they read 75 % of the step's bytes, so they decide the tokens/s the path delivers.
+ * 16-bit dtypes only; hidden sizes K in {512, 1024, 1792, 2048, 3584, 4096, 7168, 8192, 14336}.
+ * status: device int32, stays 0; a kernel whose bounded wait on a copy ran out writes a code there.
+ *
+ * omnikv_decode_qkv: x = RMSNorm(h) * norm_w; [q|k|v] = w_qkv x (rows: H q heads, KVH k heads, KVH v
+ *   heads, 128 rows each); RoPE at position *rope_pos with inv_freq[64] (rotate_half convention);
+ *   q -> q_out [H*128]; k, v -> row *cache_pos of k_cache_seq / v_cache_seq (one sequence's
+ *   [KVH, rows, 128] cache with the given element strides).
+ * omnikv_decode_gemv_residual: out[N] = (resid ? resid : 0) + w[N,K] x.  out may alias resid.
+ * omnikv_decode_gate_up: x = RMSNorm(h) * norm_w; act[i] = silu(w[i] . x) * (w[inter + i] . x).
+ * omnikv_decode_logits: x = RMSNorm(h) * norm_w; logits[r] = w_head[r] . x (fp32); token_out (optional)
+ *   = row_offset + argmax (lowest index among equal maxima); best_scratch: 8 bytes of device scratch.
+ * ------------------------------------------------------------------------------------------ */
+int omnikv_decode_qkv(int dtype, const void* h, const void* norm_w, float eps, const void* w_qkv, int hidden,
+                      int H, int KVH, int head_dim, const float* inv_freq, const int32_t* rope_pos,
+                      void* q_out, void* k_cache_seq, void* v_cache_seq, int64_t kv_stride_h,
+                      int64_t kv_stride_row, const int32_t* cache_pos, int32_t* status, void* stream);
+int omnikv_decode_gemv_residual(int dtype, const void* w, int N, int K, const void* x, const void* resid,
+                                void* out, int32_t* status, void* stream);
+int omnikv_decode_gate_up(int dtype, const void* h, const void* norm_w, float eps, const void* w_gate_up,
+                          int hidden, int inter, void* act_out, int32_t* status, void* stream);
+int omnikv_decode_logits(int dtype, const void* h, const void* norm_w, float eps, const void* w_head,
+                         int hidden, int vocab_rows, int row_offset, float* logits,
+                         unsigned long long* best_scratch, int64_t* token_out, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -254,6 +254,7 @@ class OmniKVMulLayer(nn.Module):
         self.window_size = config.get("window_size", 16)
         self.decode_step = 0
         self.is_filter = layer_idx in self.do_select_layers
+        self._fused_cache = {}
 
     # -- selection state -------------------------------------------------------------------------
     def _init_selection_state(self, cache: OmniKVMultiStageCache, device) -> None:
@@ -320,8 +321,78 @@ class OmniKVMulLayer(nn.Module):
         torch.clamp(st.nptw - 1, min=0, out=st.nptw)
         cache.set_idx_device(st.idx, st.count, self.layer_idx)
 
+    # -- batch-1 decode through the fused weight-streaming kernels -----------------------------------
+    def _fused_ok(self, hidden_states) -> bool:
+        if hidden_states.shape[0] != 1 or hidden_states.shape[1] != 1 or not hidden_states.is_cuda:
+            return False
+        key = hidden_states.dtype
+        ok = self._fused_cache.get(key)
+        if ok is None:
+            a = self.self_attn
+            ok = self.config.get("fused_decode", True) and ops.fused_decode_supported(
+                key, self.config.hidden_size, self.mlp.intermediate_size, a.num_heads * a.head_dim, 8)
+            self._fused_cache[key] = ok
+        return ok
+
+    def _forward_decode_fused(self, hidden_states, cache, position_embeddings):
+        """One decode token, batch 1: QKV+RoPE+append, attention (+scores, top-k on filter layers), output
+        projection + residual, gate/up + SiLU, down projection + residual -- five weight/KV streaming
+        launches plus the split merge.  The residual stream ``hidden_states`` is updated in place."""
+        attn, mlp, tp = self.self_attn, self.mlp, self.tp
+        h = hidden_states.view(-1)
+        dev, dt = h.device, h.dtype
+        bufs = cache.fused_bufs
+        if bufs is None:
+            bufs = cache.fused_bufs = SimpleNamespace(
+                q=torch.empty(1, attn.num_heads, attn.head_dim, dtype=dt, device=dev),
+                o=torch.empty(1, attn.num_heads, attn.head_dim, dtype=dt, device=dev),
+                act=torch.empty(mlp.intermediate_size, dtype=dt, device=dev))
+        selecting = self.is_filter
+        score_out = score_len = None
+        if selecting:
+            if not self.config.get("dense_more", False):
+                raise ValueError("dense_more=False is not supported")
+            st = cache.sel_state.get(self.layer_idx)
+            if st is None:
+                st = self._init_selection_state(cache, dev)
+            if self.selector_cls == "last":
+                if st.planes is None:
+                    st.planes = torch.zeros(attn.num_key_value_heads, 1, st.max_len, dtype=torch.float32, device=dev)
+                score_out, score_len = st.planes, cache.prefill_len_dev
+            else:
+                self._select(self.input_layernorm(hidden_states), position_embeddings, cache)
+        k_seq, v_seq, pos = cache.write_target(self.layer_idx)
+        ops.decode_qkv(h, self.input_layernorm.weight, self.input_layernorm.variance_epsilon, attn.qkv_weight,
+                       attn.num_heads, attn.num_key_value_heads, attn.rotary_emb.inv_freq, cache.pos_dev, bufs.q,
+                       k_seq, v_seq, pos)
+        cache.attend(bufs.q, self.layer_idx, out=bufs.o, score_out=score_out, score_len=score_len)
+        if selecting:
+            if score_out is not None:
+                if tp is not None:
+                    tp.all_reduce_max(st.planes)
+                ops.topk(st.planes, cache.prefill_len_dev, st.k0, idx_out=st.idx, count_out=st.count, max_len=st.max_len)
+                cache.set_idx_device(st.idx, st.count, self.layer_idx)
+            cache.stage = "decoding"
+            self.decode_step += 1
+        lead = tp is None or tp.rank == 0  # with tensor parallelism only one rank adds the residual before the SUM
+        ops.decode_gemv_residual(attn.o_weight, bufs.o.view(-1), h if lead else None, h)
+        if tp is not None:
+            tp.all_reduce_sum(h)
+        ops.decode_gate_up(h, self.post_attention_layernorm.weight, self.post_attention_layernorm.variance_epsilon,
+                           mlp.gate_up_weight, bufs.act)
+        ops.decode_gemv_residual(mlp.down_weight, bufs.act, h if lead else None, h)
+        if tp is not None:
+            tp.all_reduce_sum(h)
+        return (hidden_states,)
+
     def forward(self, hidden_states, attention_mask=None, position_ids=None, past_key_value=None,
                 output_attentions=False, use_cache=False, cache_position=None, position_embeddings=None):
+        if (past_key_value is not None and not output_attentions and position_embeddings is not None
+                and self._fused_ok(hidden_states)):
+            if not isinstance(past_key_value, self.cache_cls):
+                raise AssertionError(f"expected a {self.cache_cls.__name__}")
+            out = self._forward_decode_fused(hidden_states, past_key_value, position_embeddings)
+            return out + ((past_key_value,) if use_cache else ())
         residual = hidden_states
         hidden_states = self.input_layernorm(hidden_states)
         n = hidden_states.shape[1]
@@ -393,8 +464,8 @@ class OmniKVMulModel(nn.Module):
 
     def forward(self, input_ids=None, attention_mask=None, position_ids=None, past_key_values=None,
                 inputs_embeds=None, use_cache=None, output_attentions=None, output_hidden_states=None,
-                return_dict=None, cache_position=None):
-        h = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
+                return_dict=None, cache_position=None, apply_final_norm=True):
+        h = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds.clone()
         B, n, _ = h.shape
         cache = past_key_values
         if n == 1:
@@ -409,7 +480,8 @@ class OmniKVMulModel(nn.Module):
                       use_cache=use_cache, cache_position=cache_position, position_embeddings=pos_emb)[0]
             if n > 1:
                 h = h.contiguous()
-        h = self.norm(h)
+        if apply_final_norm:
+            h = self.norm(h)
         return SimpleNamespace(last_hidden_state=h, past_key_values=cache, hidden_states=None, attentions=None)
 
 
@@ -565,10 +637,30 @@ class OmniKVMulLM(nn.Module):
                                       hidden_states=None, attentions=None)
 
     # -- decode engine ---------------------------------------------------------------------------
-    def _decode_step(self, tokens: torch.Tensor, cache) -> torch.Tensor:
-        """One decode step for tokens ``[B, 1]`` (device): fp32 logits ``[B, vocab]``.  No host sync."""
-        out = self.model(input_ids=tokens, past_key_values=cache)
-        return self._gather_logits(self.lm_head(out.last_hidden_state[:, -1])).float()
+    def _decode_step(self, tokens: torch.Tensor, cache):
+        """One decode step for tokens ``[B, 1]`` (device): (fp32 logits ``[B, vocab]``, greedy next token
+        ``[B, 1]`` int64).  No host synchronisation.  At batch 1 in a 16-bit dtype the final norm, the
+        lm_head and the arg-max run in one fused weight-streaming kernel."""
+        layer0 = self.model.layers[0]
+        fused = tokens.shape[0] == 1 and layer0._fused_ok(self.model.embed_tokens.weight[:1].view(1, 1, -1))
+        out = self.model(input_ids=tokens, past_key_values=cache, apply_final_norm=not fused)
+        h = out.last_hidden_state[:, -1]
+        if not fused:
+            logits = self._gather_logits(self.lm_head(h)).float()
+            return logits, logits.argmax(-1, keepdim=True)
+        fb = cache.fused_bufs
+        if getattr(fb, "logits", None) is None:
+            fb.logits = torch.empty(1, self.lm_head.weight.shape[0], dtype=torch.float32, device=h.device)
+            fb.best = torch.zeros(1, dtype=torch.int64, device=h.device)
+            fb.token = torch.zeros(1, 1, dtype=torch.int64, device=h.device)
+        tp = self.tp
+        lo = tp.shard(self.vocab_size)[0] if tp is not None else 0
+        ops.decode_logits(h.reshape(-1), self.model.norm.weight, self.model.norm.variance_epsilon, self.lm_head.weight,
+                          lo, fb.logits, fb.best, fb.token if tp is None else None)
+        if tp is None:
+            return fb.logits, fb.token
+        logits = tp.all_gather_last(fb.logits)
+        return logits, logits.argmax(-1, keepdim=True)
 
     def _gather_logits(self, local):
         return self.tp.all_gather_last(local) if self.tp is not None else local
@@ -621,9 +713,8 @@ class DecodeRunner:
 
     def _step(self):
         n0 = ops.launch_count()
-        logits = self.lm._decode_step(self.token, self.cache)
+        logits, nxt = self.lm._decode_step(self.token, self.cache)
         self.launches_per_step = ops.launch_count() - n0  # kernels of this package launched by one step
-        nxt = logits.argmax(-1, keepdim=True)
         self.token.copy_(nxt)
         self.out.scatter_(1, self.step_dev, nxt)
         self.step_dev.add_(1)

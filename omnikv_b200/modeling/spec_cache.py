@@ -87,6 +87,7 @@ class OmniKVMultiStageCache:
         self._staged: Dict[int, torch.Tensor] = {}  # same keys -> device [nl, 2, KVH, kcap, d]
         self._idx: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}  # filter layer -> (idx int32 [B,kcap], count int32 [B])
         self._gather_done: Dict[int, torch.cuda.Event] = {}
+        self.fused_bufs = None                       # scratch of the fused batch-1 decode kernels (q, o, act, logits)
         self.sel_state: Dict[int, Any] = {}         # filter layer -> device-side selection state (k, ranges, index buffers)
         self._side_stream: Optional[torch.cuda.Stream] = None
         self.prefill_len: Optional[int] = None      # host copy (max over the batch)
@@ -247,6 +248,12 @@ class OmniKVMultiStageCache:
         from .. import ops
         pos = self.tail_pos_dev if self.is_offloaded(layer_idx) else self.pos_dev
         ops.kv_append(k_new, v_new, self._k[layer_idx], self._v[layer_idx], pos)
+
+    def write_target(self, layer_idx: int):
+        """(k rows, v rows, row index tensor) the current token of sequence 0 is written to: ``[KVH, rows, d]``
+        views of the layer's buffer and the int32 device position (tail-relative for offloaded layers)."""
+        pos = self.tail_pos_dev if self.is_offloaded(layer_idx) else self.pos_dev
+        return self._k[layer_idx][0], self._v[layer_idx][0], pos
 
     def _compat_kv(self, layer_idx):
         n = self._seen_tokens

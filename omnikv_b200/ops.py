@@ -283,3 +283,71 @@ def host_device_pointer(t: torch.Tensor) -> int:
     if t.is_cuda or not t.is_pinned():
         raise abi.OmniKVError("expected a pinned CPU tensor")
     return t.data_ptr()
+
+
+# ------------------------------------------------------------------------------------------------
+# batch-1 decode step: fused weight-streaming kernels
+# ------------------------------------------------------------------------------------------------
+FUSED_K = (512, 1024, 1792, 2048, 3584, 4096, 7168, 8192, 14336)
+_status = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """The device int32 the kernels report bounded-wait failures into (stays 0)."""
+    key = torch.device(device).index
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device) -> None:
+    """Synchronises and raises if a kernel recorded that a bounded wait ran out."""
+    code = int(status_word(device).item())
+    if code:
+        status_word(device).zero_()
+        raise abi.OmniKVError(f"a decode kernel gave up waiting for a shared-memory copy (code {code})")
+
+
+def rows_per_stage(K: int) -> int:
+    return 8 if K <= 4096 else (4 if K <= 8192 else 2)
+
+
+def fused_decode_supported(dtype, hidden: int, inter: int, n_q_rows: int, vocab_rows: int) -> bool:
+    """Whether the fused decode kernels cover these (local) shapes; otherwise callers use the torch ops."""
+    return (dtype in (torch.bfloat16, torch.float16) and hidden in FUSED_K and inter in FUSED_K
+            and n_q_rows in FUSED_K and hidden % rows_per_stage(inter) == 0 and hidden % rows_per_stage(n_q_rows) == 0
+            and inter % (rows_per_stage(hidden) // 2) == 0 and vocab_rows % rows_per_stage(hidden) == 0)
+
+
+def decode_qkv(h, norm_w, eps, w_qkv, H, KVH, inv_freq, rope_pos, q_out, k_cache_seq, v_cache_seq, cache_pos):
+    """h ``[hidden]``; w_qkv ``[(H+2KVH)*128, hidden]``; k/v_cache_seq: one sequence's ``[KVH, rows, 128]``."""
+    abi.check(abi.lib().omnikv_decode_qkv(_DT[h.dtype], h.data_ptr(), norm_w.data_ptr(), float(eps), w_qkv.data_ptr(),
+                                          w_qkv.shape[1], H, KVH, 128, inv_freq.data_ptr(), rope_pos.data_ptr(),
+                                          q_out.data_ptr(), k_cache_seq.data_ptr(), v_cache_seq.data_ptr(),
+                                          k_cache_seq.stride(0), k_cache_seq.stride(1), cache_pos.data_ptr(),
+                                          status_word(h.device).data_ptr(), _stream()), "omnikv_decode_qkv")
+    _count(1)
+
+
+def decode_gemv_residual(w, x, resid, out):
+    """out ``[N]`` = (resid or 0) + w ``[N,K]`` @ x ``[K]``; ``out`` may be ``resid``."""
+    abi.check(abi.lib().omnikv_decode_gemv_residual(_DT[x.dtype], w.data_ptr(), w.shape[0], w.shape[1], x.data_ptr(),
+                                                    _ptr(resid), out.data_ptr(), status_word(x.device).data_ptr(),
+                                                    _stream()), "omnikv_decode_gemv_residual")
+    _count(1)
+
+
+def decode_gate_up(h, norm_w, eps, w_gate_up, act_out):
+    abi.check(abi.lib().omnikv_decode_gate_up(_DT[h.dtype], h.data_ptr(), norm_w.data_ptr(), float(eps),
+                                              w_gate_up.data_ptr(), w_gate_up.shape[1], w_gate_up.shape[0] // 2,
+                                              act_out.data_ptr(), status_word(h.device).data_ptr(), _stream()),
+              "omnikv_decode_gate_up")
+    _count(1)
+
+
+def decode_logits(h, norm_w, eps, w_head, row_offset, logits, best, token_out=None):
+    abi.check(abi.lib().omnikv_decode_logits(_DT[h.dtype], h.data_ptr(), norm_w.data_ptr(), float(eps), w_head.data_ptr(),
+                                             w_head.shape[1], w_head.shape[0], int(row_offset), logits.data_ptr(),
+                                             best.data_ptr(), _ptr(token_out), status_word(h.device).data_ptr(),
+                                             _stream()), "omnikv_decode_logits")
+    _count(2 if token_out is not None else 1)

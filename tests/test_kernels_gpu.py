@@ -343,3 +343,105 @@ def test_offload_gather(dtype):
     want = host[idx].permute(1, 2, 3, 0, 4)  # [layers, 2, KVH, n, d]
     assert torch.equal(staged[:, :, :, :n].cpu(), want)
     assert staged[:, :, :, n:].float().abs().sum().item() == 0.0
+
+
+# ------------------------------------------------------------------------------------------
+# fused batch-1 decode kernels (weight streaming with TMA bulk copies) at Llama-3-8B shapes
+# ------------------------------------------------------------------------------------------
+def _close(got, ref, rel=1e-2, absol=1e-2):
+    err = (got.float().cpu() - ref.float().cpu()).abs()
+    lim = rel * ref.float().cpu().abs() + absol
+    assert bool((err <= lim).all()), (err.max().item(), (err - lim).max().item())
+
+
+def _rms(x, w, eps):
+    x = x.float()
+    return x * torch.rsqrt(x.pow(2).mean() + eps) * w.float()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("hidden,H,KVH", [(4096, 32, 8), (512, 4, 1), (8192, 8, 1)])
+def test_fused_qkv_rope_append(dtype, hidden, H, KVH):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    rn = lambda *s: torch.randn(*s, generator=g, device="cuda")  # noqa: E731
+    h = rn(hidden).to(dtype)
+    nw = (1 + 0.1 * rn(hidden)).to(dtype)
+    w = (rn((H + 2 * KVH) * 128, hidden) / hidden ** 0.5).to(dtype)
+    inv_freq = (1.0 / (500000.0 ** (torch.arange(0, 128, 2, dtype=torch.float32) / 128))).cuda()
+    pos = 70001
+    cap = 16
+    kc = torch.zeros(KVH, cap, 128, dtype=dtype, device="cuda")
+    vc = torch.zeros(KVH, cap, 128, dtype=dtype, device="cuda")
+    q = torch.zeros(H * 128, dtype=dtype, device="cuda")
+    ops().decode_qkv(h, nw, 1e-5, w, H, KVH, inv_freq, dev_i32([pos]), q, kc, vc, dev_i32([5]))
+    ops().check_status("cuda")
+    x = _rms(h, nw, 1e-5)
+    y = (w.float() @ x).view(H + 2 * KVH, 128)
+    ang = pos * inv_freq
+    cos, sin = torch.cat([ang.cos(), ang.cos()]), torch.cat([ang.sin(), ang.sin()])
+    rot = lambda t: t * cos + torch.cat([-t[:, 64:], t[:, :64]], dim=1) * sin  # noqa: E731
+    _close(q.view(H, 128), rot(y[:H]))
+    _close(kc[:, 5], rot(y[H:H + KVH]))
+    _close(vc[:, 5], y[H + KVH:])
+    assert kc[:, :5].abs().sum().item() == 0 and kc[:, 6:].abs().sum().item() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("N,K", [(4096, 4096), (4096, 14336), (512, 1024), (4096, 7168), (4096, 3584), (4096, 1792),
+                                 (8192, 8192), (4096, 2048), (4096, 512)])
+def test_fused_gemv_residual(dtype, N, K):
+    g = torch.Generator(device="cuda").manual_seed(2)
+    rn = lambda *s: torch.randn(*s, generator=g, device="cuda")  # noqa: E731
+    w = (rn(N, K) / K ** 0.5).to(dtype)
+    x, r = rn(K).to(dtype), rn(N).to(dtype)
+    out = torch.empty(N, dtype=dtype, device="cuda")
+    ops().decode_gemv_residual(w, x, r, out)
+    ref = w.float() @ x.float()
+    _close(out, ref + r.float())
+    ops().decode_gemv_residual(w, x, None, out)
+    _close(out, ref)
+    h = r.clone()
+    ops().decode_gemv_residual(w, x, h, h)  # in place
+    ops().check_status("cuda")
+    _close(h, ref + r.float())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("hidden,inter", [(4096, 14336), (512, 1024), (4096, 1792), (8192, 3584)])
+def test_fused_gate_up(dtype, hidden, inter):
+    g = torch.Generator(device="cuda").manual_seed(3)
+    rn = lambda *s: torch.randn(*s, generator=g, device="cuda")  # noqa: E731
+    h, nw = rn(hidden).to(dtype), (1 + 0.1 * rn(hidden)).to(dtype)
+    w = (rn(2 * inter, hidden) / hidden ** 0.5).to(dtype)
+    act = torch.empty(inter, dtype=dtype, device="cuda")
+    ops().decode_gate_up(h, nw, 1e-5, w, act)
+    ops().check_status("cuda")
+    y = w.float() @ _rms(h, nw, 1e-5)
+    _close(act, torch.nn.functional.silu(y[:inter]) * y[inter:])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("hidden,vocab,off", [(4096, 128256, 0), (512, 1000, 0), (4096, 16032, 32064)])
+def test_fused_logits_argmax(dtype, hidden, vocab, off):
+    g = torch.Generator(device="cuda").manual_seed(4)
+    rn = lambda *s: torch.randn(*s, generator=g, device="cuda")  # noqa: E731
+    h, nw = rn(hidden).to(dtype), (1 + 0.1 * rn(hidden)).to(dtype)
+    w = (rn(vocab, hidden) / hidden ** 0.5).to(dtype)
+    logits = torch.empty(vocab, dtype=torch.float32, device="cuda")
+    best = torch.zeros(1, dtype=torch.int64, device="cuda")
+    tok = torch.zeros(1, dtype=torch.int64, device="cuda")
+    for _ in range(2):  # the scratch word is re-initialised by every call
+        ops().decode_logits(h, nw, 1e-5, w, off, logits, best, tok)
+    ops().check_status("cuda")
+    ref = w.float() @ _rms(h, nw, 1e-5)
+    assert (logits - ref).abs().max().item() <= 2e-3
+    assert tok.item() == off + int(logits.argmax().item())
+    # ties: the lowest index wins
+    w[7] = w[3]
+    ops().decode_logits(h, nw, 1e-5, w, off, logits, best, tok)
+    big = logits.max().item()
+    h2 = h.clone()
+    w[3] = w[7] = (w[int(logits.argmax().item())].float() * 1.5).to(dtype)
+    ops().decode_logits(h2, nw, 1e-5, w, off, logits, best, tok)
+    if logits[3].item() == logits.max().item():
+        assert tok.item() == off + 3
