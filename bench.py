@@ -162,6 +162,8 @@ def main():
     ap.add_argument("--layers", type=int, default=32, help="decoder layers (the benchmark's is 32)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-chain", action="store_true", help="one launch per weight-streaming phase instead of the "
+                    "cooperative multi-phase launch")
     ap.add_argument("--profile-step", action="store_true",
                     help="after the warm-up, run ONE step between cudaProfilerStart/Stop and exit (for ncu "
                          "--profile-from-start off); prints no benchmark line")
@@ -184,6 +186,7 @@ def main():
     warmup = max(3, args.warmup)
     cfg = LlamaCompressorConfig(num_hidden_layers=args.layers)
     cfg.set_config_of_compressor(**OMNI)
+    cfg.set_config_of_compressor(fused_decode=True, chained_decode=not args.no_chain)
     lm = OmniKVMulLM.from_config(cfg, dtype=torch.bfloat16, device=dev, seed=0, tp=tp)
     graph_warm = 2
     reserve = graph_warm + 2 * (warmup + args.steps) + 16

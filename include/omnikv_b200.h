@@ -103,7 +103,10 @@ typedef struct {
   const int32_t* score_len;   /* device [B]: positions >= score_len[b] are not written */
   /* split-K */
   int32_t n_splits;           /* >= 1; rows of a sequence are cut into n_splits contiguous chunks */
-  void* workspace;            /* omnikv_decode_attn_workspace_bytes(B, H, n_splits) bytes */
+  void* workspace;            /* omnikv_decode_attn_workspace_bytes(B, H, n_splits) bytes, 16-byte aligned.  Its first
+                                 16 KiB are arrival counters (B*KVH <= 4096, n_splits <= 512): they must be ZERO before the first call
+                                 that uses this workspace; every call leaves them zero.  Calls that share a workspace
+                                 must not overlap on the GPU. */
   size_t workspace_bytes;
 } omnikv_attn_params;
 
@@ -218,6 +221,61 @@ int omnikv_decode_gate_up(int dtype, const void* h, const void* norm_w, float ep
 int omnikv_decode_logits(int dtype, const void* h, const void* norm_w, float eps, const void* w_head,
                          int hidden, int vocab_rows, int row_offset, float* logits,
                          unsigned long long* best_scratch, int64_t* token_out, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * omnikv_decode_chain: the weight-streaming phases between two attention calls of a batch-1 decode
+ * step in ONE cooperative launch (one CTA per SM, grid-wide barriers between phases):
+ *   [h += w_o attn_out] -> [act = silu(gate) * up of RMSNorm(h)] -> [h += w_down act]
+ *   -> [next layer's omnikv_decode_qkv on h]  or  [omnikv_decode_logits on h]
+ * Same arithmetic as the four single calls above; what it adds is that the weight stream never
+ * stops: while the CTAs wait at a barrier or load the next phase's activations, the producer
+ * thread keeps copying the next phase's rows into the shared-memory ring.  A phase whose weight
+ * pointer is NULL is skipped (w_o; w_gate_up together with w_down; w_qkv; w_head; w_qkv and w_head
+ * exclude each other).  Single GPU only: there is no collective between the phases.
+ * grid_sync: one device uint32, zero before the first use; the kernel leaves it ready for reuse.
+ * chunk_counters: four device int32 that are ZERO when the launch starts (the kernel does not reset them):
+ * CTAs then take weight chunks from shared counters as they become ready, which evens out SMs that get
+ * less memory bandwidth; NULL: static round-robin assignment.
+ * omnikv_decode_chain_supported: 1 when a kernel is built for (dtype, hidden, inter, H), else 0.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+  int32_t dtype, hidden, inter, H, KVH;
+  float eps;
+  void* h;                 /* [hidden] residual stream, updated in place */
+  const void* w_o;         /* [hidden, hidden] or NULL */
+  const void* attn_out;    /* [hidden] */
+  const void* post_norm_w; /* [hidden] */
+  const void* w_gate_up;   /* [2*inter, hidden] or NULL */
+  const void* w_down;      /* [hidden, inter] */
+  void* act_scratch;       /* [inter] */
+  const void* in_norm_w;   /* next layer's input norm [hidden] */
+  const void* w_qkv;       /* next layer's [(H+2KVH)*128, hidden] or NULL */
+  const float* inv_freq;
+  const int32_t* rope_pos;
+  void* q_out;
+  void* k_cache_seq;
+  void* v_cache_seq;
+  int64_t kv_stride_h, kv_stride_row;
+  const int32_t* cache_pos;
+  const void* final_norm_w;
+  const void* w_head;      /* [vocab_rows, hidden] or NULL */
+  int32_t vocab_rows;
+  float* logits;
+  unsigned long long* best_scratch;
+  int64_t* token_out;      /* may be NULL */
+  uint32_t* grid_sync;
+  int32_t* chunk_counters; /* may be NULL */
+  int32_t* status;
+  const void* next_w;      /* optional: the weights the NEXT launch will read first (next layer's w_o); the kernel asks
+                              for next_w_bytes of them to be brought into L2 when its own copies are issued */
+  size_t next_w_bytes;
+  void* trace;             /* optional profiling aid: device uint64 [n_SMs][32] of %globaltimer stamps per CTA
+                              ([0] start; [1+3p..3+3p] phase p: barrier passed, activations ready, rows done;
+                              [16+p] producer issued all copies of phase p); NULL: nothing is recorded */
+} omnikv_chain_params;
+
+int omnikv_decode_chain(const omnikv_chain_params* p, void* stream);
+int omnikv_decode_chain_supported(int dtype, int hidden, int inter, int H);
 
 #ifdef __cplusplus
 }

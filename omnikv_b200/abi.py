@@ -52,6 +52,23 @@ class WindowParams(C.Structure):
     ]
 
 
+class ChainParams(C.Structure):
+    """Mirror of ``omnikv_chain_params``."""
+
+    _fields_ = [
+        ("dtype", C.c_int32), ("hidden", C.c_int32), ("inter", C.c_int32), ("H", C.c_int32), ("KVH", C.c_int32),
+        ("eps", C.c_float),
+        ("h", C.c_void_p), ("w_o", C.c_void_p), ("attn_out", C.c_void_p), ("post_norm_w", C.c_void_p),
+        ("w_gate_up", C.c_void_p), ("w_down", C.c_void_p), ("act_scratch", C.c_void_p),
+        ("in_norm_w", C.c_void_p), ("w_qkv", C.c_void_p), ("inv_freq", C.c_void_p), ("rope_pos", C.c_void_p),
+        ("q_out", C.c_void_p), ("k_cache_seq", C.c_void_p), ("v_cache_seq", C.c_void_p),
+        ("kv_stride_h", C.c_int64), ("kv_stride_row", C.c_int64), ("cache_pos", C.c_void_p),
+        ("final_norm_w", C.c_void_p), ("w_head", C.c_void_p), ("vocab_rows", C.c_int32),
+        ("logits", C.c_void_p), ("best_scratch", C.c_void_p), ("token_out", C.c_void_p),
+        ("grid_sync", C.c_void_p), ("chunk_counters", C.c_void_p), ("status", C.c_void_p), ("next_w", C.c_void_p), ("next_w_bytes", C.c_size_t), ("trace", C.c_void_p),
+    ]
+
+
 # name -> (restype, argtypes); every symbol the header declares
 SIGNATURES = {
     "omnikv_abi_version": (C.c_int, []),
@@ -78,6 +95,8 @@ SIGNATURES = {
                                         C.c_void_p, C.c_void_p, C.c_void_p]),
     "omnikv_decode_logits": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_int, C.c_int,
                                        C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "omnikv_decode_chain": (C.c_int, [C.POINTER(ChainParams), C.c_void_p]),
+    "omnikv_decode_chain_supported": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "omnikv_kv_append": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
                                    C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
                                    C.c_void_p]),

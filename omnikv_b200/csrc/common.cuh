@@ -109,6 +109,7 @@ struct AttnWorkspace {
   float* o;
   float* ml;
 };
+constexpr size_t kAttnCntBytes = 16384;  // split-arrival counters at the start of the decode-attention workspace
 __host__ __device__ inline size_t attn_ws_o_floats(int B, int H, int S) { return (size_t)B * H * S * kHeadDim; }
 __host__ __device__ inline size_t attn_ws_ml_floats(int B, int H, int S) { return (size_t)B * H * S * 2; }
 

@@ -8,7 +8,8 @@
 // fp32: CUDA-core kernel (tensor cores would have to round the operands to tf32).
 //
 // Grid (n_splits, KVH, B).  Every CTA owns one contiguous chunk of the sequence's row list and
-// writes one un-normalised partial (o, m, l) per query head; a second kernel merges the splits.
+// writes one un-normalised partial (o, m, l) per query head; the CTA that finishes last for a (sequence,
+// KV head) merges that group's splits into the output, so an attention call is a single launch.
 #include "common.cuh"
 
 namespace omnikv {
@@ -33,6 +34,8 @@ struct AttnArgs {
   const int* score_len;
   float* ws_o;
   float* ws_ml;
+  unsigned* ws_cnt;   // [B*KVH] arrival counters of the splits, zero between launches
+  int out_is_T;       // unused placeholder for alignment
   int B, H, KVH, G, S;
   float scale;
 };
@@ -59,9 +62,68 @@ __device__ __forceinline__ void split_range(int n, int S, int split, int& r0, in
   r1 = min(n, r0 + chunk);
 }
 
+// After a CTA has written its partials: count it in; the CTA that completes the count of its (b, kvh)
+// merges the S partials of the group's heads into the output (log-sum-exp merge) and clears the counter.
+// Must be called by all NTHREADS threads.  One warp per head (the group's heads in parallel), a lane owns
+// four output dims.  w_s: shared scratch of NWARPS * S floats.
+template <typename T>
+__device__ __forceinline__ void finish_group(const AttnArgs& a, int b, int kvh, float* w_s, int* flag_s) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned prev = atomicAdd(a.ws_cnt + b * a.KVH + kvh, 1u);
+    *flag_s = (prev == (unsigned)(a.S - 1));
+  }
+  __syncthreads();
+  if (!*flag_s) return;
+  __threadfence();
+  const int G = a.G, S = a.S;
+  float* w = w_s + (size_t)warp * S;
+  for (int r = warp; r < G; r += NWARPS) {
+    const int h = kvh * G + r;
+    const size_t base = (size_t)(b * a.H + h) * S;
+    float M = -INFINITY;
+    for (int s = lane; s < S; s += 32) M = fmaxf(M, __ldcg(a.ws_ml + (base + s) * 2));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+    const float Mu = (M == -INFINITY) ? 0.f : M;
+    float l = 0.f;
+    __syncwarp();
+    for (int s = lane; s < S; s += 32) {
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.ws_ml + (base + s) * 2));
+      const float wt = (ml.x == -INFINITY) ? 0.f : exp2f((ml.x - Mu) * kLog2e);
+      w[s] = wt;
+      l = fmaf(ml.y, wt, l);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+    __syncwarp();
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4* op = reinterpret_cast<const float4*>(a.ws_o + base * kHeadDim) + lane;
+#pragma unroll 8
+    for (int s = 0; s < S; ++s) {
+      const float4 o = __ldcg(op + (size_t)s * (kHeadDim / 4));
+      const float wt = w[s];
+      acc.x = fmaf(o.x, wt, acc.x);
+      acc.y = fmaf(o.y, wt, acc.y);
+      acc.z = fmaf(o.z, wt, acc.z);
+      acc.w = fmaf(o.w, wt, acc.w);
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    T* dst = static_cast<T*>(a.out) + (size_t)b * a.q_sb + (size_t)h * a.q_sh + lane * 4;
+    dst[0] = from_float<T>(acc.x * inv);
+    dst[1] = from_float<T>(acc.y * inv);
+    dst[2] = from_float<T>(acc.z * inv);
+    dst[3] = from_float<T>(acc.w * inv);
+  }
+  if (tid == 0) a.ws_cnt[b * a.KVH + kvh] = 0u;
+}
+
 template <typename T, bool WITH_V, bool WITH_SCORE>
 __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const AttnArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ int last_flag;
   constexpr int STAGE_BYTES = (WITH_V ? 2 : 1) * TILE_BYTES;
   unsigned char* q_s = smem + STAGES * STAGE_BYTES;
 
@@ -88,6 +150,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
           ws_ml[base * 2 + 1] = 0.f;
         }
       }
+      finish_group<T>(a, b, kvh, reinterpret_cast<float*>(smem), &last_flag);
     }
     return;
   }
@@ -103,26 +166,34 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
     unsigned char* ks = smem + slot * STAGE_BYTES;
     unsigned char* vs = ks + TILE_BYTES;
     const int cc = tid & 15, rowi = tid >> 4;
+    // First resolve every row of the tile to its cache position (the index loads go out together), then
+    // issue the copies: the copies are asm statements the compiler will not move loads across.
+    long long off[TILE / 8];
+#pragma unroll
+    for (int i = 0; i < TILE / 8; ++i) {
+      const int R = r0 + tile * TILE + rowi + 8 * i;
+      off[i] = -1;
+      if (R < r1) {
+        if (R < nA) {
+          const long long pos = idx ? (long long)__ldg(idx + R) : (long long)R;
+          off[i] = pos * a.a_sr;
+        } else {
+          off[i] = ((long long)(startB + (R - nA)) * a.b_sr) | (1ll << 62);  // bit 62: segment B
+        }
+      }
+    }
 #pragma unroll
     for (int i = 0; i < TILE / 8; ++i) {
       const int row = rowi + 8 * i;
-      const int R = r0 + tile * TILE + row;
-      const bool valid = R < r1;
-      const T* ksrc = kA;
-      const T* vsrc = vA;
-      if (valid) {
-        if (R < nA) {
-          const size_t pos = idx ? (size_t)idx[R] : (size_t)R;
-          ksrc = kA + pos * a.a_sr;
-          if (WITH_V) vsrc = vA + pos * a.a_sr;
-        } else {
-          const size_t pos = (size_t)(startB + (R - nA));
-          ksrc = kB + pos * a.b_sr;
-          if (WITH_V) vsrc = vB + pos * a.b_sr;
-        }
-      }
+      const bool valid = off[i] >= 0;
+      const bool segB = valid && (off[i] >> 62);
+      const long long o = off[i] & ~(1ll << 62);
+      const T* ksrc = valid ? (segB ? kB : kA) + o : kA;
       cp_async16(ks + row * PITCH + cc * 16, ksrc + cc * 8, valid);
-      if (WITH_V) cp_async16(vs + row * PITCH + cc * 16, vsrc + cc * 8, valid);
+      if (WITH_V) {
+        const T* vsrc = valid ? (segB ? vB : vA) + o : vA;
+        cp_async16(vs + row * PITCH + cc * 16, vsrc + cc * 8, valid);
+      }
     }
   };
 
@@ -294,6 +365,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
       ws_ml[base * 2 + 1] = l;
     }
   }
+  // the shared scratch of finish_group starts behind the cross-warp merge area used above
+  finish_group<T>(a, b, kvh, ml_s + NWARPS * 16 * 2, &last_flag);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -305,6 +378,8 @@ __global__ void __launch_bounds__(NTHREADS) decode_attn_f32_kernel(const AttnArg
                                                                     const bool with_score) {
   __shared__ float o_s[NWARPS][G][kHeadDim];
   __shared__ float ml_s[NWARPS][G][2];
+  __shared__ float w_s[NWARPS * 512];
+  __shared__ int last_flag;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nA = a.lenA[b];
@@ -425,26 +500,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attn_f32_kernel(const AttnArg
       a.ws_ml[base * 2 + 1] = lv;
     }
   }
-}
-
-// Merge of the split-K partials: grid (H, B), one thread per output dim.
-template <typename T>
-__global__ void __launch_bounds__(kHeadDim) splitk_merge_kernel(const float* __restrict__ ws_o,
-                                                                const float* __restrict__ ws_ml, T* out,
-                                                                int64_t out_sb, int64_t out_sh, int H, int S) {
-  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
-  const size_t base = (size_t)(b * H + h) * S;
-  float M = -INFINITY;
-  for (int s = 0; s < S; ++s) M = fmaxf(M, ws_ml[(base + s) * 2]);
-  const float Mu = (M == -INFINITY) ? 0.f : M;
-  float acc = 0.f, l = 0.f;
-  for (int s = 0; s < S; ++s) {
-    const float ms = ws_ml[(base + s) * 2];
-    const float w = (ms == -INFINITY) ? 0.f : exp2f((ms - Mu) * kLog2e);
-    acc = fmaf(ws_o[(base + s) * kHeadDim + tid], w, acc);
-    l = fmaf(ws_ml[(base + s) * 2 + 1], w, l);
-  }
-  out[(size_t)b * out_sb + (size_t)h * out_sh + tid] = from_float<T>(l > 0.f ? acc / l : 0.f);
+  finish_group<float>(a, b, kvh, w_s, &last_flag);
 }
 
 template <typename T>
@@ -464,11 +520,6 @@ int launch_mma(const AttnArgs& a, bool with_v, bool with_score, cudaStream_t st)
     kern<<<grid, block, mma_smem_bytes<false>(), st>>>(a);
   }
   OMNIKV_CUDA_OK(cudaGetLastError());
-  if (with_v) {
-    splitk_merge_kernel<T><<<dim3(a.H, a.B), kHeadDim, 0, st>>>(a.ws_o, a.ws_ml, static_cast<T*>(a.out), a.q_sb,
-                                                                  a.q_sh, a.H, a.S);
-    OMNIKV_CUDA_OK(cudaGetLastError());
-  }
   return OMNIKV_OK;
 }
 
@@ -482,11 +533,6 @@ int launch_f32(const AttnArgs& a, bool with_v, bool with_score, cudaStream_t st)
     default: return OMNIKV_E_UNSUPPORTED;
   }
   OMNIKV_CUDA_OK(cudaGetLastError());
-  if (with_v) {
-    splitk_merge_kernel<float><<<dim3(a.H, a.B), kHeadDim, 0, st>>>(a.ws_o, a.ws_ml, static_cast<float*>(a.out),
-                                                                      a.q_sb, a.q_sh, a.H, a.S);
-    OMNIKV_CUDA_OK(cudaGetLastError());
-  }
   return OMNIKV_OK;
 }
 
@@ -497,7 +543,10 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 extern "C" size_t omnikv_decode_attn_workspace_bytes(int B, int H, int n_splits) {
   if (B <= 0 || H <= 0 || n_splits <= 0) return 0;
-  return (omnikv::attn_ws_o_floats(B, H, n_splits) + omnikv::attn_ws_ml_floats(B, H, n_splits)) * sizeof(float);
+  // [arrival counters: a fixed 16 KiB region, so that calls of different shapes sharing one workspace agree
+  //  on where it is][o partials][m, l partials]
+  return omnikv::kAttnCntBytes +
+         (omnikv::attn_ws_o_floats(B, H, n_splits) + omnikv::attn_ws_ml_floats(B, H, n_splits)) * sizeof(float);
 }
 
 extern "C" int omnikv_decode_attn(const omnikv_attn_params* p, void* stream) {
@@ -538,8 +587,11 @@ extern "C" int omnikv_decode_attn(const omnikv_attn_params* p, void* stream) {
   a.b_sb = p->b_stride_b; a.b_sh = p->b_stride_h; a.b_sr = p->b_stride_row;
   a.startB = p->startB; a.lenB = p->lenB;
   a.score_out = p->score_out; a.score_stride = p->score_stride; a.score_len = p->score_len;
-  a.ws_o = static_cast<float*>(p->workspace);
+  a.ws_cnt = static_cast<unsigned*>(p->workspace);
+  a.ws_o = with_v ? reinterpret_cast<float*>(static_cast<unsigned char*>(p->workspace) + kAttnCntBytes) : nullptr;
   a.ws_ml = with_v ? a.ws_o + attn_ws_o_floats(p->B, p->H, p->n_splits) : nullptr;
+  a.out_is_T = 0;
+  if (with_v && (p->n_splits > 512 || (size_t)p->B * p->KVH * 4 > kAttnCntBytes)) return OMNIKV_E_UNSUPPORTED;
   a.B = p->B; a.H = p->H; a.KVH = p->KVH; a.G = G; a.S = p->n_splits;
   a.scale = p->scale;
   cudaStream_t st = static_cast<cudaStream_t>(stream);

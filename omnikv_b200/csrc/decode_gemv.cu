@@ -52,6 +52,8 @@ struct GemvArgs {
   unsigned long long* best;         // packed (key << 32 | ~index), reduced with atomicMax
   int row_offset;                   // global index of row 0 (vocabulary shards)
   int* status;                      // device status word (0 = ok)
+  int* next_chunk;                  // device counter (zero at launch) for dynamic chunk scheduling, or nullptr:
+                                    // static round-robin over the CTAs
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
@@ -90,6 +92,11 @@ __device__ __forceinline__ void tma_bulk_g2s(void* smem_dst, const void* gmem_sr
                : "memory");
 }
 
+// Ask the memory system to bring [src, src + bytes) into L2; nothing waits for it.
+__device__ __forceinline__ void l2_prefetch(const void* gmem_src, unsigned bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(gmem_src), "r"(bytes) : "memory");
+}
+
 template <typename T>
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]);
 template <>
@@ -112,97 +119,146 @@ __device__ __forceinline__ void unpack8<__half>(const uint4& v, float (&f)[8]) {
   }
 }
 
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
+  return t;
+}
+
+// Shared-memory ring shared by the producer thread and the consumer warps of a CTA.
+struct Ring {
+  unsigned char* smem;      // GV_STAGES slots of slot_bytes
+  uint64_t* full_bar;
+  uint64_t* empty_bar;
+  unsigned slot_bytes;
+  int* slot_chunk;          // chunk held by each slot, -1 = the phase has no more chunks for this CTA
+  unsigned char* stage_x;   // staging area for the phase's activations (and norm weights), 16-byte aligned
+};
+
+// First row of the two pieces of chunk c.
+template <int HALF, int EPI>
+__device__ __forceinline__ void piece_rows(const GemvArgs& a, int c, int& row0, int& row1) {
+  if (EPI == EPI_QKV) {
+    constexpr int per_head = 64 / HALF;
+    const int head = c / per_head, j = c % per_head;
+    row0 = head * 128 + j * HALF;
+    row1 = row0 + 64;
+  } else if (EPI == EPI_GATEUP) {
+    row0 = c * HALF;
+    row1 = row0 + a.partner_rows;
+  } else {
+    row0 = c * 2 * HALF;
+    row1 = row0 + HALF;
+  }
+}
+
 // KV: 16-byte vectors per lane per K-slice; WK: warps along K.  K = WK * KV * 256.
 // RPS = 8 / WK rows per stage, in two pieces of RPS/2 rows.
+// Producer side of one phase: called by ONE thread.  `it` is the CTA's running chunk number (ring position).
 template <typename T, int KV, int WK, int EPI>
-__global__ void __launch_bounds__(GV_THREADS, 1) decode_gemv_kernel(const GemvArgs a) {
+__device__ __forceinline__ bool produce_phase(const GemvArgs& a, const Ring& ring, int& it) {
+  constexpr int HALF = GV_CONSUMER_WARPS / WK / 2;
+  constexpr int K = WK * KV * 256;
+  constexpr unsigned PIECE_BYTES = HALF * K * 2;
+  const T* W = static_cast<const T*>(a.W);
+  int i = 0;
+  for (;; ++it) {
+    const int slot = it % GV_STAGES;
+    if (it >= GV_STAGES && !mbar_wait(&ring.empty_bar[slot], ((it / GV_STAGES) - 1) & 1)) {
+      atomicExch(a.status, 1);
+      return false;
+    }
+    // next chunk: from the shared counter (whoever is ready takes the next one, so slow SMs take fewer),
+    // or this CTA's static share
+    int c;
+    if (a.next_chunk) {
+      c = atomicAdd(a.next_chunk, 1);
+    } else {
+      c = (int)blockIdx.x + i * (int)gridDim.x;
+      ++i;
+    }
+    if (c >= a.n_chunks) {  // end marker: the slot carries no data
+      ring.slot_chunk[slot] = -1;
+      mbar_arrive(&ring.full_bar[slot]);
+      ++it;
+      return true;
+    }
+    ring.slot_chunk[slot] = c;
+    int row0, row1;
+    piece_rows<HALF, EPI>(a, c, row0, row1);
+    unsigned char* dst = ring.smem + (size_t)slot * ring.slot_bytes;
+    mbar_expect_tx(&ring.full_bar[slot], 2 * PIECE_BYTES);
+    tma_bulk_g2s(dst, W + (size_t)row0 * K, PIECE_BYTES, &ring.full_bar[slot]);
+    tma_bulk_g2s(dst + PIECE_BYTES, W + (size_t)row1 * K, PIECE_BYTES, &ring.full_bar[slot]);
+  }
+}
+
+// The shared-memory ring covers about 4 us of HBM time; the pause between two phases (grid barrier + loading
+// the new activations) is longer.  So when the producer has issued the last copy of a phase it asks for the
+// first chunks of the NEXT phase to be brought into L2 (this CTA's round-robin share of them); the ring's
+// copies then find them there and HBM keeps working through the pause.
+constexpr int GV_L2_AHEAD = 4;  // chunks per CTA
+
+template <typename T, int KV, int WK, int EPI>
+__device__ __forceinline__ void prefetch_phase_head(const GemvArgs& a) {
+  constexpr int HALF = GV_CONSUMER_WARPS / WK / 2;
+  constexpr int K = WK * KV * 256;
+  constexpr unsigned PIECE_BYTES = HALF * K * 2;
+  const T* W = static_cast<const T*>(a.W);
+  for (int j = 0; j < GV_L2_AHEAD; ++j) {
+    const int c = (int)blockIdx.x + j * (int)gridDim.x;
+    if (c >= a.n_chunks) break;
+    int row0, row1;
+    piece_rows<HALF, EPI>(a, c, row0, row1);
+    l2_prefetch(W + (size_t)row0 * K, PIECE_BYTES);
+    l2_prefetch(W + (size_t)row1 * K, PIECE_BYTES);
+  }
+}
+
+// Scratch in static shared memory used by the consumers.
+struct ConsumerShared {
+  float part[2][GV_CONSUMER_WARPS][4];
+  float ssq[GV_CONSUMER_WARPS];
+  unsigned long long best[GV_CONSUMER_WARPS];
+  int fail;
+};
+
+__device__ __forceinline__ void consumer_bar() {
+  asm volatile("bar.sync 1, %0;\n" ::"n"(GV_CONSUMER_WARPS * 32) : "memory");
+}
+
+// Consumer side of one phase: called by the 256 consumer threads.  COHERENT: x and resid were written by
+// other CTAs of this same launch, so they are read through L2 (ld.global.cg), never from a stale L1 line.
+template <typename T, int KV, int WK, int EPI, bool COHERENT>
+__device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& ring, ConsumerShared& cs, int& it,
+                                              unsigned long long* stamp = nullptr) {
   constexpr int RPS = GV_CONSUMER_WARPS / WK;
   constexpr int HALF = RPS / 2;
   constexpr int K = WK * KV * 256;
   constexpr unsigned ROW_BYTES = K * 2;
-  constexpr unsigned PIECE_BYTES = HALF * ROW_BYTES;
-  constexpr unsigned STAGE_BYTES = 2 * PIECE_BYTES;
-  extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ __align__(8) uint64_t full_bar[GV_STAGES];
-  __shared__ __align__(8) uint64_t empty_bar[GV_STAGES];
-  __shared__ float part[2][RPS][WK];
-  __shared__ float ssq[GV_CONSUMER_WARPS];
-  __shared__ unsigned long long best_s[RPS];
-  __shared__ int fail_s;
-
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n_mine = a.n_chunks > (int)blockIdx.x ? (a.n_chunks - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-
-  if (tid == 0) {
-    fail_s = 0;
-#pragma unroll
-    for (int s = 0; s < GV_STAGES; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], GV_CONSUMER_WARPS);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-  }
-  __syncthreads();
-
-  // first row of the two pieces of chunk c
-  auto piece_rows = [&](int c, int& row0, int& row1) {
-    if (EPI == EPI_QKV) {
-      constexpr int per_head = 64 / HALF;
-      const int head = c / per_head, j = c % per_head;
-      row0 = head * 128 + j * HALF;
-      row1 = row0 + 64;
-    } else if (EPI == EPI_GATEUP) {
-      row0 = c * HALF;
-      row1 = row0 + a.partner_rows;
-    } else {
-      row0 = c * RPS;
-      row1 = row0 + HALF;
-    }
-  };
-
-  if (warp == GV_CONSUMER_WARPS) {
-    // ---------------- producer: one thread feeds the ring ----------------
-    if (lane == 0) {
-      const T* W = static_cast<const T*>(a.W);
-      for (int it = 0; it < n_mine; ++it) {
-        const int slot = it % GV_STAGES;
-        if (it >= GV_STAGES) {
-          if (!mbar_wait(&empty_bar[slot], ((it / GV_STAGES) - 1) & 1)) {
-            atomicExch(a.status, 1);
-            break;
-          }
-        }
-        int row0, row1;
-        piece_rows((int)blockIdx.x + it * (int)gridDim.x, row0, row1);
-        unsigned char* dst = smem + (size_t)slot * STAGE_BYTES;
-        mbar_expect_tx(&full_bar[slot], STAGE_BYTES);
-        tma_bulk_g2s(dst, W + (size_t)row0 * K, PIECE_BYTES, &full_bar[slot]);
-        tma_bulk_g2s(dst + PIECE_BYTES, W + (size_t)row1 * K, PIECE_BYTES, &full_bar[slot]);
-      }
-    }
-    return;
-  }
-
-  // ---------------- consumers ----------------
   const int wk = warp % WK;   // K-slice
   const int wr = warp / WK;   // row within the stage
-  // this warp's slice of x as fp32, times the norm weight; sum of squares of the raw x
-  float xr[KV][8];
+
+  // The activations (and the norm weights) are fetched ONCE per CTA into shared memory -- every SM reads the
+  // same few KB right after a barrier, and eight warps each fetching all of it made those L2 lines a hot
+  // spot -- then every warp takes its slice as fp32 registers, times the norm weight.
+  uint4* xs = reinterpret_cast<uint4*>(ring.stage_x);
+  uint4* ns = xs + K / 8;
   float sq = 0.f;
+  consumer_bar();  // the previous phase no longer reads the staging area
   {
-    const uint4* xv = reinterpret_cast<const uint4*>(static_cast<const T*>(a.x) + (size_t)wk * KV * 256);
-    const uint4* nv = a.norm_w ? reinterpret_cast<const uint4*>(static_cast<const T*>(a.norm_w) + (size_t)wk * KV * 256) : nullptr;
+    const uint4* xg = reinterpret_cast<const uint4*>(a.x);
+    const uint4* ng = reinterpret_cast<const uint4*>(a.norm_w);
+    for (int v = tid; v < K / 8; v += GV_CONSUMER_WARPS * 32) {
+      const uint4 raw = COHERENT ? __ldcg(xg + v) : xg[v];
+      xs[v] = raw;
+      if (ng) {
+        ns[v] = ng[v];
+        float f[8];
+        unpack8<T>(raw, f);
 #pragma unroll
-    for (int j = 0; j < KV; ++j) {
-      unpack8<T>(xv[j * 32 + lane], xr[j]);
-      if (nv) {
-        float nw[8];
-        unpack8<T>(nv[j * 32 + lane], nw);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          sq = fmaf(xr[j][e], xr[j][e], sq);
-          xr[j][e] *= nw[e];
-        }
+        for (int e = 0; e < 8; ++e) sq = fmaf(f[e], f[e], sq);
       }
     }
   }
@@ -210,25 +266,45 @@ __global__ void __launch_bounds__(GV_THREADS, 1) decode_gemv_kernel(const GemvAr
   if (a.norm_w) {
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
-    if (lane == 0) ssq[warp] = sq;
-    asm volatile("bar.sync 1, %0;\n" ::"n"(GV_CONSUMER_WARPS * 32) : "memory");
+    if (lane == 0) cs.ssq[warp] = sq;
+  }
+  consumer_bar();
+  if (a.norm_w) {
     float tot = 0.f;
 #pragma unroll
-    for (int w = 0; w < WK; ++w) tot += ssq[w];  // warps 0..WK-1 cover K once
+    for (int w = 0; w < GV_CONSUMER_WARPS; ++w) tot += cs.ssq[w];
     rstd = rsqrtf(tot / (float)K + a.eps);
   }
-
+  float xr[KV][8];
+#pragma unroll
+  for (int j = 0; j < KV; ++j) {
+    unpack8<T>(xs[wk * KV * 32 + j * 32 + lane], xr[j]);
+    if (a.norm_w) {
+      float nw[8];
+      unpack8<T>(ns[wk * KV * 32 + j * 32 + lane], nw);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) xr[j][e] *= nw[e];
+    }
+  }
+  if (stamp && threadIdx.x == 0) *stamp = globaltimer_ns();  // activations loaded, norm known
   unsigned long long my_best = 0ull;
-  for (int it = 0; it < n_mine; ++it) {
+  for (;; ++it) {
     const int slot = it % GV_STAGES;
-    bool ok = mbar_wait(&full_bar[slot], (it / GV_STAGES) & 1);
+    const bool ok = mbar_wait(&ring.full_bar[slot], (it / GV_STAGES) & 1);
     if (!ok) {  // the copy never landed: flag it; every consumer leaves together after the barrier below
-      fail_s = 1;
+      cs.fail = 1;
       atomicExch(a.status, 2);
+    }
+    const int chunk = ok ? ring.slot_chunk[slot] : -1;
+    if (ok && chunk < 0) {  // end marker of the phase: hand the slot back and stop
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ring.empty_bar[slot]);
+      ++it;
+      break;
     }
     float acc = 0.f;
     if (ok) {
-      const uint4* wsm = reinterpret_cast<const uint4*>(smem + (size_t)slot * STAGE_BYTES + (size_t)wr * ROW_BYTES) + wk * KV * 32;
+      const uint4* wsm = reinterpret_cast<const uint4*>(ring.smem + (size_t)slot * ring.slot_bytes + (size_t)wr * ROW_BYTES) + wk * KV * 32;
       float acc2[2] = {0.f, 0.f};
 #pragma unroll
       for (int j = 0; j < KV; ++j) {
@@ -241,11 +317,11 @@ __global__ void __launch_bounds__(GV_THREADS, 1) decode_gemv_kernel(const GemvAr
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
       __syncwarp();
-      if (lane == 0) mbar_arrive(&empty_bar[slot]);
+      if (lane == 0) mbar_arrive(&ring.empty_bar[slot]);
     }
-    if (lane == 0) part[it & 1][wr][wk] = acc;
-    asm volatile("bar.sync 1, %0;\n" ::"n"(GV_CONSUMER_WARPS * 32) : "memory");
-    if (fail_s) break;  // uniform: written before the barrier, never cleared
+    if (lane == 0) cs.part[it & 1][wr][wk] = acc;
+    consumer_bar();
+    if (cs.fail) return false;  // uniform: written before the barrier, never cleared
 
     // ---- epilogue: HALF threads, each owning row p of piece 0 and row p of piece 1 ----
     if (tid < HALF) {
@@ -253,20 +329,32 @@ __global__ void __launch_bounds__(GV_THREADS, 1) decode_gemv_kernel(const GemvAr
       float r0 = 0.f, r1 = 0.f;
 #pragma unroll
       for (int w = 0; w < WK; ++w) {
-        r0 += part[it & 1][p][w];
-        r1 += part[it & 1][p + HALF][w];
+        r0 += cs.part[it & 1][p][w];
+        r1 += cs.part[it & 1][p + HALF][w];
       }
       r0 *= rstd;
       r1 *= rstd;
       int row0, row1;
-      piece_rows((int)blockIdx.x + it * (int)gridDim.x, row0, row1);
+      piece_rows<HALF, EPI>(a, chunk, row0, row1);
       row0 += p;
       row1 += p;
       if (EPI == EPI_RESID) {
         const T* rs = static_cast<const T*>(a.resid);
         T* out = static_cast<T*>(a.out);
-        out[row0] = from_float<T>(r0 + (rs ? to_float(rs[row0]) : 0.f));
-        out[row1] = from_float<T>(r1 + (rs ? to_float(rs[row1]) : 0.f));
+        float b0 = 0.f, b1 = 0.f;
+        if (rs) {
+          if (COHERENT) {
+            const unsigned short u0 = __ldcg(reinterpret_cast<const unsigned short*>(rs) + row0);
+            const unsigned short u1 = __ldcg(reinterpret_cast<const unsigned short*>(rs) + row1);
+            b0 = to_float(*reinterpret_cast<const T*>(&u0));
+            b1 = to_float(*reinterpret_cast<const T*>(&u1));
+          } else {
+            b0 = to_float(rs[row0]);
+            b1 = to_float(rs[row1]);
+          }
+        }
+        out[row0] = from_float<T>(r0 + b0);
+        out[row1] = from_float<T>(r1 + b1);
       } else if (EPI == EPI_GATEUP) {
         const float sg = r0 / (1.f + __expf(-r0));
         static_cast<T*>(a.out)[row0] = from_float<T>(sg * r1);
@@ -277,13 +365,13 @@ __global__ void __launch_bounds__(GV_THREADS, 1) decode_gemv_kernel(const GemvAr
         const unsigned long long c1 = ((unsigned long long)float_to_key(r1) << 32) | (0xffffffffu - (unsigned)(a.row_offset + row1));
         my_best = max(my_best, max(c0, c1));
       } else {  // EPI_QKV
-        const int head = row0 >> 7, i = row0 & 127;  // i in [0, 64)
+        const int head = row0 >> 7, i2 = row0 & 127;  // i2 in [0, 64)
         float o0 = r0, o1 = r1;
         if (head < a.H + a.KVH) {
-          float sn, cs;
-          sincosf((float)(*a.rope_pos) * a.inv_freq[i], &sn, &cs);
-          o0 = r0 * cs - r1 * sn;
-          o1 = r1 * cs + r0 * sn;
+          float sn, cs_;
+          sincosf((float)(*a.rope_pos) * a.inv_freq[i2], &sn, &cs_);
+          o0 = r0 * cs_ - r1 * sn;
+          o1 = r1 * cs_ + r0 * sn;
         }
         T* dst;
         if (head < a.H) {
@@ -293,20 +381,176 @@ __global__ void __launch_bounds__(GV_THREADS, 1) decode_gemv_kernel(const GemvAr
         } else {
           dst = static_cast<T*>(a.v_cache) + (size_t)(head - a.H - a.KVH) * a.kv_sh + (size_t)(*a.pos) * a.kv_sr;
         }
-        dst[i] = from_float<T>(o0);
-        dst[i + 64] = from_float<T>(o1);
+        dst[i2] = from_float<T>(o0);
+        dst[i2 + 64] = from_float<T>(o1);
       }
     }
   }
   if (EPI == EPI_LOGITS) {
-    if (tid < HALF) best_s[tid] = my_best;
-    asm volatile("bar.sync 1, %0;\n" ::"n"(GV_CONSUMER_WARPS * 32) : "memory");
+    consumer_bar();
+    if (tid < HALF) cs.best[tid] = my_best;
+    consumer_bar();
     if (tid == 0) {
       unsigned long long b = 0ull;
 #pragma unroll
-      for (int i = 0; i < HALF; ++i) b = max(b, best_s[i]);
-      if (n_mine > 0) atomicMax(a.best, b);
+      for (int i = 0; i < HALF; ++i) b = max(b, cs.best[i]);
+      if (b != 0ull) atomicMax(a.best, b);
     }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void ring_init(uint64_t* full_bar, uint64_t* empty_bar, ConsumerShared& cs) {
+  if (threadIdx.x == 0) {
+    cs.fail = 0;
+#pragma unroll
+    for (int s = 0; s < GV_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], GV_CONSUMER_WARPS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncthreads();
+}
+
+// ---- one phase per launch ----------------------------------------------------------------------
+template <typename T, int KV, int WK, int EPI>
+__global__ void __launch_bounds__(GV_THREADS, 1) decode_gemv_kernel(const GemvArgs a) {
+  constexpr int K = WK * KV * 256;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) uint64_t full_bar[GV_STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[GV_STAGES];
+  __shared__ ConsumerShared cs;
+  __shared__ int slot_chunk[GV_STAGES];
+  ring_init(full_bar, empty_bar, cs);
+  constexpr unsigned SLOT = GV_CONSUMER_WARPS / WK * K * 2;
+  Ring ring{smem, full_bar, empty_bar, SLOT, slot_chunk, smem + GV_STAGES * SLOT};
+  int it = 0;
+  if ((threadIdx.x >> 5) == GV_CONSUMER_WARPS) {
+    if ((threadIdx.x & 31) == 0) produce_phase<T, KV, WK, EPI>(a, ring, it);
+    return;
+  }
+  consume_phase<T, KV, WK, EPI, false>(a, ring, cs, it);
+}
+
+// ---- the GEMV chain of a decoder layer in ONE cooperative launch -----------------------------------
+// Phases: [output projection + residual] -> [RMSNorm + gate/up + SiLU] -> [down projection + residual]
+// -> [RMSNorm + next layer's QKV + RoPE + append | final RMSNorm + logits + arg-max].  Between phases the
+// activations (a few KB) go through global memory and a grid-wide barrier; the weight stream does not
+// stop there: the producer thread keeps filling the ring with the next phase's rows, which depend on
+// nothing, so HBM stays busy across the barrier and across the per-phase prologue.
+struct ChainArgs {
+  GemvArgs ph[4];
+  int kind[4];          // ChainKind, or -1 when the phase is skipped
+  unsigned* grid_sync;  // one word: arrivals | generation << 16; zero before the first launch, self-resetting
+  unsigned long long* trace;  // optional [gridDim.x][32] globaltimer stamps (profiling), or nullptr
+  const void* next_w;         // optional: weights the next launch reads first, prefetched into L2 at the end
+  size_t next_w_bytes;
+};
+enum ChainKind { CK_O = 0, CK_GATEUP = 1, CK_DOWN = 2, CK_QKV = 3, CK_LOGITS = 4 };
+
+__device__ __forceinline__ unsigned ld_volatile_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.volatile.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Called by ONE thread per CTA after a CTA-level barrier.  One 32-bit word: arrivals in the low half,
+// generation in the high half.  The last arriver adds (1 << 16) - n_blocks, which clears the count and
+// bumps the generation in a single atomic; the others poll for the generation to change.  Bounded.
+__device__ __forceinline__ bool grid_barrier(unsigned* sync, unsigned n_blocks) {
+  __threadfence();
+  const unsigned old = atomicAdd(sync, 1u);
+  if ((old & 0xffffu) == n_blocks - 1) {
+    atomicAdd(sync, 0x10000u - n_blocks);
+  } else {
+    const unsigned gen = old >> 16;
+    unsigned spin = 0;
+    while ((ld_volatile_u32(sync) >> 16) == gen) {
+      if (++spin > GV_SPIN_LIMIT) return false;
+    }
+  }
+  __threadfence();
+  return true;
+}
+
+template <typename T, int KVH_, int WKH_, int KVI_, int WKI_>
+__global__ void __launch_bounds__(GV_THREADS, 1) decode_chain_kernel(const ChainArgs c) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) uint64_t full_bar[GV_STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[GV_STAGES];
+  __shared__ ConsumerShared cs;
+  constexpr unsigned SLOT_H = GV_CONSUMER_WARPS / WKH_ * (WKH_ * KVH_ * 256) * 2;
+  constexpr unsigned SLOT_I = GV_CONSUMER_WARPS / WKI_ * (WKI_ * KVI_ * 256) * 2;
+  unsigned long long* tr = c.trace ? c.trace + (size_t)blockIdx.x * 32 : nullptr;
+  if (tr && threadIdx.x == 0) tr[0] = globaltimer_ns();
+  __shared__ int slot_chunk[GV_STAGES];
+  ring_init(full_bar, empty_bar, cs);
+  constexpr unsigned SLOT = SLOT_H > SLOT_I ? SLOT_H : SLOT_I;
+  Ring ring{smem, full_bar, empty_bar, SLOT, slot_chunk, smem + GV_STAGES * SLOT};
+  int it = 0;
+  if ((threadIdx.x >> 5) == GV_CONSUMER_WARPS) {
+    if ((threadIdx.x & 31) == 0) {
+      for (int p = 0; p < 4; ++p) {
+        bool ok = true;
+        switch (c.kind[p]) {
+          case CK_O: ok = produce_phase<T, KVH_, WKH_, EPI_RESID>(c.ph[p], ring, it); break;
+          case CK_GATEUP: ok = produce_phase<T, KVH_, WKH_, EPI_GATEUP>(c.ph[p], ring, it); break;
+          case CK_DOWN: ok = produce_phase<T, KVI_, WKI_, EPI_RESID>(c.ph[p], ring, it); break;
+          case CK_QKV: ok = produce_phase<T, KVH_, WKH_, EPI_QKV>(c.ph[p], ring, it); break;
+          case CK_LOGITS: ok = produce_phase<T, KVH_, WKH_, EPI_LOGITS>(c.ph[p], ring, it); break;
+          default: break;
+        }
+        if (tr) tr[16 + p] = globaltimer_ns();  // all copies of phase p issued
+        if (!ok) break;
+        int nx = p + 1;
+        while (nx < 4 && c.kind[nx] < 0) ++nx;
+        if (nx < 4) {
+          switch (c.kind[nx]) {
+            case CK_GATEUP: prefetch_phase_head<T, KVH_, WKH_, EPI_GATEUP>(c.ph[nx]); break;
+            case CK_DOWN: prefetch_phase_head<T, KVI_, WKI_, EPI_RESID>(c.ph[nx]); break;
+            case CK_QKV: prefetch_phase_head<T, KVH_, WKH_, EPI_QKV>(c.ph[nx]); break;
+            case CK_LOGITS: prefetch_phase_head<T, KVH_, WKH_, EPI_LOGITS>(c.ph[nx]); break;
+            default: break;
+          }
+        } else if (c.next_w) {
+          // the weights the NEXT launch starts with: they wait in L2 while the attention kernel runs
+          const size_t per = ((c.next_w_bytes / gridDim.x) / 16) * 16;
+          const unsigned char* src = static_cast<const unsigned char*>(c.next_w) + (size_t)blockIdx.x * per;
+          for (size_t off = 0; off < per; off += 65536) l2_prefetch(src + off, (unsigned)(per - off < 65536 ? per - off : 65536));
+          break;
+        }
+      }
+    }
+    return;
+  }
+  bool first = true;
+  for (int p = 0; p < 4; ++p) {
+    if (c.kind[p] < 0) continue;
+    unsigned long long* st = tr ? tr + 1 + 3 * p : nullptr;  // [barrier passed, activations ready, rows done]
+    if (!first) {
+      // every CTA's outputs of the previous phase must be visible before this phase reads them
+      consumer_bar();
+      if (threadIdx.x == 0 && !grid_barrier(c.grid_sync, gridDim.x)) {
+        cs.fail = 1;
+        atomicExch(c.ph[p].status, 3);
+      }
+      consumer_bar();
+      if (cs.fail) return;
+    }
+    first = false;
+    if (st && threadIdx.x == 0) st[0] = globaltimer_ns();
+    bool ok = true;
+    switch (c.kind[p]) {
+      case CK_O: ok = consume_phase<T, KVH_, WKH_, EPI_RESID, true>(c.ph[p], ring, cs, it, st ? st + 1 : nullptr); break;
+      case CK_GATEUP: ok = consume_phase<T, KVH_, WKH_, EPI_GATEUP, true>(c.ph[p], ring, cs, it, st ? st + 1 : nullptr); break;
+      case CK_DOWN: ok = consume_phase<T, KVI_, WKI_, EPI_RESID, true>(c.ph[p], ring, cs, it, st ? st + 1 : nullptr); break;
+      case CK_QKV: ok = consume_phase<T, KVH_, WKH_, EPI_QKV, true>(c.ph[p], ring, cs, it, st ? st + 1 : nullptr); break;
+      case CK_LOGITS: ok = consume_phase<T, KVH_, WKH_, EPI_LOGITS, true>(c.ph[p], ring, cs, it, st ? st + 1 : nullptr); break;
+      default: break;
+    }
+    if (!ok) return;
+    if (st && threadIdx.x == 0) st[2] = globaltimer_ns();
   }
 }
 
@@ -318,7 +562,7 @@ template <typename T, int KV, int WK, int EPI>
 int launch_one(const GemvArgs& a, int n_sms, cudaStream_t st) {
   constexpr int K = WK * KV * 256;
   constexpr int RPS = GV_CONSUMER_WARPS / WK;
-  const size_t smem = (size_t)GV_STAGES * RPS * K * 2;
+  const size_t smem = (size_t)GV_STAGES * RPS * K * 2 + (size_t)K * 4;  // ring + staged activations and norm weights
   auto kern = decode_gemv_kernel<T, KV, WK, EPI>;
   OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int grid = a.n_chunks < n_sms ? a.n_chunks : n_sms;
@@ -351,6 +595,23 @@ int dispatch(int dtype, const GemvArgs& a, cudaStream_t st) {
   if (dtype == OMNIKV_BF16) return dispatch_k<__nv_bfloat16, EPI>(a, n_sms, st);
   if (dtype == OMNIKV_F16) return dispatch_k<__half, EPI>(a, n_sms, st);
   return OMNIKV_E_UNSUPPORTED;
+}
+
+template <typename T, int KVH_, int WKH_, int KVI_, int WKI_>
+int launch_chain(const ChainArgs& c, int n_sms, cudaStream_t st) {
+  constexpr unsigned SLOT_H = GV_CONSUMER_WARPS / WKH_ * (WKH_ * KVH_ * 256) * 2;
+  constexpr unsigned SLOT_I = GV_CONSUMER_WARPS / WKI_ * (WKI_ * KVI_ * 256) * 2;
+  constexpr int K_H = WKH_ * KVH_ * 256, K_I = WKI_ * KVI_ * 256;
+  const size_t smem = (size_t)GV_STAGES * (SLOT_H > SLOT_I ? SLOT_H : SLOT_I) + (size_t)(4 * K_H > 2 * K_I ? 4 * K_H : 2 * K_I);
+  auto kern = decode_chain_kernel<T, KVH_, WKH_, KVI_, WKI_>;
+  OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int per_sm = 0;
+  OMNIKV_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, GV_THREADS, smem));
+  if (per_sm < 1) return OMNIKV_E_UNSUPPORTED;
+  void* args[] = {const_cast<ChainArgs*>(&c)};
+  // cooperative: every CTA must be resident, the phases are separated by grid-wide barriers
+  OMNIKV_CUDA_OK(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kern), dim3(n_sms), dim3(GV_THREADS), args, smem, st));
+  return OMNIKV_OK;
 }
 
 int rows_per_stage(int K) {
@@ -426,4 +687,88 @@ extern "C" int omnikv_decode_logits(int dtype, const void* h, const void* norm_w
     OMNIKV_CUDA_OK(cudaGetLastError());
   }
   return OMNIKV_OK;
+}
+
+extern "C" int omnikv_decode_chain(const omnikv_chain_params* p, void* stream) {
+  using namespace omnikv;
+  if (!p || !p->h || !p->grid_sync || !p->status) return OMNIKV_E_BADARG;
+  if (p->dtype != OMNIKV_BF16 && p->dtype != OMNIKV_F16) return OMNIKV_E_UNSUPPORTED;
+  const int hidden = p->hidden, inter = p->inter;
+  if (p->H * kHeadDim != hidden) return OMNIKV_E_UNSUPPORTED;  // the output projection is square
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ChainArgs c = {};
+  for (int i = 0; i < 4; ++i) c.kind[i] = -1;
+  c.grid_sync = p->grid_sync;
+  c.trace = static_cast<unsigned long long*>(p->trace);
+  int* counters = p->chunk_counters;  // 4 ints, zero at launch (dynamic scheduling), or NULL (static)
+  c.next_w = p->next_w;
+  c.next_w_bytes = p->next_w ? p->next_w_bytes : 0;
+  const int rps_h = rows_per_stage(hidden), rps_i = rows_per_stage(inter);
+  if (p->w_o) {
+    if (!p->attn_out || !al16(p->w_o) || !al16(p->attn_out) || hidden % rps_h) return OMNIKV_E_BADARG;
+    GemvArgs& a = c.ph[0];
+    a.W = p->w_o; a.x = p->attn_out; a.N = hidden; a.K = hidden; a.n_chunks = hidden / rps_h;
+    a.resid = p->h; a.out = p->h; a.status = p->status; a.next_chunk = counters ? counters + 0 : nullptr;
+    c.kind[0] = CK_O;
+  }
+  if (p->w_gate_up) {
+    if (!p->w_down || !p->post_norm_w || !p->act_scratch || !al16(p->w_gate_up) || !al16(p->w_down) ||
+        !al16(p->act_scratch) || inter % (rps_h / 2) || hidden % rps_i)
+      return OMNIKV_E_BADARG;
+    GemvArgs& g = c.ph[1];
+    g.W = p->w_gate_up; g.x = p->h; g.norm_w = p->post_norm_w; g.eps = p->eps; g.N = 2 * inter; g.K = hidden;
+    g.n_chunks = inter / (rps_h / 2); g.partner_rows = inter; g.out = p->act_scratch; g.status = p->status;
+    g.next_chunk = counters ? counters + 1 : nullptr;
+    c.kind[1] = CK_GATEUP;
+    GemvArgs& d = c.ph[2];
+    d.W = p->w_down; d.x = p->act_scratch; d.N = hidden; d.K = inter; d.n_chunks = hidden / rps_i;
+    d.resid = p->h; d.out = p->h; d.status = p->status; d.next_chunk = counters ? counters + 2 : nullptr;
+    c.kind[2] = CK_DOWN;
+  }
+  if (p->w_qkv && p->w_head) return OMNIKV_E_BADARG;
+  if (p->w_qkv) {
+    if (!p->in_norm_w || !p->inv_freq || !p->rope_pos || !p->q_out || !p->k_cache_seq || !p->v_cache_seq ||
+        !p->cache_pos || !al16(p->w_qkv))
+      return OMNIKV_E_BADARG;
+    GemvArgs& a = c.ph[3];
+    a.W = p->w_qkv; a.x = p->h; a.norm_w = p->in_norm_w; a.eps = p->eps; a.N = (p->H + 2 * p->KVH) * kHeadDim;
+    a.K = hidden; a.n_chunks = a.N / rps_h; a.partner_rows = 64;
+    a.q_out = p->q_out; a.k_cache = p->k_cache_seq; a.v_cache = p->v_cache_seq; a.kv_sh = p->kv_stride_h;
+    a.kv_sr = p->kv_stride_row; a.pos = p->cache_pos; a.rope_pos = p->rope_pos; a.inv_freq = p->inv_freq;
+    a.H = p->H; a.KVH = p->KVH; a.status = p->status; a.next_chunk = counters ? counters + 3 : nullptr;
+    c.kind[3] = CK_QKV;
+  } else if (p->w_head) {
+    if (!p->final_norm_w || !p->logits || !p->best_scratch || p->vocab_rows <= 0 || p->vocab_rows % rps_h ||
+        !al16(p->w_head))
+      return OMNIKV_E_BADARG;
+    OMNIKV_CUDA_OK(cudaMemsetAsync(p->best_scratch, 0, sizeof(unsigned long long), st));
+    GemvArgs& a = c.ph[3];
+    a.W = p->w_head; a.x = p->h; a.norm_w = p->final_norm_w; a.eps = p->eps; a.N = p->vocab_rows; a.K = hidden;
+    a.n_chunks = p->vocab_rows / rps_h; a.logits = p->logits; a.best = p->best_scratch; a.row_offset = 0;
+    a.status = p->status; a.next_chunk = counters ? counters + 3 : nullptr;
+    c.kind[3] = CK_LOGITS;
+  }
+  int dev = 0, n_sms = 0;
+  OMNIKV_CUDA_OK(cudaGetDevice(&dev));
+  OMNIKV_CUDA_OK(cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev));
+  int rc = OMNIKV_E_UNSUPPORTED;
+  const bool bf = p->dtype == OMNIKV_BF16;
+  if (hidden == 4096 && inter == 14336)
+    rc = bf ? launch_chain<__nv_bfloat16, 16, 1, 14, 4>(c, n_sms, st) : launch_chain<__half, 16, 1, 14, 4>(c, n_sms, st);
+  else if (hidden == 512 && inter == 1024)
+    rc = bf ? launch_chain<__nv_bfloat16, 2, 1, 4, 1>(c, n_sms, st) : launch_chain<__half, 2, 1, 4, 1>(c, n_sms, st);
+  else if (hidden == 2048 && inter == 7168)
+    rc = bf ? launch_chain<__nv_bfloat16, 8, 1, 14, 2>(c, n_sms, st) : launch_chain<__half, 8, 1, 14, 2>(c, n_sms, st);
+  if (rc != OMNIKV_OK) return rc;
+  if (p->w_head && p->token_out) {
+    argmax_finalize_kernel<<<1, 1, 0, st>>>(p->best_scratch, reinterpret_cast<long long*>(p->token_out));
+    OMNIKV_CUDA_OK(cudaGetLastError());
+  }
+  return OMNIKV_OK;
+}
+
+extern "C" int omnikv_decode_chain_supported(int dtype, int hidden, int inter, int H) {
+  if (dtype != OMNIKV_BF16 && dtype != OMNIKV_F16) return 0;
+  if (H * omnikv::kHeadDim != hidden) return 0;
+  return (hidden == 4096 && inter == 14336) || (hidden == 512 && inter == 1024) || (hidden == 2048 && inter == 7168);
 }

@@ -334,46 +334,65 @@ class OmniKVMulLayer(nn.Module):
             self._fused_cache[key] = ok
         return ok
 
+    def _fused_bufs(self, cache, dev, dt):
+        bufs = cache.fused_bufs
+        if bufs is None:
+            attn, mlp = self.self_attn, self.mlp
+            bufs = cache.fused_bufs = SimpleNamespace(
+                q=torch.empty(1, attn.num_heads, attn.head_dim, dtype=dt, device=dev),
+                o=torch.empty(1, attn.num_heads, attn.head_dim, dtype=dt, device=dev),
+                act=torch.empty(mlp.intermediate_size, dtype=dt, device=dev))
+        return bufs
+
+    def _decode_select_begin(self, hidden_states, cache, position_embeddings):
+        """Filter layer, before its attention: selector ``last`` hands the attention kernel the score planes to
+        fill; the window selectors run their own scoring kernels on the observation window now.
+        Returns (score_out, score_len)."""
+        if not self.is_filter:
+            return None, None
+        if not self.config.get("dense_more", False):
+            raise ValueError("dense_more=False is not supported")  # as modeling/omnikv.py:211-214
+        dev = hidden_states.device
+        st = cache.sel_state.get(self.layer_idx)
+        if st is None:  # first decode step on this cache (host reads of the lengths happen once, here)
+            st = self._init_selection_state(cache, dev)
+        if self.selector_cls == "last":
+            if st.planes is None:
+                st.planes = torch.zeros(self.self_attn.num_key_value_heads, hidden_states.shape[0], st.max_len,
+                                        dtype=torch.float32, device=dev)
+            return st.planes, cache.prefill_len_dev
+        if position_embeddings is None:
+            position_embeddings = self.self_attn.rotary_emb(hidden_states, cache.pos_dev[:, None])
+        self._select(self.input_layernorm(hidden_states), position_embeddings, cache)
+        return None, None
+
+    def _decode_select_end(self, cache, score_out):
+        """Filter layer, after its attention: top-k of the planes the attention kernel filled (selector ``last``)."""
+        if not self.is_filter:
+            return
+        if score_out is not None:
+            st = cache.sel_state[self.layer_idx]
+            if self.tp is not None:  # plane j <- max over ranks of their j-th local KV head: order independent
+                self.tp.all_reduce_max(st.planes)
+            ops.topk(st.planes, cache.prefill_len_dev, st.k0, idx_out=st.idx, count_out=st.count, max_len=st.max_len)
+            cache.set_idx_device(st.idx, st.count, self.layer_idx)
+        cache.stage = "decoding"
+        self.decode_step += 1
+
     def _forward_decode_fused(self, hidden_states, cache, position_embeddings):
         """One decode token, batch 1: QKV+RoPE+append, attention (+scores, top-k on filter layers), output
         projection + residual, gate/up + SiLU, down projection + residual -- five weight/KV streaming
         launches plus the split merge.  The residual stream ``hidden_states`` is updated in place."""
         attn, mlp, tp = self.self_attn, self.mlp, self.tp
         h = hidden_states.view(-1)
-        dev, dt = h.device, h.dtype
-        bufs = cache.fused_bufs
-        if bufs is None:
-            bufs = cache.fused_bufs = SimpleNamespace(
-                q=torch.empty(1, attn.num_heads, attn.head_dim, dtype=dt, device=dev),
-                o=torch.empty(1, attn.num_heads, attn.head_dim, dtype=dt, device=dev),
-                act=torch.empty(mlp.intermediate_size, dtype=dt, device=dev))
-        selecting = self.is_filter
-        score_out = score_len = None
-        if selecting:
-            if not self.config.get("dense_more", False):
-                raise ValueError("dense_more=False is not supported")
-            st = cache.sel_state.get(self.layer_idx)
-            if st is None:
-                st = self._init_selection_state(cache, dev)
-            if self.selector_cls == "last":
-                if st.planes is None:
-                    st.planes = torch.zeros(attn.num_key_value_heads, 1, st.max_len, dtype=torch.float32, device=dev)
-                score_out, score_len = st.planes, cache.prefill_len_dev
-            else:
-                self._select(self.input_layernorm(hidden_states), position_embeddings, cache)
+        bufs = self._fused_bufs(cache, h.device, h.dtype)
+        score_out, score_len = self._decode_select_begin(hidden_states, cache, position_embeddings)
         k_seq, v_seq, pos = cache.write_target(self.layer_idx)
         ops.decode_qkv(h, self.input_layernorm.weight, self.input_layernorm.variance_epsilon, attn.qkv_weight,
                        attn.num_heads, attn.num_key_value_heads, attn.rotary_emb.inv_freq, cache.pos_dev, bufs.q,
                        k_seq, v_seq, pos)
         cache.attend(bufs.q, self.layer_idx, out=bufs.o, score_out=score_out, score_len=score_len)
-        if selecting:
-            if score_out is not None:
-                if tp is not None:
-                    tp.all_reduce_max(st.planes)
-                ops.topk(st.planes, cache.prefill_len_dev, st.k0, idx_out=st.idx, count_out=st.count, max_len=st.max_len)
-                cache.set_idx_device(st.idx, st.count, self.layer_idx)
-            cache.stage = "decoding"
-            self.decode_step += 1
+        self._decode_select_end(cache, score_out)
         lead = tp is None or tp.rank == 0  # with tensor parallelism only one rank adds the residual before the SUM
         ops.decode_gemv_residual(attn.o_weight, bufs.o.view(-1), h if lead else None, h)
         if tp is not None:
@@ -409,30 +428,12 @@ class OmniKVMulLayer(nn.Module):
         selecting = n == 1 and past_key_value is not None and self.is_filter
         score_out = score_len = None
         if selecting:
-            if not self.config.get("dense_more", False):
-                raise ValueError("dense_more=False is not supported")  # as modeling/omnikv.py:211-214
-            st = past_key_value.sel_state.get(self.layer_idx)
-            if st is None:  # first decode step on this cache (host reads of the lengths happen once, here)
-                st = self._init_selection_state(past_key_value, hidden_states.device)
-            if self.selector_cls == "last":
-                if st.planes is None:
-                    st.planes = torch.zeros(self.self_attn.num_key_value_heads, hidden_states.shape[0], st.max_len,
-                                            dtype=torch.float32, device=hidden_states.device)
-                score_out, score_len = st.planes, past_key_value.prefill_len_dev
-            else:
-                self._select(hidden_states, position_embeddings, past_key_value)
+            score_out, score_len = self._decode_select_begin(residual, past_key_value, position_embeddings)
 
         hidden_states = self.self_attn(hidden_states, position_embeddings, past_key_value, score_out=score_out,
                                        score_len=score_len)
         if selecting:
-            if score_out is not None:  # selector "last": the scores came out of the attention kernel
-                if self.tp is not None:  # plane j <- max over ranks of their j-th local KV head: order independent
-                    self.tp.all_reduce_max(st.planes)
-                ops.topk(st.planes, past_key_value.prefill_len_dev, st.k0, idx_out=st.idx, count_out=st.count,
-                         max_len=st.max_len)
-                past_key_value.set_idx_device(st.idx, st.count, self.layer_idx)
-            past_key_value.stage = "decoding"
-            self.decode_step += 1
+            self._decode_select_end(past_key_value, score_out)
         hidden_states = residual + hidden_states
 
         residual = hidden_states
@@ -643,6 +644,10 @@ class OmniKVMulLM(nn.Module):
         lm_head and the arg-max run in one fused weight-streaming kernel."""
         layer0 = self.model.layers[0]
         fused = tokens.shape[0] == 1 and layer0._fused_ok(self.model.embed_tokens.weight[:1].view(1, 1, -1))
+        if fused and self.tp is None and self.config.get("chained_decode", True) and ops.decode_chain_supported(
+                self.lm_head.weight.dtype, self.config.hidden_size, layer0.mlp.intermediate_size,
+                layer0.self_attn.num_heads) and self.lm_head.weight.shape[0] % 8 == 0:
+            return self._decode_step_chained(tokens, cache)
         out = self.model(input_ids=tokens, past_key_values=cache, apply_final_norm=not fused)
         h = out.last_hidden_state[:, -1]
         if not fused:
@@ -661,6 +666,46 @@ class OmniKVMulLM(nn.Module):
             return fb.logits, fb.token
         logits = tp.all_gather_last(fb.logits)
         return logits, logits.argmax(-1, keepdim=True)
+
+    def _decode_step_chained(self, tokens, cache):
+        """Batch-1 decode step as 33 cooperative weight-streaming launches interleaved with the 32 attention
+        launches: [QKV of layer 0], then per layer [attention] and [output projection, MLP, next layer's QKV
+        (or the final norm, lm_head and arg-max)] -- see ``omnikv_decode_chain``."""
+        layers = self.model.layers
+        cfg = self.config
+        cache.begin_decode_step()
+        h = self.model.embed_tokens(tokens).view(-1)
+        fb = layers[0]._fused_bufs(cache, h.device, h.dtype)
+        if getattr(fb, "logits", None) is None:
+            fb.logits = torch.empty(1, self.lm_head.weight.shape[0], dtype=torch.float32, device=h.device)
+            fb.best = torch.zeros(1, dtype=torch.int64, device=h.device)
+            fb.token = torch.zeros(1, 1, dtype=torch.int64, device=h.device)
+            fb.counters = torch.zeros(len(layers) + 1, 4, dtype=torch.int32, device=h.device)
+        fb.counters.zero_()  # chunk counters of this step's launches (dynamic scheduling)
+        a0 = layers[0].self_attn
+        common = dict(eps=cfg.rms_norm_eps, H=a0.num_heads, KVH=a0.num_key_value_heads, inter=layers[0].mlp.intermediate_size)
+
+        def qkv_args(layer):
+            k_seq, v_seq, pos = cache.write_target(layer.layer_idx)
+            return dict(in_norm_w=layer.input_layernorm.weight, w_qkv=layer.self_attn.qkv_weight,
+                        inv_freq=layer.self_attn.rotary_emb.inv_freq, rope_pos=cache.pos_dev, q_out=fb.q,
+                        k_cache_seq=k_seq, v_cache_seq=v_seq, cache_pos=pos)
+
+        ops.decode_chain(h, **common, chunk_counters=fb.counters[0], next_w=layers[0].self_attn.o_weight,
+                         **qkv_args(layers[0]))
+        hs = h.view(1, 1, -1)
+        for i, layer in enumerate(layers):
+            score_out, score_len = layer._decode_select_begin(hs, cache, None)
+            cache.attend(fb.q, i, out=fb.o, score_out=score_out, score_len=score_len)
+            layer._decode_select_end(cache, score_out)
+            tail = (qkv_args(layers[i + 1]) if i + 1 < len(layers) else
+                    dict(final_norm_w=self.model.norm.weight, w_head=self.lm_head.weight, logits=fb.logits, best=fb.best,
+                         token_out=fb.token))
+            ops.decode_chain(h, **common, w_o=layer.self_attn.o_weight, attn_out=fb.o,
+                             post_norm_w=layer.post_attention_layernorm.weight, w_gate_up=layer.mlp.gate_up_weight,
+                             w_down=layer.mlp.down_weight, act=fb.act, chunk_counters=fb.counters[i + 1],
+                             next_w=layers[i + 1].self_attn.o_weight if i + 1 < len(layers) else None, **tail)
+        return fb.logits, fb.token
 
     def _gather_logits(self, local):
         return self.tp.all_gather_last(local) if self.tp is not None else local

@@ -62,7 +62,8 @@ def workspace(device, nbytes: int, tag: str = "default") -> torch.Tensor:
     key = (torch.device(device).index, tag)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        # zero-filled: the decode-attention workspace starts with arrival counters that must be zero
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
 
@@ -148,7 +149,7 @@ def decode_attn(
             ws = workspace(q.device, need, "attn")
         p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
     abi.check(abi.lib().omnikv_decode_attn(C.byref(p), _stream()), "omnikv_decode_attn")
-    _count(1 if scores_only else 2)  # the attention kernel + the split merge
+    _count(1)  # one kernel: the last CTA of every (sequence, KV head) merges the splits
     return out
 
 
@@ -351,3 +352,46 @@ def decode_logits(h, norm_w, eps, w_head, row_offset, logits, best, token_out=No
                                              best.data_ptr(), _ptr(token_out), status_word(h.device).data_ptr(),
                                              _stream()), "omnikv_decode_logits")
     _count(2 if token_out is not None else 1)
+
+
+_grid_sync = {}
+
+
+def grid_sync_words(device) -> torch.Tensor:
+    """Two zeroed uint32 words per device for the grid-wide barrier of ``omnikv_decode_chain``."""
+    key = torch.device(device).index
+    if key not in _grid_sync:
+        _grid_sync[key] = torch.zeros(2, dtype=torch.int32, device=device)
+    return _grid_sync[key]
+
+
+def decode_chain_supported(dtype, hidden: int, inter: int, H: int) -> bool:
+    return dtype in _DT and bool(abi.lib().omnikv_decode_chain_supported(_DT[dtype], hidden, inter, H))
+
+
+def decode_chain(h, *, eps, H, KVH, inter, w_o=None, attn_out=None, post_norm_w=None, w_gate_up=None, w_down=None,
+                 act=None, in_norm_w=None, w_qkv=None, inv_freq=None, rope_pos=None, q_out=None, k_cache_seq=None,
+                 v_cache_seq=None, cache_pos=None, final_norm_w=None, w_head=None, logits=None, best=None,
+                 token_out=None, trace=None, chunk_counters=None, next_w=None):
+    """``omnikv_decode_chain``: the weight-streaming phases between two attention calls in one cooperative
+    launch.  h ``[hidden]`` is updated in place."""
+    p = abi.ChainParams()
+    p.dtype, p.hidden, p.inter, p.H, p.KVH, p.eps = _DT[h.dtype], h.numel(), int(inter), int(H), int(KVH), float(eps)
+    p.h = h.data_ptr()
+    p.w_o, p.attn_out = _ptr(w_o), _ptr(attn_out)
+    p.post_norm_w, p.w_gate_up, p.w_down, p.act_scratch = _ptr(post_norm_w), _ptr(w_gate_up), _ptr(w_down), _ptr(act)
+    p.in_norm_w, p.w_qkv, p.inv_freq, p.rope_pos, p.q_out = _ptr(in_norm_w), _ptr(w_qkv), _ptr(inv_freq), _ptr(rope_pos), _ptr(q_out)
+    if k_cache_seq is not None:
+        p.k_cache_seq, p.v_cache_seq = k_cache_seq.data_ptr(), v_cache_seq.data_ptr()
+        p.kv_stride_h, p.kv_stride_row = k_cache_seq.stride(0), k_cache_seq.stride(1)
+    p.cache_pos = _ptr(cache_pos)
+    p.final_norm_w, p.w_head = _ptr(final_norm_w), _ptr(w_head)
+    p.vocab_rows = 0 if w_head is None else w_head.shape[0]
+    p.logits, p.best_scratch, p.token_out = _ptr(logits), _ptr(best), _ptr(token_out)
+    p.grid_sync, p.status = grid_sync_words(h.device).data_ptr(), status_word(h.device).data_ptr()
+    p.trace = _ptr(trace)
+    p.chunk_counters = _ptr(chunk_counters)
+    if next_w is not None:
+        p.next_w, p.next_w_bytes = next_w.data_ptr(), next_w.numel() * next_w.element_size()
+    abi.check(abi.lib().omnikv_decode_chain(C.byref(p), _stream()), "omnikv_decode_chain")
+    _count(2 if (w_head is not None and token_out is not None) else 1)

@@ -16,9 +16,71 @@ import torch
 from . import ops
 
 
+def gemv_cases(reps: int, n_sets: int = 8):
+    """The four weight-streaming kernels of a Llama-3-8B decoder layer, each over ``n_sets`` distinct weight
+    sets back to back (so that no launch finds its weights in L2), timed per launch with CUDA events."""
+    dev, dt = "cuda", torch.bfloat16
+    hidden, inter, H, KVH = 4096, 14336, 32, 8
+    mk = lambda n, k: [torch.randn(n, k, device=dev, dtype=torch.float32).mul_(k ** -0.5).to(dt) for _ in range(n_sets)]  # noqa: E731
+    w_qkv, w_o, w_gu, w_d = mk((H + 2 * KVH) * 128, hidden), mk(hidden, hidden), mk(2 * inter, hidden), mk(hidden, inter)
+    h = torch.randn(hidden, device=dev).to(dt)
+    nw = torch.ones(hidden, device=dev, dtype=dt)
+    inv_freq = (1.0 / (500000.0 ** (torch.arange(0, 128, 2, dtype=torch.float32) / 128))).to(dev)
+    pos = torch.tensor([5], dtype=torch.int32, device=dev)
+    q = torch.zeros(H * 128, dtype=dt, device=dev)
+    kc = torch.zeros(KVH, 16, 128, dtype=dt, device=dev)
+    vc = torch.zeros_like(kc)
+    act = torch.zeros(inter, dtype=dt, device=dev)
+    out = torch.zeros(hidden, dtype=dt, device=dev)
+    def layer_separate(i):
+        ops.decode_gemv_residual(w_o[i], q, h, out)
+        ops.decode_gate_up(out, nw, 1e-5, w_gu[i], act)
+        ops.decode_gemv_residual(w_d[i], act, out, out)
+        ops.decode_qkv(out, nw, 1e-5, w_qkv[i], H, KVH, inv_freq, pos, q, kc, vc, pos)
+
+    counters = torch.zeros(n_sets, 4, dtype=torch.int32, device=dev)
+
+    def layer_chain(i):
+        if i == 0:
+            counters.zero_()
+        ops.decode_chain(out, chunk_counters=counters[i], eps=1e-5, H=H, KVH=KVH, inter=inter, w_o=w_o[i], attn_out=q, post_norm_w=nw,
+                         w_gate_up=w_gu[i], w_down=w_d[i], act=act, in_norm_w=nw, w_qkv=w_qkv[i], inv_freq=inv_freq,
+                         rope_pos=pos, q_out=q, k_cache_seq=kc, v_cache_seq=vc, cache_pos=pos)
+
+    layer_bytes = (w_qkv[0].numel() + w_o[0].numel() + w_gu[0].numel() + w_d[0].numel()) * 2
+    kinds = {
+        "qkv+rope+append": (lambda i: ops.decode_qkv(h, nw, 1e-5, w_qkv[i], H, KVH, inv_freq, pos, q, kc, vc, pos), w_qkv[0].numel() * 2),
+        "o_proj+residual": (lambda i: ops.decode_gemv_residual(w_o[i], q, h, out), w_o[0].numel() * 2),
+        "gate_up+silu": (lambda i: ops.decode_gate_up(h, nw, 1e-5, w_gu[i], act), w_gu[0].numel() * 2),
+        "down+residual": (lambda i: ops.decode_gemv_residual(w_d[i], act, h, out), w_d[0].numel() * 2),
+        "layer: 4 launches": (layer_separate, layer_bytes),
+        "layer: 1 chained launch": (layer_chain, layer_bytes),
+    }
+    # every kind is captured in a CUDA graph (8 launches over 8 distinct weight sets) so that the host's
+    # launch cost does not show in the per-launch time
+    for name, (fn, nbytes) in kinds.items():
+        fn(0)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(n_sets):
+                fn(i)
+        g.replay()
+        torch.cuda.synchronize()
+        for r in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / n_sets
+            print(f"{name} rep {r}: {ms * 1e3:.1f} us per launch, {nbytes / 1e6:.1f} MB, {nbytes / ms / 1e6:.0f} GB/s")
+    ops.check_status(dev)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["dense_attn", "sparse_attn", "topk", "score_window", "offload_gather"])
+    ap.add_argument("case", choices=["dense_attn", "sparse_attn", "topk", "score_window", "offload_gather", "gemv"])
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--ctx", type=int, default=131072)
     ap.add_argument("--splits", type=int, default=0)
@@ -29,8 +91,11 @@ def main():
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)  # noqa: E731
     g = torch.Generator(device=dev).manual_seed(0)
     rnd = lambda *s: torch.randn(*s, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)  # noqa: E731
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # larger than L2
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)  # 256 MB, larger than L2; READ between launches
+    sink = torch.zeros(1, dtype=torch.float32, device=dev)
 
+    if args.case == "gemv":
+        return gemv_cases(args.reps)
     if args.case in ("dense_attn", "sparse_attn", "score_window"):
         kc, q = rnd(B, KVH, L + 64, d), rnd(B, H, d)
     if args.case == "dense_attn":
@@ -72,14 +137,19 @@ def main():
 
     fn()
     torch.cuda.synchronize()
-    for r in range(args.reps):
-        flush.zero_()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
+    # timed inside a CUDA graph (L2 flush, then the launch) so that the host's launch cost does not show
+    g = torch.cuda.CUDAGraph()
+    ev = [torch.cuda.Event(enable_timing=True, external=True) for _ in range(2)]
+    with torch.cuda.graph(g):
+        torch.sum(flush, dim=0, keepdim=True, out=sink)  # evicts L2 with clean lines (a write flush would leave
+        # dirty lines whose write-back then competes with the measured kernel)
+        ev[0].record()
         fn()
-        b.record()
+        ev[1].record()
+    for r in range(args.reps):
+        g.replay()
         torch.cuda.synchronize()
-        ms = a.elapsed_time(b)
+        ms = ev[0].elapsed_time(ev[1])
         print(f"{args.case} rep {r}: {ms * 1e3:.1f} us, {nbytes / 1e6:.1f} MB algorithmic, {nbytes / ms / 1e6:.0f} GB/s")
 
 

@@ -69,7 +69,7 @@ def test_library_exports_every_declared_symbol():
         assert getattr(lib, name) is not None
     assert lib.omnikv_abi_version() == abi.ABI_VERSION == int(re.search(r"OMNIKV_ABI_VERSION (\d+)", header).group(1))
     assert b"workspace" in lib.omnikv_strerror(-3)
-    assert lib.omnikv_decode_attn_workspace_bytes(1, 32, 37) == (32 * 37 * 128 + 32 * 37 * 2) * 4
+    assert lib.omnikv_decode_attn_workspace_bytes(1, 32, 37) == 16384 + (32 * 37 * 128 + 32 * 37 * 2) * 4
     assert lib.omnikv_topk_workspace_bytes(2, 1000) == 2 * 1000 * 4
 
 

@@ -445,3 +445,63 @@ def test_fused_logits_argmax(dtype, hidden, vocab, off):
     ops().decode_logits(h2, nw, 1e-5, w, off, logits, best, tok)
     if logits[3].item() == logits.max().item():
         assert tok.item() == off + 3
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("hidden,inter,H,KVH,vocab", [(4096, 14336, 32, 8, 128256), (512, 1024, 4, 1, 1000)])
+def test_decode_chain_equals_single_calls(dtype, hidden, inter, H, KVH, vocab):
+    """The cooperative multi-phase launch computes exactly what the four single-phase calls compute
+    (same per-row arithmetic), with the activations crossing its grid-wide barriers."""
+    assert ops().decode_chain_supported(dtype, hidden, inter, H)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    rn = lambda *s: torch.randn(*s, generator=g, device="cuda")  # noqa: E731
+    h0, attn = rn(hidden).to(dtype), rn(hidden).to(dtype)
+    nw1, nw2 = (1 + 0.1 * rn(hidden)).to(dtype), (1 + 0.1 * rn(hidden)).to(dtype)
+    w_o = (rn(hidden, hidden) / hidden ** 0.5).to(dtype)
+    w_gu = (rn(2 * inter, hidden) / hidden ** 0.5).to(dtype)
+    w_d = (rn(hidden, inter) / inter ** 0.5).to(dtype)
+    w_qkv = (rn((H + 2 * KVH) * 128, hidden) / hidden ** 0.5).to(dtype)
+    w_head = (rn(vocab, hidden) / hidden ** 0.5).to(dtype)
+    inv_freq = (1.0 / (500000.0 ** (torch.arange(0, 128, 2, dtype=torch.float32) / 128))).cuda()
+    rope_pos, cpos = dev_i32([131080]), dev_i32([3])
+
+    def fresh():
+        return dict(h=h0.clone(), act=torch.zeros(inter, dtype=dtype, device="cuda"),
+                    q=torch.zeros(H * 128, dtype=dtype, device="cuda"), kc=torch.zeros(KVH, 8, 128, dtype=dtype, device="cuda"),
+                    vc=torch.zeros(KVH, 8, 128, dtype=dtype, device="cuda"),
+                    logits=torch.zeros(vocab, dtype=torch.float32, device="cuda"),
+                    best=torch.zeros(1, dtype=torch.int64, device="cuda"), tok=torch.zeros(1, dtype=torch.int64, device="cuda"))
+
+    for tail in ("qkv", "logits"):
+        a, b = fresh(), fresh()
+        # single calls
+        ops().decode_gemv_residual(w_o, attn, a["h"], a["h"])
+        ops().decode_gate_up(a["h"], nw1, 1e-5, w_gu, a["act"])
+        ops().decode_gemv_residual(w_d, a["act"], a["h"], a["h"])
+        if tail == "qkv":
+            ops().decode_qkv(a["h"], nw2, 1e-5, w_qkv, H, KVH, inv_freq, rope_pos, a["q"], a["kc"], a["vc"], cpos)
+        else:
+            ops().decode_logits(a["h"], nw2, 1e-5, w_head, 0, a["logits"], a["best"], a["tok"])
+        # one chained launch, three times (the grid barrier word must be reusable); static chunk assignment
+        # first, then dynamic scheduling from zeroed counters
+        for rep in range(3):
+            b = fresh()
+            kw = dict(eps=1e-5, H=H, KVH=KVH, inter=inter, w_o=w_o, attn_out=attn, post_norm_w=nw1, w_gate_up=w_gu,
+                      w_down=w_d, act=b["act"],
+                      chunk_counters=None if rep == 0 else torch.zeros(4, dtype=torch.int32, device="cuda"))
+            if tail == "qkv":
+                kw.update(in_norm_w=nw2, w_qkv=w_qkv, inv_freq=inv_freq, rope_pos=rope_pos, q_out=b["q"],
+                          k_cache_seq=b["kc"], v_cache_seq=b["vc"], cache_pos=cpos)
+            else:
+                kw.update(final_norm_w=nw2, w_head=w_head, logits=b["logits"], best=b["best"], token_out=b["tok"])
+            ops().decode_chain(b["h"], **kw)
+            ops().check_status("cuda")
+            for name in a:
+                assert torch.equal(a[name], b[name]), (tail, rep, name)
+    # a lone QKV phase (the first launch of a step)
+    a, b = fresh(), fresh()
+    ops().decode_qkv(a["h"], nw2, 1e-5, w_qkv, H, KVH, inv_freq, rope_pos, a["q"], a["kc"], a["vc"], cpos)
+    ops().decode_chain(b["h"], eps=1e-5, H=H, KVH=KVH, inter=inter, in_norm_w=nw2, w_qkv=w_qkv, inv_freq=inv_freq,
+                       rope_pos=rope_pos, q_out=b["q"], k_cache_seq=b["kc"], v_cache_seq=b["vc"], cache_pos=cpos)
+    ops().check_status("cuda")
+    assert torch.equal(a["q"], b["q"]) and torch.equal(a["kc"], b["kc"]) and torch.equal(a["vc"], b["vc"])

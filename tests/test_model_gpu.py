@@ -134,8 +134,8 @@ def test_fused_decode_kernels_match_torch_ops(dtype, selector):
     ids = torch.randint(0, 1000, (1, 300), generator=g).cuda()
     toks = torch.randint(0, 1000, (6, 1, 1), generator=g).cuda()
     outs = {}
-    for fused in (True, False):
-        cfg = small_config(selector_cls=selector, fused_decode=fused)
+    for fused in (True, "unchained", False):
+        cfg = small_config(selector_cls=selector, fused_decode=bool(fused), chained_decode=fused is True)
         lm, _ = build(cfg, dtype)
         out = lm(input_ids=ids)
         cache = out.past_key_values
@@ -149,6 +149,7 @@ def test_fused_decode_kernels_match_torch_ops(dtype, selector):
         outs[fused] = (torch.cat(logits).float().cpu(), torch.cat(nxt).cpu(), [l for l in logits])
         assert all(torch.equal(lg.argmax(-1, keepdim=True).cpu(), tk.cpu()) for lg, tk in zip(logits, nxt))
     assert (outs[True][0] - outs[False][0]).abs().max().item() <= 2e-2
+    assert torch.equal(outs[True][0], outs["unchained"][0])  # the chained launch is the same arithmetic
 
 
 @pytest.mark.parametrize("selector,offload", [("last", False), ("exp", False), ("last", True)])
@@ -168,19 +169,22 @@ def test_batch_ragged_synthetic_cache_matches_per_sequence_oracle():
     """Batch > 1 is undefined in the reference (its index list is flattened over the batch); here every
     sequence selects for itself: a batched step must equal the per-sequence single-batch steps."""
     from omnikv_b200 import ops
+    # fp32: the test is about the batch semantics of selection and attention; in 16-bit a batched GEMM and a
+    # GEMV round differently and a single threshold swap in the index list moves the logits by more than 2e-2
+    dt = torch.float32
     cfg = small_config(selector_cls="last", num_of_selected_tokens=50)
-    lm, _ = build(cfg, torch.bfloat16)
+    lm, _ = build(cfg, dt)
     lens = [700, 300, 512]
-    cache = lm.new_cache().init_synthetic(3, 1, 128, lens, torch.bfloat16, "cuda", seed=5, reserve=64)
+    cache = lm.new_cache().init_synthetic(3, 1, 128, lens, dt, "cuda", seed=5, reserve=64)
     tok = torch.tensor([[1], [2], [3]], device="cuda")
     batched = lm(input_ids=tok, past_key_values=cache).logits
     for b, n in enumerate(lens):
-        c1 = lm.new_cache().init_synthetic(1, 1, 128, [n], torch.bfloat16, "cuda", seed=5, reserve=64)
+        c1 = lm.new_cache().init_synthetic(1, 1, 128, [n], dt, "cuda", seed=5, reserve=64)
         for layer in range(cfg.num_hidden_layers):  # same rows as sequence b of the batched cache
             c1._k[layer][0, :, :n].copy_(cache._k[layer][b, :, :n])
             c1._v[layer][0, :, :n].copy_(cache._v[layer][b, :, :n])
         single = lm(input_ids=tok[b:b + 1], past_key_values=c1).logits
-        assert (single - batched[b:b + 1]).abs().max().item() <= 2e-2
+        assert (single - batched[b:b + 1]).abs().max().item() <= 1e-4
 
 
 def test_selector_function_matches_reference_fixture():
