@@ -114,6 +114,30 @@ size_t omnikv_decode_attn_workspace_bytes(int B, int H, int n_splits);
 int omnikv_decode_attn(const omnikv_attn_params* p, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * omnikv_decode_attn_no_alloc: omnikv_decode_attn for callers that have no way to allocate device
+ * memory (no counterpart in the reference, whose tensors all come from PyTorch's allocator).
+ *
+ * Who needs it: code that is handed tensors but no allocator -- an operator plugged into another runtime
+ * that owns all device memory, a process whose memory budget is fixed at start-up, a latency-critical loop
+ * that must never reach cudaMalloc (which can block and synchronise the device).  The split partials and arrival counters that omnikv_decode_attn
+ * takes from the caller's workspace come instead from a fixed array inside the library:
+ * OMNIKV_NO_ALLOC_SCRATCH_BYTES (4 MiB) of device memory on every GPU that loads the library, held until
+ * the process exits.  p->workspace and p->workspace_bytes are ignored; inputs and outputs are the caller's.
+ *
+ * Limit: omnikv_decode_attn_workspace_bytes(B, H, n_splits) must not exceed OMNIKV_NO_ALLOC_SCRATCH_BYTES
+ * (B * H * n_splits <= 8034, e.g. batch 1, 32 heads, 251 splits); larger problems return OMNIKV_E_WORKSPACE
+ * and launch nothing.  Nothing is allocated or freed, here or in any routine it calls.
+ *
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
+ * current); make that first call outside stream capture.  All calls on a device share the one array: it
+ * keeps the previous call's contents (the counters are cleared at the start of every call, on the given
+ * stream), and two calls that overlap on the GPU -- different streams, or graphs replayed concurrently --
+ * race on it.  Keep them on one stream, or order them with events.
+ * ------------------------------------------------------------------------------------------ */
+#define OMNIKV_NO_ALLOC_SCRATCH_BYTES (4 * 1024 * 1024)
+int omnikv_decode_attn_no_alloc(const omnikv_attn_params* p, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Window-selector scores (modeling/omnikv.py:49-105), replaces the per-window-query Python
  * loop of matmul + softmax + max + sum and the repeat_kv copy of :38.
  *

@@ -13,6 +13,7 @@ _lib = None
 ABI_VERSION = 1
 F32, BF16, F16 = 0, 1, 2
 SEL_SOFTMAX_LAST, SEL_UNIFORM, SEL_EXP = 0, 1, 2
+NO_ALLOC_SCRATCH_BYTES = 4 * 1024 * 1024
 
 c_i32p = C.POINTER(C.c_int32)
 c_f32p = C.POINTER(C.c_float)
@@ -76,6 +77,7 @@ SIGNATURES = {
     "omnikv_last_cuda_error": (C.c_char_p, []),
     "omnikv_decode_attn_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "omnikv_decode_attn": (C.c_int, [C.POINTER(AttnParams), C.c_void_p]),
+    "omnikv_decode_attn_no_alloc": (C.c_int, [C.POINTER(AttnParams), C.c_void_p]),
     "omnikv_score_window_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "omnikv_score_window": (C.c_int, [C.POINTER(WindowParams), C.c_void_p]),
     "omnikv_window_fold": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_void_p, C.c_int,

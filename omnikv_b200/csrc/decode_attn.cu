@@ -601,3 +601,58 @@ extern "C" int omnikv_decode_attn(const omnikv_attn_params* p, void* stream) {
     default: return launch_f32(a, with_v, with_score, st);
   }
 }
+
+// ---------------------------------------------------------------------------------------------
+// Decode attention for callers that cannot allocate device memory.
+//
+// Some hosts of this library have no allocator to hand: a plugin that is only given tensors by a runtime
+// that owns all device memory, a process with a memory budget fixed at start-up, a real-time loop that must
+// not touch cudaMalloc (it can block and synchronise the device).  For
+// them the split partials and arrival counters live in the array below, which is part of the library's
+// image: every GPU that loads the library holds these 4 MiB until the process exits.
+// ---------------------------------------------------------------------------------------------
+namespace omnikv {
+namespace {
+
+static __device__ __align__(256) unsigned char g_no_alloc_scratch[OMNIKV_NO_ALLOC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+void* g_no_alloc_ptr[kMaxDevices] = {};  // device address of the array, per device ordinal
+
+// The array's name is only a handle on the host; the device address has to be asked for, once per
+// device and with that device current.
+int no_alloc_scratch(void** out) {
+  int dev = 0;
+  OMNIKV_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return OMNIKV_E_UNSUPPORTED;
+  if (!g_no_alloc_ptr[dev]) {
+    void* ptr = nullptr;
+    OMNIKV_CUDA_OK(cudaGetSymbolAddress(&ptr, g_no_alloc_scratch));
+    if (!ptr) return OMNIKV_E_CUDA;
+    g_no_alloc_ptr[dev] = ptr;
+  }
+  *out = g_no_alloc_ptr[dev];
+  return OMNIKV_OK;
+}
+
+}  // namespace
+}  // namespace omnikv
+
+extern "C" int omnikv_decode_attn_no_alloc(const omnikv_attn_params* p, void* stream) {
+  using namespace omnikv;
+  if (!p) return OMNIKV_E_BADARG;
+  if (p->B <= 0 || p->H <= 0 || p->n_splits <= 0) return OMNIKV_E_BADARG;
+  if (p->out && omnikv_decode_attn_workspace_bytes(p->B, p->H, p->n_splits) > (size_t)OMNIKV_NO_ALLOC_SCRATCH_BYTES)
+    return OMNIKV_E_WORKSPACE;  // B * H * n_splits is more than the built-in scratch can hold
+  void* scratch = nullptr;
+  const int rc = no_alloc_scratch(&scratch);
+  if (rc != OMNIKV_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The array keeps what the previous call left.  Only the arrival counters have to start at zero (a call
+  // that ran to completion leaves them so, one that was cut short may not): clear them on the same stream.
+  OMNIKV_CUDA_OK(cudaMemsetAsync(scratch, 0, kAttnCntBytes, st));
+  omnikv_attn_params q = *p;
+  q.workspace = scratch;
+  q.workspace_bytes = OMNIKV_NO_ALLOC_SCRATCH_BYTES;
+  return omnikv_decode_attn(&q, stream);
+}

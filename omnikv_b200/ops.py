@@ -395,3 +395,38 @@ def decode_chain(h, *, eps, H, KVH, inter, w_o=None, attn_out=None, post_norm_w=
         p.next_w, p.next_w_bytes = next_w.data_ptr(), next_w.numel() * next_w.element_size()
     abi.check(abi.lib().omnikv_decode_chain(C.byref(p), _stream()), "omnikv_decode_chain")
     _count(2 if (w_head is not None and token_out is not None) else 1)
+
+
+def decode_attn_no_alloc(q, k, v, len_a, out, *, n_splits, idx=None, k_tail=None, v_tail=None, tail_start=None,
+                         tail_len=None, scale=None) -> torch.Tensor:
+    """``omnikv_decode_attn_no_alloc``: decode attention that touches no allocator -- not PyTorch's, not
+    CUDA's.  For callers that only hold tensors (a plugin inside a runtime that owns all device memory, a
+    process with a fixed memory budget, a loop that must never reach ``cudaMalloc``): the split partials go to a 4 MiB array built
+    into the library instead of a workspace tensor, and ``out`` ``[B,H,d]`` must be passed in.
+
+    ``B * H * n_splits`` may not exceed 8034 (the array's size); beyond that an ``OmniKVError`` is raised and
+    nothing is launched.  All calls on a device share that array: keep them on one stream (calls that overlap
+    on the GPU race on it), and make the first call on a device outside stream capture."""
+    _need_cuda(q, k, v, len_a, out, idx, k_tail, v_tail)
+    B, H, d = q.shape
+    need = abi.lib().omnikv_decode_attn_workspace_bytes(B, H, int(n_splits))
+    if need > abi.NO_ALLOC_SCRATCH_BYTES:
+        raise abi.OmniKVError(
+            f"omnikv_decode_attn_no_alloc: B*H*n_splits = {B * H * int(n_splits)} needs {need} bytes of scratch, the "
+            f"library's built-in scratch holds {abi.NO_ALLOC_SCRATCH_BYTES}; use fewer splits or omnikv_decode_attn")
+    p = abi.AttnParams()
+    p.dtype, p.B, p.H, p.KVH, p.head_dim = _DT[q.dtype], B, H, k.shape[1], d
+    p.scale = float(scale if scale is not None else 1.0 / math.sqrt(d))
+    p.q, p.q_stride_b, p.q_stride_h, p.out = q.data_ptr(), q.stride(0), q.stride(1), out.data_ptr()
+    p.kA, p.vA = k.data_ptr(), v.data_ptr()
+    p.a_stride_b, p.a_stride_h, p.a_stride_row = _kv_strides(k)
+    if idx is not None:
+        p.idxA, p.idx_stride = idx.data_ptr(), idx.stride(0)
+    p.lenA = len_a.data_ptr()
+    if tail_len is not None:
+        p.kB, p.vB = k_tail.data_ptr(), v_tail.data_ptr()
+        p.b_stride_b, p.b_stride_h, p.b_stride_row = _kv_strides(k_tail)
+        p.startB, p.lenB = tail_start.data_ptr(), tail_len.data_ptr()
+    p.n_splits = int(n_splits)
+    abi.check(abi.lib().omnikv_decode_attn_no_alloc(C.byref(p), _stream()), "omnikv_decode_attn_no_alloc")
+    return out
