@@ -162,8 +162,8 @@ def main():
     ap.add_argument("--layers", type=int, default=32, help="decoder layers (the benchmark's is 32)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--no-chain", action="store_true", help="one launch per weight-streaming phase instead of the "
-                    "cooperative multi-phase launch")
+    ap.add_argument("--chain", action="store_true", help="run the weight-streaming phases between two attention calls "
+                    "as one cooperative multi-phase launch instead of one launch per phase (measured slower so far)")
     ap.add_argument("--profile-step", action="store_true",
                     help="after the warm-up, run ONE step between cudaProfilerStart/Stop and exit (for ncu "
                          "--profile-from-start off); prints no benchmark line")
@@ -186,7 +186,7 @@ def main():
     warmup = max(3, args.warmup)
     cfg = LlamaCompressorConfig(num_hidden_layers=args.layers)
     cfg.set_config_of_compressor(**OMNI)
-    cfg.set_config_of_compressor(fused_decode=True, chained_decode=not args.no_chain)
+    cfg.set_config_of_compressor(fused_decode=True, chained_decode=args.chain)
     lm = OmniKVMulLM.from_config(cfg, dtype=torch.bfloat16, device=dev, seed=0, tp=tp)
     graph_warm = 2
     reserve = graph_warm + 2 * (warmup + args.steps) + 16
@@ -270,13 +270,11 @@ def main():
     dur_ms = statistics.mean(durs)
     peak, peak_kind = measured_peak_gbs()
     achieved = alg_bytes / (dur_ms * 1e-3) / 1e9
-    traffic = None
-    tf = ROOT / "profiles" / "decode_attn_dense_traffic.json"
-    if tf.exists():
-        tj = json.loads(tf.read_text())
-        traffic = tj["dram_bytes_per_row"] * rows * kvh_local / tj["kvh"]
+    # DRAM bytes per (row, KV head) of this kernel from the ncu capture summarised in profiles/decode_attn_dense.md
+    # (dram__bytes_read + dram__bytes_write = 545.06 MB for 131073 rows x 8 KV heads), scaled to this launch
+    traffic = 519.8 * rows * kvh_local
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": traffic, "kernel": "decode_attn_mma_kernel (dense layer, split-K + merge)",
+                "traffic": traffic, "kernel": "decode_attn_mma_kernel (dense layer, split-K, merge by the last CTA)",
                 "algorithmic_bytes_per_launch": alg_bytes, "launch_ms": dur_ms, "peak_kind": peak_kind}
 
     # whole-step algorithmic bytes (KV + weights) for context

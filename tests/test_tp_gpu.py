@@ -1,0 +1,69 @@
+"""KV-head tensor parallelism on 2 GPUs (NCCL): a sharded model built from the full model's weights gives the
+full model's logits, and every rank selects the same index list (MAX all-reduce of the score planes)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, selector, ret):
+    import logging
+    logging.disable(logging.WARNING)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    from omnikv_b200 import parallel
+    from omnikv_b200.modeling import LlamaCompressorConfig, OmniKVMulLM
+    tp = parallel.init(world, rank, dev)
+    try:
+        def cfg():
+            c = LlamaCompressorConfig(num_hidden_layers=4, hidden_size=1024, intermediate_size=2048,
+                                      num_attention_heads=8, num_key_value_heads=2, vocab_size=1024, head_dim=128)
+            c.set_config_of_compressor(model_cls="multi", cache_cls="multi", do_select_layers="1", num_wait_load_layers=1,
+                                       real_offload=False, dense_more=True, num_of_selected_tokens=0.25,
+                                       selector_cls=selector, window_size=16)
+            return c
+        full = OmniKVMulLM.from_config(cfg(), dtype=torch.float32, device=dev, seed=0)
+        with torch.no_grad():
+            for layer in full.model.layers:
+                layer.self_attn.qkv_weight.mul_(4.0)
+        shard = OmniKVMulLM.from_config(cfg(), dtype=torch.float32, device=dev, seed=None, tp=tp)
+        shard.load_hf_state_dict(full.hf_state_dict())
+        g = torch.Generator().manual_seed(1)
+        ids = torch.randint(0, 1024, (1, 300), generator=g).to(dev)
+        toks = torch.randint(0, 1024, (6, 1, 1), generator=g).to(dev)
+        o1, o2 = full(input_ids=ids), shard(input_ids=ids)
+        err = (o1.logits - o2.logits).abs().max().item()
+        for t in toks:
+            o1 = full(input_ids=t, past_key_values=o1.past_key_values)
+            o2 = shard(input_ids=t, past_key_values=o2.past_key_values)
+            err = max(err, (o1.logits - o2.logits).abs().max().item())
+        i1, c1 = o1.past_key_values._idx[1]
+        i2, c2 = o2.past_key_values._idx[1]
+        same_idx = torch.equal(i1[:, :c1[0]], i2[:, :c2[0]])
+        ret[rank] = (err, bool(same_idx))
+    finally:
+        torch.distributed.destroy_process_group()
+
+
+@pytest.mark.parametrize("selector", ["last", "exp"])
+def test_tp2_matches_single_gpu(selector):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world, port = 2, _free_port()
+    ret = mp.get_context("spawn").Manager().dict()
+    mp.spawn(_worker, args=(world, port, selector, ret), nprocs=world, join=True)
+    for rank in range(world):
+        err, same = ret[rank]
+        assert err <= 1e-4, (rank, err)
+        assert same
