@@ -164,6 +164,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--chain", action="store_true", help="run the weight-streaming phases between two attention calls "
                     "as one cooperative multi-phase launch instead of one launch per phase (measured slower so far)")
+    ap.add_argument("--nccl-allreduce", action="store_true", help="multi-GPU: NCCL all-reduce after the row-parallel "
+                    "projections instead of the fused peer-memory exchange")
     ap.add_argument("--profile-step", action="store_true",
                     help="after the warm-up, run ONE step between cudaProfilerStart/Stop and exit (for ncu "
                          "--profile-from-start off); prints no benchmark line")
@@ -182,6 +184,8 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     tp = parallel.init(world, rank, dev) if world > 1 else None
+    if tp is not None and not args.nccl_allreduce:
+        tp.enable_peer_exchange(4096, dev)
 
     warmup = max(3, args.warmup)
     cfg = LlamaCompressorConfig(num_hidden_layers=args.layers)
@@ -255,16 +259,25 @@ def main():
     # ---- roofline of the dominant kernel: dense decode attention, timed live on its stream -------
     dense_layers = [i for i, s in cache.layer_state.items() if not s[0]]
     q = torch.randn(1, cfg.num_attention_heads // (world if tp else 1), cfg.head_dim, device=dev).to(torch.bfloat16)
-    durs = []
-    for rep in range(3):
+    # The dense layers' attention calls are captured in a CUDA graph (as they are in the timed step) and
+    # bracketed by events on the launching stream, so the host's launch cost is not part of the duration; the
+    # launches read 8 x 537 MB of distinct K/V, far more than L2 holds.
+    for layer in dense_layers:
+        cache.attend(q, layer)
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True, external=True) for _ in range(2)]
+    g_att = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g_att):
+        ev[0].record()
         for layer in dense_layers:
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
             cache.attend(q, layer)
-            b.record()
-            torch.cuda.synchronize()
-            if rep > 0:
-                durs.append(a.elapsed_time(b))
+        ev[1].record()
+    durs = []
+    for rep in range(4):
+        g_att.replay()
+        torch.cuda.synchronize()
+        if rep > 0:
+            durs.append(ev[0].elapsed_time(ev[1]) / len(dense_layers))
     rows = cache._seen_tokens
     alg_bytes = 2 * kvh_local * cfg.head_dim * 2 * rows  # K and V rows of every local KV head, read once
     dur_ms = statistics.mean(durs)
@@ -283,14 +296,28 @@ def main():
                   (int(0.067 * args.ctx) + runner.steps_done) + 2 * (n_params_local - cfg.vocab_size * cfg.hidden_size))
     step_gbs = step_bytes / (ms / args.steps * 1e-3) / 1e9
 
+    def finish():
+        """Leave in step on every rank: drop the captured graph, sync, barrier, destroy the group, then exit
+        without running interpreter-exit hooks (NCCL teardown after a captured graph has hung there)."""
+        sys.stdout.flush()
+        if tp is None:
+            return
+        runner.graph = None
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+        sys.stderr.flush()
+        os._exit(0)
+
     if rank != 0:
-        return
+        return finish()
     line = {
         "metric": "decode tokens/s at 128K ctx (Llama-3-8B shape)", "value": args.steps / (ms * 1e-3),
         "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD, "batch": 1, "seq_len": args.ctx, "layers": args.layers,
-                   "parallelism": f"kv-head tp{world}" if world > 1 else "single gpu",
+                   "parallelism": (f"kv-head tp{world}, " + ("fused peer-memory all-reduce" if tp.exchange is not None
+                                                                    else "nccl all-reduce")) if world > 1 else "single gpu",
                    "l2": "inputs larger than L2 (about 20 GB of KV and weights are read per step)",
                    "cuda_graph": not args.no_graph, "kv_fill": "seeded N(0,1), no prefill run"},
         "clocks": clocks,
@@ -309,8 +336,7 @@ def main():
                       "full size, scaled by the step's layer counts (8 dense / 3 filter / 24 sparse / 32)",
             "parts_s": parts}
     print(json.dumps(line), flush=True)
-    if tp is not None:
-        torch.distributed.destroy_process_group()
+    finish()
 
 
 if __name__ == "__main__":

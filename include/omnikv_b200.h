@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define OMNIKV_ABI_VERSION 1
+#define OMNIKV_ABI_VERSION 2
 
 typedef enum {
   OMNIKV_OK = 0,
@@ -234,17 +234,46 @@ int omnikv_kv_append(int dtype, const void* k_new, const void* v_new, void* k_ca
  * omnikv_decode_logits: x = RMSNorm(h) * norm_w; logits[r] = w_head[r] . x (fp32); token_out (optional)
  *   = row_offset + argmax (lowest index among equal maxima); best_scratch: 8 bytes of device scratch.
  * ------------------------------------------------------------------------------------------ */
+/* Tensor parallelism: the SUM all-reduce that follows a row-parallel projection (output projection, MLP down
+ * projection; the all_reduce calls of lightllm/common/basemodel/layer_infer/template/
+ * transformer_layer_infer_template.py:119-120, :128-129 in the reference's fork) is fused into the kernels on
+ * both sides of it, over peer-mapped memory:
+ *   producer  omnikv_decode_gemv_residual(tp_out = x): every rank stores its fp32 partial sums straight into
+ *             EVERY rank's exchange buffer (plain peer stores over NVLink); the CTA that finishes last raises
+ *             this rank's flag word on every rank.  `resid` and `out` are then unused (may be NULL).
+ *   consumer  omnikv_decode_gate_up / _qkv / _logits(tp_in = x): once all ranks' flags of that exchange have
+ *             arrived (bounded wait), the activations are h + sum over ranks of the partials, rounded once to the
+ *             storage type; they are also written to h_inout (the updated residual stream), which must be a
+ *             DIFFERENT buffer than h: other CTAs of the same launch are still reading h.
+ * peer_base[r]: rank r's exchange buffer (omnikv_tp_exchange_bytes(hidden) bytes, zero before first use) as
+ * mapped into THIS process (peer_base[rank] = the local one).  Exchanges alternate between two slots
+ * (seq & 1); seq numbers the exchanges of a decode step 0, 1, 2, ... (< 256) and must follow program order;
+ * *epoch is a local device word that every rank bumps once per decode step.  All ranks must issue the same
+ * sequence of calls.  world <= 8.  NULL or world <= 1: no exchange. */
+typedef struct {
+  int32_t world, rank;
+  void* peer_base[8];
+  uint32_t* done_counter; /* local device word, zero before first use (producers) */
+  const uint32_t* epoch;
+  int32_t seq;
+  int32_t hidden;
+} omnikv_tp_exchange;
+
+size_t omnikv_tp_exchange_bytes(int hidden);
 int omnikv_decode_qkv(int dtype, const void* h, const void* norm_w, float eps, const void* w_qkv, int hidden,
                       int H, int KVH, int head_dim, const float* inv_freq, const int32_t* rope_pos,
                       void* q_out, void* k_cache_seq, void* v_cache_seq, int64_t kv_stride_h,
-                      int64_t kv_stride_row, const int32_t* cache_pos, int32_t* status, void* stream);
+                      int64_t kv_stride_row, const int32_t* cache_pos, const omnikv_tp_exchange* tp_in,
+                      void* h_inout, int32_t* status, void* stream);
 int omnikv_decode_gemv_residual(int dtype, const void* w, int N, int K, const void* x, const void* resid,
-                                void* out, int32_t* status, void* stream);
+                                void* out, const omnikv_tp_exchange* tp_out, int32_t* status, void* stream);
 int omnikv_decode_gate_up(int dtype, const void* h, const void* norm_w, float eps, const void* w_gate_up,
-                          int hidden, int inter, void* act_out, int32_t* status, void* stream);
+                          int hidden, int inter, void* act_out, const omnikv_tp_exchange* tp_in, void* h_inout,
+                          int32_t* status, void* stream);
 int omnikv_decode_logits(int dtype, const void* h, const void* norm_w, float eps, const void* w_head,
                          int hidden, int vocab_rows, int row_offset, float* logits,
-                         unsigned long long* best_scratch, int64_t* token_out, int32_t* status, void* stream);
+                         unsigned long long* best_scratch, int64_t* token_out, const omnikv_tp_exchange* tp_in,
+                         int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * omnikv_decode_chain: the weight-streaming phases between two attention calls of a batch-1 decode

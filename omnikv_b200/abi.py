@@ -10,7 +10,7 @@ from pathlib import Path
 _LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libomnikv_b200.so"
 _lib = None
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 F32, BF16, F16 = 0, 1, 2
 SEL_SOFTMAX_LAST, SEL_UNIFORM, SEL_EXP = 0, 1, 2
 NO_ALLOC_SCRATCH_BYTES = 4 * 1024 * 1024
@@ -53,6 +53,13 @@ class WindowParams(C.Structure):
     ]
 
 
+class TpExchange(C.Structure):
+    """Mirror of ``omnikv_tp_exchange``."""
+
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("peer_base", C.c_void_p * 8),
+                ("done_counter", C.c_void_p), ("epoch", C.c_void_p), ("seq", C.c_int32), ("hidden", C.c_int32)]
+
+
 class ChainParams(C.Structure):
     """Mirror of ``omnikv_chain_params``."""
 
@@ -88,15 +95,17 @@ SIGNATURES = {
                               C.c_void_p]),
     "omnikv_offload_gather": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                         C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
+    "omnikv_tp_exchange_bytes": (C.c_size_t, [C.c_int]),
     "omnikv_decode_qkv": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                     C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
-                                    C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
+                                    C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "omnikv_decode_gemv_residual": (C.c_int, [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
-                                              C.c_void_p, C.c_void_p, C.c_void_p]),
+                                              C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "omnikv_decode_gate_up": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_int, C.c_int,
-                                        C.c_void_p, C.c_void_p, C.c_void_p]),
+                                        C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "omnikv_decode_logits": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_int, C.c_int,
-                                       C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+                                       C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                       C.c_void_p]),
     "omnikv_decode_chain": (C.c_int, [C.POINTER(ChainParams), C.c_void_p]),
     "omnikv_decode_chain_supported": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "omnikv_kv_append": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,

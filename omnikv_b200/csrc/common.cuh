@@ -24,6 +24,32 @@ int record_cuda_error(cudaError_t e, const char* where);
 
 __host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// ---- programmatic dependent launch ----------------------------------------------------------------
+// A kernel launched with launch_pdl() may start while its predecessor in the stream is still running.
+// pdl_trigger(): this CTA allows the NEXT kernel's CTAs to be scheduled (they take SMs as CTAs of this grid
+// exit).  pdl_wait(): blocks until the PREVIOUS kernel has completed and its writes are visible; everything
+// that reads or overwrites data shared with earlier kernels must come after it.  Both are no-ops for a
+// kernel launched without the attribute.  Only grids that are fully resident may trigger early.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+bool pdl_enabled();  // OMNIKV_PDL=0 in the environment turns it off
+
+template <typename Kern, typename Args>
+inline cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, const Args& a) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, a);
+}
+
 // ---- cp.async (16-byte, L1-bypassing) with zero fill when !valid ---------------------------
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, bool valid) {
   unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));

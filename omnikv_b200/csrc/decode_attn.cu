@@ -35,7 +35,7 @@ struct AttnArgs {
   float* ws_o;
   float* ws_ml;
   unsigned* ws_cnt;   // [B*KVH] arrival counters of the splits, zero between launches
-  int out_is_T;       // unused placeholder for alignment
+  int pdl_trigger;    // 1: the grid is fully resident, the next kernel may be scheduled early
   int B, H, KVH, G, S;
   float scale;
 };
@@ -131,6 +131,12 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int G = a.G;
+  // Programmatic dependent launch: everything this kernel reads (q, the current token's K/V row, lengths, the
+  // index list) comes from the kernels before it, so it waits first; what it gains is that its CTAs are already
+  // resident when the previous kernel ends.  It lets its successor be scheduled early only when its own grid is
+  // fully resident (a.pdl_trigger, decided by the host from the grid size).
+  pdl_wait();
+  if (a.pdl_trigger) pdl_trigger();
   const int nA = a.lenA[b];
   const int nB = a.lenB ? a.lenB[b] : 0;
   const int n = nA + nB;
@@ -504,20 +510,24 @@ __global__ void __launch_bounds__(NTHREADS) decode_attn_f32_kernel(const AttnArg
 }
 
 template <typename T>
-int launch_mma(const AttnArgs& a, bool with_v, bool with_score, cudaStream_t st) {
+int launch_mma(AttnArgs a, bool with_v, bool with_score, cudaStream_t st) {
   dim3 grid(a.S, a.KVH, a.B), block(NTHREADS);
+  int dev = 0, n_sms = 0;
+  OMNIKV_CUDA_OK(cudaGetDevice(&dev));
+  OMNIKV_CUDA_OK(cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev));
+  a.pdl_trigger = ((long long)a.S * a.KVH * a.B <= 2ll * n_sms) ? 1 : 0;  // two CTAs of this kernel fit per SM
   if (with_v && with_score) {
     auto kern = decode_attn_mma_kernel<T, true, true>;
     OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, mma_smem_bytes<true>()));
-    kern<<<grid, block, mma_smem_bytes<true>(), st>>>(a);
+    OMNIKV_CUDA_OK(launch_pdl(kern, grid, block, mma_smem_bytes<true>(), st, a));
   } else if (with_v) {
     auto kern = decode_attn_mma_kernel<T, true, false>;
     OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, mma_smem_bytes<true>()));
-    kern<<<grid, block, mma_smem_bytes<true>(), st>>>(a);
+    OMNIKV_CUDA_OK(launch_pdl(kern, grid, block, mma_smem_bytes<true>(), st, a));
   } else {
     auto kern = decode_attn_mma_kernel<T, false, true>;
     OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, mma_smem_bytes<false>()));
-    kern<<<grid, block, mma_smem_bytes<false>(), st>>>(a);
+    OMNIKV_CUDA_OK(launch_pdl(kern, grid, block, mma_smem_bytes<false>(), st, a));
   }
   OMNIKV_CUDA_OK(cudaGetLastError());
   return OMNIKV_OK;
@@ -590,10 +600,10 @@ extern "C" int omnikv_decode_attn(const omnikv_attn_params* p, void* stream) {
   a.ws_cnt = static_cast<unsigned*>(p->workspace);
   a.ws_o = with_v ? reinterpret_cast<float*>(static_cast<unsigned char*>(p->workspace) + kAttnCntBytes) : nullptr;
   a.ws_ml = with_v ? a.ws_o + attn_ws_o_floats(p->B, p->H, p->n_splits) : nullptr;
-  a.out_is_T = 0;
   if (with_v && (p->n_splits > 512 || (size_t)p->B * p->KVH * 4 > kAttnCntBytes)) return OMNIKV_E_UNSUPPORTED;
   a.B = p->B; a.H = p->H; a.KVH = p->KVH; a.G = G; a.S = p->n_splits;
   a.scale = p->scale;
+  a.pdl_trigger = 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (p->dtype) {
     case OMNIKV_BF16: return launch_mma<__nv_bfloat16>(a, with_v, with_score, st);

@@ -54,6 +54,19 @@ struct GemvArgs {
   int* status;                      // device status word (0 = ok)
   int* next_chunk;                  // device counter (zero at launch) for dynamic chunk scheduling, or nullptr:
                                     // static round-robin over the CTAs
+  // ---- tensor parallelism: the SUM all-reduce of a row-parallel projection, fused over peer memory ----
+  // producer side (EPI_RESID): this rank's partial outputs are stored straight into every rank's exchange
+  // buffer; when the whole grid is done, a flag word is stored on every rank
+  int tp_world;                     // 0/1: off
+  float* tp_peer_partial[8];        // rank p's slot for MY partials: [N] fp32
+  unsigned* tp_peer_flag[8];        // rank p's flag word for (slot, me)
+  unsigned* tp_done;                // local counter of finished CTAs (self-resetting)
+  // consumer side (phases with a norm): x = resid + sum over ranks of their partials, once the flags arrived
+  const float* tp_my_partials;      // local [8][K] fp32 of the slot to consume, or nullptr
+  const unsigned* tp_my_flags;      // local [8]
+  void* tp_h_out;                   // local [K]: CTA 0 stores the summed residual stream here
+  const unsigned* tp_epoch;         // device word bumped once per decode step
+  unsigned tp_seq;                  // flag value = epoch * 256 + seq + 1
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
@@ -117,6 +130,12 @@ __device__ __forceinline__ void unpack8<__half>(const uint4& v, float (&f)[8]) {
     f[2 * i] = t.x;
     f[2 * i + 1] = t.y;
   }
+}
+
+__device__ __forceinline__ unsigned ld_volatile_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.volatile.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
 }
 
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
@@ -247,11 +266,47 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
   uint4* ns = xs + K / 8;
   float sq = 0.f;
   consumer_bar();  // the previous phase no longer reads the staging area
+  const bool tp_consume = a.tp_world > 1 && a.tp_my_partials != nullptr;
+  if (tp_consume) {
+    // every rank's partial sums of the previous projection must have landed in this GPU's memory: each rank
+    // stores a flag here after its last store.  Bounded wait, one poller per CTA.
+    if (tid == 0) {
+      const unsigned want = __ldcg(a.tp_epoch) * 256u + a.tp_seq + 1u;
+      for (int r = 0; r < a.tp_world; ++r) {
+        unsigned spin = 0;
+        while ((int)(ld_volatile_u32(a.tp_my_flags + r) - want) < 0) {
+          if (++spin > GV_SPIN_LIMIT) {
+            cs.fail = 1;
+            atomicExch(a.status, 4);
+            break;
+          }
+        }
+      }
+      __threadfence_system();
+    }
+    consumer_bar();
+    if (cs.fail) return false;
+  }
   {
     const uint4* xg = reinterpret_cast<const uint4*>(a.x);
     const uint4* ng = reinterpret_cast<const uint4*>(a.norm_w);
     for (int v = tid; v < K / 8; v += GV_CONSUMER_WARPS * 32) {
-      const uint4 raw = COHERENT ? __ldcg(xg + v) : xg[v];
+      uint4 raw = (COHERENT || tp_consume) ? __ldcg(xg + v) : xg[v];
+      if (tp_consume) {  // residual + the ranks' partials (fp32), rounded once to the storage type
+        float f[8];
+        unpack8<T>(raw, f);
+        for (int r = 0; r < a.tp_world; ++r) {
+          const float4* pp = reinterpret_cast<const float4*>(a.tp_my_partials + (size_t)r * K) + 2 * v;
+          const float4 p0 = __ldcg(pp), p1 = __ldcg(pp + 1);
+          f[0] += p0.x; f[1] += p0.y; f[2] += p0.z; f[3] += p0.w;
+          f[4] += p1.x; f[5] += p1.y; f[6] += p1.z; f[7] += p1.w;
+        }
+        raw.x = pack2<T>(f[0], f[1]);
+        raw.y = pack2<T>(f[2], f[3]);
+        raw.z = pack2<T>(f[4], f[5]);
+        raw.w = pack2<T>(f[6], f[7]);
+        if (blockIdx.x == 0 && a.tp_h_out) reinterpret_cast<uint4*>(a.tp_h_out)[v] = raw;
+      }
       xs[v] = raw;
       if (ng) {
         ns[v] = ng[v];
@@ -338,7 +393,12 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
       piece_rows<HALF, EPI>(a, chunk, row0, row1);
       row0 += p;
       row1 += p;
-      if (EPI == EPI_RESID) {
+      if (EPI == EPI_RESID && a.tp_world > 1) {
+        for (int pr = 0; pr < a.tp_world; ++pr) {
+          a.tp_peer_partial[pr][row0] = r0;
+          a.tp_peer_partial[pr][row1] = r1;
+        }
+      } else if (EPI == EPI_RESID) {
         const T* rs = static_cast<const T*>(a.resid);
         T* out = static_cast<T*>(a.out);
         float b0 = 0.f, b1 = 0.f;
@@ -386,6 +446,21 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
       }
     }
   }
+  if (EPI == EPI_RESID && a.tp_world > 1) {
+    // all of this CTA's stores (to every rank) are ordered before its count; the CTA that completes the count
+    // raises this rank's flag on every rank
+    consumer_bar();
+    if (tid == 0) {
+      __threadfence_system();
+      if (atomicAdd(a.tp_done, 1u) == gridDim.x - 1) {
+        atomicExch(a.tp_done, 0u);
+        __threadfence_system();
+        const unsigned val = __ldcg(a.tp_epoch) * 256u + a.tp_seq + 1u;
+        for (int pr = 0; pr < a.tp_world; ++pr)
+          asm volatile("st.volatile.global.u32 [%0], %1;\n" ::"l"(a.tp_peer_flag[pr]), "r"(val) : "memory");
+      }
+    }
+  }
   if (EPI == EPI_LOGITS) {
     consumer_bar();
     if (tid < HALF) cs.best[tid] = my_best;
@@ -426,10 +501,15 @@ __global__ void __launch_bounds__(GV_THREADS, 1) decode_gemv_kernel(const GemvAr
   constexpr unsigned SLOT = GV_CONSUMER_WARPS / WK * K * 2;
   Ring ring{smem, full_bar, empty_bar, SLOT, slot_chunk, smem + GV_STAGES * SLOT};
   int it = 0;
+  // Programmatic dependent launch: the grid is one CTA per SM, all resident, so the next kernel may be
+  // scheduled behind it right away.  The producer starts streaming weights at once (they depend on nothing);
+  // the consumers wait for the previous kernel before they touch activations or write any output.
+  pdl_trigger();
   if ((threadIdx.x >> 5) == GV_CONSUMER_WARPS) {
     if ((threadIdx.x & 31) == 0) produce_phase<T, KV, WK, EPI>(a, ring, it);
     return;
   }
+  pdl_wait();
   consume_phase<T, KV, WK, EPI, false>(a, ring, cs, it);
 }
 
@@ -448,12 +528,6 @@ struct ChainArgs {
   size_t next_w_bytes;
 };
 enum ChainKind { CK_O = 0, CK_GATEUP = 1, CK_DOWN = 2, CK_QKV = 3, CK_LOGITS = 4 };
-
-__device__ __forceinline__ unsigned ld_volatile_u32(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.volatile.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 
 // Called by ONE thread per CTA after a CTA-level barrier.  One 32-bit word: arrivals in the low half,
 // generation in the high half.  The last arriver adds (1 << 16) - n_blocks, which clears the count and
@@ -566,8 +640,7 @@ int launch_one(const GemvArgs& a, int n_sms, cudaStream_t st) {
   auto kern = decode_gemv_kernel<T, KV, WK, EPI>;
   OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int grid = a.n_chunks < n_sms ? a.n_chunks : n_sms;
-  kern<<<grid, GV_THREADS, smem, st>>>(a);
-  OMNIKV_CUDA_OK(cudaGetLastError());
+  OMNIKV_CUDA_OK(launch_pdl(kern, dim3(grid), dim3(GV_THREADS), smem, st, a));
   return OMNIKV_OK;
 }
 
@@ -614,6 +687,44 @@ int launch_chain(const ChainArgs& c, int n_sms, cudaStream_t st) {
   return OMNIKV_OK;
 }
 
+// Exchange buffer of one rank: [2 slots][8 ranks][hidden] fp32 partials, then [2][8] flag words.
+size_t tp_partials_bytes(int hidden) { return (size_t)2 * 8 * hidden * sizeof(float); }
+
+// Producer fields: where MY partials of exchange `seq` go on every rank.
+int tp_fill_producer(GemvArgs& a, const omnikv_tp_exchange* t, int n_rows) {
+  if (!t || t->world <= 1) return OMNIKV_OK;
+  if (t->world > 8 || t->rank < 0 || t->rank >= t->world || !t->done_counter || !t->epoch || t->hidden != n_rows)
+    return OMNIKV_E_BADARG;
+  const int slot = t->seq & 1;
+  a.tp_world = t->world;
+  for (int p = 0; p < t->world; ++p) {
+    if (!t->peer_base[p]) return OMNIKV_E_BADARG;
+    unsigned char* base = static_cast<unsigned char*>(t->peer_base[p]);
+    a.tp_peer_partial[p] = reinterpret_cast<float*>(base) + ((size_t)slot * 8 + t->rank) * t->hidden;
+    a.tp_peer_flag[p] = reinterpret_cast<unsigned*>(base + tp_partials_bytes(t->hidden)) + slot * 8 + t->rank;
+  }
+  a.tp_done = t->done_counter;
+  a.tp_epoch = t->epoch;
+  a.tp_seq = (unsigned)t->seq;
+  return OMNIKV_OK;
+}
+
+// Consumer fields: the local slot holding every rank's partials of exchange `seq`.
+int tp_fill_consumer(GemvArgs& a, const omnikv_tp_exchange* t, int k, void* h_out) {
+  if (!t || t->world <= 1) return OMNIKV_OK;
+  if (t->world > 8 || t->rank < 0 || t->rank >= t->world || !t->epoch || t->hidden != k || !t->peer_base[t->rank])
+    return OMNIKV_E_BADARG;
+  const int slot = t->seq & 1;
+  unsigned char* base = static_cast<unsigned char*>(t->peer_base[t->rank]);
+  a.tp_world = t->world;
+  a.tp_my_partials = reinterpret_cast<const float*>(base) + (size_t)slot * 8 * t->hidden;
+  a.tp_my_flags = reinterpret_cast<const unsigned*>(base + tp_partials_bytes(t->hidden)) + slot * 8;
+  a.tp_h_out = h_out;
+  a.tp_epoch = t->epoch;
+  a.tp_seq = (unsigned)t->seq;
+  return OMNIKV_OK;
+}
+
 int rows_per_stage(int K) {
   const int wk = K <= 4096 ? 1 : (K <= 8192 ? 2 : 4);
   return GV_CONSUMER_WARPS / wk;
@@ -627,7 +738,8 @@ inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) =
 extern "C" int omnikv_decode_qkv(int dtype, const void* h, const void* norm_w, float eps, const void* w_qkv, int hidden,
                                  int H, int KVH, int head_dim, const float* inv_freq, const int32_t* rope_pos,
                                  void* q_out, void* k_cache_seq, void* v_cache_seq, int64_t kv_stride_h,
-                                 int64_t kv_stride_row, const int32_t* cache_pos, int32_t* status, void* stream) {
+                                 int64_t kv_stride_row, const int32_t* cache_pos, const omnikv_tp_exchange* tp_in,
+                                 void* h_inout, int32_t* status, void* stream) {
   using namespace omnikv;
   if (!h || !norm_w || !w_qkv || !inv_freq || !rope_pos || !q_out || !k_cache_seq || !v_cache_seq || !cache_pos || !status)
     return OMNIKV_E_BADARG;
@@ -638,23 +750,28 @@ extern "C" int omnikv_decode_qkv(int dtype, const void* h, const void* norm_w, f
   a.n_chunks = a.N / rows_per_stage(hidden); a.partner_rows = 64;
   a.q_out = q_out; a.k_cache = k_cache_seq; a.v_cache = v_cache_seq; a.kv_sh = kv_stride_h; a.kv_sr = kv_stride_row;
   a.pos = cache_pos; a.rope_pos = rope_pos; a.inv_freq = inv_freq; a.H = H; a.KVH = KVH; a.status = status;
+  if (const int rc = tp_fill_consumer(a, tp_in, hidden, h_inout)) return rc;
   return dispatch<EPI_QKV>(dtype, a, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int omnikv_decode_gemv_residual(int dtype, const void* w, int N, int K, const void* x, const void* resid,
-                                           void* out, int32_t* status, void* stream) {
+                                           void* out, const omnikv_tp_exchange* tp_out, int32_t* status,
+                                           void* stream) {
   using namespace omnikv;
-  if (!w || !x || !out || !status || N <= 0) return OMNIKV_E_BADARG;
+  const bool exchange = tp_out && tp_out->world > 1;
+  if (!w || !x || (!out && !exchange) || !status || N <= 0) return OMNIKV_E_BADARG;
   if (!al16(w) || !al16(x)) return OMNIKV_E_BADARG;
   const int rps = rows_per_stage(K);
   if (N % rps) return OMNIKV_E_UNSUPPORTED;
   GemvArgs a = {};
   a.W = w; a.x = x; a.N = N; a.K = K; a.n_chunks = N / rps; a.resid = resid; a.out = out; a.status = status;
+  if (const int rc = tp_fill_producer(a, tp_out, N)) return rc;
   return dispatch<EPI_RESID>(dtype, a, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int omnikv_decode_gate_up(int dtype, const void* h, const void* norm_w, float eps, const void* w_gate_up,
-                                     int hidden, int inter, void* act_out, int32_t* status, void* stream) {
+                                     int hidden, int inter, void* act_out, const omnikv_tp_exchange* tp_in,
+                                     void* h_inout, int32_t* status, void* stream) {
   using namespace omnikv;
   if (!h || !norm_w || !w_gate_up || !act_out || !status || inter <= 0) return OMNIKV_E_BADARG;
   if (!al16(h) || !al16(norm_w) || !al16(w_gate_up)) return OMNIKV_E_BADARG;
@@ -663,13 +780,14 @@ extern "C" int omnikv_decode_gate_up(int dtype, const void* h, const void* norm_
   GemvArgs a = {};
   a.W = w_gate_up; a.x = h; a.norm_w = norm_w; a.eps = eps; a.N = 2 * inter; a.K = hidden;
   a.n_chunks = inter / half; a.partner_rows = inter; a.out = act_out; a.status = status;
+  if (const int rc = tp_fill_consumer(a, tp_in, hidden, h_inout)) return rc;
   return dispatch<EPI_GATEUP>(dtype, a, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int omnikv_decode_logits(int dtype, const void* h, const void* norm_w, float eps, const void* w_head,
                                     int hidden, int vocab_rows, int row_offset, float* logits,
-                                    unsigned long long* best_scratch, int64_t* token_out, int32_t* status,
-                                    void* stream) {
+                                    unsigned long long* best_scratch, int64_t* token_out,
+                                    const omnikv_tp_exchange* tp_in, int32_t* status, void* stream) {
   using namespace omnikv;
   if (!h || !norm_w || !w_head || !logits || !best_scratch || !status || vocab_rows <= 0) return OMNIKV_E_BADARG;
   if (!al16(h) || !al16(norm_w) || !al16(w_head)) return OMNIKV_E_BADARG;
@@ -680,6 +798,7 @@ extern "C" int omnikv_decode_logits(int dtype, const void* h, const void* norm_w
   GemvArgs a = {};
   a.W = w_head; a.x = h; a.norm_w = norm_w; a.eps = eps; a.N = vocab_rows; a.K = hidden; a.n_chunks = vocab_rows / rps;
   a.logits = logits; a.best = best_scratch; a.row_offset = row_offset; a.status = status;
+  if (const int rc0 = tp_fill_consumer(a, tp_in, hidden, nullptr)) return rc0;
   const int rc = dispatch<EPI_LOGITS>(dtype, a, st);
   if (rc != OMNIKV_OK) return rc;
   if (token_out) {
@@ -771,4 +890,9 @@ extern "C" int omnikv_decode_chain_supported(int dtype, int hidden, int inter, i
   if (dtype != OMNIKV_BF16 && dtype != OMNIKV_F16) return 0;
   if (H * omnikv::kHeadDim != hidden) return 0;
   return (hidden == 4096 && inter == 14336) || (hidden == 512 && inter == 1024) || (hidden == 2048 && inter == 7168);
+}
+
+extern "C" size_t omnikv_tp_exchange_bytes(int hidden) {
+  if (hidden <= 0) return 0;
+  return omnikv::tp_partials_bytes(hidden) + 2 * 8 * sizeof(unsigned) + 192;  // padded to a multiple of 256
 }

@@ -1,5 +1,6 @@
 // ABI bookkeeping, the KV append, the offload gather and the window-plane fold.
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -12,6 +13,14 @@ int record_cuda_error(cudaError_t e, const char* where) {
   snprintf(g_last_error, sizeof(g_last_error), "%s: %s (%s)", where, cudaGetErrorName(e), cudaGetErrorString(e));
   (void)cudaGetLastError();  // clear the sticky-less error state
   return OMNIKV_E_CUDA;
+}
+
+bool pdl_enabled() {
+  static const int on = [] {
+    const char* e = getenv("OMNIKV_PDL");
+    return (e && e[0] == '0') ? 0 : 1;
+  }();
+  return on != 0;
 }
 
 namespace {

@@ -386,8 +386,44 @@ class OmniKVMulLayer(nn.Module):
         attn, mlp, tp = self.self_attn, self.mlp, self.tp
         h = hidden_states.view(-1)
         bufs = self._fused_bufs(cache, h.device, h.dtype)
+        xc = tp.exchange if (tp is not None and getattr(cache, "xchg_on", False)) else None
+        if xc is not None and self.is_filter and self.selector_cls != "last" and self.layer_idx > 0:
+            raise NotImplementedError("window selectors read the completed hidden state before the QKV kernel "
+                                      "has summed the peers' partials; use the NCCL path for them")
         score_out, score_len = self._decode_select_begin(hidden_states, cache, position_embeddings)
         k_seq, v_seq, pos = cache.write_target(self.layer_idx)
+        if xc is not None:
+            # Fused projection + all-reduce over peer memory: a projection's partial sums go straight to every rank
+            # and the NEXT kernel adds them to the residual stream while it loads its activations, storing the
+            # completed stream to the other of two buffers (the kernel's other CTAs still read the old one).  The
+            # down projection's partials are consumed by the next layer's QKV kernel, or by the logits kernel.
+            if getattr(bufs, "hx", None) is None:
+                bufs.hx = [torch.empty_like(h), torch.empty_like(h)]
+                bufs.hx_i = 0
+
+            def next_h():
+                t = bufs.hx[bufs.hx_i]
+                bufs.hx_i ^= 1
+                return t
+
+            if self.layer_idx > 0:
+                h_new = next_h()
+                ops.decode_qkv(h, self.input_layernorm.weight, self.input_layernorm.variance_epsilon, attn.qkv_weight,
+                               attn.num_heads, attn.num_key_value_heads, attn.rotary_emb.inv_freq, cache.pos_dev, bufs.q,
+                               k_seq, v_seq, pos, tp_in=xc.at(2 * self.layer_idx - 1), h_out=h_new)
+                h = h_new
+            else:
+                ops.decode_qkv(h, self.input_layernorm.weight, self.input_layernorm.variance_epsilon, attn.qkv_weight,
+                               attn.num_heads, attn.num_key_value_heads, attn.rotary_emb.inv_freq, cache.pos_dev, bufs.q,
+                               k_seq, v_seq, pos)
+            cache.attend(bufs.q, self.layer_idx, out=bufs.o, score_out=score_out, score_len=score_len)
+            self._decode_select_end(cache, score_out)
+            ops.decode_gemv_residual(attn.o_weight, bufs.o.view(-1), None, None, tp_out=xc.at(2 * self.layer_idx))
+            h_new = next_h()
+            ops.decode_gate_up(h, self.post_attention_layernorm.weight, self.post_attention_layernorm.variance_epsilon,
+                               mlp.gate_up_weight, bufs.act, tp_in=xc.at(2 * self.layer_idx), h_out=h_new)
+            ops.decode_gemv_residual(mlp.down_weight, bufs.act, None, None, tp_out=xc.at(2 * self.layer_idx + 1))
+            return (h_new.view(1, 1, -1),)
         ops.decode_qkv(h, self.input_layernorm.weight, self.input_layernorm.variance_epsilon, attn.qkv_weight,
                        attn.num_heads, attn.num_key_value_heads, attn.rotary_emb.inv_freq, cache.pos_dev, bufs.q,
                        k_seq, v_seq, pos)
@@ -648,7 +684,15 @@ class OmniKVMulLM(nn.Module):
                 self.lm_head.weight.dtype, self.config.hidden_size, layer0.mlp.intermediate_size,
                 layer0.self_attn.num_heads) and self.lm_head.weight.shape[0] % 8 == 0:
             return self._decode_step_chained(tokens, cache)
-        out = self.model(input_ids=tokens, past_key_values=cache, apply_final_norm=not fused)
+        tp = self.tp
+        xc = tp.exchange if (fused and tp is not None and self._exchange_ok()) else None
+        cache.xchg_on = xc is not None
+        if xc is not None:
+            xc.begin_step()
+        try:
+            out = self.model(input_ids=tokens, past_key_values=cache, apply_final_norm=not fused)
+        finally:
+            cache.xchg_on = False
         h = out.last_hidden_state[:, -1]
         if not fused:
             logits = self._gather_logits(self.lm_head(h)).float()
@@ -658,14 +702,22 @@ class OmniKVMulLM(nn.Module):
             fb.logits = torch.empty(1, self.lm_head.weight.shape[0], dtype=torch.float32, device=h.device)
             fb.best = torch.zeros(1, dtype=torch.int64, device=h.device)
             fb.token = torch.zeros(1, 1, dtype=torch.int64, device=h.device)
-        tp = self.tp
         lo = tp.shard(self.vocab_size)[0] if tp is not None else 0
+        n_layers = len(self.model.layers)
         ops.decode_logits(h.reshape(-1), self.model.norm.weight, self.model.norm.variance_epsilon, self.lm_head.weight,
-                          lo, fb.logits, fb.best, fb.token if tp is None else None)
+                          lo, fb.logits, fb.best, fb.token if tp is None else None,
+                          tp_in=xc.at(2 * n_layers - 1) if xc is not None else None)
         if tp is None:
             return fb.logits, fb.token
         logits = tp.all_gather_last(fb.logits)
         return logits, logits.argmax(-1, keepdim=True)
+
+    def _exchange_ok(self) -> bool:
+        """The fused projection + all-reduce path covers selector ``last`` (the window selectors need the completed
+        hidden state on the host side of the layer) and fewer than 128 layers (exchange numbers stay below 256)."""
+        return (self.tp is not None and self.tp.exchange is not None and len(self.model.layers) < 128
+                and self.config.get("selector_cls", "softmax_before_last") == "last"
+                and self.config.get("peer_exchange", True))
 
     def _decode_step_chained(self, tokens, cache):
         """Batch-1 decode step as 33 cooperative weight-streaming launches interleaved with the 32 attention

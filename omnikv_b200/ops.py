@@ -320,37 +320,47 @@ def fused_decode_supported(dtype, hidden: int, inter: int, n_q_rows: int, vocab_
             and inter % (rows_per_stage(hidden) // 2) == 0 and vocab_rows % rows_per_stage(hidden) == 0)
 
 
-def decode_qkv(h, norm_w, eps, w_qkv, H, KVH, inv_freq, rope_pos, q_out, k_cache_seq, v_cache_seq, cache_pos):
-    """h ``[hidden]``; w_qkv ``[(H+2KVH)*128, hidden]``; k/v_cache_seq: one sequence's ``[KVH, rows, 128]``."""
+def _xref(x):
+    return None if x is None else C.byref(x)
+
+
+def decode_qkv(h, norm_w, eps, w_qkv, H, KVH, inv_freq, rope_pos, q_out, k_cache_seq, v_cache_seq, cache_pos,
+               tp_in=None, h_out=None):
+    """h ``[hidden]``; w_qkv ``[(H+2KVH)*128, hidden]``; k/v_cache_seq: one sequence's ``[KVH, rows, 128]``.
+    ``tp_in`` (an ``abi.TpExchange``): h is first completed with every rank's partial sums of that exchange and
+    the completed vector is stored to ``h_out`` -- a DIFFERENT buffer than ``h``, which other CTAs still read."""
     abi.check(abi.lib().omnikv_decode_qkv(_DT[h.dtype], h.data_ptr(), norm_w.data_ptr(), float(eps), w_qkv.data_ptr(),
                                           w_qkv.shape[1], H, KVH, 128, inv_freq.data_ptr(), rope_pos.data_ptr(),
                                           q_out.data_ptr(), k_cache_seq.data_ptr(), v_cache_seq.data_ptr(),
                                           k_cache_seq.stride(0), k_cache_seq.stride(1), cache_pos.data_ptr(),
+                                          _xref(tp_in), _ptr(h_out),
                                           status_word(h.device).data_ptr(), _stream()), "omnikv_decode_qkv")
     _count(1)
 
 
-def decode_gemv_residual(w, x, resid, out):
-    """out ``[N]`` = (resid or 0) + w ``[N,K]`` @ x ``[K]``; ``out`` may be ``resid``."""
+def decode_gemv_residual(w, x, resid, out, tp_out=None):
+    """out ``[N]`` = (resid or 0) + w ``[N,K]`` @ x ``[K]``; ``out`` may be ``resid``.  With ``tp_out`` the fp32
+    partial sums go to every rank's exchange buffer instead and ``resid`` / ``out`` are not used."""
     abi.check(abi.lib().omnikv_decode_gemv_residual(_DT[x.dtype], w.data_ptr(), w.shape[0], w.shape[1], x.data_ptr(),
-                                                    _ptr(resid), out.data_ptr(), status_word(x.device).data_ptr(),
-                                                    _stream()), "omnikv_decode_gemv_residual")
+                                                    _ptr(resid), _ptr(out), _xref(tp_out),
+                                                    status_word(x.device).data_ptr(), _stream()),
+              "omnikv_decode_gemv_residual")
     _count(1)
 
 
-def decode_gate_up(h, norm_w, eps, w_gate_up, act_out):
+def decode_gate_up(h, norm_w, eps, w_gate_up, act_out, tp_in=None, h_out=None):
     abi.check(abi.lib().omnikv_decode_gate_up(_DT[h.dtype], h.data_ptr(), norm_w.data_ptr(), float(eps),
                                               w_gate_up.data_ptr(), w_gate_up.shape[1], w_gate_up.shape[0] // 2,
-                                              act_out.data_ptr(), status_word(h.device).data_ptr(), _stream()),
-              "omnikv_decode_gate_up")
+                                              act_out.data_ptr(), _xref(tp_in), _ptr(h_out),
+                                              status_word(h.device).data_ptr(), _stream()), "omnikv_decode_gate_up")
     _count(1)
 
 
-def decode_logits(h, norm_w, eps, w_head, row_offset, logits, best, token_out=None):
+def decode_logits(h, norm_w, eps, w_head, row_offset, logits, best, token_out=None, tp_in=None):
     abi.check(abi.lib().omnikv_decode_logits(_DT[h.dtype], h.data_ptr(), norm_w.data_ptr(), float(eps), w_head.data_ptr(),
                                              w_head.shape[1], w_head.shape[0], int(row_offset), logits.data_ptr(),
-                                             best.data_ptr(), _ptr(token_out), status_word(h.device).data_ptr(),
-                                             _stream()), "omnikv_decode_logits")
+                                             best.data_ptr(), _ptr(token_out), _xref(tp_in),
+                                             status_word(h.device).data_ptr(), _stream()), "omnikv_decode_logits")
     _count(2 if token_out is not None else 1)
 
 

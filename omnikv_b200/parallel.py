@@ -14,6 +14,12 @@ need no communication.  The exchanges of a decode step are:
   max over ALL heads, and MAX is order independent, so after it every rank holds bit-identical planes
   and runs the same deterministic top-k: no index broadcast is needed;
 * ``all_gather`` of the vocabulary-sharded logits.
+
+At batch 1 the two SUM all-reduces per layer are latency, not bandwidth (8 KB of hidden state): with
+``PeerExchange`` they are fused into the weight-streaming kernels on both sides -- the projection kernel
+stores its partial sums straight into every rank's peer-mapped buffer over NVLink and raises a flag, the next
+kernel waits for the flags (bounded) and adds the partials while it loads its activations
+(``omnikv_tp_exchange`` in the C header).  NCCL remains the transport for the score planes and the logits.
 """
 from __future__ import annotations
 
@@ -23,9 +29,69 @@ import torch
 import torch.distributed as dist
 
 
+class PeerExchange:
+    """Peer-mapped exchange buffers of the fused projection + all-reduce kernels (one per process)."""
+
+    def __init__(self, world: int, rank: int, hidden: int, device: torch.device, group=None):
+        import torch.distributed._symmetric_memory as symm
+
+        from . import abi
+        self.world, self.rank, self.hidden = world, rank, hidden
+        nbytes = abi.lib().omnikv_tp_exchange_bytes(hidden)
+        self.buf = symm.empty(nbytes, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        torch.cuda.synchronize(device)
+        grp = group if group is not None else dist.group.WORLD
+        try:
+            self.handle = symm.rendezvous(self.buf, grp)
+        except Exception:
+            symm.enable_symm_mem_for_group(grp.group_name)
+            self.handle = symm.rendezvous(self.buf, grp)
+        self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.done = torch.zeros(1, dtype=torch.int32, device=device)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self._structs = {}
+        dist.barrier(group=group)  # every rank's buffer is zeroed and mapped before anyone stores into it
+
+    def begin_step(self) -> None:
+        """Once per decode step on every rank (graph-capturable): flags carry the step number."""
+        self.epoch.add_(1)
+
+    def at(self, seq: int):
+        """The ``omnikv_tp_exchange`` describing exchange number ``seq`` of the step."""
+        from . import abi
+        x = self._structs.get(seq)
+        if x is None:
+            x = abi.TpExchange()
+            x.world, x.rank, x.seq, x.hidden = self.world, self.rank, seq, self.hidden
+            for r, ptr in enumerate(self.peer_ptrs):
+                x.peer_base[r] = ptr
+            x.done_counter, x.epoch = self.done.data_ptr(), self.epoch.data_ptr()
+            self._structs[seq] = x
+        return x
+
+
 class TPGroup:
     def __init__(self, world: int, rank: int, group=None):
         self.world, self.rank, self.group = world, rank, group
+        self.exchange: Optional[PeerExchange] = None
+
+    def enable_peer_exchange(self, hidden: int, device: torch.device) -> bool:
+        """Set up the peer-mapped buffers for the fused projection + all-reduce kernels.  Returns False (and
+        keeps NCCL all-reduces) when symmetric memory cannot be set up on this machine."""
+        if self.world <= 1 or self.world > 8:
+            return False
+        try:
+            self.exchange = PeerExchange(self.world, self.rank, hidden, device, self.group)
+        except Exception as e:  # no peer access between the GPUs, or no symmetric-memory support
+            import logging
+            logging.getLogger("omnikv_b200").warning(f"peer exchange unavailable, using NCCL all-reduce: {e}")
+            self.exchange = None
+        ok = torch.tensor([1 if self.exchange is not None else 0], device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        if int(ok.item()) == 0:
+            self.exchange = None
+        return self.exchange is not None
 
     def shard(self, n: int) -> Tuple[int, int]:
         """[lo, hi) of this rank's contiguous share of ``n`` items (``n`` divisible by the world size)."""

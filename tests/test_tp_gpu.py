@@ -67,3 +67,54 @@ def test_tp2_matches_single_gpu(selector):
         err, same = ret[rank]
         assert err <= 1e-4, (rank, err)
         assert same
+
+
+def _worker_engine(rank, world, port, ret):
+    import logging
+    logging.disable(logging.WARNING)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    from omnikv_b200 import ops, parallel
+    from omnikv_b200.modeling import LlamaCompressorConfig, OmniKVMulLM
+    tp = parallel.init(world, rank, dev)
+    try:
+        has_x = tp.enable_peer_exchange(1024, dev)
+
+        def cfg(peer):
+            c = LlamaCompressorConfig(num_hidden_layers=4, hidden_size=1024, intermediate_size=2048,
+                                      num_attention_heads=8, num_key_value_heads=2, vocab_size=1024, head_dim=128)
+            c.set_config_of_compressor(model_cls="multi", cache_cls="multi", do_select_layers="1", num_wait_load_layers=1,
+                                       real_offload=False, dense_more=True, num_of_selected_tokens=0.25,
+                                       selector_cls="last", window_size=16, peer_exchange=peer)
+            return c
+        g = torch.Generator().manual_seed(1)
+        ids = torch.randint(0, 1024, (1, 300), generator=g).to(dev)
+        outs = {}
+        for peer in (True, False):
+            lm = OmniKVMulLM.from_config(cfg(peer), dtype=torch.bfloat16, device=dev, seed=0, tp=tp)
+            outs[peer] = (lm.generate_greedy(ids, 16, use_cuda_graph=False).cpu(),
+                          lm.generate_greedy(ids, 16, use_cuda_graph=True).cpu())
+            ops.check_status(dev)
+        ret[rank] = (bool(has_x), bool(torch.equal(outs[True][0], outs[True][1])),
+                     bool(torch.equal(outs[False][0], outs[False][1])),
+                     float((outs[True][0] == outs[False][0]).float().mean()))
+    finally:
+        torch.distributed.destroy_process_group()
+
+
+def test_tp2_fused_peer_exchange_engine():
+    """Decode engine on 2 GPUs, bf16, fused kernels: the peer-memory exchange and the NCCL all-reduce paths generate
+    (almost) the same tokens -- they differ only in where the partial sums are rounded -- and CUDA-graph replay
+    equals eager on both."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world, port = 2, _free_port()
+    ret = mp.get_context("spawn").Manager().dict()
+    mp.spawn(_worker_engine, args=(world, port, ret), nprocs=world, join=True)
+    for rank in range(world):
+        has_x, graph_eq_peer, graph_eq_nccl, agree = ret[rank]
+        assert has_x, "symmetric memory / peer access unavailable"
+        assert graph_eq_peer and graph_eq_nccl
+        assert agree >= 0.75
+    assert ret[0] == ret[1]
