@@ -40,6 +40,22 @@ struct AttnArgs {
   float scale;
 };
 
+#ifdef OMNIKV_ATTN_TRACE
+// Profiling build only (-DOMNIKV_ATTN_TRACE): per-CTA %globaltimer stamps of the mma kernel's stages.
+__device__ unsigned long long g_attn_trace[4096 * 8];
+__device__ __forceinline__ void attn_stamp(int slot) {
+  if (threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
+    const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    if (cta < 4096) g_attn_trace[cta * 8 + slot] = t;
+  }
+}
+#define ATTN_STAMP(i) attn_stamp(i)
+#else
+#define ATTN_STAMP(i)
+#endif
+
 namespace {
 
 constexpr int TILE = 64;       // rows per pipeline stage
@@ -101,7 +117,7 @@ __device__ __forceinline__ void finish_group(const AttnArgs& a, int b, int kvh, 
     __syncwarp();
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     const float4* op = reinterpret_cast<const float4*>(a.ws_o + base * kHeadDim) + lane;
-#pragma unroll 8
+#pragma unroll 16
     for (int s = 0; s < S; ++s) {
       const float4 o = __ldcg(op + (size_t)s * (kHeadDim / 4));
       const float wt = w[s];
@@ -135,10 +151,26 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
   // index list) comes from the kernels before it, so it waits first; what it gains is that its CTAs are already
   // resident when the previous kernel ends.  It lets its successor be scheduled early only when its own grid is
   // fully resident (a.pdl_trigger, decided by the host from the grid size).
+  ATTN_STAMP(0);
   pdl_wait();
   if (a.pdl_trigger) pdl_trigger();
+  ATTN_STAMP(1);
+  // Every global load of the prologue that depends on nothing is issued here, together: the lengths, the tail
+  // start and this thread's two 16-byte pieces of the group's queries.  (Chained one after the other, these
+  // round trips were most of a sparse layer's time.)
+  uint4 q_reg[2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int i = tid + j * NTHREADS, r = i >> 4, c = i & 15;
+    q_reg[j] = make_uint4(0, 0, 0, 0);
+    if (r < G) {
+      const T* qp = static_cast<const T*>(a.q) + (size_t)b * a.q_sb + (size_t)(kvh * G + r) * a.q_sh;
+      q_reg[j] = __ldg(reinterpret_cast<const uint4*>(qp + c * 8));
+    }
+  }
   const int nA = a.lenA[b];
   const int nB = a.lenB ? a.lenB[b] : 0;
+  const int startB = a.startB ? a.startB[b] : 0;
   const int n = nA + nB;
   int r0, r1;
   split_range(n, a.S, split, r0, r1);
@@ -166,20 +198,19 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
   const T* kB = a.kB ? static_cast<const T*>(a.kB) + (size_t)b * a.b_sb + (size_t)kvh * a.b_sh : nullptr;
   const T* vB = (WITH_V && a.vB) ? static_cast<const T*>(a.vB) + (size_t)b * a.b_sb + (size_t)kvh * a.b_sh : nullptr;
   const int* idx = a.idxA ? a.idxA + (size_t)b * a.idx_stride : nullptr;
-  const int startB = a.startB ? a.startB[b] : 0;
 
-  auto issue_tile = [&](int tile, int slot) {
-    unsigned char* ks = smem + slot * STAGE_BYTES;
-    unsigned char* vs = ks + TILE_BYTES;
-    const int cc = tid & 15, rowi = tid >> 4;
-    // First resolve every row of the tile to its cache position (the index loads go out together), then
-    // issue the copies: the copies are asm statements the compiler will not move loads across.
-    long long off[TILE / 8];
+  // A tile is issued in two steps: resolve() turns its rows into cache offsets (for a sparse layer this is a
+  // lookup in the index list), issue() starts the copies.  resolve() of the NEXT tile runs right after issue() of
+  // the current one, so the index loads are in flight during a whole tile of compute and never sit between a
+  // warp and its copies (the copies are asm statements the compiler does not move loads across).
+  constexpr int RPT = TILE / 8;  // rows per thread and tile
+  const int cc = tid & 15, rowi = tid >> 4;
+  auto resolve = [&](int tile, long long (&off)[RPT]) {
 #pragma unroll
-    for (int i = 0; i < TILE / 8; ++i) {
+    for (int i = 0; i < RPT; ++i) {
       const int R = r0 + tile * TILE + rowi + 8 * i;
       off[i] = -1;
-      if (R < r1) {
+      if (tile < ntiles && R < r1) {
         if (R < nA) {
           const long long pos = idx ? (long long)__ldg(idx + R) : (long long)R;
           off[i] = pos * a.a_sr;
@@ -188,8 +219,12 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
         }
       }
     }
+  };
+  auto issue = [&](int slot, const long long (&off)[RPT]) {
+    unsigned char* ks = smem + slot * STAGE_BYTES;
+    unsigned char* vs = ks + TILE_BYTES;
 #pragma unroll
-    for (int i = 0; i < TILE / 8; ++i) {
+    for (int i = 0; i < RPT; ++i) {
       const int row = rowi + 8 * i;
       const bool valid = off[i] >= 0;
       const bool segB = valid && (off[i] >> 62);
@@ -203,21 +238,23 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
     }
   };
 
+  // the index lookups of the first STAGES tiles go out together, then the copies of the first STAGES-1 tiles
+  long long off_first[STAGES - 1][RPT];
+  long long off_next[RPT];
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) resolve(s, off_first[s]);
+  resolve(STAGES - 1, off_next);
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
-    if (s < ntiles) issue_tile(s, s);
+    if (s < ntiles) issue(s, off_first[s]);
     cp_async_commit();
   }
 
-  // Q tile: 16 rows x 128, rows >= G are zero.
-  for (int i = tid; i < 16 * 16; i += NTHREADS) {
-    const int r = i >> 4, c = i & 15;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < G) {
-      const T* qp = static_cast<const T*>(a.q) + (size_t)b * a.q_sb + (size_t)(kvh * G + r) * a.q_sh;
-      v = *reinterpret_cast<const uint4*>(qp + c * 8);
-    }
-    *reinterpret_cast<uint4*>(q_s + r * PITCH + c * 16) = v;
+  // Q tile: 16 rows x 128, rows >= G are zero (loaded into registers at the top of the kernel).
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int i = tid + j * NTHREADS, r = i >> 4, c = i & 15;
+    *reinterpret_cast<uint4*>(q_s + r * PITCH + c * 16) = q_reg[j];
   }
   __syncthreads();
   unsigned qf[8][4];
@@ -228,6 +265,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
     ldmatrix_x4(qf[kk], q_s + row * PITCH + col * 2);
   }
 
+  ATTN_STAMP(2);  // copies of the first tiles issued, Q fragments loaded
   float m_row[2] = {-INFINITY, -INFINITY};
   float l_row[2] = {0.f, 0.f};
   float o[16][4];
@@ -244,8 +282,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
     __syncthreads();
     {
       const int nt = tile + STAGES - 1;
-      if (nt < ntiles) issue_tile(nt, nt % STAGES);
+      if (nt < ntiles) issue(nt % STAGES, off_next);
       cp_async_commit();
+      resolve(nt + 1, off_next);
     }
     const unsigned char* ks = smem + (tile % STAGES) * STAGE_BYTES;
     const unsigned char* vs = ks + TILE_BYTES;
@@ -326,6 +365,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
     }
   }
   cp_async_wait<0>();
+  ATTN_STAMP(3);  // all tiles consumed
   if (!WITH_V) return;
   __syncthreads();  // every warp is done with the ring: reuse it for the cross-warp merge
 
@@ -371,8 +411,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
       ws_ml[base * 2 + 1] = l;
     }
   }
+  ATTN_STAMP(4);  // partials written
   // the shared scratch of finish_group starts behind the cross-warp merge area used above
   finish_group<T>(a, b, kvh, ml_s + NWARPS * 16 * 2, &last_flag);
+  ATTN_STAMP(5);  // counted in (and, for the last CTA of the group, merged)
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -666,3 +708,9 @@ extern "C" int omnikv_decode_attn_no_alloc(const omnikv_attn_params* p, void* st
   q.workspace_bytes = OMNIKV_NO_ALLOC_SCRATCH_BYTES;
   return omnikv_decode_attn(&q, stream);
 }
+
+#ifdef OMNIKV_ATTN_TRACE
+extern "C" int omnikv_debug_attn_trace(unsigned long long* host_out, int n_words) {
+  return (int)cudaMemcpyFromSymbol(host_out, omnikv::g_attn_trace, (size_t)n_words * 8);
+}
+#endif

@@ -31,12 +31,13 @@ struct TopkArgs {
   int* count_out;
   unsigned* gkeys;  // workspace [B][max_len] when the slice does not fit shared memory
   int max_len;
+  int vec4;         // scores, strides and slices allow 16-byte loads
 };
 
 struct TkShared {
-  unsigned hist[2][256];
-  unsigned total[256];
-  unsigned cnt_gt, cnt_eq;           // this CTA's counts in the final pass (read by peers)
+  unsigned hist[256];                // this CTA's histogram of the current digit
+  unsigned total[2][256];            // cluster-wide histogram, filled by remote atomics from every CTA (double-buffered)
+  unsigned cnt_all[TK_MAX_CLUSTER][2];  // (greater, equal) counts of every CTA, pushed by their owners
   unsigned warp_gt[TK_WARPS], warp_eq[TK_WARPS];
   unsigned sel_digit, sel_remaining;
 };
@@ -66,30 +67,48 @@ __global__ void __launch_bounds__(TK_THREADS, 1) topk_kernel(const TopkArgs a) {
   unsigned* gk = RESIDENT ? nullptr : a.gkeys + (size_t)b * a.max_len + s0;
 
   // ---- load: max over planes, map to keys ---------------------------------------------------
+  // four consecutive scores per thread and plane (16-byte loads, all planes' loads of an iteration in flight)
   const float* sc = a.scores + (size_t)b * a.batch_stride + s0;
-  for (int i = tid; i < cnt; i += TK_THREADS) {
+  for (int i = tid; i < 256; i += TK_THREADS) sh.total[0][i] = sh.total[1][i] = 0;
+  if (a.vec4) {
+    const int n4 = cnt >> 2;
+    for (int i4 = tid; i4 < n4; i4 += TK_THREADS) {
+      float4 v = __ldcg(reinterpret_cast<const float4*>(sc) + i4);
+      for (int p = 1; p < a.n_planes; ++p) {
+        const float4 w = __ldcg(reinterpret_cast<const float4*>(sc + (size_t)p * a.plane_stride) + i4);
+        v.x = (w.x > v.x || w.x != w.x) ? w.x : v.x;  // NaN wins, as in torch.topk
+        v.y = (w.y > v.y || w.y != w.y) ? w.y : v.y;
+        v.z = (w.z > v.z || w.z != w.z) ? w.z : v.z;
+        v.w = (w.w > v.w || w.w != w.w) ? w.w : v.w;
+      }
+      const uint4 key = make_uint4(float_to_key(v.x), float_to_key(v.y), float_to_key(v.z), float_to_key(v.w));
+      if (RESIDENT) reinterpret_cast<uint4*>(skeys)[i4] = key; else reinterpret_cast<uint4*>(gk)[i4] = key;
+    }
+  }
+  for (int i = (a.vec4 ? (cnt & ~3) : 0) + tid; i < cnt; i += TK_THREADS) {
     float v = sc[i];
     for (int p = 1; p < a.n_planes; ++p) {
       const float w = sc[(size_t)p * a.plane_stride + i];
-      v = (w > v || w != w) ? w : v;  // NaN wins, as in torch.topk
+      v = (w > v || w != w) ? w : v;
     }
     const unsigned key = float_to_key(v);
     if (RESIDENT) skeys[i] = key; else gk[i] = key;
   }
-  if (tid == 0) {
-    sh.cnt_gt = 0;
-    sh.cnt_eq = 0;
-  }
-  __syncthreads();
+  cluster.sync();  // every CTA's totals are zeroed before anyone adds to them
 
   // ---- radix select --------------------------------------------------------------------------
+  // Each pass: local histogram of the digit (shared-memory atomics, aggregated per warp), pushed into EVERY
+  // CTA's cluster-wide histogram with remote atomics, one cluster barrier, then every CTA scans its own copy.
   unsigned prefix = 0, mask = 0;
   unsigned remaining = (unsigned)kk;
   if (kk > 0) {
     for (int pass = 0; pass < 4; ++pass) {
       const int shift = 24 - 8 * pass;
-      unsigned* hist = sh.hist[pass & 1];
-      for (int i = tid; i < 256; i += TK_THREADS) hist[i] = 0;
+      unsigned* tot = sh.total[pass & 1];
+      for (int i = tid; i < 256; i += TK_THREADS) {
+        sh.hist[i] = 0;
+        sh.total[(pass + 1) & 1][i] = 0;  // the next pass's buffer: nobody adds to it before the barrier below
+      }
       __syncthreads();
       for (int i0 = 0; i0 < cnt; i0 += TK_THREADS) {
         const int i = i0 + tid;
@@ -103,19 +122,16 @@ __global__ void __launch_bounds__(TK_THREADS, 1) topk_kernel(const TopkArgs a) {
         const unsigned actmask = __ballot_sync(0xffffffffu, act);
         if (act) {
           const unsigned peers = __match_any_sync(actmask, bin);
-          if ((unsigned)lane == (unsigned)(__ffs(peers) - 1)) atomicAdd(&hist[bin], (unsigned)__popc(peers));
+          if ((unsigned)lane == (unsigned)(__ffs(peers) - 1)) atomicAdd(&sh.hist[bin], (unsigned)__popc(peers));
         }
-      }
-      cluster.sync();  // every CTA's histogram of this pass is complete
-      for (int i = tid; i < 256; i += TK_THREADS) {
-        unsigned s = 0;
-        for (int r = 0; r < csize; ++r) {
-          const unsigned* rh = cluster.map_shared_rank(hist, r);
-          s += rh[i];
-        }
-        sh.total[i] = s;
       }
       __syncthreads();
+      for (int i = tid; i < 256 * csize; i += TK_THREADS) {
+        const int bin = i & 255, r = i >> 8;
+        const unsigned v = sh.hist[bin];
+        if (v) atomicAdd(cluster.map_shared_rank(&tot[bin], r), v);
+      }
+      cluster.sync();
       if (warp == 0) {
         // find the digit d with count(bins > d) < remaining <= count(bins >= d); 8 bins per lane,
         // lane 0 holds the highest bins
@@ -123,7 +139,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1) topk_kernel(const TopkArgs a) {
         unsigned mine = 0;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          c[j] = sh.total[255 - (lane * 8 + j)];
+          c[j] = tot[255 - (lane * 8 + j)];
           mine += c[j];
         }
         unsigned incl = mine;  // inclusive scan over lanes
@@ -149,8 +165,6 @@ __global__ void __launch_bounds__(TK_THREADS, 1) topk_kernel(const TopkArgs a) {
       prefix |= sh.sel_digit << shift;
       mask |= 255u << shift;
       remaining = sh.sel_remaining;
-      // the next pass uses the other histogram buffer; this one is only re-zeroed two passes
-      // later, after another cluster.sync, so peers may still be reading it now
     }
   }
   const unsigned T = prefix;  // key of the k-th largest score; `remaining` ties of it are taken
@@ -178,21 +192,22 @@ __global__ void __launch_bounds__(TK_THREADS, 1) topk_kernel(const TopkArgs a) {
     sh.warp_eq[warp] = my_eq;
   }
   __syncthreads();
-  if (tid == 0) {
+  if (tid < csize) {  // thread r pushes this CTA's counts into CTA r's table
     unsigned g = 0, e = 0;
     for (int w = 0; w < TK_WARPS; ++w) {
       g += sh.warp_gt[w];
       e += sh.warp_eq[w];
     }
-    sh.cnt_gt = g;
-    sh.cnt_eq = e;
+    unsigned* dst = cluster.map_shared_rank(&sh.cnt_all[crank][0], tid);
+    dst[0] = g;
+    dst[1] = e;
   }
-  cluster.sync();  // counts of every CTA are visible
+  cluster.sync();  // counts of every CTA have arrived in this CTA's table
   // positions selected / ties seen before this CTA, then before this warp
   unsigned eq_before = 0, sel_before = 0;
   for (int r = 0; r < crank; ++r) {
-    const unsigned rg = *cluster.map_shared_rank(&sh.cnt_gt, r);
-    const unsigned re = *cluster.map_shared_rank(&sh.cnt_eq, r);
+    const unsigned rg = sh.cnt_all[r][0];
+    const unsigned re = sh.cnt_all[r][1];
     const unsigned take = (remaining > eq_before) ? min(re, remaining - eq_before) : 0u;
     sel_before += rg + take;
     eq_before += re;
@@ -251,6 +266,9 @@ extern "C" int omnikv_topk(const float* scores, int n_planes, int64_t plane_stri
   a.scores = scores; a.n_planes = n_planes; a.plane_stride = plane_stride; a.batch_stride = batch_stride;
   a.len = len; a.k = k; a.append_n = append_n; a.idx_out = idx_out; a.idx_stride = idx_stride;
   a.count_out = count_out; a.gkeys = static_cast<unsigned*>(workspace); a.max_len = max_len;
+  a.vec4 = ((reinterpret_cast<uintptr_t>(scores) & 15) == 0 && batch_stride % 4 == 0 &&
+            (n_planes == 1 || plane_stride % 4 == 0) && (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15) == 0) &&
+            max_len % 4 == 0) ? 1 : 0;
 
   int csize = 1;
   while (csize < TK_MAX_CLUSTER && ceil_div(max_len, csize) > 8192) csize *= 2;

@@ -155,8 +155,7 @@ class OmniKVMultiStageCache:
             self._k[layer_idx] = torch.zeros(B, KVH, self.reserve, d, dtype=dtype, device=device)
             self._v[layer_idx] = torch.zeros(B, KVH, self.reserve, d, dtype=dtype, device=device)
         else:
-            self._k[layer_idx] = torch.zeros(B, KVH, P + self.reserve, d, dtype=dtype, device=device)
-            self._v[layer_idx] = torch.zeros(B, KVH, P + self.reserve, d, dtype=dtype, device=device)
+            self._k[layer_idx], self._v[layer_idx] = self._alloc_kv(layer_idx, B, KVH, P + self.reserve, d, dtype, device)
         while len(self.key_cache) <= layer_idx:
             self.key_cache.append(None)
             self.value_cache.append(None)
@@ -167,6 +166,22 @@ class OmniKVMultiStageCache:
         else:
             self.key_cache[layer_idx] = self._k[layer_idx]
             self.value_cache[layer_idx] = self._v[layer_idx]
+
+    def _alloc_kv(self, layer_idx, B, KVH, cap, d, dtype, device):
+        """K and V of a layer in ONE buffer, as ``[B, KVH, cap, d]`` views (rows stay 16-byte aligned and
+        contiguous; the kernels take the strides).  The physical order follows how the layer reads it:
+
+        * dense layers stream whole heads: ``[B, KVH, cap, K|V, d]`` -- a head's K and V rows interleaved, so a
+          tile of 64 tokens is one contiguous 32 KB block;
+        * sparse layers gather a few thousand scattered tokens: ``[B, cap, KVH, K|V, d]`` -- token-major, so all
+          the K and V rows of a selected token (4 KB for 8 KV heads) sit together and a gather touches one DRAM
+          page per token instead of sixteen (random 256-byte reads reach under half of the HBM bandwidth).
+        """
+        if self.is_sparse(layer_idx):
+            kv = torch.zeros(B, cap, KVH, 2, d, dtype=dtype, device=device)
+            return kv[:, :, :, 0, :].permute(0, 2, 1, 3), kv[:, :, :, 1, :].permute(0, 2, 1, 3)
+        kv = torch.zeros(B, KVH, cap, 2, d, dtype=dtype, device=device)
+        return kv[:, :, :, 0, :], kv[:, :, :, 1, :]
 
     def init_synthetic(self, B: int, KVH: int, d: int, prefill_lens: Sequence[int], dtype, device, seed: int = 0,
                        reserve: Optional[int] = None) -> "OmniKVMultiStageCache":

@@ -96,16 +96,20 @@ def main():
 
     if args.case == "gemv":
         return gemv_cases(args.reps)
-    if args.case in ("dense_attn", "sparse_attn", "score_window"):
-        kc, q = rnd(B, KVH, L + 64, d), rnd(B, H, d)
+    # K and V share one buffer as in the package's cache: head-major with K|V rows interleaved for a dense layer,
+    # token-major for a sparse layer
+    if args.case in ("dense_attn", "score_window"):
+        kv = rnd(B, KVH, L + 64, 2, d)
+        kc, vc, q = kv[:, :, :, 0, :], kv[:, :, :, 1, :], rnd(B, H, d)
+    if args.case == "sparse_attn":
+        kv = rnd(B, L + 64, KVH, 2, d)
+        kc, vc, q = kv[:, :, :, 0, :].permute(0, 2, 1, 3), kv[:, :, :, 1, :].permute(0, 2, 1, 3), rnd(B, H, d)
     if args.case == "dense_attn":
-        vc = rnd(B, KVH, L + 64, d)
         planes = torch.empty(KVH, B, L, dtype=torch.float32, device=dev)
         n_all, n_p = i32([L + 1]), i32([L])
         fn = lambda: ops.decode_attn(q, kc, vc, n_all, score_out=planes, score_len=n_p, n_splits=args.splits or None)  # noqa: E731
         nbytes = 2 * KVH * d * 2 * (L + 1)
     elif args.case == "sparse_attn":
-        vc = rnd(B, KVH, L + 64, d)
         idx = torch.sort(torch.randperm(L, generator=g, device=dev)[:k_sel]).values.to(torch.int32)[None].contiguous()
         cnt, n_p, one = i32([k_sel]), i32([L]), i32([1])
         fn = lambda: ops.decode_attn(q, kc, vc, cnt, idx=idx, k_tail=kc, v_tail=vc, tail_start=n_p, tail_len=one,  # noqa: E731
