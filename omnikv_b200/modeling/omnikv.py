@@ -833,6 +833,7 @@ class DecodeRunner:
 
     def run(self, n_steps: int) -> None:
         n_steps = max(0, min(n_steps, self.max_new_tokens - 1 - self.steps_done))
+        self.cache.check_room(n_steps)
         for _ in range(n_steps):
             if self.graph is not None:
                 self.graph.replay()

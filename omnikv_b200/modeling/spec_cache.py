@@ -252,11 +252,19 @@ class OmniKVMultiStageCache:
         """Advance the device-side counters by one token (graph-capturable).  Called once per decode
         step before layer 0 appends (the reference bumps ``_seen_tokens`` at layer 0, :315-316):
         ``update`` does it for layer 0; callers of ``append_kv`` do it themselves."""
+        self.check_room(1)
         self.cur_len_dev.add_(1)
         self.tail_len_dev.add_(1)
         self.pos_dev.add_(1)
         self.tail_pos_dev.add_(1)
         self._seen_tokens += 1
+
+    def check_room(self, n_tokens: int) -> None:
+        """Raise before a decode step would write past the preallocated rows (``reserve`` behind the prompt)."""
+        if self.prefill_len is not None and self._seen_tokens + n_tokens > self.prefill_len + self.reserve:
+            raise RuntimeError(
+                f"KV cache is full: {self._seen_tokens} tokens held, room for {self.prefill_len + self.reserve}; "
+                "set cache.reserve (rows kept free behind the prompt) before the prefill")
 
     def append_kv(self, k_new: torch.Tensor, v_new: torch.Tensor, layer_idx: int) -> None:
         """Write the current token's rows ``[B, KVH, d]`` in place (``omnikv_kv_append``)."""

@@ -105,3 +105,12 @@ def test_product_package_does_not_import_the_oracle():
     for f in (ROOT / "omnikv_b200").rglob("*.py"):
         text = f.read_text()
         assert "import oracle" not in text and "from oracle" not in text, f
+
+
+def test_cache_refuses_to_overflow_its_reserve():
+    from omnikv_b200.modeling import OmniKVMultiStageCache
+    c = OmniKVMultiStageCache([0, 2], 2, 0, False)
+    c.prefill_len, c.reserve, c._seen_tokens = 100, 4, 103
+    c.check_room(1)
+    with pytest.raises(RuntimeError, match="KV cache is full"):
+        c.check_room(2)

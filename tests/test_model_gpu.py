@@ -6,6 +6,7 @@ oracle's (positions may differ only inside a 1e-4 band around the k-th score).
 """
 import json
 from pathlib import Path
+from types import SimpleNamespace
 
 import numpy as np
 import pytest
@@ -221,3 +222,40 @@ def test_selector_function_matches_reference_fixture():
         want = gold[key].astype(np.int64)
         diff = set(idx[0].tolist()) ^ set(want[0].tolist())
         assert len(diff) <= 2, (sel, len(diff))
+
+
+def test_chat_api_factory_with_a_checkpoint_on_disk(tmp_path):
+    """``get_any_chat_api`` end to end: a tiny random Llama saved as a Hugging Face checkpoint (config.json +
+    safetensors), the experiment JSON with the reference's keys, a stand-in tokenizer."""
+    from safetensors.torch import save_file
+
+    from omnikv_b200.infer import get_any_chat_api
+    cfg = small_config()
+    lm, _ = build(cfg, torch.float16)
+    ckpt = tmp_path / "tiny-llama"
+    ckpt.mkdir()
+    arch = {k: getattr(cfg, k) for k in ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers",
+                                          "num_attention_heads", "num_key_value_heads", "rms_norm_eps", "rope_theta",
+                                          "head_dim", "eos_token_id", "bos_token_id")}
+    (ckpt / "config.json").write_text(json.dumps(arch))
+    save_file({k: v.detach().clone().contiguous().cpu() for k, v in lm.hf_state_dict().items()}, str(ckpt / "model.safetensors"))
+    exp = json.loads((G / "example_config.json").read_text())
+    exp.update(model_name=str(ckpt), do_select_layers="1,3", num_of_selected_tokens=0.25, max_context_len=4096)
+    (tmp_path / "exp.json").write_text(json.dumps(exp))
+
+    class Tok:
+        def __call__(self, prompt, return_tensors="pt"):
+            return {"input_ids": torch.tensor([[ord(c) % 1000 for c in prompt]])}
+
+        def batch_decode(self, rows, **kw):
+            return [" ".join(str(t) for t in r) for r in rows]
+
+    chat, tok, max_len, extra = get_any_chat_api(str(tmp_path / "exp.json"), tokenizer=Tok())
+    assert max_len == 4096 and "eos_token_id" in extra
+    prompt = "a long prompt " * 30
+    text = chat(prompt, max_new_tokens=12)
+    ids = Tok()(prompt)["input_ids"].cuda()
+    want = lm.generate_greedy(ids, 12, use_cuda_graph=False)[0].tolist()
+    assert text == " ".join(str(t) for t in want)
+    sampled = chat(prompt, generation_config=SimpleNamespace(do_sample=True, temperature=0.7, top_p=0.9, max_new_tokens=5))
+    assert 1 <= len(sampled.split()) <= 5
