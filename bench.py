@@ -155,13 +155,15 @@ def run_reference_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctx", type=int, default=CTX, help="prompt length (the benchmark's is 131072)")
     ap.add_argument("--layers", type=int, default=32, help="decoder layers (the benchmark's is 32)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--real-prefill", action="store_true", help="prefill a prompt of uniform-random token ids through the "
+                    "model (PyTorch SDPA) instead of filling the KV cache with seeded values; single GPU")
     ap.add_argument("--chain", action="store_true", help="run the weight-streaming phases between two attention calls "
                     "as one cooperative multi-phase launch instead of one launch per phase (measured slower so far)")
     ap.add_argument("--nccl-allreduce", action="store_true", help="multi-GPU: NCCL all-reduce after the row-parallel "
@@ -195,9 +197,23 @@ def main():
     graph_warm = 2
     reserve = graph_warm + 2 * (warmup + args.steps) + 16
     kvh_local = cfg.num_key_value_heads // (world if tp else 1)
-    cache = lm.new_cache().init_synthetic(1, kvh_local, cfg.head_dim, [args.ctx], torch.bfloat16, dev,
-                                          seed=1 + rank, reserve=reserve)
-    first = torch.tensor([[1]], device=dev)
+    prefill_s = None
+    if args.real_prefill and tp is None:
+        cache = lm.new_cache()
+        cache.reserve = reserve
+        gen = torch.Generator(device=dev).manual_seed(3)
+        ids = torch.randint(0, cfg.vocab_size, (1, args.ctx), generator=gen, device=dev)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = lm(input_ids=ids, past_key_values=cache)
+        torch.cuda.synchronize()
+        prefill_s = time.perf_counter() - t0
+        first = out.logits[:, -1].argmax(-1, keepdim=True)
+        del out, ids
+    else:
+        cache = lm.new_cache().init_synthetic(1, kvh_local, cfg.head_dim, [args.ctx], torch.bfloat16, dev,
+                                              seed=1 + rank, reserve=reserve)
+        first = torch.tensor([[1]], device=dev)
     total = graph_warm + 2 * (warmup + args.steps) + 2
     runner = DecodeRunner(lm, None, cache=cache, first_token=first, max_new_tokens=total,
                           use_cuda_graph=not args.no_graph, warmup_steps=graph_warm)
@@ -319,7 +335,9 @@ def main():
                    "parallelism": (f"kv-head tp{world}, " + ("fused peer-memory all-reduce" if tp.exchange is not None
                                                                     else "nccl all-reduce")) if world > 1 else "single gpu",
                    "l2": "inputs larger than L2 (about 20 GB of KV and weights are read per step)",
-                   "cuda_graph": not args.no_graph, "kv_fill": "seeded N(0,1), no prefill run"},
+                   "cuda_graph": not args.no_graph,
+                   "kv_fill": (f"real prefill of {args.ctx} uniform-random token ids ({prefill_s:.1f} s)" if prefill_s
+                               else "seeded N(0,1), no prefill run")},
         "clocks": clocks,
         "e2e": {"value": args.steps / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 8,
                 "d2h_bytes_per_step": 8 + cfg.vocab_size * 4, "ms_per_step": ms_e2e / args.steps},

@@ -7,9 +7,9 @@
 // heads, so K is streamed twice:
 //   pass 1  grid (splits, KVH, B): per-row online (max, sum-exp) of the CTA's chunk of keys;
 //           a small kernel merges the splits into (m, 1/l) per row;
-//   pass 2  grid (chunks, B): every CTA walks its chunk of key positions for ALL KV heads
-//           (queries of all heads stay in shared memory), so the max over heads is finished in
-//           registers and each score is written once -- no atomics, deterministic.
+//   pass 2  grid (chunks of 512 positions, B): every CTA walks its chunk of key positions for ALL KV heads,
+//           one head after the other, keeping the running max over heads in shared memory, so each score
+//           is written once -- no atomics, deterministic.
 // The [G x 16 window slots] x 128 query block of one KV head against a tile of keys is a dense
 // contraction: bf16/fp16 run it on m16n8k16 tensor-core MMAs with the K tile staged by cp.async;
 // fp32 uses CUDA cores.  Query rows are laid out head-major with the window padded to 16 slots,
@@ -26,7 +26,7 @@ constexpr int PITCH = 272;
 constexpr int TILE_BYTES = TILE * PITCH;
 constexpr int WPAD = 16;  // window slots per head after padding
 constexpr int P1_STAGES = 3;
-constexpr int P2_STAGES = 4;
+constexpr int P2_STAGES = 3;
 
 struct WinArgs {
   const void* qw;
@@ -212,24 +212,34 @@ __device__ __forceinline__ float slot_weight(int selector, int W, int w) {
 }
 
 // ---- pass 2: normalise, max over heads, weighted window sum -----------------------------------
+// grid (ceil(max_len / P2_CHUNK), B).  A CTA owns P2_CHUNK key positions and walks the KV heads one after the
+// other: it loads the head's query group (and its softmax statistics), streams the head's K rows of the chunk,
+// and keeps the running max over heads of every (position, window slot) weight in shared memory -- each thread
+// always owns the same entries, so there is no atomic and no barrier around them.  After the last head the
+// weighted window sum is written once.  Shared memory per CTA is ~111 KB (G = 4): two CTAs per SM.
+constexpr int P2_CHUNK = 512;
+constexpr int HM_PITCH = 20;  // floats per position: 16 slots + pad; conflict-free for the fragment layout
+
 template <typename T, int G>
-__global__ void __launch_bounds__(NTHREADS, 1) window_pass2_mma(const WinArgs a) {
+__global__ void __launch_bounds__(NTHREADS, 2) window_pass2_mma(const WinArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* q_s = smem + P2_STAGES * TILE_BYTES;                    // [H*16][PITCH]
-  float* st_s = reinterpret_cast<float*>(q_s + (size_t)a.H * WPAD * PITCH);  // [H*16][2]
+  unsigned char* q_s = smem + P2_STAGES * TILE_BYTES;                             // [G*16][PITCH]
+  float* hm_s = reinterpret_cast<float*>(q_s + (size_t)G * WPAD * PITCH);         // [P2_CHUNK][HM_PITCH]
+  float* st_s = hm_s + P2_CHUNK * HM_PITCH;                                       // [G*16][2]
   const int b = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int n = a.consider_len[b];
-  const int r0 = blockIdx.x * a.chunk2;
-  const int r1 = min(n, r0 + a.chunk2);
+  const int r0 = blockIdx.x * P2_CHUNK;
+  const int r1 = min(n, r0 + P2_CHUNK);
   if (r0 >= r1) return;
   const int ntiles = ceil_div(r1 - r0, TILE);
   const int KVH = a.KVH;
-  const int nsteps = ntiles * KVH;  // step s: tile s / KVH, kv head s % KVH
+  const int nsteps = ntiles * KVH;  // step s: kv head s / ntiles, tile s % ntiles
   const T* kb = static_cast<const T*>(a.k) + (size_t)b * a.k_sb;
+  const T* qb = static_cast<const T*>(a.qw) + (size_t)b * a.H * a.W * kHeadDim;
 
   auto issue = [&](int s) {
-    const int tile = s / KVH, kvh = s % KVH;
+    const int kvh = s / ntiles, tile = s % ntiles;
     issue_k_tile<T>(smem + (s % P2_STAGES) * TILE_BYTES, kb + (size_t)kvh * a.k_sh, a.k_sr, r0 + tile * TILE, r1, tid);
   };
 #pragma unroll
@@ -237,14 +247,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) window_pass2_mma(const WinArgs a)
     if (s < nsteps) issue(s);
     cp_async_commit();
   }
-  load_q<T>(q_s, static_cast<const T*>(a.qw) + (size_t)b * a.H * a.W * kHeadDim, 0, a.H, a.W, tid);
-  for (int i = tid; i < a.H * WPAD * 2; i += NTHREADS) st_s[i] = a.stats[(size_t)b * a.H * WPAD * 2 + i];
   const float wt0 = slot_weight(a.selector, a.W, g), wt1 = slot_weight(a.selector, a.W, g + 8);
-  __syncthreads();
 
-  float hm[2][4];
   for (int s = 0; s < nsteps; ++s) {
-    const int tile = s / KVH, kvh = s % KVH;
+    const int kvh = s / ntiles, tile = s % ntiles;
+    if (tile == 0) {  // next KV head: its queries and softmax statistics
+      __syncthreads();  // every warp is done with the previous head's queries
+      load_q<T>(q_s, qb, kvh * G, G, a.W, tid);
+      for (int i = tid; i < G * WPAD * 2; i += NTHREADS)
+        st_s[i] = a.stats[((size_t)b * a.H + kvh * G) * WPAD * 2 + i];
+    }
     cp_async_wait<P2_STAGES - 2>();
     __syncthreads();
     {
@@ -252,27 +264,35 @@ __global__ void __launch_bounds__(NTHREADS, 1) window_pass2_mma(const WinArgs a)
       if (ns < nsteps) issue(ns);
       cp_async_commit();
     }
-    if (kvh == 0) {
-#pragma unroll
-      for (int j = 0; j < 2; ++j) hm[j][0] = hm[j][1] = hm[j][2] = hm[j][3] = 0.f;
-    }
     float acc[G][2][4];
-    qk_tile<T, G>(acc, q_s + (size_t)kvh * G * WPAD * PITCH, smem + (s % P2_STAGES) * TILE_BYTES, warp, lane);
+    qk_tile<T, G>(acc, q_s, smem + (s % P2_STAGES) * TILE_BYTES, warp, lane);
     const int cbase = r0 + tile * TILE + warp * 16 + 2 * t;
+    float hm[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) hm[j][0] = hm[j][1] = hm[j][2] = hm[j][3] = 0.f;
 #pragma unroll
     for (int i = 0; i < G; ++i)
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const float* st = st_s + ((kvh * G + i) * WPAD + g + 8 * h) * 2;
+        const float* st = st_s + (i * WPAD + g + 8 * h) * 2;
         const float ml2 = st[0] * kLog2e, inv_l = st[1];
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int R = cbase + 8 * j + e;
-            const float p = (R < r1) ? exp2f(fmaf(acc[i][j][2 * h + e] * a.scale, kLog2e, -ml2)) * inv_l : 0.f;
-            hm[j][2 * h + e] = fmaxf(hm[j][2 * h + e], p);
+            const float pw = (R < r1) ? exp2f(fmaf(acc[i][j][2 * h + e] * a.scale, kLog2e, -ml2)) * inv_l : 0.f;
+            hm[j][2 * h + e] = fmaxf(hm[j][2 * h + e], pw);
           }
+      }
+    // running max over KV heads of this thread's (position, slot) entries
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float* cell = hm_s + (tile * TILE + warp * 16 + 8 * j + 2 * t + (e & 1)) * HM_PITCH + g + 8 * (e >> 1);
+        if (kvh > 0) hm[j][e] = fmaxf(hm[j][e], *cell);
+        if (kvh < KVH - 1) *cell = hm[j][e];
       }
     if (kvh == KVH - 1) {
       if (a.planes_out) {
@@ -423,10 +443,11 @@ __global__ void __launch_bounds__(NTHREADS) window_pass2_f32(const WinArgs a) {
 }
 
 template <typename T, int G>
-int launch_mma(const WinArgs& a, int n_chunks2, cudaStream_t st) {
+int launch_mma(const WinArgs& a, int n_chunks2, int max_len, cudaStream_t st) {
   const int smem1 = P1_STAGES * TILE_BYTES + G * WPAD * PITCH;
-  const int smem2 = P2_STAGES * TILE_BYTES + a.H * WPAD * PITCH + a.H * WPAD * 2 * (int)sizeof(float);
-  if (smem2 > 227 * 1024) return OMNIKV_E_UNSUPPORTED;
+  const int smem2 = P2_STAGES * TILE_BYTES + G * WPAD * PITCH + P2_CHUNK * HM_PITCH * (int)sizeof(float) +
+                    G * WPAD * 2 * (int)sizeof(float);
+  (void)n_chunks2;
   OMNIKV_CUDA_OK(cudaFuncSetAttribute(window_pass1_mma<T, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1));
   OMNIKV_CUDA_OK(cudaFuncSetAttribute(window_pass2_mma<T, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
   window_pass1_mma<T, G><<<dim3(a.S, a.KVH, a.B), NTHREADS, smem1, st>>>(a);
@@ -434,18 +455,18 @@ int launch_mma(const WinArgs& a, int n_chunks2, cudaStream_t st) {
   const int rows = a.B * a.H * WPAD;
   window_stats_merge<<<ceil_div(rows, 128), 128, 0, st>>>(a.part, a.stats, rows, a.S);
   OMNIKV_CUDA_OK(cudaGetLastError());
-  window_pass2_mma<T, G><<<dim3(n_chunks2, a.B), NTHREADS, smem2, st>>>(a);
+  window_pass2_mma<T, G><<<dim3(ceil_div(max_len, P2_CHUNK), a.B), NTHREADS, smem2, st>>>(a);
   OMNIKV_CUDA_OK(cudaGetLastError());
   return OMNIKV_OK;
 }
 
 template <typename T>
-int dispatch_mma(const WinArgs& a, int n_chunks2, cudaStream_t st) {
+int dispatch_mma(const WinArgs& a, int n_chunks2, int max_len, cudaStream_t st) {
   switch (a.G) {
-    case 1: return launch_mma<T, 1>(a, n_chunks2, st);
-    case 2: return launch_mma<T, 2>(a, n_chunks2, st);
-    case 4: return launch_mma<T, 4>(a, n_chunks2, st);
-    case 8: return launch_mma<T, 8>(a, n_chunks2, st);
+    case 1: return launch_mma<T, 1>(a, n_chunks2, max_len, st);
+    case 2: return launch_mma<T, 2>(a, n_chunks2, max_len, st);
+    case 4: return launch_mma<T, 4>(a, n_chunks2, max_len, st);
+    case 8: return launch_mma<T, 8>(a, n_chunks2, max_len, st);
     default: return OMNIKV_E_UNSUPPORTED;
   }
 }
@@ -507,8 +528,8 @@ extern "C" int omnikv_score_window(const omnikv_window_params* p, void* stream) 
   const int n_chunks2 = ceil_div(p->max_len, a.chunk2);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (p->dtype) {
-    case OMNIKV_BF16: return dispatch_mma<__nv_bfloat16>(a, n_chunks2, st);
-    case OMNIKV_F16: return dispatch_mma<__half>(a, n_chunks2, st);
+    case OMNIKV_BF16: return dispatch_mma<__nv_bfloat16>(a, n_chunks2, p->max_len, st);
+    case OMNIKV_F16: return dispatch_mma<__half>(a, n_chunks2, p->max_len, st);
     case OMNIKV_F32: return launch_f32(a, p->max_len, st);
     default: return OMNIKV_E_UNSUPPORTED;
   }
