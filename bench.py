@@ -5,9 +5,9 @@
 
 One "step" is one greedy decode step (one token per sequence) through all 32 layers: 8 dense layers
 (3 of them filter layers that emit selection scores and run the top-k), 24 sparse layers reading the
-selected 8781 prompt rows + the decode-time tail.  The prompt KV (131072 tokens) is filled with seeded
-N(0,1) values instead of running a 128K prefill (the decode step's work does not depend on the values);
-weights are seeded N(0, 0.02) bf16.  Prints ONE JSON line (rank 0).
+selected 8781 prompt rows + the decode-time tail.  The prompt is 131072 uniform-random token ids, prefilled
+through the model before the timed region (PyTorch SDPA; --synthetic-kv fills the cache with seeded N(0,1)
+values instead); weights are seeded N(0, 0.02) bf16.  Prints ONE JSON line (rank 0).
 """
 from __future__ import annotations
 
@@ -162,8 +162,8 @@ def main():
     ap.add_argument("--layers", type=int, default=32, help="decoder layers (the benchmark's is 32)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--real-prefill", action="store_true", help="prefill a prompt of uniform-random token ids through the "
-                    "model (PyTorch SDPA) instead of filling the KV cache with seeded values; single GPU")
+    ap.add_argument("--synthetic-kv", action="store_true", help="fill the prompt KV with seeded N(0,1) values instead of "
+                    "prefilling a prompt of uniform-random token ids through the model (about 7 s at 128K on one GPU)")
     ap.add_argument("--chain", action="store_true", help="run the weight-streaming phases between two attention calls "
                     "as one cooperative multi-phase launch instead of one launch per phase (measured slower so far)")
     ap.add_argument("--nccl-allreduce", action="store_true", help="multi-GPU: NCCL all-reduce after the row-parallel "
@@ -198,10 +198,10 @@ def main():
     reserve = graph_warm + 2 * (warmup + args.steps) + 16
     kvh_local = cfg.num_key_value_heads // (world if tp else 1)
     prefill_s = None
-    if args.real_prefill and tp is None:
+    if not args.synthetic_kv:
         cache = lm.new_cache()
         cache.reserve = reserve
-        gen = torch.Generator(device=dev).manual_seed(3)
+        gen = torch.Generator(device=dev).manual_seed(3)  # the same prompt on every rank
         ids = torch.randint(0, cfg.vocab_size, (1, args.ctx), generator=gen, device=dev)
         torch.cuda.synchronize()
         t0 = time.perf_counter()
