@@ -126,6 +126,25 @@ def cpu_baseline_sample(threads: int, seed: int = 0):
     return step, t
 
 
+_REAL_STDOUT = None
+
+
+def quiet_stdout():
+    """Everything libraries print on stdout (NCCL's version banner, for one) goes to stderr from here on; the one
+    JSON line is written to the real stdout by emit()."""
+    global _REAL_STDOUT
+    if _REAL_STDOUT is None:
+        sys.stdout.flush()
+        _REAL_STDOUT = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    out = _REAL_STDOUT or sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
+
+
 def run_reference_arm(args):
     """The reference's CPU-runnable path (oracle port) with every host thread, as its own bench arm."""
     rank = int(os.environ.get("RANK", "0"))
@@ -146,7 +165,7 @@ def run_reference_arm(args):
         "cpu_baseline": {"value": 1.0 / step, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": 1.0 / step, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -172,6 +191,7 @@ def main():
                     help="after the warm-up, run ONE step between cudaProfilerStart/Stop and exit (for ncu "
                          "--profile-from-start off); prints no benchmark line")
     args = ap.parse_args()
+    quiet_stdout()
     if args.impl == "reference":
         return run_reference_arm(args)
 
@@ -353,7 +373,7 @@ def main():
             "sample": "one filter layer, one sparse layer, one layer of weight GEMVs and the lm_head timed once each at "
                       "full size, scaled by the step's layer counts (8 dense / 3 filter / 24 sparse / 32)",
             "parts_s": parts}
-    print(json.dumps(line), flush=True)
+    emit(line)
     finish()
 
 
