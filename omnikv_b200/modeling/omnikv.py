@@ -635,6 +635,20 @@ class OmniKVMulLM(nn.Module):
             sd[p + "post_attention_layernorm.weight"] = layer.post_attention_layernorm.weight
         return sd
 
+    @torch.no_grad()
+    def prepare_synthetic_decode(self, batch: int, seed: int = 0) -> None:
+        """Throughput runs that fill the KV cache directly (no prefill): give every filter layer the state a prefill
+        would have left -- for the window selectors a seeded observation window of normalised hidden states -- so
+        that decoding can start."""
+        dev, dt = self.lm_head.weight.device, self.lm_head.weight.dtype
+        g = torch.Generator(device=dev).manual_seed(seed)
+        for layer in self.model.layers:
+            layer.decode_step = 0
+            if layer.is_filter and "last" not in layer.selector_cls:
+                layer.hidden_state_window = torch.randn(batch, layer.window_size, self.config.hidden_size, generator=g,
+                                                        device=dev, dtype=torch.float32).to(dt)
+                layer.decode_step = 1
+
     # -- cache -----------------------------------------------------------------------------------
     def new_cache(self, past_key_values=None):
         """The cache wrap of modeling/omnikv.py:315-341."""

@@ -1,0 +1,86 @@
+"""Run the batched (window selector) and the offload decode workloads on one GPU with synthetic inputs:
+
+    python -m omnikv_b200.run_config batch16   [--steps 64]     # batch 16, contexts U[16384, 32768], selector exp, k = 2048
+    python -m omnikv_b200.run_config offload   [--steps 32]     # batch 1, context 450000, real_offload (pinned host KV)
+
+Random-init Llama-3-8B (bf16), KV cache filled with seeded N(0,1) rows, greedy decoding captured in a CUDA graph.
+Prints one JSON line with tokens/s, ms/step and the algorithmic bytes moved per step (HBM, and host link for
+the offload run).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import time
+
+import torch
+
+from . import ops
+from .modeling import LlamaCompressorConfig, OmniKVMulLM
+from .modeling.omnikv import DecodeRunner
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("workload", choices=["batch16", "offload"])
+    ap.add_argument("--steps", type=int, default=0)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--ctx", type=int, default=0, help="override the context length (offload: 450000)")
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = LlamaCompressorConfig(num_hidden_layers=args.layers)
+    base = dict(model_cls="multi", cache_cls="multi", do_select_layers="2,8,18", num_wait_load_layers=1, dense_more=True,
+                window_size=16)
+    g = torch.Generator().manual_seed(0)
+    if args.workload == "batch16":
+        steps = args.steps or 64
+        B = 16
+        lens = torch.randint(16384, 32769, (B,), generator=g).tolist()
+        cfg.set_config_of_compressor(**base, real_offload=False, selector_cls="exp", num_of_selected_tokens=2048)
+    else:
+        steps = args.steps or 32
+        B, lens = 1, [args.ctx or 450000]
+        cfg.set_config_of_compressor(**base, real_offload=True, selector_cls="last", num_of_selected_tokens=0.067)
+    lm = OmniKVMulLM.from_config(cfg, dtype=torch.bfloat16, device=dev, seed=0)
+    total = 2 + args.warmup + steps + 2
+    t0 = time.perf_counter()
+    cache = lm.new_cache().init_synthetic(B, cfg.num_key_value_heads, cfg.head_dim, lens, torch.bfloat16, dev, seed=1,
+                                          reserve=total + 16)
+    torch.cuda.synchronize()
+    fill_s = time.perf_counter() - t0
+    lm.prepare_synthetic_decode(B, seed=2)
+    first = torch.ones(B, 1, dtype=torch.int64, device=dev)
+    runner = DecodeRunner(lm, None, cache=cache, first_token=first, max_new_tokens=total,
+                          use_cuda_graph=not args.no_graph, warmup_steps=2)
+    runner.run(args.warmup)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    runner.run(steps)
+    e1.record()
+    torch.cuda.synchronize()
+    ops.check_status(dev)
+    ms = e0.elapsed_time(e1) / steps
+    # algorithmic bytes per step
+    dense = [i for i, s in cache.layer_state.items() if not s[0]]
+    n_sparse = cfg.num_hidden_layers - len(dense)
+    row = cfg.num_key_value_heads * cfg.head_dim * 2 * 2  # K + V bytes per token per layer
+    k0 = [2048 if args.workload == "batch16" else int(0.067 * n) for n in lens]
+    hbm = sum(len(dense) * row * n + n_sparse * row * k for n, k in zip(lens, k0))
+    if args.workload == "batch16":
+        hbm += 3 * sum(lens) * row // 2  # the window selectors read the filter layers' K a second time
+    weights = 2 * sum(p.numel() for n_, p in lm.named_parameters() if "embed_tokens" not in n_)
+    link = n_sparse * row * k0[0] if args.workload == "offload" else 0
+    line = {"workload": args.workload, "batch": B, "context": lens if B > 1 else lens[0], "steps": steps,
+            "ms_per_step": ms, "tokens_per_s": B * 1e3 / ms, "kv_bytes_per_step": hbm, "weight_bytes_per_step": weights,
+            "hbm_gbs": (hbm + weights + link) / ms / 1e6, "host_link_bytes_per_step": link,
+            "host_link_gbs": link / ms / 1e6 if link else None, "kv_fill_s": fill_s, "cuda_graph": not args.no_graph,
+            "selector": cfg.selector_cls, "launches_per_step": runner.launches_per_step}
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()
