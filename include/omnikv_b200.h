@@ -110,6 +110,12 @@ typedef struct {
   size_t workspace_bytes;
 } omnikv_attn_params;
 
+/* Stream order: the kernel is launched as a programmatic dependent launch (unless OMNIKV_PDL=0).  When the
+ * call right before it on the stream is one of this library's weight-streaming calls (omnikv_decode_qkv ...),
+ * the kernel reads the lengths, the index list and K/V rows OTHER than the last row of each sequence while
+ * that call is still finishing; q, the last row and everything it writes wait for the call to complete.  So
+ * such a call may produce q and the newest K/V row (what omnikv_decode_qkv does) but nothing else that this
+ * kernel reads.  After any other kernel the launch is ordered like a plain one. */
 size_t omnikv_decode_attn_workspace_bytes(int B, int H, int n_splits);
 int omnikv_decode_attn(const omnikv_attn_params* p, void* stream);
 

@@ -147,27 +147,14 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int G = a.G;
-  // Programmatic dependent launch: everything this kernel reads (q, the current token's K/V row, lengths, the
-  // index list) comes from the kernels before it, so it waits first; what it gains is that its CTAs are already
-  // resident when the previous kernel ends.  It lets its successor be scheduled early only when its own grid is
+  // Programmatic dependent launch.  Of what this kernel reads, only q and the CURRENT token's K/V row (the last
+  // row of the sequence) come from the kernel right before it (the QKV kernel); the lengths, the index list and
+  // all older rows were written by kernels that had completed before that one could start.  So the lengths, the
+  // index lookups and the copies of the first tiles go out BEFORE the wait and overlap the previous kernel's
+  // last CTAs; the wait comes before q is read and before anything is written.  Only a split whose first
+  // tiles already reach the last row waits first.  The successor may be scheduled early only when this grid is
   // fully resident (a.pdl_trigger, decided by the host from the grid size).
   ATTN_STAMP(0);
-  pdl_wait();
-  if (a.pdl_trigger) pdl_trigger();
-  ATTN_STAMP(1);
-  // Every global load of the prologue that depends on nothing is issued here, together: the lengths, the tail
-  // start and this thread's two 16-byte pieces of the group's queries.  (Chained one after the other, these
-  // round trips were most of a sparse layer's time.)
-  uint4 q_reg[2];
-#pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    const int i = tid + j * NTHREADS, r = i >> 4, c = i & 15;
-    q_reg[j] = make_uint4(0, 0, 0, 0);
-    if (r < G) {
-      const T* qp = static_cast<const T*>(a.q) + (size_t)b * a.q_sb + (size_t)(kvh * G + r) * a.q_sh;
-      q_reg[j] = __ldg(reinterpret_cast<const uint4*>(qp + c * 8));
-    }
-  }
   const int nA = a.lenA[b];
   const int nB = a.lenB ? a.lenB[b] : 0;
   const int startB = a.startB ? a.startB[b] : 0;
@@ -175,6 +162,11 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
   int r0, r1;
   split_range(n, a.S, split, r0, r1);
   const int ntiles = r1 > r0 ? ceil_div(r1 - r0, TILE) : 0;
+  const bool early = ntiles > 0 && (r1 < n || ntiles > STAGES - 1);
+  if (!early) {
+    pdl_wait();
+    if (a.pdl_trigger) pdl_trigger();
+  }
 
   float* ws_o = a.ws_o;
   float* ws_ml = a.ws_ml;
@@ -250,11 +242,21 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
     cp_async_commit();
   }
 
-  // Q tile: 16 rows x 128, rows >= G are zero (loaded into registers at the top of the kernel).
+  if (early) {
+    pdl_wait();
+    if (a.pdl_trigger) pdl_trigger();
+  }
+  ATTN_STAMP(1);
+  // Q tile: 16 rows x 128, rows >= G are zero.
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
     const int i = tid + j * NTHREADS, r = i >> 4, c = i & 15;
-    *reinterpret_cast<uint4*>(q_s + r * PITCH + c * 16) = q_reg[j];
+    uint4 qv = make_uint4(0, 0, 0, 0);
+    if (r < G) {
+      const T* qp = static_cast<const T*>(a.q) + (size_t)b * a.q_sb + (size_t)(kvh * G + r) * a.q_sh;
+      qv = *reinterpret_cast<const uint4*>(qp + c * 8);
+    }
+    *reinterpret_cast<uint4*>(q_s + r * PITCH + c * 16) = qv;
   }
   __syncthreads();
   unsigned qf[8][4];
