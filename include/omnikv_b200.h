@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define OMNIKV_ABI_VERSION 2
+#define OMNIKV_ABI_VERSION 3
 
 typedef enum {
   OMNIKV_OK = 0,
@@ -68,11 +68,14 @@ const char* omnikv_last_cuda_error(void);
  *       A = prompt rows at the selected indices (replaces the index_select of :297-303 and
  *       the torch.cat of :349-356: no gathered copy is materialised), B = the decode-time tail.
  *   offloaded sparse layer: A = the staged rows written by omnikv_offload_gather (idxA = NULL).
+ *   paged pool (omnikv-lightllm/lightllm/common/mem_manager.py:102-104, req_manager.py:12-17): A = the pool
+ *       [tokens, 2*KVH, d] (a_stride_b = 0, a_stride_h = d, a_stride_row = 2*KVH*d; V = K + KVH*d),
+ *       idxA = req_to_token_indexs, idx_row = b_req_idx, lenA = b_seq_len.
  *
- * score_out (optional, dense only): the filter layer's selection score of selector "last"
+ * score_out (optional): the filter layer's selection score of selector "last"
  * (modeling/omnikv.py:40-46) for free while K streams through: for every position
- * p < score_len[b], score_out[kvh][b][p] = max over the query heads of KV head kvh of the
- * scaled raw logit.  The max over KV heads is taken by omnikv_topk (n_planes = KVH), or by a
+ * p < score_len[b] of segment A (the position j, not the cache row it maps to),
+ * score_out[kvh][b][p] = max over the query heads of KV head kvh of the scaled raw logit.  The max over KV heads is taken by omnikv_topk (n_planes = KVH), or by a
  * MAX all-reduce of the planes when KV heads are sharded over GPUs.
  *
  * out == NULL with score_out != NULL computes scores only (V is never read).
@@ -90,6 +93,8 @@ typedef struct {
   int64_t a_stride_b, a_stride_h, a_stride_row; /* elements; a row is head_dim contiguous elements */
   const int32_t* idxA; /* device [B, idx_stride] or NULL */
   int64_t idx_stride;
+  const int32_t* idx_row; /* device [B] or NULL: batch entry b uses row idx_row[b] of the index table instead of
+                             row b (a paged pool shared by requests: the table has one row per request slot) */
   const int32_t* lenA; /* device [B] */
   /* segment B (all NULL / 0 when unused) */
   const void* kB;

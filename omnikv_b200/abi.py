@@ -10,7 +10,7 @@ from pathlib import Path
 _LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libomnikv_b200.so"
 _lib = None
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 F32, BF16, F16 = 0, 1, 2
 SEL_SOFTMAX_LAST, SEL_UNIFORM, SEL_EXP = 0, 1, 2
 NO_ALLOC_SCRATCH_BYTES = 4 * 1024 * 1024
@@ -29,7 +29,7 @@ class AttnParams(C.Structure):
         ("out", C.c_void_p),
         ("kA", C.c_void_p), ("vA", C.c_void_p),
         ("a_stride_b", C.c_int64), ("a_stride_h", C.c_int64), ("a_stride_row", C.c_int64),
-        ("idxA", C.c_void_p), ("idx_stride", C.c_int64), ("lenA", C.c_void_p),
+        ("idxA", C.c_void_p), ("idx_stride", C.c_int64), ("idx_row", C.c_void_p), ("lenA", C.c_void_p),
         ("kB", C.c_void_p), ("vB", C.c_void_p),
         ("b_stride_b", C.c_int64), ("b_stride_h", C.c_int64), ("b_stride_row", C.c_int64),
         ("startB", C.c_void_p), ("lenB", C.c_void_p),

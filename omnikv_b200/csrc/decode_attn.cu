@@ -22,6 +22,7 @@ struct AttnArgs {
   const void* vA;
   int64_t a_sb, a_sh, a_sr;
   const int* idxA;
+  const int* idx_row;  // row of the index table that batch entry b uses, or nullptr: row b
   int64_t idx_stride;
   const int* lenA;
   const void* kB;
@@ -189,7 +190,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
   const T* vA = WITH_V ? static_cast<const T*>(a.vA) + (size_t)b * a.a_sb + (size_t)kvh * a.a_sh : nullptr;
   const T* kB = a.kB ? static_cast<const T*>(a.kB) + (size_t)b * a.b_sb + (size_t)kvh * a.b_sh : nullptr;
   const T* vB = (WITH_V && a.vB) ? static_cast<const T*>(a.vB) + (size_t)b * a.b_sb + (size_t)kvh * a.b_sh : nullptr;
-  const int* idx = a.idxA ? a.idxA + (size_t)b * a.idx_stride : nullptr;
+  const int* idx = a.idxA ? a.idxA + (size_t)(a.idx_row ? a.idx_row[b] : b) * a.idx_stride : nullptr;
 
   // A tile is issued in two steps: resolve() turns its rows into cache offsets (for a sparse layer this is a
   // lookup in the index list), issue() starts the copies.  resolve() of the NEXT tile runs right after issue() of
@@ -442,7 +443,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attn_f32_kernel(const AttnArg
   const float* vA = with_v ? static_cast<const float*>(a.vA) + (size_t)b * a.a_sb + (size_t)kvh * a.a_sh : nullptr;
   const float* kB = a.kB ? static_cast<const float*>(a.kB) + (size_t)b * a.b_sb + (size_t)kvh * a.b_sh : nullptr;
   const float* vB = (with_v && a.vB) ? static_cast<const float*>(a.vB) + (size_t)b * a.b_sb + (size_t)kvh * a.b_sh : nullptr;
-  const int* idx = a.idxA ? a.idxA + (size_t)b * a.idx_stride : nullptr;
+  const int* idx = a.idxA ? a.idxA + (size_t)(a.idx_row ? a.idx_row[b] : b) * a.idx_stride : nullptr;
   const int startB = a.startB ? a.startB[b] : 0;
   const int score_lim = with_score ? min(a.score_len[b], nA) : 0;
   float* score_row = with_score ? a.score_out + ((size_t)kvh * a.B + b) * a.score_stride : nullptr;
@@ -614,7 +615,8 @@ extern "C" int omnikv_decode_attn(const omnikv_attn_params* p, void* stream) {
   const bool with_score = p->score_out != nullptr;
   if (!with_v && !with_score) return OMNIKV_E_BADARG;
   if (with_v && !p->vA) return OMNIKV_E_BADARG;
-  if (with_score && (p->idxA || !p->score_len || p->score_stride <= 0)) return OMNIKV_E_BADARG;
+  if (with_score && (!p->score_len || p->score_stride <= 0)) return OMNIKV_E_BADARG;
+  if (p->idx_row && !p->idxA) return OMNIKV_E_BADARG;
   if (p->lenB && (!p->kB || !p->startB || (with_v && !p->vB))) return OMNIKV_E_BADARG;
   const int esz = p->dtype == OMNIKV_F32 ? 4 : 2;
   const int vec = 16 / esz;  // elements per 16-byte vector
@@ -636,7 +638,7 @@ extern "C" int omnikv_decode_attn(const omnikv_attn_params* p, void* stream) {
   AttnArgs a;
   a.q = p->q; a.q_sb = p->q_stride_b; a.q_sh = p->q_stride_h; a.out = p->out;
   a.kA = p->kA; a.vA = p->vA; a.a_sb = p->a_stride_b; a.a_sh = p->a_stride_h; a.a_sr = p->a_stride_row;
-  a.idxA = p->idxA; a.idx_stride = p->idx_stride; a.lenA = p->lenA;
+  a.idxA = p->idxA; a.idx_row = p->idx_row; a.idx_stride = p->idx_stride; a.lenA = p->lenA;
   a.kB = p->lenB ? p->kB : nullptr; a.vB = p->lenB ? p->vB : nullptr;
   a.b_sb = p->b_stride_b; a.b_sh = p->b_stride_h; a.b_sr = p->b_stride_row;
   a.startB = p->startB; a.lenB = p->lenB;

@@ -87,6 +87,7 @@ def decode_attn(
     len_a: torch.Tensor,
     *,
     idx: Optional[torch.Tensor] = None,
+    idx_row: Optional[torch.Tensor] = None,
     k_tail: Optional[torch.Tensor] = None,
     v_tail: Optional[torch.Tensor] = None,
     tail_start: Optional[torch.Tensor] = None,
@@ -101,11 +102,12 @@ def decode_attn(
     scores_only: bool = False,
 ) -> Optional[torch.Tensor]:
     """``omnikv_decode_attn``.  q ``[B,H,d]``; k, v ``[B,KVH,rows,d]``; ``len_a`` int32 ``[B]`` on
-    the device; ``idx`` int32 ``[B, >=len_a]`` selects rows of (k, v); the tail is
+    the device; ``idx`` int32 ``[B, >=len_a]`` selects rows of (k, v) (with ``idx_row`` int32 ``[B]``, batch
+    entry b reads row ``idx_row[b]`` of ``idx`` -- a request table over a paged pool); the tail is
     ``tail_len[b]`` rows of (k_tail, v_tail) from ``tail_start[b]``.  ``score_out``
     ``[KVH,B,stride]`` fp32 receives the per-KV-head selector-``last`` scores of positions
     ``< score_len[b]``.  Returns ``out`` ``[B,H,d]`` (None when ``scores_only``)."""
-    _need_cuda(q, k, v, len_a, idx, k_tail, v_tail, out, score_out)
+    _need_cuda(q, k, v, len_a, idx, idx_row, k_tail, v_tail, out, score_out)
     B, H, d = q.shape
     KVH = k.shape[1]
     if q.stride(2) != 1:
@@ -129,6 +131,12 @@ def decode_attn(
         if idx.dtype != torch.int32 or idx.stride(-1) != 1:
             raise abi.OmniKVError("idx must be contiguous int32")
         p.idxA, p.idx_stride = idx.data_ptr(), idx.stride(0) if idx.dim() == 2 else 0
+        if idx_row is not None:
+            if idx_row.dtype != torch.int32 or not idx_row.is_contiguous() or idx_row.numel() != B:
+                raise abi.OmniKVError("idx_row must be contiguous int32 [B]")
+            p.idx_row = idx_row.data_ptr()
+    elif idx_row is not None:
+        raise abi.OmniKVError("idx_row needs idx")
     if len_a.dtype != torch.int32:
         raise abi.OmniKVError("len_a must be int32")
     p.lenA = len_a.data_ptr()

@@ -114,3 +114,26 @@ def test_cache_refuses_to_overflow_its_reserve():
     c.check_room(1)
     with pytest.raises(RuntimeError, match="KV cache is full"):
         c.check_room(2)
+
+
+def test_paged_oracle_consistency():
+    """The paged-pool oracle: keeping every token equals dense attention; kept positions are ascending and
+    end with the forced recent ones."""
+    import torch
+    from oracle import lightllm_oracle as lo
+
+    g = torch.Generator().manual_seed(0)
+    KVH, H, d, n = 2, 4, 128, 300
+    pool = torch.randn(512, 2 * KVH, d, generator=g)
+    table = torch.zeros(3, 400, dtype=torch.int32)
+    table[2, :n] = torch.randperm(512, generator=g)[:n].to(torch.int32)
+    q = torch.randn(1, H, d, generator=g)
+    req, lens = torch.tensor([2]), [n]
+    dense = lo.paged_decode_attention(q, pool[:, :KVH], pool[:, KVH:], table, req, lens)
+    pos_all = lo.select_positions(q, pool[:, :KVH], table, req, lens, num_imp_tokens=2048)
+    assert torch.equal(pos_all[0], torch.arange(n))
+    again = lo.selected_decode_attention(q, pool[:, :KVH], pool[:, KVH:], table, req, pos_all)
+    assert torch.allclose(dense, again, atol=1e-6)
+    pos = lo.select_positions(q, pool[:, :KVH], table, req, lens, num_imp_tokens=64, keep_recent=5)[0]
+    assert pos.numel() == 64 and torch.equal(pos[-5:], torch.arange(n - 5, n))
+    assert torch.equal(pos, torch.sort(pos).values)
