@@ -202,6 +202,23 @@ int omnikv_topk(const float* scores, int n_planes, int64_t plane_stride, int64_t
                 void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Lazy re-gather rule: replaces get_idx_iou_score + the skip test of OmniKVLazyCache.set_out_idx,
+ * modeling/spec_cache.py:10-31, :539-548 (cache_cls "lazy"), without the .cpu() round trip.
+ *
+ * Per sequence b: new_idx[b][0..new_count[b]) is the selection just made, live_idx[b][0..live_count[b]) the
+ * one in use (both ascending, no duplicates; live_count = 0: none yet).  With inter = |new & live|:
+ * the new list REPLACES the one in use (copied into live_idx, live_count = new_count, applied[b] = 1)
+ * unless inter / new_count > skip_threshold (compared in double, as the reference's Python floats), in
+ * which case the one in use is kept (applied[b] = 0).  gather_n[b] (optional) = new_count[b] when replaced,
+ * else 0: passed as n_idx to omnikv_offload_gather it turns the host gather into a no-op on kept steps.
+ * overlap[b] (optional) = inter.  capacity bounds both counts; new_idx and live_idx must not alias.
+ * ------------------------------------------------------------------------------------------ */
+int omnikv_idx_commit(const int32_t* new_idx, int64_t new_stride, const int32_t* new_count, int32_t* live_idx,
+                      int64_t live_stride, int32_t* live_count, int B, int capacity, double skip_threshold,
+                      int32_t* applied, int32_t* gather_n /* may be NULL */, int32_t* overlap /* may be NULL */,
+                      void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Offload gather: replaces the CPU index_select + .cuda(non_blocking=True) of
  * modeling/spec_cache.py:293-303 (real_offload).  The prompt KV of the sparse layers of one
  * group lives in PINNED, device-mapped host memory, token-major:

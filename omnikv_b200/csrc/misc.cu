@@ -81,6 +81,48 @@ __global__ void __launch_bounds__(256) offload_gather_kernel(const unsigned char
   }
 }
 
+// Lazy re-gather rule, one CTA per sequence.  Both lists are ascending and free of duplicates, so the
+// intersection is counted by a binary search of every new entry in the list in use.
+__global__ void __launch_bounds__(1024) idx_commit_kernel(const int* __restrict__ new_idx, int64_t new_stride,
+                                                          const int* __restrict__ new_count, int* live_idx,
+                                                          int64_t live_stride, int* live_count, int capacity,
+                                                          double skip_threshold, int* applied, int* gather_n,
+                                                          int* overlap) {
+  __shared__ int s_inter;
+  const int b = blockIdx.x, tid = threadIdx.x;
+  const int n = min(new_count[b], capacity), m = min(live_count[b], capacity);
+  const int* nw = new_idx + (size_t)b * new_stride;
+  int* lv = live_idx + (size_t)b * live_stride;
+  if (tid == 0) s_inter = 0;
+  __syncthreads();
+  int c = 0;
+  if (m > 0) {
+    for (int j = tid; j < n; j += blockDim.x) {
+      const int v = nw[j];
+      int lo = 0, hi = m;  // first position with lv[pos] >= v
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (lv[mid] < v) lo = mid + 1; else hi = mid;
+      }
+      c += (lo < m && lv[lo] == v) ? 1 : 0;
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) c += __shfl_xor_sync(0xffffffffu, c, off);
+  if ((tid & 31) == 0 && c) atomicAdd(&s_inter, c);
+  __syncthreads();  // also: every read of the list in use is done before it is overwritten
+  const int inter = s_inter;
+  const bool take = m == 0 || n == 0 || !((double)inter / (double)n > skip_threshold);
+  if (take)
+    for (int j = tid; j < n; j += blockDim.x) lv[j] = nw[j];
+  if (tid == 0) {
+    if (take) live_count[b] = n;
+    applied[b] = take ? 1 : 0;
+    if (gather_n) gather_n[b] = take ? n : 0;
+    if (overlap) overlap[b] = inter;
+  }
+}
+
 __global__ void window_fold_kernel(const float* __restrict__ planes, float* __restrict__ score_out, int W,
                                    int64_t score_stride, const int* __restrict__ consider_len, int selector) {
   const int b = blockIdx.y;
@@ -160,6 +202,21 @@ extern "C" int omnikv_offload_gather(const void* host_kv, int64_t token_stride_b
   offload_gather_kernel<<<n_ctas, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const unsigned char*>(host_kv), token_stride_bytes, rows_per_token, row_bytes, idx, n_idx,
       n_idx_capacity, static_cast<unsigned char*>(staged));
+  OMNIKV_CUDA_OK(cudaGetLastError());
+  return OMNIKV_OK;
+}
+
+extern "C" int omnikv_idx_commit(const int32_t* new_idx, int64_t new_stride, const int32_t* new_count,
+                                 int32_t* live_idx, int64_t live_stride, int32_t* live_count, int B, int capacity,
+                                 double skip_threshold, int32_t* applied, int32_t* gather_n, int32_t* overlap,
+                                 void* stream) {
+  using namespace omnikv;
+  if (!new_idx || !new_count || !live_idx || !live_count || !applied || B <= 0 || capacity <= 0)
+    return OMNIKV_E_BADARG;
+  if (new_stride < capacity || live_stride < capacity || new_idx == live_idx) return OMNIKV_E_BADARG;
+  idx_commit_kernel<<<B, 1024, 0, static_cast<cudaStream_t>(stream)>>>(new_idx, new_stride, new_count, live_idx,
+                                                                       live_stride, live_count, capacity,
+                                                                       skip_threshold, applied, gather_n, overlap);
   OMNIKV_CUDA_OK(cudaGetLastError());
   return OMNIKV_OK;
 }

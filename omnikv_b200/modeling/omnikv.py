@@ -26,7 +26,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
-from .. import ops
+from .. import ops, tensor_tools
 from .omnikv_config import logger
 from .spec_cache import OmniKVMultiStageCache, WOPackCache, full_attn_layers_of, get_cache_cls  # noqa: F401
 
@@ -319,7 +319,19 @@ class OmniKVMulLayer(nn.Module):
         ops.topk(st.planes, st.consider, st.k, append_n=st.nptw, idx_out=st.idx, count_out=st.count,
                  max_len=st.max_len)
         torch.clamp(st.nptw - 1, min=0, out=st.nptw)
+        self._trace_selection(cache, st)
         cache.set_idx_device(st.idx, st.count, self.layer_idx)
+
+    def _trace_selection(self, cache, st) -> None:
+        """Hand the selection to the index recorder, if one is active (tiny_tools/tensor_tools.py:64-74)."""
+        tracer = tensor_tools.idx_tracer
+        if tracer is None:
+            return
+        scores = st.planes if st.planes.dim() == 2 else st.planes.max(dim=0).values  # [B, L]
+        kmax = int(st.count.max().item())
+        idx = st.idx[:, :kmax].long()
+        val = scores.gather(1, idx.clamp(max=scores.shape[1] - 1))
+        tracer.append_spec_layer(idx, val, cache.prefill_len, self.layer_idx)
 
     # -- batch-1 decode through the fused weight-streaming kernels -----------------------------------
     def _fused_ok(self, hidden_states) -> bool:
@@ -375,6 +387,7 @@ class OmniKVMulLayer(nn.Module):
             if self.tp is not None:  # plane j <- max over ranks of their j-th local KV head: order independent
                 self.tp.all_reduce_max(st.planes)
             ops.topk(st.planes, cache.prefill_len_dev, st.k0, idx_out=st.idx, count_out=st.count, max_len=st.max_len)
+            self._trace_selection(cache, st)
             cache.set_idx_device(st.idx, st.count, self.layer_idx)
         cache.stage = "decoding"
         self.decode_step += 1
@@ -653,15 +666,19 @@ class OmniKVMulLM(nn.Module):
     def new_cache(self, past_key_values=None):
         """The cache wrap of modeling/omnikv.py:315-341."""
         cache_cls_name = self.config.get("cache_cls", "default")
-        if cache_cls_name not in ("multi", "without_pack"):
+        if cache_cls_name not in ("multi", "without_pack", "lazy"):
             raise NotImplementedError
         do_sel_layers = [int(i) for i in self.config.get("do_select_layers").split(",")]
+        kwargs = {}
+        if cache_cls_name == "lazy":  # modeling/offload_select_once.py:275-276
+            kwargs["skip_threshold"] = self.config.get("skip_threshold", 0.4)
         return self.cache_cls.from_dynamic_cache(
             past_key_values,
             full_attn_layers=full_attn_layers_of(do_sel_layers, self.config.num_hidden_layers),
             num_hidden_layers=self.config.num_hidden_layers,
             num_wait_load_layers=self.config.get("num_wait_load_layers", 2),
             real_offload=self.config.get("real_offload", True),
+            **kwargs,
         )
 
     # -- reference forward -----------------------------------------------------------------------
@@ -815,7 +832,7 @@ class DecodeRunner:
         self.max_new_tokens = max_new_tokens
         self.graph = None
         self.launches_per_step = 0
-        if use_cuda_graph:
+        if use_cuda_graph and tensor_tools.idx_tracer is None:  # recording reads the selection on the host
             for _ in range(min(warmup_steps, max_new_tokens - 1)):
                 self._step()
                 self.steps_done += 1

@@ -1,5 +1,6 @@
-"""KV caches of the OmniKV decode path: ``OmniKVMultiStageCache`` (``cache_cls = "multi"``) and
-``WOPackCache`` (``"without_pack"``), mirroring modeling/spec_cache.py:253-520 of the reference.
+"""KV caches of the OmniKV decode path: ``OmniKVMultiStageCache`` (``cache_cls = "multi"``),
+``WOPackCache`` (``"without_pack"``) and ``OmniKVLazyCache`` (``"lazy"``), mirroring
+modeling/spec_cache.py:253-557 of the reference.
 
 Same public surface -- ``from_dynamic_cache``, ``update``, ``set_idx_on_gpu``, ``stage``,
 ``layer_state``, ``key_cache`` / ``value_cache``, ``part_key`` / ``part_value``, ``tail_k`` /
@@ -23,6 +24,7 @@ batch 1; here every sequence has its own index list, lengths and tail.
 """
 from __future__ import annotations
 
+from types import SimpleNamespace
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -318,6 +320,10 @@ class OmniKVMultiStageCache:
         if self.real_offload and self.pack_gather and sel_layer_idx in self.groups:
             self._launch_gather(sel_layer_idx, sel_layer_idx)
 
+    def _gather_count(self, sel_layer_idx: int, count: torch.Tensor) -> torch.Tensor:
+        """Number of rows the host gather of this group fetches (a device int32): all selected rows."""
+        return count
+
     # ------------------------------------------------------------------------------------------
     # offload gather
     # ------------------------------------------------------------------------------------------
@@ -333,6 +339,7 @@ class OmniKVMultiStageCache:
     def _launch_gather(self, key: int, sel_layer_idx: int, side: bool = True) -> None:
         from .. import ops
         idx32, count = self._idx[sel_layer_idx]
+        count = self._gather_count(sel_layer_idx, count)
         staged = self._staged_for(key, idx32.shape[1])
         if not side:
             ops.offload_gather(self._host[key], idx32[0], count, staged)
@@ -396,11 +403,59 @@ class WOPackCache(OmniKVMultiStageCache):
         return c
 
 
+class OmniKVLazyCache(OmniKVMultiStageCache):
+    """``cache_cls = "lazy"``: the re-gather rule of the reference's OmniKVLazyCache.set_out_idx
+    (modeling/spec_cache.py:523-557) on top of the multi-stage cache.  When a filter layer's new selection
+    overlaps the one in use by more than ``skip_threshold`` (|new & old| / |new|, :10-31), the group keeps the
+    old selection: its sparse layers attend over the same rows and, with ``real_offload``, nothing crosses the
+    host link in that step.  The decision is taken on the device (``omnikv_idx_commit``), so the decode step
+    stays free of host synchronisation and can be captured in a CUDA graph.
+
+    The reference offers this class to its older single-filter model (modeling/offload_select_once.py:275-276,
+    config key ``skip_threshold``, default 0.4); here it plugs into ``OmniKVMulLM`` per filter group."""
+
+    def __init__(self, *args, skip_threshold: float = 0.4, **kw):
+        super().__init__(*args, **kw)
+        self.skip_threshold = float(skip_threshold)
+        self._lazy: Dict[int, SimpleNamespace] = {}
+
+    @staticmethod
+    def from_dynamic_cache(cache, full_attn_layers: List, num_hidden_layers, num_wait_load_layers=2,
+                           real_offload=True, skip_threshold=0.4):
+        c = OmniKVLazyCache(full_attn_layers, num_hidden_layers, num_wait_load_layers, real_offload,
+                            skip_threshold=skip_threshold)
+        c._adopt(cache)
+        return c
+
+    def set_idx_device(self, idx32: torch.Tensor, count: torch.Tensor, sel_layer_idx: int) -> None:
+        from .. import ops
+        st = self._lazy.get(sel_layer_idx)
+        if st is None or st.live_idx.shape != idx32.shape:
+            z = lambda: torch.zeros_like(count)  # noqa: E731
+            st = SimpleNamespace(live_idx=torch.zeros_like(idx32), live_count=z(), applied=z(), gather_n=z(),
+                                 overlap=z(), offered=0)
+            self._lazy[sel_layer_idx] = st
+        ops.idx_commit(idx32, count, st.live_idx, st.live_count, self.skip_threshold, st.applied, st.gather_n,
+                       st.overlap)
+        st.offered += 1
+        super().set_idx_device(st.live_idx, st.live_count, sel_layer_idx)
+
+    def _gather_count(self, sel_layer_idx: int, count: torch.Tensor) -> torch.Tensor:
+        return self._lazy[sel_layer_idx].gather_n
+
+    def lazy_state(self, sel_layer_idx: int) -> Dict[str, List[int]]:
+        """Outcome of the last selection offered to a filter group (synchronises): per sequence whether it
+        replaced the one in use and how many entries the two shared."""
+        st = self._lazy[sel_layer_idx]
+        return {"applied": st.applied.tolist(), "overlap": st.overlap.tolist(), "count": st.live_count.tolist()}
+
+
 def get_cache_cls(config):
-    """modeling/spec_cache.py:829-837.  Only the two classes of the decode-selection path exist here;
-    the reference's other entries (``lazy``, ``default``, ``eff``) are older ablations."""
-    name2cls = {"multi": OmniKVMultiStageCache, "without_pack": WOPackCache}
+    """modeling/spec_cache.py:829-837.  ``multi`` and ``without_pack`` are the classes of the decode-selection
+    path; ``lazy`` adds the reference's IoU-skip rule to ``multi``.  The reference's ``default`` and ``eff``
+    belong to its older models (``eff`` is broken upstream)."""
+    name2cls = {"multi": OmniKVMultiStageCache, "without_pack": WOPackCache, "lazy": OmniKVLazyCache}
     name = config.get("cache_cls", "default")
     if name not in name2cls:
-        raise NotImplementedError(f"cache_cls={name!r}: only 'multi' and 'without_pack' are implemented")
+        raise NotImplementedError(f"cache_cls={name!r}: only 'multi', 'without_pack' and 'lazy' are implemented")
     return name2cls[name]

@@ -285,6 +285,25 @@ def offload_gather(host_kv: torch.Tensor, idx: torch.Tensor, n_idx: torch.Tensor
     _count(1)
 
 
+def idx_commit(new_idx: torch.Tensor, new_count: torch.Tensor, live_idx: torch.Tensor, live_count: torch.Tensor,
+               skip_threshold: float, applied: torch.Tensor, gather_n: Optional[torch.Tensor] = None,
+               overlap: Optional[torch.Tensor] = None) -> None:
+    """``omnikv_idx_commit``: the lazy re-gather rule.  int32 device tensors: new_idx / live_idx ``[B, cap]``
+    ascending, new_count / live_count / applied / gather_n / overlap ``[B]``."""
+    _need_cuda(new_idx, new_count, live_idx, live_count, applied, gather_n, overlap)
+    for t in (new_idx, new_count, live_idx, live_count, applied, gather_n, overlap):
+        if t is not None and t.dtype != torch.int32:
+            raise abi.OmniKVError("idx_commit: int32 tensors expected")
+    if new_idx.dim() != 2 or live_idx.dim() != 2 or new_idx.stride(1) != 1 or live_idx.stride(1) != 1:
+        raise abi.OmniKVError("idx_commit: index lists must be [B, capacity] with contiguous rows")
+    B, cap = new_idx.shape[0], min(new_idx.shape[1], live_idx.shape[1])
+    abi.check(abi.lib().omnikv_idx_commit(new_idx.data_ptr(), new_idx.stride(0), new_count.data_ptr(),
+                                          live_idx.data_ptr(), live_idx.stride(0), live_count.data_ptr(), B, cap,
+                                          float(skip_threshold), applied.data_ptr(), _ptr(gather_n), _ptr(overlap),
+                                          _stream()), "omnikv_idx_commit")
+    _count(1)
+
+
 def host_device_pointer(t: torch.Tensor) -> int:
     """Device-visible address of a pinned host tensor.  With unified virtual addressing (every
     64-bit Linux CUDA process) a page-locked allocation made by the CUDA runtime is mapped into

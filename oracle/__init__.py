@@ -8,7 +8,7 @@ is shipped or measured as the product.
 Parity status: the selector, the layer plan and the cache flow are PINNED --
 ``tests/golden/make_golden.py`` runs the reference's own
 ``select_tokens_by_attn_universal``, ``OmniKVMultiStageCache`` and
-``WOPackCache`` on seeded inputs and the committed fixtures hold their
+``WOPackCache`` (and ``OmniKVLazyCache.set_out_idx`` for the lazy re-gather rule) on seeded inputs and the committed fixtures hold their
 outputs; ``tests/test_oracle_golden.py`` checks this restatement against
 them.  The attention arithmetic itself (softmax(q K^T / sqrt(d)) V) and the
 decoder wrapper are third-party code in the reference (transformers 4.41.2,
@@ -28,4 +28,7 @@ from .omnikv_oracle import (  # noqa: F401
     topk_ascending,
     OracleMultiStageCache,
     OracleWOPackCache,
+    OracleLazyRule,
+    OracleLazyMultiStageCache,
+    idx_iou_score,
 )

@@ -53,9 +53,12 @@ class OracleLM:
         self.selected = {}  # (decode forward number, layer) -> idx, for the tests
 
     def new_cache(self):
-        cls = oo.OracleMultiStageCache if self.cfg.get("cache_cls", "multi") == "multi" else oo.OracleWOPackCache
+        name = self.cfg.get("cache_cls", "multi")
         full = oo.full_attn_layers_of(self.sel_layers, self.n_layers)
-        return cls(full, self.n_layers, self.cfg.get("num_wait_load_layers", 2), self.cfg.get("real_offload", True))
+        args = (full, self.n_layers, self.cfg.get("num_wait_load_layers", 2), self.cfg.get("real_offload", True))
+        if name == "lazy":
+            return oo.OracleLazyMultiStageCache(*args, skip_threshold=self.cfg.get("skip_threshold", 0.4))
+        return (oo.OracleMultiStageCache if name == "multi" else oo.OracleWOPackCache)(*args)
 
     def _layer(self, i, h, position_ids, cache, fwd_no):
         p = f"model.layers.{i}."

@@ -285,6 +285,52 @@ class OracleWOPackCache(OracleMultiStageCache):
         self.part_value[layer_idx] = torch.index_select(self.value_cache[layer_idx], 2, self.idx)
 
 
+def idx_iou_score(new_idx: torch.Tensor, old_idx: torch.Tensor) -> float:
+    """Overlap score of two index lists, modeling/spec_cache.py:10-31: the size of the intersection (counted as
+    ``|new| + |old| - |unique(cat(new, old))|``) divided by ``|new|`` -- not a true IoU, the reference's
+    comment says so."""
+    new_idx, old_idx = new_idx.reshape(-1), old_idx.reshape(-1)
+    un = torch.cat([new_idx, old_idx]).unique().numel()
+    return (new_idx.numel() + old_idx.numel() - un) / new_idx.numel()
+
+
+class OracleLazyRule:
+    """The re-gather rule of OmniKVLazyCache.set_out_idx, modeling/spec_cache.py:539-557: a new index list
+    replaces the one in use unless its overlap score with it is ABOVE ``skip_threshold``; the first list is
+    always taken."""
+
+    def __init__(self, skip_threshold: float = 0.4):
+        self.skip_threshold = skip_threshold
+        self.live: Dict[int, torch.Tensor] = {}
+        self.last: Dict[int, Tuple[bool, float]] = {}  # outcome of the latest offer per group
+
+    def offer(self, idx: torch.Tensor, sid: int) -> Tuple[bool, float]:
+        """Returns (taken, score against the list in use or -1.0)."""
+        score = -1.0
+        if sid in self.live:
+            score = idx_iou_score(idx, self.live[sid])
+            if score > self.skip_threshold:
+                self.last[sid] = (False, score)
+                return False, score
+        self.live[sid] = idx.clone()
+        self.last[sid] = (True, score)
+        return True, score
+
+
+class OracleLazyMultiStageCache(OracleMultiStageCache):
+    """The multi-stage cache with the lazy rule in front of ``set_idx_on_gpu``: a filter group keeps its
+    gathered rows while consecutive selections overlap enough (the rule of :539-557 applied per group)."""
+
+    def __init__(self, *a, skip_threshold: float = 0.4, **kw):
+        super().__init__(*a, **kw)
+        self.rule = OracleLazyRule(skip_threshold)
+
+    def set_idx_on_gpu(self, idx, sel_layer_idx):
+        taken, _ = self.rule.offer(idx, sel_layer_idx)
+        if taken:
+            super().set_idx_on_gpu(idx, sel_layer_idx)
+
+
 # ----------------------------------------------------------------------------------------------
 # Decode attention (the third-party part of the reference path: the mathematical definition)
 # ----------------------------------------------------------------------------------------------

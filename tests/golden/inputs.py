@@ -59,6 +59,25 @@ def cache_flow_inputs():
     return dict(k_pre=k_pre, v_pre=v_pre, k_new=k_new, v_new=v_new, idx=idx)
 
 
+LAZY_RULE = dict(seed=11, P=4000, k=300, steps=24, thresholds=[0.4, 0.7, 0.95])
+
+
+def lazy_rule_inputs():
+    """A drifting sequence of ascending index lists [steps][1, k]: each step replaces a random share
+    (0 .. 80 %) of the previous list's entries, so consecutive overlaps cover the whole range."""
+    c = LAZY_RULE
+    rng = np.random.default_rng(c["seed"])
+    cur = np.sort(rng.choice(c["P"], size=c["k"], replace=False))
+    out = [cur[None, :].astype(np.int64)]
+    for _ in range(c["steps"] - 1):
+        n_new = int(rng.uniform(0.0, 0.8) * c["k"])
+        keep = rng.choice(cur, size=c["k"] - n_new, replace=False)
+        pool = np.setdiff1d(np.arange(c["P"]), keep)
+        cur = np.sort(np.concatenate([keep, rng.choice(pool, size=n_new, replace=False)]))
+        out.append(cur[None, :].astype(np.int64))
+    return out
+
+
 OPERATOR = dict(seed=2024, L=16384, H=32, KVH=8, d=128, W=16, k=1098)
 
 

@@ -213,6 +213,30 @@ def make_operator_fixture(ref_omnikv, ref_cache):
     print("operator: |idx & hot| =", len(set(idx[0].tolist()) & set(x["hot"].tolist())), "of", len(x["hot"]))
 
 
+def make_lazy_rule_fixture(ref_cache):
+    """The reference's OmniKVLazyCache.set_out_idx on a drifting index sequence: which steps re-gather and
+    which keep the previous selection (modeling/spec_cache.py:539-557), plus the overlap score of :10-31."""
+    from inputs import LAZY_RULE, lazy_rule_inputs
+    c = LAZY_RULE
+    seq = lazy_rule_inputs()
+    res = {}
+    for thr in c["thresholds"]:
+        cache = ref_cache.OmniKVLazyCache(offload_start_id=1, num_total_layers=3, skip_threshold=thr)
+        cache.mamba_k = torch.arange(c["P"] * 4, dtype=torch.float32).view(1, c["P"], 4)
+        cache.mamba_v = -cache.mamba_k
+        applied, scores, live_sum = [], [], []
+        for idx in seq:
+            t = torch.from_numpy(idx)
+            scores.append(float(ref_cache.get_idx_iou_score(t.view(-1), cache.idx[1].view(-1))) if 1 in cache.idx else -1.0)
+            cache.set_out_idx(t, 1)
+            applied.append(bool(torch.equal(cache.idx[1], t)))
+            # the staged rows follow the live selection: row j of part_key[1] is token live[j]
+            live_sum.append(float(cache.part_key[1][0, 0, :].sum()))
+        res[str(thr)] = dict(applied=applied, scores=scores, live_sum=live_sum)
+    (HERE / "lazy_rule.json").write_text(json.dumps(dict(c, input_checksum=checksum(seq), results=res)))
+    print("lazy rule:", {k: sum(v["applied"]) for k, v in res.items()}, "re-gathers of", c["steps"])
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the OmniKV checkout")
@@ -223,6 +247,7 @@ def main():
     make_plan_fixture(ref_cache)
     make_cache_flow_fixture(ref_cache)
     make_operator_fixture(ref_omnikv, ref_cache)
+    make_lazy_rule_fixture(ref_cache)
 
 
 if __name__ == "__main__":

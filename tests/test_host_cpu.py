@@ -54,6 +54,11 @@ def test_get_cache_cls():
     assert get_cache_cls(c) is OmniKVMultiStageCache
     c.cache_cls = "without_pack"
     assert get_cache_cls(c) is WOPackCache
+    from omnikv_b200.modeling import OmniKVLazyCache
+    c.cache_cls = "lazy"
+    assert get_cache_cls(c) is OmniKVLazyCache
+    lz = OmniKVLazyCache.from_dynamic_cache(None, [0, 1, 4], 4, 1, False, skip_threshold=0.7)
+    assert lz.skip_threshold == 0.7 and lz.layer_state == OmniKVMultiStageCache([0, 1, 4], 4, 1, False).layer_state
     c.cache_cls = "eff"
     with pytest.raises(NotImplementedError):
         get_cache_cls(c)
@@ -137,3 +142,27 @@ def test_paged_oracle_consistency():
     pos = lo.select_positions(q, pool[:, :KVH], table, req, lens, num_imp_tokens=64, keep_recent=5)[0]
     assert pos.numel() == 64 and torch.equal(pos[-5:], torch.arange(n - 5, n))
     assert torch.equal(pos, torch.sort(pos).values)
+
+
+def test_index_tracer_roundtrip(tmp_path):
+    """The recorder's pickle has the reference's layout and its reader returns the four parts."""
+    import torch
+    from omnikv_b200 import tensor_tools as tt
+
+    tr = tt.SelectedIndexTracer(desc="cpu", directory=str(tmp_path / "logs"))
+    tr.append_spec_layer(torch.tensor([[1, 5, 9]]), torch.tensor([[0.5, 0.25, 2.0]]), 100, 8)
+    tr.append_spec_layer(torch.tensor([[2, 5, 7]]), torch.tensor([[1.5, 0.25, 0.1]]), 100, 8)
+    tr.append(torch.tensor([3]), torch.tensor([0.1]))
+    tr.append_prefill(torch.tensor([[4]]), torch.tensor([[0.3]]), 8)
+    tr.append_out(("pred", "truth"))
+    with pytest.raises(AssertionError):
+        tr.append_spec_layer(torch.tensor([1]), torch.tensor([1.0]), 100, 8)
+    tr.save_idx()
+    assert tr.num_samples == 1
+    idx, out, layers_idx, prefill_res = tt.read_idx_tracer(tr.save_path)
+    assert out == [("pred", "truth")]
+    assert [r["idx"].tolist() for r in layers_idx[0][8]] == [[[1, 5, 9]], [[2, 5, 7]]]
+    assert layers_idx[0][8][0]["prefill_len"] == 100
+    assert idx[0][0]["idx"].tolist() == [3] and prefill_res[0]["idx"].tolist() == [[4]]
+    prev = tt.set_tracer(tr)
+    assert tt.idx_tracer is tr and tt.set_tracer(prev) is tr and tt.idx_tracer is prev

@@ -505,3 +505,55 @@ def test_decode_chain_equals_single_calls(dtype, hidden, inter, H, KVH, vocab):
                        rope_pos=rope_pos, q_out=b["q"], k_cache_seq=b["kc"], v_cache_seq=b["vc"], cache_pos=cpos)
     ops().check_status("cuda")
     assert torch.equal(a["q"], b["q"]) and torch.equal(a["kc"], b["kc"]) and torch.equal(a["vc"], b["vc"])
+
+
+@pytest.mark.parametrize("thr", ["0.4", "0.7", "0.95"])
+def test_idx_commit_follows_reference_rule(thr):
+    """omnikv_idx_commit on the fixture's drifting index sequence: the same kept/replaced decisions as the
+    reference's OmniKVLazyCache.set_out_idx, overlap counts equal to the oracle's score times |new|."""
+    meta = json.loads((Path(__file__).resolve().parent / "golden" / "lazy_rule.json").read_text())
+    gold = meta["results"][thr]
+    seq = gi.lazy_rule_inputs()
+    k = seq[0].shape[1]
+    cap = k + 20
+    live = torch.zeros(1, cap, dtype=torch.int32, device="cuda")
+    live_n, applied, gather_n, overlap = (torch.zeros(1, dtype=torch.int32, device="cuda") for _ in range(4))
+    rule = oracle.OracleLazyRule(float(thr))
+    for s, idx in enumerate(seq):
+        new = torch.zeros(1, cap, dtype=torch.int32, device="cuda")
+        new[0, :k] = torch.from_numpy(idx[0]).to(torch.int32)
+        n = dev_i32([k])
+        ops().idx_commit(new, n, live, live_n, float(thr), applied, gather_n, overlap)
+        taken, score = rule.offer(torch.from_numpy(idx), 1)
+        assert bool(applied.item()) == gold["applied"][s] == taken
+        assert gather_n.item() == (k if taken else 0)
+        if s > 0:
+            assert overlap.item() == round(score * k)
+        assert live_n.item() == k
+        assert torch.equal(live[0, :k].cpu().long(), rule.live[1][0])
+
+
+def test_idx_commit_batch_and_edges():
+    """Per-sequence decisions in a batch, ragged counts, an empty list in use, identical lists (overlap 1 > any
+    threshold below 1: kept), and argument checks."""
+    cap = 64
+    new = torch.zeros(3, cap, dtype=torch.int32, device="cuda")
+    live = torch.zeros(3, cap, dtype=torch.int32, device="cuda")
+    new[0, :5] = torch.tensor([1, 3, 5, 7, 9]); live[0, :5] = torch.tensor([1, 3, 5, 7, 9])       # identical
+    new[1, :4] = torch.tensor([2, 4, 6, 8]); live[1, :6] = torch.tensor([0, 1, 2, 3, 5, 7])        # 1 of 4 shared
+    new[2, :3] = torch.tensor([10, 20, 30])                                                         # nothing in use
+    n = dev_i32([5, 4, 3]); m = dev_i32([5, 6, 0])
+    applied, gather_n, overlap = (torch.full((3,), -1, dtype=torch.int32, device="cuda") for _ in range(3))
+    ops().idx_commit(new, n, live, m, 0.5, applied, gather_n, overlap)
+    assert applied.tolist() == [0, 1, 1] and gather_n.tolist() == [0, 4, 3] and overlap.tolist() == [5, 1, 0]
+    assert m.tolist() == [5, 4, 3]
+    assert live[1, :4].tolist() == [2, 4, 6, 8] and live[2, :3].tolist() == [10, 20, 30]
+    assert live[0, :5].tolist() == [1, 3, 5, 7, 9]
+    # exactly at the threshold is NOT above it: replaced (2 of 4 shared, threshold 0.5)
+    new[1, :4] = torch.tensor([2, 4, 60, 80])
+    ops().idx_commit(new, n, live, m, 0.5, applied, gather_n, overlap)
+    assert applied.tolist()[1] == 1 and overlap.tolist()[1] == 2
+    with pytest.raises(Exception):
+        ops().idx_commit(new, n, new, m, 0.5, applied)
+    with pytest.raises(Exception):
+        ops().idx_commit(new.long(), n, live, m, 0.5, applied)

@@ -82,6 +82,52 @@ def test_fp32_logits_and_selection_match_oracle(selector, nsel, cache_cls, offlo
         assert len(set(mine.tolist()) ^ set(ref.tolist())) <= 2  # threshold-band swaps only
 
 
+@pytest.mark.parametrize("thr", [0.0, 0.5, 0.8, 1.0])
+@pytest.mark.parametrize("offload", [False, True])
+def test_lazy_cache_matches_oracle(thr, offload):
+    """cache_cls "lazy": a filter group keeps its rows while consecutive selections overlap by more than the
+    threshold.  Logits and the kept/replaced decisions follow the oracle with the same rule; at threshold 1
+    nothing is ever kept and the run equals the "multi" cache."""
+    cfg = small_config(cache_cls="lazy", skip_threshold=thr, real_offload=offload, num_of_selected_tokens=0.25)
+    lm, oracle = build(cfg, torch.float32)
+    g = torch.Generator().manual_seed(4)
+    ids = torch.randint(0, 1000, (1, 300), generator=g)
+    steps = 16
+    out = lm(input_ids=ids.cuda())
+    cache = out.past_key_values
+    lo, ocache = oracle.forward(ids)
+    kept = 0
+    for s in range(steps):
+        tok = lo[:, -1].argmax(-1, keepdim=True)
+        out = lm(input_ids=tok.cuda(), past_key_values=cache)
+        lo, ocache = oracle.forward(tok, ocache, fwd_no=s)
+        assert (out.logits.cpu() - lo).abs().max().item() <= 1e-4, s
+        for sid in (1, 3):
+            st = cache.lazy_state(sid)
+            taken, score = ocache.rule.last[sid]
+            assert st["applied"][0] == int(taken), (s, sid, score)
+            live = cache._idx[sid][0][0, : st["count"][0]].cpu().long()
+            assert torch.equal(live, ocache.rule.live[sid][0]), (s, sid)
+            if score >= 0:
+                assert st["overlap"][0] == round(score * oracle.selected[(s, sid)].shape[1])
+            kept += int(not taken)
+    if thr >= 1.0:
+        assert kept == 0
+    if thr == 0.0:
+        assert kept >= 2 * (steps - 1) - 2  # after the first step nearly every selection shares a token with the one in use
+
+
+def test_lazy_cache_in_cuda_graph():
+    """The rule runs on the device, so the lazy cache's decode step replays in a CUDA graph like the others."""
+    cfg = small_config(cache_cls="lazy", skip_threshold=0.5, real_offload=True)
+    lm, _ = build(cfg, torch.bfloat16)
+    g = torch.Generator().manual_seed(6)
+    ids = torch.randint(0, 1000, (1, 200), generator=g).cuda()
+    a = lm.generate_greedy(ids, max_new_tokens=12, use_cuda_graph=False)
+    b = lm.generate_greedy(ids, max_new_tokens=12, use_cuda_graph=True)
+    assert torch.equal(a, b)
+
+
 def _torch_attend(cache, q, layer_idx, out=None, score_out=None, score_len=None):
     """The reference's way on the same GPU: materialise what ``update`` returns (selected rows + tail, or the
     whole cache) and run softmax(q K^T / sqrt d) V with torch ops; filter layers also fill the score planes."""
@@ -259,3 +305,37 @@ def test_chat_api_factory_with_a_checkpoint_on_disk(tmp_path):
     assert text == " ".join(str(t) for t in want)
     sampled = chat(prompt, generation_config=SimpleNamespace(do_sample=True, temperature=0.7, top_p=0.9, max_new_tokens=5))
     assert 1 <= len(sampled.split()) <= 5
+
+
+def test_selected_index_tracer_records_what_was_selected(tmp_path):
+    """With a tracer installed every decode-time selection of every filter layer is recorded (indices, their
+    scores, prompt length) and the pickle reads back through read_idx_tracer in the reference's layout."""
+    from omnikv_b200 import tensor_tools as tt
+    cfg = small_config(selector_cls="last")
+    lm, oracle = build(cfg, torch.float32)
+    g = torch.Generator().manual_seed(8)
+    ids = torch.randint(0, 1000, (1, 200), generator=g)
+    tracer = tt.SelectedIndexTracer(desc="unit", directory=str(tmp_path))
+    prev = tt.set_tracer(tracer)
+    try:
+        steps = 5
+        got, want, cache = run_both(lm, oracle, ids, steps=steps)
+        tracer.append_out("sample 0")
+        tracer.save_idx()
+    finally:
+        tt.set_tracer(prev)
+    idx, out, layers_idx, prefill_res = tt.read_idx_tracer(str(tmp_path / "selected_index_unit.pkl"))
+    assert out == ["sample 0"] and tracer.num_samples == 1 and prefill_res == {} and idx == {}
+    assert sorted(layers_idx[0]) == [1, 3]
+    for layer in (1, 3):
+        recs = layers_idx[0][layer]
+        assert len(recs) == steps
+        for s, r in enumerate(recs):
+            ref = oracle.selected[(s, layer)]
+            assert r["prefill_len"] == 200 and r["idx"].dtype == torch.int64 and r["idx"].shape == ref.shape
+            assert len(set(r["idx"][0].tolist()) ^ set(ref[0].tolist())) <= 2
+            assert r["value"].shape == r["idx"].shape and r["value"].dtype == torch.float32
+            # recorded scores are those of the selected positions: all >= every unselected score is implied by
+            # top-k; here: finite and sorted positions
+            assert torch.isfinite(r["value"]).all()
+            assert torch.equal(r["idx"][0], torch.sort(r["idx"][0]).values)

@@ -125,3 +125,20 @@ def test_k_rule():
     assert oracle.selector_k_rule(2048, 20000, "exp", 16, 1) == (2033, 19985, 15)
     assert oracle.selector_k_rule(2048, 20000, "exp", 16, 40) == (2048, 20000, 0)
     assert oracle.selector_k_rule(3, 100, "uniform", 16, 2) == (1, 86, 14)
+
+
+@pytest.mark.parametrize("thr", ["0.4", "0.7", "0.95"])
+def test_lazy_rule_matches_reference(thr):
+    """Which steps re-gather, the overlap scores and the rows in use, against the reference's
+    OmniKVLazyCache.set_out_idx run on the same drifting index sequence."""
+    meta = json.loads((G / "lazy_rule.json").read_text())
+    seq = gi.lazy_rule_inputs()
+    assert abs(gi.checksum(seq) - meta["input_checksum"]) < 1e-6 * max(1.0, abs(meta["input_checksum"]))
+    gold = meta["results"][thr]
+    rule = oracle.OracleLazyRule(float(thr))
+    for s, idx in enumerate(seq):
+        taken, score = rule.offer(torch.from_numpy(idx), 1)
+        assert taken == gold["applied"][s]
+        assert abs(score - gold["scores"][s]) < 1e-9
+        # fixture rows: feature 0 of token t is 4 t, so the sum identifies the list in use
+        assert float(rule.live[1].sum()) * 4.0 == gold["live_sum"][s]
