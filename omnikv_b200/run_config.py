@@ -28,6 +28,9 @@ def main():
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--ctx", type=int, default=0, help="override the context length (offload: 450000)")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--skip-threshold", type=float, default=None,
+                    help="offload: use cache_cls lazy with this threshold (0 keeps the first selection for good: "
+                         "the step time without host-link traffic)")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -43,6 +46,8 @@ def main():
     else:
         steps = args.steps or 32
         B, lens = 1, [args.ctx or 450000]
+        if args.skip_threshold is not None:
+            base.update(cache_cls="lazy", skip_threshold=args.skip_threshold)
         cfg.set_config_of_compressor(**base, real_offload=True, selector_cls="last", num_of_selected_tokens=0.067)
     lm = OmniKVMulLM.from_config(cfg, dtype=torch.bfloat16, device=dev, seed=0)
     total = 2 + args.warmup + steps + 2
@@ -74,11 +79,18 @@ def main():
         hbm += 3 * sum(lens) * row // 2  # the window selectors read the filter layers' K a second time
     weights = 2 * sum(p.numel() for n_, p in lm.named_parameters() if "embed_tokens" not in n_)
     link = n_sparse * row * k0[0] if args.workload == "offload" else 0
+    regathers = None
+    if args.skip_threshold is not None and args.workload == "offload":
+        # selections that replaced the one in use during the last step, out of the filter groups
+        regathers = sum(cache.lazy_state(sel)["applied"][0] for sel in cache.groups)
+        if regathers == 0:
+            link = 0
     line = {"workload": args.workload, "batch": B, "context": lens if B > 1 else lens[0], "steps": steps,
             "ms_per_step": ms, "tokens_per_s": B * 1e3 / ms, "kv_bytes_per_step": hbm, "weight_bytes_per_step": weights,
             "hbm_gbs": (hbm + weights + link) / ms / 1e6, "host_link_bytes_per_step": link,
             "host_link_gbs": link / ms / 1e6 if link else None, "kv_fill_s": fill_s, "cuda_graph": not args.no_graph,
-            "selector": cfg.selector_cls, "launches_per_step": runner.launches_per_step}
+            "selector": cfg.selector_cls, "launches_per_step": runner.launches_per_step,
+            "cache_cls": cfg.get("cache_cls"), "regathers_last_step": regathers}
     print(json.dumps(line), flush=True)
 
 
