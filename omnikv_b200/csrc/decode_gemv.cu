@@ -23,6 +23,9 @@ namespace {
 constexpr int GV_CONSUMER_WARPS = 8;
 constexpr int GV_THREADS = (GV_CONSUMER_WARPS + 1) * 32;  // + one producer warp
 constexpr int GV_STAGES = 3;
+#ifndef GV_PACED_FILL
+#define GV_PACED_FILL 1
+#endif
 constexpr unsigned GV_SPIN_LIMIT = 1u << 24;
 
 enum Epilogue { EPI_QKV = 0, EPI_RESID = 1, EPI_GATEUP = 2, EPI_LOGITS = 3 };
@@ -67,7 +70,23 @@ struct GemvArgs {
   void* tp_h_out;                   // local [K]: CTA 0 stores the summed residual stream here
   const unsigned* tp_epoch;         // device word bumped once per decode step
   unsigned tp_seq;                  // flag value = epoch * 256 + seq + 1
+  int trace_slot;                   // profiling build: which slot of the stamp array this launch writes
 };
+
+#ifdef OMNIKV_GEMV_TRACE
+// Profiling build only (-DOMNIKV_GEMV_TRACE): per-CTA %globaltimer stamps of the single-phase kernel, one
+// slot per launch (the host numbers the launches 0..63 round-robin).
+__device__ unsigned long long g_gemv_trace[64 * 160 * 8];
+int g_trace_launch = 0;  // host: launches so far
+#define GEMV_STAMP(a, i)                                                                            \
+  do {                                                                                              \
+    unsigned long long t_;                                                                          \
+    asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t_));                                         \
+    if (blockIdx.x < 160) g_gemv_trace[((a).trace_slot * 160 + blockIdx.x) * 8 + (i)] = t_;         \
+  } while (0)
+#else
+#define GEMV_STAMP(a, i)
+#endif
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
 
@@ -187,6 +206,14 @@ __device__ __forceinline__ bool produce_phase(const GemvArgs& a, const Ring& rin
       atomicExch(a.status, 1);
       return false;
     }
+    // The first fill of the ring is paced: a chunk is asked for when the one before it has landed.  One
+    // chunk per SM in flight already saturates HBM; three per SM at once (28 MB) only build a queue that the
+    // consumers' loads of the activations -- issued a little later, and on the critical path of the whole
+    // kernel -- would have to wait behind (measured: 3.5 us instead of about 1).
+    if (GV_PACED_FILL && it > 0 && it < GV_STAGES && !mbar_wait(&ring.full_bar[it - 1], 0)) {
+      atomicExch(a.status, 1);
+      return false;
+    }
     // next chunk: from the shared counter (whoever is ready takes the next one, so slow SMs take fewer),
     // or this CTA's static share
     int c;
@@ -266,6 +293,7 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
   uint4* ns = xs + K / 8;
   float sq = 0.f;
   consumer_bar();  // the previous phase no longer reads the staging area
+  if (threadIdx.x == 0) GEMV_STAMP(a, 6);
   const bool tp_consume = a.tp_world > 1 && a.tp_my_partials != nullptr;
   if (tp_consume) {
     // every rank's partial sums of the previous projection must have landed in this GPU's memory: each rank
@@ -324,6 +352,7 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
     if (lane == 0) cs.ssq[warp] = sq;
   }
   consumer_bar();
+  if (threadIdx.x == 0) GEMV_STAMP(a, 7);
   if (a.norm_w) {
     float tot = 0.f;
 #pragma unroll
@@ -342,10 +371,18 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
     }
   }
   if (stamp && threadIdx.x == 0) *stamp = globaltimer_ns();  // activations loaded, norm known
+  if (threadIdx.x == 0) GEMV_STAMP(a, 2);
+#ifdef OMNIKV_GEMV_TRACE
+  bool first_stage = true;
+#endif
   unsigned long long my_best = 0ull;
   for (;; ++it) {
     const int slot = it % GV_STAGES;
     const bool ok = mbar_wait(&ring.full_bar[slot], (it / GV_STAGES) & 1);
+#ifdef OMNIKV_GEMV_TRACE
+    if (first_stage && threadIdx.x == 0) GEMV_STAMP(a, 3);  // first chunk has landed
+    first_stage = false;
+#endif
     if (!ok) {  // the copy never landed: flag it; every consumer leaves together after the barrier below
       cs.fail = 1;
       atomicExch(a.status, 2);
@@ -505,12 +542,18 @@ __global__ void __launch_bounds__(GV_THREADS, 1) decode_gemv_kernel(const GemvAr
   // scheduled behind it right away.  The producer starts streaming weights at once (they depend on nothing);
   // the consumers wait for the previous kernel before they touch activations or write any output.
   pdl_trigger();
+  if (threadIdx.x == 0) GEMV_STAMP(a, 0);
   if ((threadIdx.x >> 5) == GV_CONSUMER_WARPS) {
-    if ((threadIdx.x & 31) == 0) produce_phase<T, KV, WK, EPI>(a, ring, it);
+    if ((threadIdx.x & 31) == 0) {
+      produce_phase<T, KV, WK, EPI>(a, ring, it);
+      GEMV_STAMP(a, 5);  // last copy issued
+    }
     return;
   }
   pdl_wait();
+  if (threadIdx.x == 0) GEMV_STAMP(a, 1);
   consume_phase<T, KV, WK, EPI, false>(a, ring, cs, it);
+  if (threadIdx.x == 0) GEMV_STAMP(a, 4);
 }
 
 // ---- the GEMV chain of a decoder layer in ONE cooperative launch -----------------------------------
@@ -640,7 +683,13 @@ int launch_one(const GemvArgs& a, int n_sms, cudaStream_t st) {
   auto kern = decode_gemv_kernel<T, KV, WK, EPI>;
   OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int grid = a.n_chunks < n_sms ? a.n_chunks : n_sms;
+#ifdef OMNIKV_GEMV_TRACE
+  GemvArgs b = a;
+  b.trace_slot = g_trace_launch++ % 64;
+  OMNIKV_CUDA_OK(launch_pdl(kern, dim3(grid), dim3(GV_THREADS), smem, st, b));
+#else
   OMNIKV_CUDA_OK(launch_pdl(kern, dim3(grid), dim3(GV_THREADS), smem, st, a));
+#endif
   return OMNIKV_OK;
 }
 
@@ -896,3 +945,9 @@ extern "C" size_t omnikv_tp_exchange_bytes(int hidden) {
   if (hidden <= 0) return 0;
   return omnikv::tp_partials_bytes(hidden) + 2 * 8 * sizeof(unsigned) + 192;  // padded to a multiple of 256
 }
+
+#ifdef OMNIKV_GEMV_TRACE
+extern "C" int omnikv_debug_gemv_trace(unsigned long long* host_out, int n_words) {
+  return (int)cudaMemcpyFromSymbol(host_out, omnikv::g_gemv_trace, (size_t)n_words * 8);
+}
+#endif
