@@ -113,6 +113,8 @@ typedef struct {
                                  that uses this workspace; every call leaves them zero.  Calls that share a workspace
                                  must not overlap on the GPU. */
   size_t workspace_bytes;
+  int32_t* status;            /* optional device word: set to 5 if a bounded wait for a KV copy ran out (never
+                                 in a healthy run); left untouched otherwise */
 } omnikv_attn_params;
 
 /* Stream order: the kernel is launched as a programmatic dependent launch (unless OMNIKV_PDL=0).  When the

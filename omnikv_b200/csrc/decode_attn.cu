@@ -37,6 +37,7 @@ struct AttnArgs {
   float* ws_ml;
   unsigned* ws_cnt;   // [B*KVH] arrival counters of the splits, zero between launches
   int pdl_trigger;    // 1: the grid is fully resident, the next kernel may be scheduled early
+  int* status;        // device word for bounded-wait failures, or nullptr
   int B, H, KVH, G, S;
   float scale;
 };
@@ -137,7 +138,12 @@ __device__ __forceinline__ void finish_group(const AttnArgs& a, int b, int kvh, 
   if (tid == 0) a.ws_cnt[b * a.KVH + kvh] = 0u;
 }
 
-template <typename T, bool WITH_V, bool WITH_SCORE>
+// BULK: how a tile's rows travel to shared memory.  true: one 256-byte bulk copy per row (the copy engine moves
+// it and signals the stage's mbarrier) -- sixteen times fewer instructions and request slots than cp.async, which
+// is what a sparse layer's scattered rows need (22.5 instead of 28.7 us per layer).  false: sixteen 16-byte
+// cp.async per row; for a dense layer's long contiguous streams this keeps more requests in flight and is the
+// faster of the two there (99.8 against 103.7 us per layer).
+template <typename T, bool WITH_V, bool WITH_SCORE, bool BULK>
 __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const AttnArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int last_flag;
@@ -196,24 +202,46 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
   // lookup in the index list), issue() starts the copies.  resolve() of the NEXT tile runs right after issue() of
   // the current one, so the index loads are in flight during a whole tile of compute and never sit between a
   // warp and its copies (the copies are asm statements the compiler does not move loads across).
-  constexpr int RPT = TILE / 8;  // rows per thread and tile
-  const int cc = tid & 15, rowi = tid >> 4;
-  auto resolve = [&](int tile, long long (&off)[RPT]) {
+  auto row_offset = [&](int tile, int row) -> long long {
+    const int R = r0 + tile * TILE + row;
+    if (tile >= ntiles || R >= r1) return -1;
+    if (R < nA) {
+      const long long pos = idx ? (long long)__ldg(idx + R) : (long long)R;
+      return pos * a.a_sr;
+    }
+    return ((long long)(startB + (R - nA)) * a.b_sr) | (1ll << 62);  // bit 62: segment B
+  };
+  // ---- BULK: thread t owns row t & 63 of every tile, K for t < 64 and V for t >= 64 ----
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  const int my_row = tid & (TILE - 1);
+  const bool my_v = tid >= TILE;
+  constexpr unsigned ROW_BYTES = kHeadDim * sizeof(T);
+  auto issue_bulk = [&](int tile, long long off) {
+    const int slot = tile % STAGES;
+    unsigned char* dst = smem + slot * STAGE_BYTES + (my_v ? TILE_BYTES : 0) + my_row * PITCH;
+    if (tid == 0) {  // bytes this stage will receive: its valid rows, K and V
+      const int nvalid = min(TILE, r1 - (r0 + tile * TILE));
+      mbar_expect_tx(&full_bar[slot], (unsigned)nvalid * ROW_BYTES * (WITH_V ? 2u : 1u));
+    }
+    if (my_v && !WITH_V) return;
+    if (off >= 0) {
+      const bool segB = (off >> 62) != 0;
+      const long long o = off & ~(1ll << 62);
+      const T* src = (my_v ? (segB ? vB : vA) : (segB ? kB : kA)) + o;
+      tma_bulk_g2s(dst, src, ROW_BYTES, &full_bar[slot]);
+    } else {  // a row past the end of the chunk: zeros, so that 0 * V stays 0
 #pragma unroll
-    for (int i = 0; i < RPT; ++i) {
-      const int R = r0 + tile * TILE + rowi + 8 * i;
-      off[i] = -1;
-      if (tile < ntiles && R < r1) {
-        if (R < nA) {
-          const long long pos = idx ? (long long)__ldg(idx + R) : (long long)R;
-          off[i] = pos * a.a_sr;
-        } else {
-          off[i] = ((long long)(startB + (R - nA)) * a.b_sr) | (1ll << 62);  // bit 62: segment B
-        }
-      }
+      for (int c = 0; c < (int)ROW_BYTES / 16; ++c) *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(0, 0, 0, 0);
     }
   };
-  auto issue = [&](int slot, const long long (&off)[RPT]) {
+  // ---- cp.async: thread t copies 16-byte column t & 15 of rows (t >> 4) + 8 i ----
+  constexpr int RPT = TILE / 8;  // rows per thread and tile
+  const int cc = tid & 15, rowi = tid >> 4;
+  auto resolve_cp = [&](int tile, long long (&off)[RPT]) {
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) off[i] = row_offset(tile, rowi + 8 * i);
+  };
+  auto issue_cp = [&](int slot, const long long (&off)[RPT]) {
     unsigned char* ks = smem + slot * STAGE_BYTES;
     unsigned char* vs = ks + TILE_BYTES;
 #pragma unroll
@@ -232,15 +260,32 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
   };
 
   // the index lookups of the first STAGES tiles go out together, then the copies of the first STAGES-1 tiles
-  long long off_first[STAGES - 1][RPT];
-  long long off_next[RPT];
+  long long offb_next = -1;
+  long long offc_next[RPT];
+  if constexpr (BULK) {
+    if (tid == 0) {
 #pragma unroll
-  for (int s = 0; s < STAGES - 1; ++s) resolve(s, off_first[s]);
-  resolve(STAGES - 1, off_next);
+      for (int s = 0; s < STAGES; ++s) mbar_init(&full_bar[s], 1);
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncthreads();
+    long long first[STAGES - 1];
 #pragma unroll
-  for (int s = 0; s < STAGES - 1; ++s) {
-    if (s < ntiles) issue(s, off_first[s]);
-    cp_async_commit();
+    for (int s = 0; s < STAGES - 1; ++s) first[s] = row_offset(s, my_row);
+    offb_next = row_offset(STAGES - 1, my_row);
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s)
+      if (s < ntiles) issue_bulk(s, first[s]);
+  } else {
+    long long first[STAGES - 1][RPT];
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) resolve_cp(s, first[s]);
+    resolve_cp(STAGES - 1, offc_next);
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+      if (s < ntiles) issue_cp(s, first[s]);
+      cp_async_commit();
+    }
   }
 
   if (early) {
@@ -281,13 +326,19 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
   float* score_row = WITH_SCORE ? a.score_out + ((size_t)kvh * a.B + b) * a.score_stride : nullptr;
 
   for (int tile = 0; tile < ntiles; ++tile) {
-    cp_async_wait<STAGES - 2>();
-    __syncthreads();
-    {
-      const int nt = tile + STAGES - 1;
-      if (nt < ntiles) issue(nt % STAGES, off_next);
+    const int nt = tile + STAGES - 1;
+    if constexpr (BULK) {
+      // every thread is done with tile - 1, so its slot may be refilled; then wait for this tile's bytes
+      __syncthreads();
+      if (nt < ntiles) issue_bulk(nt, offb_next);
+      offb_next = row_offset(nt + 1, my_row);
+      if (!mbar_wait(&full_bar[tile % STAGES], (tile / STAGES) & 1) && a.status) atomicExch(a.status, 5);
+    } else {
+      cp_async_wait<STAGES - 2>();
+      __syncthreads();
+      if (nt < ntiles) issue_cp(nt % STAGES, offc_next);
       cp_async_commit();
-      resolve(nt + 1, off_next);
+      resolve_cp(nt + 1, offc_next);
     }
     const unsigned char* ks = smem + (tile % STAGES) * STAGE_BYTES;
     const unsigned char* vs = ks + TILE_BYTES;
@@ -367,7 +418,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
       }
     }
   }
-  cp_async_wait<0>();
+  if constexpr (!BULK) cp_async_wait<0>();
   ATTN_STAMP(3);  // all tiles consumed
   if (!WITH_V) return;
   __syncthreads();  // every warp is done with the ring: reuse it for the cross-warp merge
@@ -561,19 +612,24 @@ int launch_mma(AttnArgs a, bool with_v, bool with_score, cudaStream_t st) {
   OMNIKV_CUDA_OK(cudaGetDevice(&dev));
   OMNIKV_CUDA_OK(cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev));
   a.pdl_trigger = ((long long)a.S * a.KVH * a.B <= 2ll * n_sms) ? 1 : 0;  // two CTAs of this kernel fit per SM
+  const bool bulk = a.idxA != nullptr;  // scattered rows: bulk copies; contiguous streams: cp.async
+  auto go = [&](auto kern, int smem) -> int {
+    OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    OMNIKV_CUDA_OK(launch_pdl(kern, grid, block, smem, st, a));
+    return OMNIKV_OK;
+  };
+  int rc;
   if (with_v && with_score) {
-    auto kern = decode_attn_mma_kernel<T, true, true>;
-    OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, mma_smem_bytes<true>()));
-    OMNIKV_CUDA_OK(launch_pdl(kern, grid, block, mma_smem_bytes<true>(), st, a));
+    rc = bulk ? go(decode_attn_mma_kernel<T, true, true, true>, mma_smem_bytes<true>())
+              : go(decode_attn_mma_kernel<T, true, true, false>, mma_smem_bytes<true>());
   } else if (with_v) {
-    auto kern = decode_attn_mma_kernel<T, true, false>;
-    OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, mma_smem_bytes<true>()));
-    OMNIKV_CUDA_OK(launch_pdl(kern, grid, block, mma_smem_bytes<true>(), st, a));
+    rc = bulk ? go(decode_attn_mma_kernel<T, true, false, true>, mma_smem_bytes<true>())
+              : go(decode_attn_mma_kernel<T, true, false, false>, mma_smem_bytes<true>());
   } else {
-    auto kern = decode_attn_mma_kernel<T, false, true>;
-    OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, mma_smem_bytes<false>()));
-    OMNIKV_CUDA_OK(launch_pdl(kern, grid, block, mma_smem_bytes<false>(), st, a));
+    rc = bulk ? go(decode_attn_mma_kernel<T, false, true, true>, mma_smem_bytes<false>())
+              : go(decode_attn_mma_kernel<T, false, true, false>, mma_smem_bytes<false>());
   }
+  if (rc != OMNIKV_OK) return rc;
   OMNIKV_CUDA_OK(cudaGetLastError());
   return OMNIKV_OK;
 }
@@ -650,6 +706,7 @@ extern "C" int omnikv_decode_attn(const omnikv_attn_params* p, void* stream) {
   a.B = p->B; a.H = p->H; a.KVH = p->KVH; a.G = G; a.S = p->n_splits;
   a.scale = p->scale;
   a.pdl_trigger = 0;
+  a.status = p->status;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (p->dtype) {
     case OMNIKV_BF16: return launch_mma<__nv_bfloat16>(a, with_v, with_score, st);

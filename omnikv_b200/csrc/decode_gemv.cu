@@ -26,7 +26,7 @@ constexpr int GV_STAGES = 3;
 #ifndef GV_PACED_FILL
 #define GV_PACED_FILL 1
 #endif
-constexpr unsigned GV_SPIN_LIMIT = 1u << 24;
+constexpr unsigned GV_SPIN_LIMIT = kSpinLimit;
 
 enum Epilogue { EPI_QKV = 0, EPI_RESID = 1, EPI_GATEUP = 2, EPI_LOGITS = 3 };
 
@@ -88,42 +88,6 @@ int g_trace_launch = 0;  // host: launches so far
 #define GEMV_STAMP(a, i)
 #endif
 
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-// Bounded wait for the phase with the given parity; false if the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
-  const unsigned addr = smem_u32(bar);
-  for (unsigned spin = 0; spin < GV_SPIN_LIMIT; ++spin) {
-    unsigned ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
-__device__ __forceinline__ void tma_bulk_g2s(void* smem_dst, const void* gmem_src, unsigned bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
-                   smem_u32(smem_dst)),
-               "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
-
 // Ask the memory system to bring [src, src + bytes) into L2; nothing waits for it.
 __device__ __forceinline__ void l2_prefetch(const void* gmem_src, unsigned bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(gmem_src), "r"(bytes) : "memory");
@@ -171,6 +135,7 @@ struct Ring {
   unsigned slot_bytes;
   int* slot_chunk;          // chunk held by each slot, -1 = the phase has no more chunks for this CTA
   unsigned char* stage_x;   // staging area for the phase's activations (and norm weights), 16-byte aligned
+  unsigned stage_bytes;     // its size
 };
 
 // First row of the two pieces of chunk c.
@@ -263,6 +228,7 @@ __device__ __forceinline__ void prefetch_phase_head(const GemvArgs& a) {
 
 // Scratch in static shared memory used by the consumers.
 struct ConsumerShared {
+  float inv_freq[64];  // EPI_QKV: the rotary frequencies, staged once
   float part[2][GV_CONSUMER_WARPS][4];
   float ssq[GV_CONSUMER_WARPS];
   unsigned long long best[GV_CONSUMER_WARPS];
@@ -344,6 +310,25 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
         for (int e = 0; e < 8; ++e) sq = fmaf(f[e], f[e], sq);
       }
     }
+  }
+  // Whatever else the epilogue needs from global memory is fetched HERE, once: a load issued in the steady
+  // state waits behind this SM's own weight copies (up to three chunks, several microseconds) and the warp
+  // that waits for it holds up every stage.  The residual vector goes to the free half of the staging area
+  // (this epilogue has no norm weights); the rotary frequencies and the two positions to shared memory /
+  // registers.
+  const T* rs_s = nullptr;
+  if (EPI == EPI_RESID && a.resid && a.tp_world <= 1 && (a.N & 7) == 0 &&
+      (size_t)K * 2 + (size_t)a.N * 2 <= ring.stage_bytes &&
+      (reinterpret_cast<uintptr_t>(a.resid) & 15) == 0) {
+    const uint4* rg = reinterpret_cast<const uint4*>(a.resid);
+    for (int v = tid; v < a.N / 8; v += GV_CONSUMER_WARPS * 32) ns[v] = COHERENT ? __ldcg(rg + v) : rg[v];
+    rs_s = reinterpret_cast<const T*>(ns);
+  }
+  int rope_pos_r = 0, cache_pos_r = 0;
+  if (EPI == EPI_QKV) {
+    if (tid < 64) cs.inv_freq[tid] = a.inv_freq[tid];
+    rope_pos_r = *a.rope_pos;
+    cache_pos_r = *a.pos;
   }
   float rstd = 1.f;
   if (a.norm_w) {
@@ -439,7 +424,10 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
         const T* rs = static_cast<const T*>(a.resid);
         T* out = static_cast<T*>(a.out);
         float b0 = 0.f, b1 = 0.f;
-        if (rs) {
+        if (rs_s) {
+          b0 = to_float(rs_s[row0]);
+          b1 = to_float(rs_s[row1]);
+        } else if (rs) {
           if (COHERENT) {
             const unsigned short u0 = __ldcg(reinterpret_cast<const unsigned short*>(rs) + row0);
             const unsigned short u1 = __ldcg(reinterpret_cast<const unsigned short*>(rs) + row1);
@@ -466,7 +454,7 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
         float o0 = r0, o1 = r1;
         if (head < a.H + a.KVH) {
           float sn, cs_;
-          sincosf((float)(*a.rope_pos) * a.inv_freq[i2], &sn, &cs_);
+          sincosf((float)rope_pos_r * cs.inv_freq[i2], &sn, &cs_);
           o0 = r0 * cs_ - r1 * sn;
           o1 = r1 * cs_ + r0 * sn;
         }
@@ -474,9 +462,9 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
         if (head < a.H) {
           dst = static_cast<T*>(a.q_out) + (size_t)head * 128;
         } else if (head < a.H + a.KVH) {
-          dst = static_cast<T*>(a.k_cache) + (size_t)(head - a.H) * a.kv_sh + (size_t)(*a.pos) * a.kv_sr;
+          dst = static_cast<T*>(a.k_cache) + (size_t)(head - a.H) * a.kv_sh + (size_t)cache_pos_r * a.kv_sr;
         } else {
-          dst = static_cast<T*>(a.v_cache) + (size_t)(head - a.H - a.KVH) * a.kv_sh + (size_t)(*a.pos) * a.kv_sr;
+          dst = static_cast<T*>(a.v_cache) + (size_t)(head - a.H - a.KVH) * a.kv_sh + (size_t)cache_pos_r * a.kv_sr;
         }
         dst[i2] = from_float<T>(o0);
         dst[i2 + 64] = from_float<T>(o1);
@@ -536,7 +524,7 @@ __global__ void __launch_bounds__(GV_THREADS, 1) decode_gemv_kernel(const GemvAr
   __shared__ int slot_chunk[GV_STAGES];
   ring_init(full_bar, empty_bar, cs);
   constexpr unsigned SLOT = GV_CONSUMER_WARPS / WK * K * 2;
-  Ring ring{smem, full_bar, empty_bar, SLOT, slot_chunk, smem + GV_STAGES * SLOT};
+  Ring ring{smem, full_bar, empty_bar, SLOT, slot_chunk, smem + GV_STAGES * SLOT, (unsigned)K * 4u};
   int it = 0;
   // Programmatic dependent launch: the grid is one CTA per SM, all resident, so the next kernel may be
   // scheduled behind it right away.  The producer starts streaming weights at once (they depend on nothing);
@@ -603,8 +591,9 @@ __global__ void __launch_bounds__(GV_THREADS, 1) decode_chain_kernel(const Chain
   if (tr && threadIdx.x == 0) tr[0] = globaltimer_ns();
   __shared__ int slot_chunk[GV_STAGES];
   ring_init(full_bar, empty_bar, cs);
+  constexpr unsigned CHAIN_STAGE_BYTES = 4u * (WKH_ * KVH_ * 256) > 2u * (WKI_ * KVI_ * 256) ? 4u * (WKH_ * KVH_ * 256) : 2u * (WKI_ * KVI_ * 256);
   constexpr unsigned SLOT = SLOT_H > SLOT_I ? SLOT_H : SLOT_I;
-  Ring ring{smem, full_bar, empty_bar, SLOT, slot_chunk, smem + GV_STAGES * SLOT};
+  Ring ring{smem, full_bar, empty_bar, SLOT, slot_chunk, smem + GV_STAGES * SLOT, CHAIN_STAGE_BYTES};
   int it = 0;
   if ((threadIdx.x >> 5) == GV_CONSUMER_WARPS) {
     if ((threadIdx.x & 31) == 0) {
