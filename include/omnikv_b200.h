@@ -246,6 +246,20 @@ int omnikv_kv_append(int dtype, const void* k_new, const void* v_new, void* k_ca
                      int64_t cache_stride_b, int64_t cache_stride_h, int64_t cache_stride_row,
                      const int32_t* pos, void* stream);
 
+/* The current token of every sequence straight from a fused QKV projection (batched decode):
+ * qkv[b] = [H query heads | KVH key heads | KVH value heads] x head_dim.  q and k are rotated (pairs (i, i+64) of
+ * a head by rope_pos[b] * inv_freq[i], the rotate_half convention of the reference's decoder; fp32 arithmetic,
+ * rounded once), q is written to q_out[b] = [H, head_dim], k and v to row cache_pos[b] of the caches
+ * (cache_pos[b] < 0: sequence skipped).  Replaces apply_rotary + the contiguous copies + omnikv_kv_append of the
+ * PyTorch path: one launch instead of thirteen. */
+int omnikv_rope_append(int dtype, const void* qkv, int64_t qkv_stride_b, int B, int H, int KVH, int head_dim,
+                       const float* inv_freq, const int32_t* rope_pos, void* q_out, int64_t q_stride_b,
+                       void* k_cache, void* v_cache, int64_t cache_stride_b, int64_t cache_stride_h,
+                       int64_t cache_stride_row, const int32_t* cache_pos, void* stream);
+/* act[b][j] = silu(gate_up[b][j]) * gate_up[b][inter + j] for j < inter (SwiGLU of a fused gate/up projection). */
+int omnikv_silu_mul(int dtype, const void* gate_up, int64_t gate_up_stride_b, void* act, int64_t act_stride_b,
+                    int B, int inter, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Batch-1 decode step: weight-streaming kernels with the element-wise work of the decoder layer
  * fused in.  In the reference these are third-party transformers modules called around the hot

@@ -73,11 +73,19 @@ constexpr int mma_smem_bytes() {
   return STAGES * (WITH_V ? 2 : 1) * TILE_BYTES + Q_BYTES;
 }
 
-// Row range [r0, r1) of split `split` out of S for a list of n rows (chunks are TILE-aligned).
-__device__ __forceinline__ void split_range(int n, int S, int split, int& r0, int& r1) {
-  int chunk = ceil_div(ceil_div(n, S), TILE) * TILE;
-  r0 = split * chunk;
+// Row range [r0, r1) of split `split` out of S for a list of n rows (chunks are TILE-aligned).  The chunk
+// length comes from the LONGEST sequence of the batch: every CTA then has the same amount of work and a
+// short sequence simply uses fewer of its S splits (the rest hand in empty partials).  Sizing the chunks
+// per sequence instead left the CTAs of short sequences idle while the longest one finished.
+__device__ __forceinline__ void split_range(int n, int n_max, int S, int split, int& r0, int& r1) {
+  int chunk = ceil_div(ceil_div(n_max, S), TILE) * TILE;
+  r0 = min(n, split * chunk);
   r1 = min(n, r0 + chunk);
+}
+__device__ __forceinline__ int batch_max_rows(const AttnArgs& a, int n) {
+  int n_max = n;
+  for (int bb = 0; bb < a.B; ++bb) n_max = max(n_max, a.lenA[bb] + (a.lenB ? a.lenB[bb] : 0));
+  return n_max;
 }
 
 // After a CTA has written its partials: count it in; the CTA that completes the count of its (b, kvh)
@@ -167,7 +175,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
   const int startB = a.startB ? a.startB[b] : 0;
   const int n = nA + nB;
   int r0, r1;
-  split_range(n, a.S, split, r0, r1);
+  split_range(n, a.B > 1 ? batch_max_rows(a, n) : n, a.S, split, r0, r1);
   const int ntiles = r1 > r0 ? ceil_div(r1 - r0, TILE) : 0;
   const bool early = ntiles > 0 && (r1 < n || ntiles > STAGES - 1);
   if (!early) {
@@ -488,7 +496,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attn_f32_kernel(const AttnArg
   const int nB = a.lenB ? a.lenB[b] : 0;
   const int n = nA + nB;
   int r0, r1;
-  split_range(n, a.S, split, r0, r1);
+  split_range(n, a.B > 1 ? batch_max_rows(a, n) : n, a.S, split, r0, r1);
 
   const float* kA = static_cast<const float*>(a.kA) + (size_t)b * a.a_sb + (size_t)kvh * a.a_sh;
   const float* vA = with_v ? static_cast<const float*>(a.vA) + (size_t)b * a.a_sb + (size_t)kvh * a.a_sh : nullptr;

@@ -43,6 +43,54 @@ __global__ void kv_append_kernel(const unsigned char* k_new, const unsigned char
   *reinterpret_cast<uint4*>(v_cache + dst) = *reinterpret_cast<const uint4*>(v_new + src);
 }
 
+// The current token of every sequence, straight from the fused QKV projection: one thread per rotary pair
+// (i, i + 64) of a head.  q and k are rotated by angle rope_pos[b] * inv_freq[i] (computed in fp32, rounded
+// once); q goes to q_out, k and v to row cache_pos[b] of the layer's cache.
+template <typename T>
+__global__ void __launch_bounds__(256) rope_append_kernel(const T* __restrict__ qkv, int64_t qkv_sb, int H, int KVH,
+                                                          const float* __restrict__ inv_freq,
+                                                          const int* __restrict__ rope_pos, T* __restrict__ q_out,
+                                                          int64_t q_sb, T* k_cache, T* v_cache, int64_t c_sb,
+                                                          int64_t c_sh, int64_t c_sr, const int* __restrict__ cache_pos) {
+  const int b = blockIdx.y;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  const int heads = H + 2 * KVH;
+  if (t >= heads * 64) return;
+  const int hh = t >> 6, i = t & 63;
+  const T* src = qkv + (size_t)b * qkv_sb + (size_t)hh * kHeadDim;
+  float x0 = to_float(src[i]), x1 = to_float(src[i + 64]);
+  if (hh < H + KVH) {
+    float sn, cs;
+    sincosf((float)rope_pos[b] * inv_freq[i], &sn, &cs);
+    const float r0 = x0 * cs - x1 * sn, r1 = x1 * cs + x0 * sn;
+    x0 = r0;
+    x1 = r1;
+  }
+  T* dst;
+  if (hh < H) {
+    dst = q_out + (size_t)b * q_sb + (size_t)hh * kHeadDim;
+  } else {
+    const int64_t p = cache_pos[b];
+    if (p < 0) return;
+    const bool is_k = hh < H + KVH;
+    const int kvh = is_k ? hh - H : hh - H - KVH;
+    dst = (is_k ? k_cache : v_cache) + (size_t)b * c_sb + (size_t)kvh * c_sh + (size_t)p * c_sr;
+  }
+  dst[i] = from_float<T>(x0);
+  dst[i + 64] = from_float<T>(x1);
+}
+
+// act[b][j] = silu(gu[b][j]) * gu[b][inter + j]: the SwiGLU product of a fused gate/up projection.
+template <typename T>
+__global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gu, int64_t gu_sb, T* __restrict__ act,
+                                                       int64_t act_sb, int inter) {
+  const int b = blockIdx.y;
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= inter) return;
+  const float g = to_float(gu[(size_t)b * gu_sb + j]), u = to_float(gu[(size_t)b * gu_sb + inter + j]);
+  act[(size_t)b * act_sb + j] = from_float<T>(g / (1.f + expf(-g)) * u);
+}
+
 // Host-link gather.  One selected token is one contiguous chunk of n_layers*2*KVH rows in pinned
 // host memory; row r of the chunk (layer l, K|V c, head h) goes to staged[l][c][h][j][:].
 // A warp copies rows with one 16-byte load per lane per step, several rows in flight.
@@ -185,6 +233,58 @@ extern "C" int omnikv_kv_append(int dtype, const void* k_new, const void* v_new,
   else
     kv_append_kernel<2><<<grid, threads, 0, st>>>(kn, vn, kc, vc, KVH, new_stride_b, new_stride_h, cache_stride_b,
                                                   cache_stride_h, cache_stride_row, pos);
+  OMNIKV_CUDA_OK(cudaGetLastError());
+  return OMNIKV_OK;
+}
+
+extern "C" int omnikv_rope_append(int dtype, const void* qkv, int64_t qkv_stride_b, int B, int H, int KVH,
+                                  int head_dim, const float* inv_freq, const int32_t* rope_pos, void* q_out,
+                                  int64_t q_stride_b, void* k_cache, void* v_cache, int64_t cache_stride_b,
+                                  int64_t cache_stride_h, int64_t cache_stride_row, const int32_t* cache_pos,
+                                  void* stream) {
+  using namespace omnikv;
+  if (!qkv || !inv_freq || !rope_pos || !q_out || !k_cache || !v_cache || !cache_pos || B <= 0 || H <= 0 || KVH <= 0)
+    return OMNIKV_E_BADARG;
+  if (head_dim != kHeadDim) return OMNIKV_E_UNSUPPORTED;
+  dim3 grid(ceil_div((H + 2 * KVH) * 64, 256), B);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define OMNIKV_ROPE_LAUNCH(T)                                                                                    \
+  rope_append_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(qkv), qkv_stride_b, H, KVH, inv_freq, rope_pos, \
+                                              static_cast<T*>(q_out), q_stride_b, static_cast<T*>(k_cache),         \
+                                              static_cast<T*>(v_cache), cache_stride_b, cache_stride_h,             \
+                                              cache_stride_row, cache_pos)
+  switch (dtype) {
+    case OMNIKV_BF16: OMNIKV_ROPE_LAUNCH(__nv_bfloat16); break;
+    case OMNIKV_F16: OMNIKV_ROPE_LAUNCH(__half); break;
+    case OMNIKV_F32: OMNIKV_ROPE_LAUNCH(float); break;
+    default: return OMNIKV_E_UNSUPPORTED;
+  }
+#undef OMNIKV_ROPE_LAUNCH
+  OMNIKV_CUDA_OK(cudaGetLastError());
+  return OMNIKV_OK;
+}
+
+extern "C" int omnikv_silu_mul(int dtype, const void* gate_up, int64_t gate_up_stride_b, void* act,
+                               int64_t act_stride_b, int B, int inter, void* stream) {
+  using namespace omnikv;
+  if (!gate_up || !act || B <= 0 || inter <= 0) return OMNIKV_E_BADARG;
+  dim3 grid(ceil_div(inter, 256), B);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case OMNIKV_BF16:
+      silu_mul_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(gate_up), gate_up_stride_b,
+                                                           static_cast<__nv_bfloat16*>(act), act_stride_b, inter);
+      break;
+    case OMNIKV_F16:
+      silu_mul_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(gate_up), gate_up_stride_b,
+                                                    static_cast<__half*>(act), act_stride_b, inter);
+      break;
+    case OMNIKV_F32:
+      silu_mul_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(gate_up), gate_up_stride_b,
+                                                   static_cast<float*>(act), act_stride_b, inter);
+      break;
+    default: return OMNIKV_E_UNSUPPORTED;
+  }
   OMNIKV_CUDA_OK(cudaGetLastError());
   return OMNIKV_OK;
 }

@@ -199,6 +199,17 @@ class OmniKVAttention(nn.Module):
     def forward(self, hidden_states, position_embeddings, past_key_value, score_out=None, score_len=None):
         B, n, _ = hidden_states.shape
         cos, sin = position_embeddings
+        rope_pos = getattr(past_key_value, "rope_pos_dev", None)
+        if n == 1 and rope_pos is not None and hidden_states.is_cuda and self.head_dim == 128:
+            # decode: rotate q and k and append k, v to the cache in one kernel, straight from the fused projection
+            qkv = F.linear(hidden_states.view(B, -1), self.qkv_weight)
+            q = torch.empty(B, self.num_heads, self.head_dim, dtype=qkv.dtype, device=qkv.device)
+            k_buf, v_buf, pos = past_key_value.write_target_batch(self.layer_idx)
+            ops.rope_append(qkv, self.num_heads, self.num_key_value_heads, self.rotary_emb.inv_freq, rope_pos, q,
+                            k_buf, v_buf, pos)
+            o = past_key_value.attend(q, self.layer_idx, score_out=score_out, score_len=score_len)
+            o = F.linear(o.view(B, 1, self.num_heads * self.head_dim), self.o_weight)
+            return self.tp.all_reduce_sum(o) if self.tp is not None else o
         q, k, v = self.qkv(hidden_states, cos, sin)
         if n > 1:  # prefill: full causal attention over the fresh keys (what cache.update returns)
             k, v = past_key_value.update(k, v, self.layer_idx)
@@ -226,8 +237,12 @@ class OmniKVMLP(nn.Module):
 
     def forward(self, x):
         gu = F.linear(x, self.gate_up_weight)
-        g, u = gu[..., : self.intermediate_size], gu[..., self.intermediate_size:]
-        o = F.linear(F.silu(g) * u, self.down_weight)
+        if x.is_cuda and x.shape[-2] == 1:  # decode: one kernel for silu(gate) * up
+            act = ops.silu_mul(gu.view(-1, 2 * self.intermediate_size)).view(*x.shape[:-1], self.intermediate_size)
+        else:
+            g, u = gu[..., : self.intermediate_size], gu[..., self.intermediate_size:]
+            act = F.silu(g) * u
+        o = F.linear(act, self.down_weight)
         return self.tp.all_reduce_sum(o) if self.tp is not None else o
 
 
@@ -522,6 +537,9 @@ class OmniKVMulModel(nn.Module):
             cache.begin_decode_step()
             if position_ids is None:
                 position_ids = cache.pos_dev[:, None]
+                cache.rope_pos_dev = cache.pos_dev
+            else:  # the caller's positions (int32 on the device) for the fused rotate-and-append kernel
+                cache.rope_pos_dev = position_ids.reshape(-1).to(torch.int32).contiguous()
         elif position_ids is None:
             position_ids = torch.arange(n, device=h.device)[None, :].expand(B, n)
         pos_emb = self.rotary_emb(h, position_ids)

@@ -274,6 +274,12 @@ class OmniKVMultiStageCache:
         pos = self.tail_pos_dev if self.is_offloaded(layer_idx) else self.pos_dev
         ops.kv_append(k_new, v_new, self._k[layer_idx], self._v[layer_idx], pos)
 
+    def write_target_batch(self, layer_idx: int):
+        """(k buffer, v buffer, row index tensor) for the current token of every sequence: the layer's
+        ``[B, KVH, rows, d]`` views and the int32 device positions (tail-relative for offloaded layers)."""
+        pos = self.tail_pos_dev if self.is_offloaded(layer_idx) else self.pos_dev
+        return self._k[layer_idx], self._v[layer_idx], pos
+
     def write_target(self, layer_idx: int):
         """(k rows, v rows, row index tensor) the current token of sequence 0 is written to: ``[KVH, rows, d]``
         views of the layer's buffer and the int32 device position (tail-relative for offloaded layers)."""

@@ -70,7 +70,11 @@ def workspace(device, nbytes: int, tag: str = "default") -> torch.Tensor:
 
 def default_splits(B: int, KVH: int, max_rows: int, device) -> int:
     """Split count that fills the GPU with about two CTAs per SM, at least 128 rows per split."""
-    s = (2 * sm_count(device)) // max(1, B * KVH)
+    ctas = B * KVH
+    if B > 1:  # ragged batches: chunks are sized by the longest sequence, so aim at two waves of equal CTAs
+        s = -(-4 * sm_count(device) // ctas)
+    else:
+        s = (2 * sm_count(device)) // max(1, ctas)
     return max(1, min(s, (max_rows + 127) // 128))
 
 
@@ -264,6 +268,42 @@ def kv_append(k_new: torch.Tensor, v_new: torch.Tensor, k_cache: torch.Tensor, v
                                          v_cache.data_ptr(), B, KVH, d, k_new.stride(0), k_new.stride(1), sb, sh, sr,
                                          pos.data_ptr(), _stream()), "omnikv_kv_append")
     _count(1)
+
+
+def rope_append(qkv: torch.Tensor, H: int, KVH: int, inv_freq: torch.Tensor, rope_pos: torch.Tensor,
+                q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cache_pos: torch.Tensor) -> None:
+    """``omnikv_rope_append``.  qkv ``[B, (H+2KVH)*128]`` (rows contiguous); q_out ``[B, H, 128]``; caches
+    ``[B, KVH, rows, 128]``; rope_pos, cache_pos int32 ``[B]`` on the device; inv_freq fp32 ``[64]``."""
+    _need_cuda(qkv, inv_freq, rope_pos, q_out, k_cache, v_cache, cache_pos)
+    B = qkv.shape[0]
+    if qkv.dim() != 2 or qkv.stride(1) != 1 or qkv.shape[1] != (H + 2 * KVH) * 128:
+        raise abi.OmniKVError("rope_append: qkv must be [B, (H+2KVH)*128] with contiguous rows")
+    if q_out.shape != (B, H, 128) or q_out.stride(2) != 1 or q_out.stride(1) != 128 or q_out.dtype != qkv.dtype:
+        raise abi.OmniKVError("rope_append: q_out must be [B, H, 128] with contiguous heads")
+    if _kv_strides(k_cache) != _kv_strides(v_cache) or k_cache.dtype != qkv.dtype:
+        raise abi.OmniKVError("rope_append: k/v cache layouts must match")
+    if inv_freq.dtype != torch.float32 or inv_freq.numel() != 64 or rope_pos.dtype != torch.int32 or cache_pos.dtype != torch.int32:
+        raise abi.OmniKVError("rope_append: inv_freq fp32 [64], positions int32")
+    sb, sh, sr = _kv_strides(k_cache)
+    abi.check(abi.lib().omnikv_rope_append(_DT[qkv.dtype], qkv.data_ptr(), qkv.stride(0), B, H, KVH, 128,
+                                           inv_freq.data_ptr(), rope_pos.data_ptr(), q_out.data_ptr(), q_out.stride(0),
+                                           k_cache.data_ptr(), v_cache.data_ptr(), sb, sh, sr, cache_pos.data_ptr(),
+                                           _stream()), "omnikv_rope_append")
+    _count(1)
+
+
+def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``omnikv_silu_mul``.  gate_up ``[B, 2*inter]`` (rows contiguous) -> ``silu(gate) * up`` ``[B, inter]``."""
+    _need_cuda(gate_up, out)
+    if gate_up.dim() != 2 or gate_up.stride(1) != 1 or gate_up.shape[1] % 2:
+        raise abi.OmniKVError("silu_mul: gate_up must be [B, 2*inter] with contiguous rows")
+    B, inter = gate_up.shape[0], gate_up.shape[1] // 2
+    if out is None:
+        out = torch.empty(B, inter, dtype=gate_up.dtype, device=gate_up.device)
+    abi.check(abi.lib().omnikv_silu_mul(_DT[gate_up.dtype], gate_up.data_ptr(), gate_up.stride(0), out.data_ptr(),
+                                        out.stride(0), B, inter, _stream()), "omnikv_silu_mul")
+    _count(1)
+    return out
 
 
 def offload_gather(host_kv: torch.Tensor, idx: torch.Tensor, n_idx: torch.Tensor, staged: torch.Tensor,

@@ -28,6 +28,8 @@ def main():
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--ctx", type=int, default=0, help="override the context length (offload: 450000)")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--profile-step", action="store_true",
+                    help="after the warm-up run ONE step between cudaProfilerStart/Stop and exit (for a launch list)")
     ap.add_argument("--skip-threshold", type=float, default=None,
                     help="offload: use cache_cls lazy with this threshold (0 keeps the first selection for good: "
                          "the step time without host-link traffic)")
@@ -62,6 +64,12 @@ def main():
                           use_cuda_graph=not args.no_graph, warmup_steps=2)
     runner.run(args.warmup)
     torch.cuda.synchronize()
+    if args.profile_step:
+        torch.cuda.profiler.start()
+        runner.run(1)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        return
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     runner.run(steps)

@@ -557,3 +557,69 @@ def test_idx_commit_batch_and_edges():
         ops().idx_commit(new, n, new, m, 0.5, applied)
     with pytest.raises(Exception):
         ops().idx_commit(new.long(), n, live, m, 0.5, applied)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 2e-2), (torch.float16, 4e-3), (torch.float32, 2e-6)])
+@pytest.mark.parametrize("B,H,KVH", [(1, 32, 8), (5, 8, 2), (16, 4, 1)])
+def test_rope_append(dtype, tol, B, H, KVH):
+    """omnikv_rope_append against the rotate_half formula: rotated q, rotated k and plain v land in
+    q_out and in row cache_pos[b] of a strided cache; other rows stay untouched; a negative position skips."""
+    g = torch.Generator(device="cuda").manual_seed(21)
+    d, cap = 128, 12
+    qkv = torch.randn(B, (H + 2 * KVH) * d, generator=g, device="cuda").to(dtype)
+    inv_freq = (1.0 / (500000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).cuda()
+    rope_pos = torch.randint(0, 200000, (B,), generator=g, device="cuda", dtype=torch.int32)
+    cache_pos = torch.randint(0, cap, (B,), generator=g, device="cuda", dtype=torch.int32)
+    if B > 1:
+        cache_pos[1] = -1
+    kv = torch.full((B, KVH, cap, 2, d), 7.0, device="cuda").to(dtype)   # K|V rows interleaved, as the caches
+    kc, vc = kv[:, :, :, 0, :], kv[:, :, :, 1, :]
+    q = torch.zeros(B, H, d, device="cuda", dtype=dtype)
+    ops().rope_append(qkv, H, KVH, inv_freq, rope_pos, q, kc, vc, cache_pos)
+    x = qkv.double().view(B, H + 2 * KVH, d)
+    # the angle is an fp32 product, as in the reference's rotary embedding; cos/sin of it in fp64
+    ang = (rope_pos.float()[:, None] * inv_freq[None, :]).double()
+    cos, sin = torch.cat([ang.cos(), ang.cos()], 1)[:, None, :], torch.cat([ang.sin(), ang.sin()], 1)[:, None, :]
+    rot = x * cos + torch.cat([-x[..., 64:], x[..., :64]], -1) * sin
+    assert (q.double() - rot[:, :H]).abs().max().item() < tol * 4
+    for b in range(B):
+        p = int(cache_pos[b])
+        if p < 0:
+            assert (kv[b].float() == 7.0).all()
+            continue
+        assert (kc[b, :, p].double() - rot[b, H:H + KVH]).abs().max().item() < tol * 4
+        assert torch.equal(vc[b, :, p], qkv[b].view(H + 2 * KVH, d)[H + KVH:])
+        mask = torch.ones(cap, dtype=torch.bool, device="cuda")
+        mask[p] = False
+        assert (kv[b][:, mask].float() == 7.0).all()
+    with pytest.raises(Exception):
+        ops().rope_append(qkv[:, :-128], H, KVH, inv_freq, rope_pos, q, kc, vc, cache_pos)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 2e-2), (torch.float32, 1e-6)])
+def test_silu_mul(dtype, tol):
+    g = torch.Generator(device="cuda").manual_seed(22)
+    gu = (3 * torch.randn(7, 2 * 1000, generator=g, device="cuda")).to(dtype)
+    act = ops().silu_mul(gu)
+    ref = torch.nn.functional.silu(gu[:, :1000].double()) * gu[:, 1000:].double()
+    assert act.shape == (7, 1000) and act.dtype == dtype
+    assert ((act.double() - ref).abs() / (1 + ref.abs())).max().item() < tol
+    with pytest.raises(Exception):
+        ops().silu_mul(gu[:, :-1])
+
+
+def test_ragged_batch_splits_cover_every_row():
+    """Chunks are sized by the longest sequence of the batch: short sequences use fewer splits.  Any split
+    count gives the oracle's attention for every sequence (lengths from 1 row to several chunks)."""
+    g = torch.Generator(device="cuda").manual_seed(23)
+    B, H, KVH, d, cap = 6, 8, 2, 128, 3000
+    lens = [1, 63, 64, 65, 1500, 2999]
+    q = torch.randn(B, H, d, generator=g, device="cuda").to(torch.bfloat16)
+    k = torch.randn(B, KVH, cap, d, generator=g, device="cuda").to(torch.bfloat16)
+    v = torch.randn(B, KVH, cap, d, generator=g, device="cuda").to(torch.bfloat16)
+    n = dev_i32(lens)
+    for s in (1, 2, 5, 11, 24):
+        o = ops().decode_attn(q, k, v, n, n_splits=s)
+        for b in range(B):
+            ref = oracle.dense_attention(q[b:b + 1].cpu(), k[b:b + 1, :, :lens[b]].cpu(), v[b:b + 1, :, :lens[b]].cpu())
+            assert (o[b:b + 1].float().cpu() - ref).abs().max().item() < 2e-2, (s, b)
