@@ -304,6 +304,18 @@ typedef struct {
 } omnikv_tp_exchange;
 
 size_t omnikv_tp_exchange_bytes(int hidden);
+
+/* SUM all-reduce of x[0..n) (bf16 / fp16 / fp32, in place) across the ranks of an exchange, for tensors too small
+ * for a ring to pay off (the hidden state of a batched decode step): every rank stores its vector into its slot of
+ * EVERY rank's exchange buffer over NVLink and raises a flag; every rank then adds the slots in rank order in
+ * fp32 (bit-identical results on all ranks).  Replaces the dist.all_reduce after the output projection and the
+ * MLP of the reference's tensor-parallel fork (lightllm/common/basemodel/layer_infer/template/
+ * transformer_layer_infer_template.py:119-120, :128-129).  The exchange describes a buffer of
+ * omnikv_tp_exchange_bytes(hidden) bytes per rank; n * element size must not exceed hidden * 4 bytes and must be
+ * a multiple of 16; seq < 256 numbers the calls of a step on THIS exchange object in program order, identically
+ * on every rank; *epoch is bumped once per step.  The wait for the peers' flags is bounded (status 4). */
+int omnikv_tp_allreduce_sum(int dtype, void* x, int64_t n, const omnikv_tp_exchange* t, int32_t* status,
+                            void* stream);
 int omnikv_decode_qkv(int dtype, const void* h, const void* norm_w, float eps, const void* w_qkv, int hidden,
                       int H, int KVH, int head_dim, const float* inv_freq, const int32_t* rope_pos,
                       void* q_out, void* k_cache_seq, void* v_cache_seq, int64_t kv_stride_h,

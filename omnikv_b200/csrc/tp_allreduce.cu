@@ -1,0 +1,167 @@
+// Small SUM all-reduce over peer-mapped memory (NVLink), for the hidden state of a batched decode step.
+//
+// At 8 ranks the hidden state of a decode step is tens to hundreds of KB: an all-reduce of that size is
+// latency, and a ring or tree pays several hops.  Here every rank stores its vector straight into a slot of
+// EVERY rank's exchange buffer (one hop, plain peer stores), the CTA that finishes last raises this rank's
+// flag on every rank, and every rank then adds the world's vectors in rank order -- so all ranks compute
+// bit-identical sums -- in fp32, rounding once.  One kernel per call on each GPU; the kernels of different
+// GPUs wait for one another's flags with a bounded spin (a rank's flag depends only on that rank's own
+// stores, never on a peer, so there is no cycle).  The grid is small enough to be resident at once.
+//
+// Exchange buffer layout and flag values are those of omnikv_tp_exchange (two alternating slots, flag =
+// step * 256 + exchange number + 1, nothing is ever reset).  No TMA, no multicast: plain loads and stores.
+#include "common.cuh"
+
+namespace omnikv {
+namespace {
+
+constexpr int AR_THREADS = 256;
+constexpr int AR_MAX_CTAS = 64;
+
+struct ArArgs {
+  void* x;                 // [n_vec] 16-byte vectors, reduced in place
+  int n_vec;
+  int world, rank;
+  uint4* peer_slot[8];     // rank p's slot region for MY vector
+  unsigned* peer_flag[8];  // rank p's flag word for (slot, me)
+  const uint4* my_slots;   // local: [8][slot_stride_vec]
+  size_t slot_stride_vec;
+  const unsigned* my_flags;  // local [8]
+  unsigned* done;          // local counter of finished CTAs (self-resetting)
+  const unsigned* epoch;
+  unsigned seq;
+  int* status;
+};
+
+__device__ __forceinline__ unsigned ld_volatile_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.volatile.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+template <typename T>
+__device__ __forceinline__ void add8(const uint4& v, float (&acc)[8]);
+template <>
+__device__ __forceinline__ void add8<float>(const uint4& v, float (&acc)[8]) {
+  acc[0] += __uint_as_float(v.x); acc[1] += __uint_as_float(v.y);
+  acc[2] += __uint_as_float(v.z); acc[3] += __uint_as_float(v.w);
+}
+template <>
+__device__ __forceinline__ void add8<__nv_bfloat16>(const uint4& v, float (&acc)[8]) {
+  const unsigned u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    acc[2 * i] += __uint_as_float(u[i] << 16);
+    acc[2 * i + 1] += __uint_as_float(u[i] & 0xffff0000u);
+  }
+}
+template <>
+__device__ __forceinline__ void add8<__half>(const uint4& v, float (&acc)[8]) {
+  const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __half22float2(h[i]);
+    acc[2 * i] += t.x;
+    acc[2 * i + 1] += t.y;
+  }
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack8(const float (&acc)[8]) {
+  return make_uint4(pack2<T>(acc[0], acc[1]), pack2<T>(acc[2], acc[3]), pack2<T>(acc[4], acc[5]), pack2<T>(acc[6], acc[7]));
+}
+template <>
+__device__ __forceinline__ uint4 pack8<float>(const float (&acc)[8]) {
+  return make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3]));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(AR_THREADS) tp_allreduce_kernel(const ArArgs a) {
+  __shared__ int fail;
+  const int tid = threadIdx.x;
+  const int stride = gridDim.x * AR_THREADS;
+  uint4* x = static_cast<uint4*>(a.x);
+  if (tid == 0) fail = 0;
+  // 1. my vector into my slot on every rank (the local one included)
+  for (int v = blockIdx.x * AR_THREADS + tid; v < a.n_vec; v += stride) {
+    const uint4 val = x[v];
+    for (int p = 0; p < a.world; ++p) a.peer_slot[p][v] = val;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) {
+    // all of this CTA's stores are ordered before its count; the CTA that completes the count raises this
+    // rank's flag on every rank
+    if (atomicAdd(a.done, 1u) == gridDim.x - 1) {
+      atomicExch(a.done, 0u);
+      __threadfence_system();
+      const unsigned val = __ldcg(a.epoch) * 256u + a.seq + 1u;
+      for (int p = 0; p < a.world; ++p)
+        asm volatile("st.volatile.global.u32 [%0], %1;\n" ::"l"(a.peer_flag[p]), "r"(val) : "memory");
+    }
+    // 2. every rank's vector must have landed here (bounded wait)
+    const unsigned want = __ldcg(a.epoch) * 256u + a.seq + 1u;
+    for (int r = 0; r < a.world; ++r) {
+      unsigned spin = 0;
+      while ((int)(ld_volatile_u32(a.my_flags + r) - want) < 0) {
+        if (++spin > kSpinLimit) {
+          fail = 1;
+          atomicExch(a.status, 4);
+          break;
+        }
+      }
+    }
+    __threadfence_system();
+  }
+  __syncthreads();
+  if (fail) return;
+  // 3. sum in rank order, fp32, rounded once
+  for (int v = blockIdx.x * AR_THREADS + tid; v < a.n_vec; v += stride) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < a.world; ++r) add8<T>(__ldcg(a.my_slots + (size_t)r * a.slot_stride_vec + v), acc);
+    x[v] = pack8<T>(acc);
+  }
+}
+
+}  // namespace
+}  // namespace omnikv
+
+extern "C" int omnikv_tp_allreduce_sum(int dtype, void* x, int64_t n, const omnikv_tp_exchange* t, int32_t* status,
+                                       void* stream) {
+  using namespace omnikv;
+  if (!x || n <= 0 || !t || !status) return OMNIKV_E_BADARG;
+  if (t->world <= 1) return OMNIKV_OK;
+  if (t->world > 8 || t->rank < 0 || t->rank >= t->world || !t->done_counter || !t->epoch || t->hidden <= 0)
+    return OMNIKV_E_BADARG;
+  if (t->seq < 0 || t->seq >= 256) return OMNIKV_E_UNSUPPORTED;
+  const int esz = dtype == OMNIKV_F32 ? 4 : 2;
+  if (dtype != OMNIKV_F32 && dtype != OMNIKV_BF16 && dtype != OMNIKV_F16) return OMNIKV_E_UNSUPPORTED;
+  const size_t bytes = (size_t)n * esz;
+  const size_t slot_bytes = (size_t)t->hidden * sizeof(float);  // one (slot, rank) region of the exchange buffer
+  if (bytes % 16 || (reinterpret_cast<uintptr_t>(x) & 15) || slot_bytes % 16) return OMNIKV_E_BADARG;
+  if (bytes > slot_bytes) return OMNIKV_E_WORKSPACE;
+  ArArgs a = {};
+  a.x = x; a.n_vec = (int)(bytes / 16); a.world = t->world; a.rank = t->rank;
+  const int slot = t->seq & 1;
+  const size_t flags_off = (size_t)2 * 8 * slot_bytes;
+  for (int p = 0; p < t->world; ++p) {
+    if (!t->peer_base[p]) return OMNIKV_E_BADARG;
+    unsigned char* base = static_cast<unsigned char*>(t->peer_base[p]);
+    a.peer_slot[p] = reinterpret_cast<uint4*>(base + ((size_t)slot * 8 + t->rank) * slot_bytes);
+    a.peer_flag[p] = reinterpret_cast<unsigned*>(base + flags_off) + slot * 8 + t->rank;
+  }
+  unsigned char* mine = static_cast<unsigned char*>(t->peer_base[t->rank]);
+  a.my_slots = reinterpret_cast<const uint4*>(mine + (size_t)slot * 8 * slot_bytes);
+  a.slot_stride_vec = slot_bytes / 16;
+  a.my_flags = reinterpret_cast<const unsigned*>(mine + flags_off) + slot * 8;
+  a.done = t->done_counter; a.epoch = t->epoch; a.seq = (unsigned)t->seq; a.status = status;
+  int grid = ceil_div(a.n_vec, AR_THREADS);
+  if (grid > AR_MAX_CTAS) grid = AR_MAX_CTAS;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case OMNIKV_BF16: tp_allreduce_kernel<__nv_bfloat16><<<grid, AR_THREADS, 0, st>>>(a); break;
+    case OMNIKV_F16: tp_allreduce_kernel<__half><<<grid, AR_THREADS, 0, st>>>(a); break;
+    default: tp_allreduce_kernel<float><<<grid, AR_THREADS, 0, st>>>(a); break;
+  }
+  OMNIKV_CUDA_OK(cudaGetLastError());
+  return OMNIKV_OK;
+}

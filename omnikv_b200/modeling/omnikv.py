@@ -533,6 +533,8 @@ class OmniKVMulModel(nn.Module):
         h = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds.clone()
         B, n, _ = h.shape
         cache = past_key_values
+        if self.tp is not None:
+            self.tp.begin_step()
         if n == 1:
             cache.begin_decode_step()
             if position_ids is None:

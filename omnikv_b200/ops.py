@@ -270,6 +270,17 @@ def kv_append(k_new: torch.Tensor, v_new: torch.Tensor, k_cache: torch.Tensor, v
     _count(1)
 
 
+def tp_allreduce_sum(x: torch.Tensor, exchange) -> None:
+    """``omnikv_tp_allreduce_sum``: in-place SUM of the contiguous tensor ``x`` over the ranks of ``exchange`` (an
+    ``abi.TpExchange`` from ``parallel.PeerExchange.at(seq)``)."""
+    _need_cuda(x)
+    if not x.is_contiguous():
+        raise abi.OmniKVError("tp_allreduce_sum: contiguous tensor expected")
+    abi.check(abi.lib().omnikv_tp_allreduce_sum(_DT[x.dtype], x.data_ptr(), x.numel(), _xref(exchange),
+                                                status_word(x.device).data_ptr(), _stream()), "omnikv_tp_allreduce_sum")
+    _count(1)
+
+
 def rope_append(qkv: torch.Tensor, H: int, KVH: int, inv_freq: torch.Tensor, rope_pos: torch.Tensor,
                 q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cache_pos: torch.Tensor) -> None:
     """``omnikv_rope_append``.  qkv ``[B, (H+2KVH)*128]`` (rows contiguous); q_out ``[B, H, 128]``; caches

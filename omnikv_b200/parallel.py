@@ -74,7 +74,9 @@ class PeerExchange:
 class TPGroup:
     def __init__(self, world: int, rank: int, group=None):
         self.world, self.rank, self.group = world, rank, group
-        self.exchange: Optional[PeerExchange] = None
+        self.exchange: Optional[PeerExchange] = None   # fused projection + all-reduce (batch-1 decode kernels)
+        self.reducer: Optional[PeerExchange] = None    # standalone small all-reduce (batched decode)
+        self._reduce_seq = 0
 
     def enable_peer_exchange(self, hidden: int, device: torch.device) -> bool:
         """Set up the peer-mapped buffers for the fused projection + all-reduce kernels.  Returns False (and
@@ -93,6 +95,32 @@ class TPGroup:
             self.exchange = None
         return self.exchange is not None
 
+    def enable_peer_reduce(self, max_bytes: int, device: torch.device) -> bool:
+        """Set up a second set of peer-mapped buffers for ``all_reduce_sum`` of tensors up to ``max_bytes`` (the
+        hidden state of a batched decode step): one NVLink hop and a rank-ordered fp32 sum instead of a NCCL
+        ring.  Returns False (NCCL stays) when symmetric memory cannot be set up."""
+        if self.world <= 1 or self.world > 8:
+            return False
+        try:
+            self.reducer = PeerExchange(self.world, self.rank, -(-max_bytes // 64) * 16, device, self.group)
+        except Exception as e:
+            import logging
+            logging.getLogger("omnikv_b200").warning(f"peer all-reduce unavailable, using NCCL: {e}")
+            self.reducer = None
+        ok = torch.tensor([1 if self.reducer is not None else 0], device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        if int(ok.item()) == 0:
+            self.reducer = None
+        self._reduce_seq = 0
+        return self.reducer is not None
+
+    def begin_step(self) -> None:
+        """Once per model forward on every rank: the peer all-reduce numbers its calls from zero again and its
+        flags carry the new step number (a device counter, so a captured step can be replayed)."""
+        if self.reducer is not None:
+            self.reducer.begin_step()
+            self._reduce_seq = 0
+
     def shard(self, n: int) -> Tuple[int, int]:
         """[lo, hi) of this rank's contiguous share of ``n`` items (``n`` divisible by the world size)."""
         if n % self.world:
@@ -101,8 +129,18 @@ class TPGroup:
         return self.rank * per, (self.rank + 1) * per
 
     def all_reduce_sum(self, t: torch.Tensor) -> torch.Tensor:
-        if self.world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+        if self.world <= 1:
+            return t
+        r = self.reducer
+        nbytes = t.numel() * t.element_size()
+        # every condition depends on shapes and call order only, so all ranks take the same branch
+        if (r is not None and t.is_cuda and t.is_contiguous() and nbytes % 16 == 0 and nbytes <= r.hidden * 4
+                and self._reduce_seq < 256 and t.dtype in (torch.bfloat16, torch.float16, torch.float32)):
+            from . import ops
+            ops.tp_allreduce_sum(t, r.at(self._reduce_seq))
+            self._reduce_seq += 1
+            return t
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
         return t
 
     def all_reduce_max(self, t: torch.Tensor) -> torch.Tensor:

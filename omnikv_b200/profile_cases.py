@@ -80,7 +80,7 @@ def gemv_cases(reps: int, n_sets: int = 8):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["dense_attn", "sparse_attn", "topk", "score_window", "offload_gather", "gemv"])
+    ap.add_argument("case", choices=["dense_attn", "sparse_attn", "topk", "score_window", "offload_gather", "gemv", "operator"])
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--ctx", type=int, default=131072)
     ap.add_argument("--splits", type=int, default=0)
@@ -96,6 +96,27 @@ def main():
 
     if args.case == "gemv":
         return gemv_cases(args.reps)
+    if args.case == "operator":
+        # the single-layer operator in fp32: context 16384, selector `last` on a filter layer's K, 1098 selected rows,
+        # decode attention over a second layer's K/V at those rows -- three launches
+        L, k_op = 16384, 1098
+        f32 = lambda *s: torch.randn(*s, generator=g, device=dev, dtype=torch.float32)  # noqa: E731
+        q, k1, k2, v2 = f32(B, H, d), f32(B, KVH, L, d), f32(B, KVH, L, d), f32(B, KVH, L, d)
+        hot = torch.randperm(L, generator=g, device=dev)[: L // 50]
+        qm = q.mean(dim=1)
+        k1[:, :, hot] += 4.0 * (qm / qm.norm())[:, None, None, :]
+        planes = torch.empty(KVH, B, L, dtype=torch.float32, device=dev)
+        idx = torch.empty(B, k_op + 6, dtype=torch.int32, device=dev)
+        cnt = torch.empty(B, dtype=torch.int32, device=dev)
+        n_p, kk = i32([L]), i32([k_op])
+        out = torch.empty(B, H, d, dtype=torch.float32, device=dev)
+
+        def fn():
+            ops.score_last(q, k1, n_p, score_out=planes)
+            ops.topk(planes, n_p, kk, idx_out=idx, count_out=cnt, max_len=L)
+            ops.decode_attn(q, k2, v2, cnt, idx=idx, out=out, max_rows=k_op)
+
+        nbytes = KVH * d * 4 * L + 2 * KVH * d * 4 * k_op
     # K and V share one buffer as in the package's cache: head-major with K|V rows interleaved for a dense layer,
     # token-major for a sparse layer
     if args.case in ("dense_attn", "score_window"):
@@ -104,7 +125,9 @@ def main():
     if args.case == "sparse_attn":
         kv = rnd(B, L + 64, KVH, 2, d)
         kc, vc, q = kv[:, :, :, 0, :].permute(0, 2, 1, 3), kv[:, :, :, 1, :].permute(0, 2, 1, 3), rnd(B, H, d)
-    if args.case == "dense_attn":
+    if args.case == "operator":
+        pass
+    elif args.case == "dense_attn":
         planes = torch.empty(KVH, B, L, dtype=torch.float32, device=dev)
         n_all, n_p = i32([L + 1]), i32([L])
         fn = lambda: ops.decode_attn(q, kc, vc, n_all, score_out=planes, score_len=n_p, n_splits=args.splits or None)  # noqa: E731

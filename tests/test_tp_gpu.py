@@ -118,3 +118,99 @@ def test_tp2_fused_peer_exchange_engine():
         assert graph_eq_peer and graph_eq_nccl
         assert agree >= 0.75
     assert ret[0] == ret[1]
+
+
+def _worker_reduce(rank, world, port, ret):
+    import logging
+    logging.disable(logging.WARNING)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    import torch.distributed as dist
+    from omnikv_b200 import ops, parallel
+    from omnikv_b200.modeling import LlamaCompressorConfig, OmniKVMulLM
+    tp = parallel.init(world, rank, dev)
+    try:
+        has = tp.enable_peer_reduce(256 << 10, dev)
+        g = torch.Generator(device=dev).manual_seed(100 + rank)
+        exact, used = True, 0
+        for step in range(6):
+            tp.begin_step()
+            for dtype, n in ((torch.bfloat16, 8), (torch.float32, 4), (torch.bfloat16, 8 * 8192), (torch.float16, 24),
+                             (torch.float32, 5000 * 4), (torch.bfloat16, 131072)):
+                x = torch.randn(n, generator=g, device=dev).to(dtype)
+                parts = [torch.empty_like(x) for _ in range(world)]
+                dist.all_gather(parts, x)
+                want = torch.zeros(n, dtype=torch.float32, device=dev)
+                for p in parts:  # rank order, fp32, rounded once: what the kernel computes
+                    want += p.float()
+                seq0 = tp._reduce_seq
+                tp.all_reduce_sum(x)
+                used += tp._reduce_seq - seq0
+                exact = exact and torch.equal(x, want.to(dtype))
+        # a tensor above the buffer's capacity goes through NCCL (same numbers up to summation order)
+        tp.begin_step()
+        big = torch.ones(1 << 20, device=dev)
+        seq0 = tp._reduce_seq
+        tp.all_reduce_sum(big)
+        fell_back = tp._reduce_seq == seq0 and bool((big == world).all())
+        # a captured step replays: begin_step bumps the device-side step counter inside the graph
+        xs = [torch.full((4096,), float(rank + 1), device=dev, dtype=torch.bfloat16) for _ in range(3)]
+        gr = torch.cuda.CUDAGraph()
+        tp.begin_step(); [tp.all_reduce_sum(t.clone()) for t in xs]  # warm-up outside the capture
+        torch.cuda.synchronize()
+        outs = [torch.empty_like(t) for t in xs]
+        with torch.cuda.graph(gr):
+            tp.begin_step()
+            for t, o in zip(xs, outs):
+                o.copy_(t)
+                tp.all_reduce_sum(o)
+        graph_ok = True
+        for _ in range(4):
+            gr.replay()
+            torch.cuda.synchronize()
+            graph_ok = graph_ok and all(bool((o.float() == sum(range(1, world + 1))).all()) for o in outs)
+        ops.check_status(dev)
+
+        # batched decode of a sharded model with the peer all-reduce against the full model on one GPU
+        def cfg():
+            c = LlamaCompressorConfig(num_hidden_layers=4, hidden_size=1024, intermediate_size=2048,
+                                      num_attention_heads=8, num_key_value_heads=2, vocab_size=1024, head_dim=128)
+            c.set_config_of_compressor(model_cls="multi", cache_cls="multi", do_select_layers="1", num_wait_load_layers=1,
+                                       real_offload=False, dense_more=True, num_of_selected_tokens=0.25,
+                                       selector_cls="last", window_size=16)
+            return c
+        full = OmniKVMulLM.from_config(cfg(), dtype=torch.float32, device=dev, seed=0)
+        shard = OmniKVMulLM.from_config(cfg(), dtype=torch.float32, device=dev, seed=None, tp=tp)
+        shard.load_hf_state_dict(full.hf_state_dict())
+        gc = torch.Generator().manual_seed(1)
+        ids = torch.randint(0, 1024, (3, 200), generator=gc).to(dev)
+        toks = torch.randint(0, 1024, (5, 3, 1), generator=gc).to(dev)
+        o1, o2 = full(input_ids=ids), shard(input_ids=ids)
+        err = (o1.logits - o2.logits).abs().max().item()
+        for t in toks:
+            o1 = full(input_ids=t, past_key_values=o1.past_key_values)
+            seq0 = tp._reduce_seq
+            o2 = shard(input_ids=t, past_key_values=o2.past_key_values)
+            err = max(err, (o1.logits - o2.logits).abs().max().item())
+        ops.check_status(dev)
+        ret[rank] = (bool(has), bool(exact), used, bool(fell_back), bool(graph_ok), err, tp._reduce_seq)
+    finally:
+        torch.distributed.destroy_process_group()
+
+
+def test_tp2_peer_allreduce():
+    """omnikv_tp_allreduce_sum on 2 GPUs: bit-exact rank-ordered fp32 sums for all dtypes and sizes over several
+    steps (slot reuse, step counter), NCCL fallback above the capacity, CUDA-graph replay, and a batch-3 decode
+    of a sharded model equal to the single-GPU model."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world, port = 2, _free_port()
+    ret = mp.get_context("spawn").Manager().dict()
+    mp.spawn(_worker_reduce, args=(world, port, ret), nprocs=world, join=True)
+    for rank in range(world):
+        has, exact, used, fell_back, graph_ok, err, last_seq = ret[rank]
+        assert has, "symmetric memory / peer access unavailable"
+        assert exact and used == 36 and fell_back and graph_ok
+        assert err <= 1e-4, err
+        assert last_seq == 8  # two all-reduces per layer of the last decode forward went through the kernel
