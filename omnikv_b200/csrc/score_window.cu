@@ -7,9 +7,10 @@
 // heads, so K is streamed twice:
 //   pass 1  grid (splits, KVH, B): per-row online (max, sum-exp) of the CTA's chunk of keys;
 //           a small kernel merges the splits into (m, 1/l) per row;
-//   pass 2  grid (chunks of 512 positions, B): every CTA walks its chunk of key positions for ALL KV heads,
-//           one head after the other, keeping the running max over heads in shared memory, so each score
-//           is written once -- no atomics, deterministic.
+//   pass 2  grid (chunks of 512 positions, KVH, B): a CTA normalises the logits of one KV head's query group
+//           for its chunk, takes the max over the group's heads in registers and folds it into per-slot
+//           planes with integer atomicMax (weights are >= 0; max is order independent: deterministic);
+//           a small kernel then forms the weighted sum over the window slots.
 // The [G x 16 window slots] x 128 query block of one KV head against a tile of keys is a dense
 // contraction: bf16/fp16 run it on m16n8k16 tensor-core MMAs with the K tile staged by cp.async;
 // fp32 uses CUDA cores.  Query rows are laid out head-major with the window padded to 16 slots,
@@ -38,6 +39,8 @@ struct WinArgs {
   float* score_out;
   float* planes_out;
   int64_t score_stride;
+  float* planes;        // [B][W][plane_stride] max over heads per window slot (zero before pass 2)
+  int64_t plane_stride;
   int B, H, KVH, G, W, S, selector, chunk2;
   float scale;
 };
@@ -107,7 +110,7 @@ __device__ __forceinline__ void merge_ml(float& m, float& l, float m2, float l2)
 
 // ---- pass 1: per-row (max, sum-exp) over the CTA's chunk -------------------------------------
 template <typename T, int G>
-__global__ void __launch_bounds__(NTHREADS, 2) window_pass1_mma(const WinArgs a) {
+__global__ void __launch_bounds__(NTHREADS, 3) window_pass1_mma(const WinArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* q_s = smem + P1_STAGES * TILE_BYTES;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -211,61 +214,50 @@ __device__ __forceinline__ float slot_weight(int selector, int W, int w) {
   return w == W - 1 ? 1.f : 0.f;
 }
 
-// ---- pass 2: normalise, max over heads, weighted window sum -----------------------------------
-// grid (ceil(max_len / P2_CHUNK), B).  A CTA owns P2_CHUNK key positions and walks the KV heads one after the
-// other: it loads the head's query group (and its softmax statistics), streams the head's K rows of the chunk,
-// and keeps the running max over heads of every (position, window slot) weight in shared memory -- each thread
-// always owns the same entries, so there is no atomic and no barrier around them.  After the last head the
-// weighted window sum is written once.  Shared memory per CTA is ~111 KB (G = 4): two CTAs per SM.
+// ---- pass 2: normalise, max over heads --------------------------------------------------------
+// grid (ceil(max_len / P2_CHUNK), KVH, B).  A CTA streams the K rows of ONE KV head for its chunk of positions,
+// normalises the logits of the head's query group with the statistics of pass 1, takes the max over the group's
+// heads in registers and folds it into the plane planes[b][w][p] with an integer atomicMax (the weights are
+// >= 0, so their bit patterns order like the values; max is order independent, so the result is deterministic).
+// The planes start at zero; the weighted window sum over w is a separate small kernel.  Walking all KV heads
+// inside one CTA with the running max in shared memory needed 111 KB per CTA and ran two CTAs of four warps per
+// SM, latency bound at 3 us per tile; without that table a CTA needs 69 KB and three are resident.
 constexpr int P2_CHUNK = 512;
-constexpr int HM_PITCH = 20;  // floats per position: 16 slots + pad; conflict-free for the fragment layout
 
 template <typename T, int G>
-__global__ void __launch_bounds__(NTHREADS, 2) window_pass2_mma(const WinArgs a) {
+__global__ void __launch_bounds__(NTHREADS, 3) window_pass2_mma(const WinArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* q_s = smem + P2_STAGES * TILE_BYTES;                             // [G*16][PITCH]
-  float* hm_s = reinterpret_cast<float*>(q_s + (size_t)G * WPAD * PITCH);         // [P2_CHUNK][HM_PITCH]
-  float* st_s = hm_s + P2_CHUNK * HM_PITCH;                                       // [G*16][2]
-  const int b = blockIdx.y;
+  float* st_s = reinterpret_cast<float*>(q_s + (size_t)G * WPAD * PITCH);         // [G*16][2]
+  const int kvh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int n = a.consider_len[b];
   const int r0 = blockIdx.x * P2_CHUNK;
   const int r1 = min(n, r0 + P2_CHUNK);
   if (r0 >= r1) return;
   const int ntiles = ceil_div(r1 - r0, TILE);
-  const int KVH = a.KVH;
-  const int nsteps = ntiles * KVH;  // step s: kv head s / ntiles, tile s % ntiles
-  const T* kb = static_cast<const T*>(a.k) + (size_t)b * a.k_sb;
+  const T* kb = static_cast<const T*>(a.k) + (size_t)b * a.k_sb + (size_t)kvh * a.k_sh;
   const T* qb = static_cast<const T*>(a.qw) + (size_t)b * a.H * a.W * kHeadDim;
 
-  auto issue = [&](int s) {
-    const int kvh = s / ntiles, tile = s % ntiles;
-    issue_k_tile<T>(smem + (s % P2_STAGES) * TILE_BYTES, kb + (size_t)kvh * a.k_sh, a.k_sr, r0 + tile * TILE, r1, tid);
-  };
 #pragma unroll
   for (int s = 0; s < P2_STAGES - 1; ++s) {
-    if (s < nsteps) issue(s);
+    if (s < ntiles) issue_k_tile<T>(smem + s * TILE_BYTES, kb, a.k_sr, r0 + s * TILE, r1, tid);
     cp_async_commit();
   }
-  const float wt0 = slot_weight(a.selector, a.W, g), wt1 = slot_weight(a.selector, a.W, g + 8);
+  load_q<T>(q_s, qb, kvh * G, G, a.W, tid);
+  for (int i = tid; i < G * WPAD * 2; i += NTHREADS) st_s[i] = a.stats[((size_t)b * a.H + kvh * G) * WPAD * 2 + i];
+  int* plane0 = reinterpret_cast<int*>(a.planes) + (size_t)b * a.W * a.plane_stride;
 
-  for (int s = 0; s < nsteps; ++s) {
-    const int kvh = s / ntiles, tile = s % ntiles;
-    if (tile == 0) {  // next KV head: its queries and softmax statistics
-      __syncthreads();  // every warp is done with the previous head's queries
-      load_q<T>(q_s, qb, kvh * G, G, a.W, tid);
-      for (int i = tid; i < G * WPAD * 2; i += NTHREADS)
-        st_s[i] = a.stats[((size_t)b * a.H + kvh * G) * WPAD * 2 + i];
-    }
+  for (int tile = 0; tile < ntiles; ++tile) {
     cp_async_wait<P2_STAGES - 2>();
-    __syncthreads();
+    __syncthreads();  // the tile has landed (and, the first time, the queries and statistics are in place)
     {
-      const int ns = s + P2_STAGES - 1;
-      if (ns < nsteps) issue(ns);
+      const int nt = tile + P2_STAGES - 1;
+      if (nt < ntiles) issue_k_tile<T>(smem + (nt % P2_STAGES) * TILE_BYTES, kb, a.k_sr, r0 + nt * TILE, r1, tid);
       cp_async_commit();
     }
     float acc[G][2][4];
-    qk_tile<T, G>(acc, q_s, smem + (s % P2_STAGES) * TILE_BYTES, warp, lane);
+    qk_tile<T, G>(acc, q_s, smem + (tile % P2_STAGES) * TILE_BYTES, warp, lane);
     const int cbase = r0 + tile * TILE + warp * 16 + 2 * t;
     float hm[2][4];
 #pragma unroll
@@ -280,46 +272,33 @@ __global__ void __launch_bounds__(NTHREADS, 2) window_pass2_mma(const WinArgs a)
         for (int j = 0; j < 2; ++j)
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int R = cbase + 8 * j + e;
-            const float pw = (R < r1) ? exp2f(fmaf(acc[i][j][2 * h + e] * a.scale, kLog2e, -ml2)) * inv_l : 0.f;
+            const float pw = exp2f(fmaf(acc[i][j][2 * h + e] * a.scale, kLog2e, -ml2)) * inv_l;
             hm[j][2 * h + e] = fmaxf(hm[j][2 * h + e], pw);
           }
       }
-    // running max over KV heads of this thread's (position, slot) entries
+    // fold into the planes: entry (slot w, position R) for this thread's eight accumulator cells
 #pragma unroll
     for (int j = 0; j < 2; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        float* cell = hm_s + (tile * TILE + warp * 16 + 8 * j + 2 * t + (e & 1)) * HM_PITCH + g + 8 * (e >> 1);
-        if (kvh > 0) hm[j][e] = fmaxf(hm[j][e], *cell);
-        if (kvh < KVH - 1) *cell = hm[j][e];
+        const int w = g + 8 * (e >> 1), R = cbase + 8 * j + (e & 1);
+        if (w < a.W && R < r1) atomicMax(plane0 + (size_t)w * a.plane_stride + R, __float_as_int(hm[j][e]));
       }
-    if (kvh == KVH - 1) {
-      if (a.planes_out) {
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int w = g + 8 * (e >> 1), R = cbase + 8 * j + (e & 1);
-            if (w < a.W && R < r1) a.planes_out[((size_t)b * a.W + w) * a.score_stride + R] = hm[j][e];
-          }
-      }
-      if (a.score_out) {
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            float v = wt0 * hm[j][e] + wt1 * hm[j][2 + e];
-            v += __shfl_xor_sync(0xffffffffu, v, 4);
-            v += __shfl_xor_sync(0xffffffffu, v, 8);
-            v += __shfl_xor_sync(0xffffffffu, v, 16);
-            const int R = cbase + 8 * j + e;
-            if (g == 0 && R < r1) a.score_out[(size_t)b * a.score_stride + R] = v;
-          }
-      }
-    }
   }
   cp_async_wait<0>();
+}
+
+// score[b][p] = sum_w weight_w * planes[b][w][p]
+__global__ void window_fold_planes(const float* __restrict__ planes, int64_t plane_stride, float* __restrict__ score_out,
+                                   int64_t score_stride, int W, const int* __restrict__ consider_len, int selector) {
+  const int b = blockIdx.y;
+  const int n = consider_len[b];
+  for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < n; p += gridDim.x * blockDim.x) {
+    const float* pl = planes + (size_t)b * W * plane_stride + p;
+    float acc = 0.f;
+    for (int w = 0; w < W; ++w) acc = fmaf(slot_weight(selector, W, w), pl[(size_t)w * plane_stride], acc);
+    score_out[(size_t)b * score_stride + p] = acc;
+  }
 }
 
 // ---- fp32 CUDA-core variants -----------------------------------------------------------------
@@ -445,18 +424,24 @@ __global__ void __launch_bounds__(NTHREADS) window_pass2_f32(const WinArgs a) {
 template <typename T, int G>
 int launch_mma(const WinArgs& a, int n_chunks2, int max_len, cudaStream_t st) {
   const int smem1 = P1_STAGES * TILE_BYTES + G * WPAD * PITCH;
-  const int smem2 = P2_STAGES * TILE_BYTES + G * WPAD * PITCH + P2_CHUNK * HM_PITCH * (int)sizeof(float) +
-                    G * WPAD * 2 * (int)sizeof(float);
+  const int smem2 = P2_STAGES * TILE_BYTES + G * WPAD * PITCH + G * WPAD * 2 * (int)sizeof(float);
   (void)n_chunks2;
   OMNIKV_CUDA_OK(cudaFuncSetAttribute(window_pass1_mma<T, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1));
   OMNIKV_CUDA_OK(cudaFuncSetAttribute(window_pass2_mma<T, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
+  // the planes receive atomic maxima: clear the part pass 2 may touch
+  OMNIKV_CUDA_OK(cudaMemsetAsync(a.planes, 0, (size_t)a.B * a.W * a.plane_stride * sizeof(float), st));
   window_pass1_mma<T, G><<<dim3(a.S, a.KVH, a.B), NTHREADS, smem1, st>>>(a);
   OMNIKV_CUDA_OK(cudaGetLastError());
   const int rows = a.B * a.H * WPAD;
   window_stats_merge<<<ceil_div(rows, 128), 128, 0, st>>>(a.part, a.stats, rows, a.S);
   OMNIKV_CUDA_OK(cudaGetLastError());
-  window_pass2_mma<T, G><<<dim3(ceil_div(max_len, P2_CHUNK), a.B), NTHREADS, smem2, st>>>(a);
+  window_pass2_mma<T, G><<<dim3(ceil_div(max_len, P2_CHUNK), a.KVH, a.B), NTHREADS, smem2, st>>>(a);
   OMNIKV_CUDA_OK(cudaGetLastError());
+  if (a.score_out) {
+    window_fold_planes<<<dim3(min(1184, ceil_div(max_len, 256)), a.B), 256, 0, st>>>(
+        a.planes, a.plane_stride, a.score_out, a.score_stride, a.W, a.consider_len, a.selector);
+    OMNIKV_CUDA_OK(cudaGetLastError());
+  }
   return OMNIKV_OK;
 }
 
@@ -486,10 +471,12 @@ int launch_f32(const WinArgs& a, int max_len, cudaStream_t st) {
   return OMNIKV_OK;
 }
 
-constexpr int kPass1Splits = 37;  // 8 KV heads x 37 = 296 CTAs = 2 per SM on 148 SMs
+constexpr int kPass1Splits = 55;  // 8 KV heads x 55 = 440 CTAs = 3 per SM on 148 SMs
 
 size_t part_floats(int B, int H, int S) { return (size_t)B * H * WPAD * S * 2; }
 size_t stats_floats(int B, int H) { return (size_t)B * H * WPAD * 2; }
+size_t plane_stride_of(int max_len) { return (size_t)ceil_div(max_len, 4) * 4; }
+size_t plane_floats(int B, int W, int max_len) { return (size_t)B * W * plane_stride_of(max_len); }
 
 }  // namespace
 }  // namespace omnikv
@@ -497,7 +484,8 @@ size_t stats_floats(int B, int H) { return (size_t)B * H * WPAD * 2; }
 extern "C" size_t omnikv_score_window_workspace_bytes(int B, int H, int W, int max_len) {
   using namespace omnikv;
   if (B <= 0 || H <= 0 || W <= 0 || max_len <= 0) return 0;
-  return (part_floats(B, H, kPass1Splits) + stats_floats(B, H)) * sizeof(float);
+  // pass-1 partials, merged statistics, and the per-slot planes of pass 2 (used when the caller gives none)
+  return (part_floats(B, H, kPass1Splits) + stats_floats(B, H) + plane_floats(B, W, max_len)) * sizeof(float);
 }
 
 extern "C" int omnikv_score_window(const omnikv_window_params* p, void* stream) {
@@ -520,6 +508,11 @@ extern "C" int omnikv_score_window(const omnikv_window_params* p, void* stream) 
   a.part = static_cast<float*>(p->workspace);
   a.stats = a.part + part_floats(p->B, p->H, kPass1Splits);
   a.score_out = p->score_out; a.planes_out = p->planes_out; a.score_stride = p->score_stride;
+  if (p->planes_out) {  // the caller's planes (tensor parallelism: they are MAX-reduced over ranks, then folded)
+    a.planes = p->planes_out; a.plane_stride = p->score_stride;
+  } else {
+    a.planes = a.stats + stats_floats(p->B, p->H); a.plane_stride = (int64_t)plane_stride_of(p->max_len);
+  }
   a.B = p->B; a.H = p->H; a.KVH = p->KVH; a.G = p->H / p->KVH; a.W = p->W; a.S = kPass1Splits;
   a.selector = p->selector; a.scale = p->scale;
   // pass 2: chunks of whole tiles, about two CTAs' worth of chunks per SM over the batch
