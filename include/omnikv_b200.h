@@ -115,6 +115,9 @@ typedef struct {
   size_t workspace_bytes;
   int32_t* status;            /* optional device word: set to 5 if a bounded wait for a KV copy ran out (never
                                  in a healthy run); left untouched otherwise */
+  int64_t a_rows;             /* optional: row capacity of segment A's cache (every row < a_rows of every (b, head)
+                                 is readable memory).  When given for a 16-bit cache without idxA and without a
+                                 segment B, tiles are fetched through a TMA tensor map; 0: unknown */
 } omnikv_attn_params;
 
 /* Stream order: the kernel is launched as a programmatic dependent launch (unless OMNIKV_PDL=0).  When the

@@ -36,7 +36,7 @@ class AttnParams(C.Structure):
         ("score_out", C.c_void_p), ("score_stride", C.c_int64), ("score_len", C.c_void_p),
         ("n_splits", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-        ("status", C.c_void_p),
+        ("status", C.c_void_p), ("a_rows", C.c_int64),
     ]
 
 

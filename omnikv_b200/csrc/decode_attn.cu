@@ -10,6 +10,11 @@
 // Grid (n_splits, KVH, B).  Every CTA owns one contiguous chunk of the sequence's row list and
 // writes one un-normalised partial (o, m, l) per query head; the CTA that finishes last for a (sequence,
 // KV head) merges that group's splits into the output, so an attention call is a single launch.
+#include <cuda.h>
+#include <stdlib.h>
+
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace omnikv {
@@ -67,6 +72,19 @@ constexpr int STAGES = 3;
 constexpr int PITCH = 272;     // bytes per staged row: 256 + 16 pad
 constexpr int TILE_BYTES = TILE * PITCH;
 constexpr int Q_BYTES = 16 * PITCH;
+
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// OMNIKV_ATTN_TMA=0 in the environment keeps dense layers on the cp.async variant.
+inline bool g_attn_tma_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("OMNIKV_ATTN_TMA");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
 
 template <bool WITH_V>
 constexpr int mma_smem_bytes() {
@@ -151,12 +169,44 @@ __device__ __forceinline__ void finish_group(const AttnArgs& a, int b, int kvh, 
 // is what a sparse layer's scattered rows need (22.5 instead of 28.7 us per layer).  false: sixteen 16-byte
 // cp.async per row; for a dense layer's long contiguous streams this keeps more requests in flight and is the
 // faster of the two there (99.8 against 103.7 us per layer).
-template <typename T, bool WITH_V, bool WITH_SCORE, bool BULK>
-__global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const AttnArgs a) {
-  extern __shared__ __align__(128) unsigned char smem[];
+//
+// MODE kCopyTma (a dense layer whose row capacity the caller states): a tile is four boxes of 64 rows x 128 bytes
+// (K low half, K high half, V low, V high) fetched by ONE thread with cp.async.bulk.tensor through a 4-D tensor
+// map [B, KVH, rows, d]; the map's 128-byte swizzle (16-byte chunk c of row r lands at chunk c ^ (r & 7)) makes
+// the unpadded rows conflict-free for ldmatrix.  Rows past the sequence but inside the capacity arrive as they
+// are in memory: their scores are masked and their V rows are zeroed in shared memory before use.
+constexpr int kCopyCpAsync = 0, kCopyBulkRows = 1, kCopyTma = 2;
+constexpr int TMA_BOX_BYTES = TILE * 128;  // 64 rows x 128 bytes
+
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n" ::
+          "r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
+      : "memory");
+}
+
+template <typename T, bool WITH_V, bool WITH_SCORE, int MODE>
+__global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const AttnArgs a,
+                                                                      const __grid_constant__ CUtensorMap tm_k,
+                                                                      const __grid_constant__ CUtensorMap tm_v) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ int last_flag;
-  constexpr int STAGE_BYTES = (WITH_V ? 2 : 1) * TILE_BYTES;
+  constexpr bool BULK = MODE == kCopyBulkRows;
+  constexpr bool TMA = MODE == kCopyTma;
+  constexpr int STAGE_BYTES = TMA ? (WITH_V ? 4 : 2) * TMA_BOX_BYTES : (WITH_V ? 2 : 1) * TILE_BYTES;
+  // the swizzled boxes want 1024-byte alignment
+  unsigned char* smem = TMA ? reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023)
+                            : smem_raw;
   unsigned char* q_s = smem + STAGES * STAGE_BYTES;
+  // byte address of the 16-byte piece at (row, byte column) of a staged K or V tile
+  auto staged = [&](const unsigned char* tile_base, int row, int colb) -> const unsigned char* {
+    if constexpr (TMA)
+      return tile_base + (colb >> 7) * TMA_BOX_BYTES + row * 128 + ((((colb & 127) >> 4) ^ (row & 7)) << 4);
+    else
+      return tile_base + row * PITCH + colb;
+  };
 
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -267,10 +317,33 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
     }
   };
 
+  auto issue_tma = [&](int tile) {  // one thread: the tile's boxes
+    const int slot = tile % STAGES;
+    unsigned char* dst = smem + slot * STAGE_BYTES;
+    mbar_expect_tx(&full_bar[slot], STAGE_BYTES);
+    const int row0 = r0 + tile * TILE;
+    tma_load_4d(dst, &tm_k, 0, row0, kvh, b, &full_bar[slot]);
+    tma_load_4d(dst + TMA_BOX_BYTES, &tm_k, 64, row0, kvh, b, &full_bar[slot]);
+    if (WITH_V) {
+      tma_load_4d(dst + 2 * TMA_BOX_BYTES, &tm_v, 0, row0, kvh, b, &full_bar[slot]);
+      tma_load_4d(dst + 3 * TMA_BOX_BYTES, &tm_v, 64, row0, kvh, b, &full_bar[slot]);
+    }
+  };
+
   // the index lookups of the first STAGES tiles go out together, then the copies of the first STAGES-1 tiles
   long long offb_next = -1;
   long long offc_next[RPT];
-  if constexpr (BULK) {
+  if constexpr (TMA) {
+    if (tid == 0) {
+#pragma unroll
+      for (int s = 0; s < STAGES; ++s) mbar_init(&full_bar[s], 1);
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+#pragma unroll
+      for (int s = 0; s < STAGES - 1; ++s)
+        if (s < ntiles) issue_tma(s);
+    }
+    __syncthreads();
+  } else if constexpr (BULK) {
     if (tid == 0) {
 #pragma unroll
       for (int s = 0; s < STAGES; ++s) mbar_init(&full_bar[s], 1);
@@ -335,7 +408,21 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
 
   for (int tile = 0; tile < ntiles; ++tile) {
     const int nt = tile + STAGES - 1;
-    if constexpr (BULK) {
+    if constexpr (TMA) {
+      __syncthreads();  // every thread is done with tile - 1: its slot may be refilled
+      if (tid == 0 && nt < ntiles) issue_tma(nt);
+      if (!mbar_wait(&full_bar[tile % STAGES], (tile / STAGES) & 1) && a.status) atomicExch(a.status, 5);
+      if (WITH_V && tile == ntiles - 1 && r0 + ntiles * TILE > r1) {
+        // the last tile reaches past the sequence: those rows hold whatever the cache holds; clear their V
+        unsigned char* vt = smem + (tile % STAGES) * STAGE_BYTES + 2 * TMA_BOX_BYTES;
+        const int first_bad = r1 - (r0 + tile * TILE);
+        for (int i = tid; i < (TILE - first_bad) * 16; i += NTHREADS) {
+          const int row = first_bad + (i >> 4), piece = i & 15;  // 16 pieces of 16 bytes per 256-byte row
+          *reinterpret_cast<uint4*>(vt + (piece >> 3) * TMA_BOX_BYTES + row * 128 + (piece & 7) * 16) = make_uint4(0, 0, 0, 0);
+        }
+        __syncthreads();
+      }
+    } else if constexpr (BULK) {
       // every thread is done with tile - 1, so its slot may be refilled; then wait for this tile's bytes
       __syncthreads();
       if (nt < ntiles) issue_bulk(nt, offb_next);
@@ -349,7 +436,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
       resolve_cp(nt + 1, offc_next);
     }
     const unsigned char* ks = smem + (tile % STAGES) * STAGE_BYTES;
-    const unsigned char* vs = ks + TILE_BYTES;
+    const unsigned char* vs = ks + (TMA ? 2 * TMA_BOX_BYTES : TILE_BYTES);
 
     // S = Q K^T for this warp's 16 rows: two n-tiles of 8 rows
     float s[2][4];
@@ -360,7 +447,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
       unsigned kf[4];
       const int row = warp * 16 + 8 * (mi >> 1) + (lane & 7);
       const int col = kk * 16 + 8 * (mi & 1);
-      ldmatrix_x4(kf, ks + row * PITCH + col * 2);
+      ldmatrix_x4(kf, staged(ks, row, col * 2));
       mma_16816<T>(s[0], qf[kk], kf[0], kf[1]);
       mma_16816<T>(s[1], qf[kk], kf[2], kf[3]);
     }
@@ -420,13 +507,13 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
         unsigned vf[4];
         const int row = warp * 16 + 8 * (mi & 1) + (lane & 7);
         const int col = nn * 16 + 8 * (mi >> 1);
-        ldmatrix_x4_trans(vf, vs + row * PITCH + col * 2);
+        ldmatrix_x4_trans(vf, staged(vs, row, col * 2));
         mma_16816<T>(o[2 * nn], pa, vf[0], vf[1]);
         mma_16816<T>(o[2 * nn + 1], pa, vf[2], vf[3]);
       }
     }
   }
-  if constexpr (!BULK) cp_async_wait<0>();
+  if constexpr (MODE == kCopyCpAsync) cp_async_wait<0>();
   ATTN_STAMP(3);  // all tiles consumed
   if (!WITH_V) return;
   __syncthreads();  // every warp is done with the ring: reuse it for the cross-warp merge
@@ -613,30 +700,80 @@ __global__ void __launch_bounds__(NTHREADS) decode_attn_f32_kernel(const AttnArg
   finish_group<float>(a, b, kvh, w_s, &last_flag);
 }
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
+PFN_encodeTiled encode_tiled_fn() {
+  static PFN_encodeTiled fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<PFN_encodeTiled>(p);
+  }();
+  return fn;
+}
+
+// 4-D map [B, KVH, rows, d] of 16-bit elements over a K or V cache given by element strides; box 64 x 64 rows,
+// 128-byte swizzle.  False when the layout cannot be described (the caller then uses the cp.async variant).
+bool make_kv_map(CUtensorMap* map, bool is_bf16, const void* base, int64_t rows, int KVH, int B, int64_t sr, int64_t sh,
+                 int64_t sb) {
+  PFN_encodeTiled enc = encode_tiled_fn();
+  if (!enc || rows <= 0 || rows > 0x7fffffffll) return false;
+  // a dimension of extent 1 still needs a legal stride
+  if (KVH == 1 && (sh <= 0 || sh % 8)) sh = sr * rows;
+  if (B == 1 && (sb <= 0 || sb % 8)) sb = sh * KVH;
+  if (sr % 8 || sh % 8 || sb % 8 || sr <= 0 || sh <= 0 || sb <= 0) return false;
+  const cuuint64_t dims[4] = {(cuuint64_t)kHeadDim, (cuuint64_t)rows, (cuuint64_t)KVH, (cuuint64_t)B};
+  const cuuint64_t strides[3] = {(cuuint64_t)sr * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};  // bytes, dims 1..3
+  const cuuint32_t box[4] = {64, (cuuint32_t)TILE, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return enc(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <typename T>
-int launch_mma(AttnArgs a, bool with_v, bool with_score, cudaStream_t st) {
+int launch_mma(AttnArgs a, bool with_v, bool with_score, int64_t a_rows, cudaStream_t st) {
   dim3 grid(a.S, a.KVH, a.B), block(NTHREADS);
   int dev = 0, n_sms = 0;
   OMNIKV_CUDA_OK(cudaGetDevice(&dev));
   OMNIKV_CUDA_OK(cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev));
   a.pdl_trigger = ((long long)a.S * a.KVH * a.B <= 2ll * n_sms) ? 1 : 0;  // two CTAs of this kernel fit per SM
-  const bool bulk = a.idxA != nullptr;  // scattered rows: bulk copies; contiguous streams: cp.async
+  // scattered rows: one bulk copy per row; a contiguous cache of known capacity: tensor-map tiles; else cp.async
+  int mode = a.idxA != nullptr ? kCopyBulkRows : kCopyCpAsync;
+  CUtensorMap tm_k = {}, tm_v = {};
+  constexpr bool is_bf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
+  if (mode == kCopyCpAsync && a_rows > 0 && !a.lenB && g_attn_tma_enabled() &&
+      make_kv_map(&tm_k, is_bf16, a.kA, a_rows, a.KVH, a.B, a.a_sr, a.a_sh, a.a_sb) &&
+      (!with_v || make_kv_map(&tm_v, is_bf16, a.vA, a_rows, a.KVH, a.B, a.a_sr, a.a_sh, a.a_sb)))
+    mode = kCopyTma;
   auto go = [&](auto kern, int smem) -> int {
     OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    OMNIKV_CUDA_OK(launch_pdl(kern, grid, block, smem, st, a));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    OMNIKV_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, a, tm_k, tm_v));
     return OMNIKV_OK;
   };
+  const int smem_v = mma_smem_bytes<true>(), smem_k = mma_smem_bytes<false>();
+  const int tma_v = STAGES * 4 * TMA_BOX_BYTES + Q_BYTES + 1024, tma_k = STAGES * 2 * TMA_BOX_BYTES + Q_BYTES + 1024;
   int rc;
-  if (with_v && with_score) {
-    rc = bulk ? go(decode_attn_mma_kernel<T, true, true, true>, mma_smem_bytes<true>())
-              : go(decode_attn_mma_kernel<T, true, true, false>, mma_smem_bytes<true>());
-  } else if (with_v) {
-    rc = bulk ? go(decode_attn_mma_kernel<T, true, false, true>, mma_smem_bytes<true>())
-              : go(decode_attn_mma_kernel<T, true, false, false>, mma_smem_bytes<true>());
-  } else {
-    rc = bulk ? go(decode_attn_mma_kernel<T, false, true, true>, mma_smem_bytes<false>())
-              : go(decode_attn_mma_kernel<T, false, true, false>, mma_smem_bytes<false>());
-  }
+#define OMNIKV_ATTN_GO(V, SC)                                                                         \
+  (mode == kCopyTma        ? go(decode_attn_mma_kernel<T, V, SC, kCopyTma>, V ? tma_v : tma_k)        \
+   : mode == kCopyBulkRows ? go(decode_attn_mma_kernel<T, V, SC, kCopyBulkRows>, V ? smem_v : smem_k) \
+                           : go(decode_attn_mma_kernel<T, V, SC, kCopyCpAsync>, V ? smem_v : smem_k))
+  if (with_v && with_score) rc = OMNIKV_ATTN_GO(true, true);
+  else if (with_v) rc = OMNIKV_ATTN_GO(true, false);
+  else rc = OMNIKV_ATTN_GO(false, true);
+#undef OMNIKV_ATTN_GO
   if (rc != OMNIKV_OK) return rc;
   OMNIKV_CUDA_OK(cudaGetLastError());
   return OMNIKV_OK;
@@ -717,8 +854,8 @@ extern "C" int omnikv_decode_attn(const omnikv_attn_params* p, void* stream) {
   a.status = p->status;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (p->dtype) {
-    case OMNIKV_BF16: return launch_mma<__nv_bfloat16>(a, with_v, with_score, st);
-    case OMNIKV_F16: return launch_mma<__half>(a, with_v, with_score, st);
+    case OMNIKV_BF16: return launch_mma<__nv_bfloat16>(a, with_v, with_score, p->a_rows, st);
+    case OMNIKV_F16: return launch_mma<__half>(a, with_v, with_score, p->a_rows, st);
     default: return launch_f32(a, with_v, with_score, st);
   }
 }

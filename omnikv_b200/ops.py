@@ -161,6 +161,7 @@ def decode_attn(
             ws = workspace(q.device, need, "attn")
         p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
     p.status = status_word(q.device).data_ptr()
+    p.a_rows = k.shape[2]
     abi.check(abi.lib().omnikv_decode_attn(C.byref(p), _stream()), "omnikv_decode_attn")
     _count(1)  # one kernel: the last CTA of every (sequence, KV head) merges the splits
     return out
