@@ -321,7 +321,7 @@ def main():
     achieved = alg_bytes / (dur_ms * 1e-3) / 1e9
     # DRAM bytes per (row, KV head) of this kernel from the ncu capture summarised in profiles/decode_attn_dense.md
     # (dram__bytes_read + dram__bytes_write = 545.06 MB for 131073 rows x 8 KV heads), scaled to this launch
-    traffic = 519.8 * rows * kvh_local
+    traffic = 519.2 * rows * kvh_local
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": traffic, "kernel": "decode_attn_mma_kernel (dense layer, split-K, merge by the last CTA)",
                 "algorithmic_bytes_per_launch": alg_bytes, "launch_ms": dur_ms, "peak_kind": peak_kind}
