@@ -323,7 +323,7 @@ def main():
     # (dram__bytes_read + dram__bytes_write = 545.06 MB for 131073 rows x 8 KV heads), scaled to this launch
     traffic = 519.2 * rows * kvh_local
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": traffic, "kernel": "decode_attn_mma_kernel (dense layer, split-K, merge by the last CTA)",
+                "traffic": traffic, "kernel": "decode_attn_mma_kernel (dense layer: TMA tensor-map tiles, split-K, merge by the last CTA)",
                 "algorithmic_bytes_per_launch": alg_bytes, "launch_ms": dur_ms, "peak_kind": peak_kind}
 
     # whole-step algorithmic bytes (KV + weights) for context

@@ -180,6 +180,7 @@ typedef struct {
   int64_t score_stride;
   void* workspace;
   size_t workspace_bytes;
+  int32_t* status;             /* optional device word: set to 5 if a bounded wait for a K tile ran out */
 } omnikv_window_params;
 
 size_t omnikv_score_window_workspace_bytes(int B, int H, int W, int max_len);

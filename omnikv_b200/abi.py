@@ -50,7 +50,7 @@ class WindowParams(C.Structure):
         ("k_stride_b", C.c_int64), ("k_stride_h", C.c_int64), ("k_stride_row", C.c_int64),
         ("consider_len", C.c_void_p), ("max_len", C.c_int32),
         ("score_out", C.c_void_p), ("planes_out", C.c_void_p), ("score_stride", C.c_int64),
-        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
     ]
 
 

@@ -1,6 +1,7 @@
 // Shared device helpers for the omnikv_b200 kernels (sm_100a).
 #pragma once
 
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -90,6 +91,32 @@ __device__ __forceinline__ void tma_bulk_g2s(void* smem_dst, const void* gmem_sr
                : "memory");
 }
 
+
+// ---- TMA tensor-map tiles of a K or V cache ----------------------------------------------------------------
+// A tile of 64 rows x 256 bytes (head_dim 128, 16-bit) is two boxes of 64 rows x 128 bytes; the map's 128-byte
+// swizzle stores the 16-byte chunk c of row r at chunk c ^ (r & 7) of that row, which makes the unpadded rows
+// conflict-free for ldmatrix.  A box must start on a 1024-byte boundary of shared memory.
+constexpr int kTmaBoxBytes = 64 * 128;
+
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n" ::
+          "r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// Address of the 16-byte piece at (row, byte column < 256) of a staged tile [box of the low 128 bytes | box of the high].
+__device__ __forceinline__ const unsigned char* swz128(const unsigned char* tile_base, int row, int colb) {
+  return tile_base + (colb >> 7) * kTmaBoxBytes + row * 128 + ((((colb & 127) >> 4) ^ (row & 7)) << 4);
+}
+
+// Host: 4-D map [B, KVH, rows, d = 128] of 16-bit elements over a cache given by element strides; box 64 elements
+// x 64 rows, 128-byte swizzle, out-of-range rows read as zero.  False when the driver entry point is missing or
+// the layout cannot be described (callers then use their cp.async variant).
+bool make_kv_tensor_map(CUtensorMap* map, bool is_bf16, const void* base, int64_t rows, int KVH, int B, int64_t sr,
+                        int64_t sh, int64_t sb);
 
 // ---- cp.async (16-byte, L1-bypassing) with zero fill when !valid ---------------------------
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, bool valid) {

@@ -10,7 +10,6 @@
 // Grid (n_splits, KVH, B).  Every CTA owns one contiguous chunk of the sequence's row list and
 // writes one un-normalised partial (o, m, l) per query head; the CTA that finishes last for a (sequence,
 // KV head) merges that group's splits into the output, so an attention call is a single launch.
-#include <cuda.h>
 #include <stdlib.h>
 
 #include <type_traits>
@@ -72,10 +71,6 @@ constexpr int STAGES = 3;
 constexpr int PITCH = 272;     // bytes per staged row: 256 + 16 pad
 constexpr int TILE_BYTES = TILE * PITCH;
 constexpr int Q_BYTES = 16 * PITCH;
-
-typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 // OMNIKV_ATTN_TMA=0 in the environment keeps dense layers on the cp.async variant.
 inline bool g_attn_tma_enabled() {
@@ -176,16 +171,7 @@ __device__ __forceinline__ void finish_group(const AttnArgs& a, int b, int kvh, 
 // the unpadded rows conflict-free for ldmatrix.  Rows past the sequence but inside the capacity arrive as they
 // are in memory: their scores are masked and their V rows are zeroed in shared memory before use.
 constexpr int kCopyCpAsync = 0, kCopyBulkRows = 1, kCopyTma = 2;
-constexpr int TMA_BOX_BYTES = TILE * 128;  // 64 rows x 128 bytes
-
-__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
-                                            uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n" ::
-          "r"(smem_u32(smem_dst)),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
-      : "memory");
-}
+constexpr int TMA_BOX_BYTES = kTmaBoxBytes;
 
 template <typename T, bool WITH_V, bool WITH_SCORE, int MODE>
 __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const AttnArgs a,
@@ -203,7 +189,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
   // byte address of the 16-byte piece at (row, byte column) of a staged K or V tile
   auto staged = [&](const unsigned char* tile_base, int row, int colb) -> const unsigned char* {
     if constexpr (TMA)
-      return tile_base + (colb >> 7) * TMA_BOX_BYTES + row * 128 + ((((colb & 127) >> 4) ^ (row & 7)) << 4);
+      return swz128(tile_base, row, colb);
     else
       return tile_base + row * PITCH + colb;
   };
@@ -700,39 +686,6 @@ __global__ void __launch_bounds__(NTHREADS) decode_attn_f32_kernel(const AttnArg
   finish_group<float>(a, b, kvh, w_s, &last_flag);
 }
 
-// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
-PFN_encodeTiled encode_tiled_fn() {
-  static PFN_encodeTiled fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return reinterpret_cast<PFN_encodeTiled>(p);
-  }();
-  return fn;
-}
-
-// 4-D map [B, KVH, rows, d] of 16-bit elements over a K or V cache given by element strides; box 64 x 64 rows,
-// 128-byte swizzle.  False when the layout cannot be described (the caller then uses the cp.async variant).
-bool make_kv_map(CUtensorMap* map, bool is_bf16, const void* base, int64_t rows, int KVH, int B, int64_t sr, int64_t sh,
-                 int64_t sb) {
-  PFN_encodeTiled enc = encode_tiled_fn();
-  if (!enc || rows <= 0 || rows > 0x7fffffffll) return false;
-  // a dimension of extent 1 still needs a legal stride
-  if (KVH == 1 && (sh <= 0 || sh % 8)) sh = sr * rows;
-  if (B == 1 && (sb <= 0 || sb % 8)) sb = sh * KVH;
-  if (sr % 8 || sh % 8 || sb % 8 || sr <= 0 || sh <= 0 || sb <= 0) return false;
-  const cuuint64_t dims[4] = {(cuuint64_t)kHeadDim, (cuuint64_t)rows, (cuuint64_t)KVH, (cuuint64_t)B};
-  const cuuint64_t strides[3] = {(cuuint64_t)sr * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};  // bytes, dims 1..3
-  const cuuint32_t box[4] = {64, (cuuint32_t)TILE, 1, 1};
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  return enc(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <typename T>
 int launch_mma(AttnArgs a, bool with_v, bool with_score, int64_t a_rows, cudaStream_t st) {
   dim3 grid(a.S, a.KVH, a.B), block(NTHREADS);
@@ -745,8 +698,8 @@ int launch_mma(AttnArgs a, bool with_v, bool with_score, int64_t a_rows, cudaStr
   CUtensorMap tm_k = {}, tm_v = {};
   constexpr bool is_bf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
   if (mode == kCopyCpAsync && a_rows > 0 && !a.lenB && g_attn_tma_enabled() &&
-      make_kv_map(&tm_k, is_bf16, a.kA, a_rows, a.KVH, a.B, a.a_sr, a.a_sh, a.a_sb) &&
-      (!with_v || make_kv_map(&tm_v, is_bf16, a.vA, a_rows, a.KVH, a.B, a.a_sr, a.a_sh, a.a_sb)))
+      make_kv_tensor_map(&tm_k, is_bf16, a.kA, a_rows, a.KVH, a.B, a.a_sr, a.a_sh, a.a_sb) &&
+      (!with_v || make_kv_tensor_map(&tm_v, is_bf16, a.vA, a_rows, a.KVH, a.B, a.a_sr, a.a_sh, a.a_sb)))
     mode = kCopyTma;
   auto go = [&](auto kern, int smem) -> int {
     OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));

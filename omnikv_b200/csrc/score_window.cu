@@ -15,6 +15,10 @@
 // contraction: bf16/fp16 run it on m16n8k16 tensor-core MMAs with the K tile staged by cp.async;
 // fp32 uses CUDA cores.  Query rows are laid out head-major with the window padded to 16 slots,
 // so one MMA m-tile is one head and the max over heads is a max over a thread's own accumulators.
+#include <stdlib.h>
+
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace omnikv {
@@ -43,6 +47,7 @@ struct WinArgs {
   int64_t plane_stride;
   int B, H, KVH, G, W, S, selector, chunk2;
   float scale;
+  int* status;          // device word for bounded-wait failures, or nullptr
 };
 
 __device__ __forceinline__ void split_range(int n, int S, int split, int& r0, int& r1) {
@@ -65,6 +70,15 @@ __device__ __forceinline__ void issue_k_tile(unsigned char* dst, const T* kbase,
   }
 }
 
+// The same tile through the tensor map: two boxes of 64 rows x 128 bytes, issued by ONE thread.
+constexpr int TMA_TILE_BYTES = 2 * kTmaBoxBytes;
+__device__ __forceinline__ void issue_k_tile_tma(unsigned char* dst, const CUtensorMap* map, int row0, int kvh, int b,
+                                                 uint64_t* bar) {
+  mbar_expect_tx(bar, TMA_TILE_BYTES);
+  tma_load_4d(dst, map, 0, row0, kvh, b, bar);
+  tma_load_4d(dst + kTmaBoxBytes, map, 64, row0, kvh, b, bar);
+}
+
 // Query rows of `nheads` heads starting at head h0 -> shared memory [nheads*16][PITCH], slots >= W zero.
 template <typename T>
 __device__ __forceinline__ void load_q(unsigned char* q_s, const T* qw_b, int h0, int nheads, int W, int tid) {
@@ -79,7 +93,7 @@ __device__ __forceinline__ void load_q(unsigned char* q_s, const T* qw_b, int h0
 
 // acc[i][j][e]: head i of the group, n-tile j (8 keys), e as in the m16n8 C fragment
 // (row g + 8*(e>>1) = window slot, column 2t + (e&1) = key).
-template <typename T, int G>
+template <typename T, int G, bool TMA>
 __device__ __forceinline__ void qk_tile(float (&acc)[G][2][4], const unsigned char* q_s, const unsigned char* ks,
                                         int warp, int lane) {
   const int mi = lane >> 3;
@@ -90,7 +104,8 @@ __device__ __forceinline__ void qk_tile(float (&acc)[G][2][4], const unsigned ch
 #pragma unroll
   for (int kk = 0; kk < 8; ++kk) {
     unsigned kf[4];
-    ldmatrix_x4(kf, ks + (warp * 16 + 8 * (mi >> 1) + (lane & 7)) * PITCH + (kk * 16 + 8 * (mi & 1)) * 2);
+    const int krow = warp * 16 + 8 * (mi >> 1) + (lane & 7), kcolb = (kk * 16 + 8 * (mi & 1)) * 2;
+    ldmatrix_x4(kf, TMA ? swz128(ks, krow, kcolb) : ks + krow * PITCH + kcolb);
 #pragma unroll
     for (int i = 0; i < G; ++i) {
       unsigned qa[4];
@@ -109,10 +124,14 @@ __device__ __forceinline__ void merge_ml(float& m, float& l, float m2, float l2)
 }
 
 // ---- pass 1: per-row (max, sum-exp) over the CTA's chunk -------------------------------------
-template <typename T, int G>
-__global__ void __launch_bounds__(NTHREADS, 3) window_pass1_mma(const WinArgs a) {
-  extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* q_s = smem + P1_STAGES * TILE_BYTES;
+template <typename T, int G, bool TMA>
+__global__ void __launch_bounds__(NTHREADS, 3) window_pass1_mma(const WinArgs a, const __grid_constant__ CUtensorMap tm_k) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[P1_STAGES];
+  constexpr int KT = TMA ? TMA_TILE_BYTES : TILE_BYTES;  // bytes of a staged K tile
+  unsigned char* smem = TMA ? reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023)
+                            : smem_raw;
+  unsigned char* q_s = smem + P1_STAGES * KT;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int n = a.consider_len[b];
@@ -121,10 +140,21 @@ __global__ void __launch_bounds__(NTHREADS, 3) window_pass1_mma(const WinArgs a)
   const int ntiles = r1 > r0 ? ceil_div(r1 - r0, TILE) : 0;
   const T* kbase = static_cast<const T*>(a.k) + (size_t)b * a.k_sb + (size_t)kvh * a.k_sh;
 
+  if constexpr (TMA) {
+    if (tid == 0) {
 #pragma unroll
-  for (int s = 0; s < P1_STAGES - 1; ++s) {
-    if (s < ntiles) issue_k_tile<T>(smem + s * TILE_BYTES, kbase, a.k_sr, r0 + s * TILE, r1, tid);
-    cp_async_commit();
+      for (int s = 0; s < P1_STAGES; ++s) mbar_init(&full_bar[s], 1);
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+#pragma unroll
+      for (int s = 0; s < P1_STAGES - 1; ++s)
+        if (s < ntiles) issue_k_tile_tma(smem + s * KT, &tm_k, r0 + s * TILE, kvh, b, &full_bar[s]);
+    }
+  } else {
+#pragma unroll
+    for (int s = 0; s < P1_STAGES - 1; ++s) {
+      if (s < ntiles) issue_k_tile<T>(smem + s * KT, kbase, a.k_sr, r0 + s * TILE, r1, tid);
+      cp_async_commit();
+    }
   }
   load_q<T>(q_s, static_cast<const T*>(a.qw) + (size_t)b * a.H * a.W * kHeadDim, kvh * G, G, a.W, tid);
   __syncthreads();
@@ -134,15 +164,22 @@ __global__ void __launch_bounds__(NTHREADS, 3) window_pass1_mma(const WinArgs a)
   for (int i = 0; i < G; ++i) m[i][0] = m[i][1] = -INFINITY, l[i][0] = l[i][1] = 0.f;
 
   for (int tile = 0; tile < ntiles; ++tile) {
-    cp_async_wait<P1_STAGES - 2>();
-    __syncthreads();
     {
       const int nt = tile + P1_STAGES - 1;
-      if (nt < ntiles) issue_k_tile<T>(smem + (nt % P1_STAGES) * TILE_BYTES, kbase, a.k_sr, r0 + nt * TILE, r1, tid);
-      cp_async_commit();
+      if constexpr (TMA) {
+        __syncthreads();  // every thread is done with tile - 1: its slot may be refilled
+        if (tid == 0 && nt < ntiles)
+          issue_k_tile_tma(smem + (nt % P1_STAGES) * KT, &tm_k, r0 + nt * TILE, kvh, b, &full_bar[nt % P1_STAGES]);
+        if (!mbar_wait(&full_bar[tile % P1_STAGES], (tile / P1_STAGES) & 1) && a.status) atomicExch(a.status, 5);
+      } else {
+        cp_async_wait<P1_STAGES - 2>();
+        __syncthreads();
+        if (nt < ntiles) issue_k_tile<T>(smem + (nt % P1_STAGES) * KT, kbase, a.k_sr, r0 + nt * TILE, r1, tid);
+        cp_async_commit();
+      }
     }
     float acc[G][2][4];
-    qk_tile<T, G>(acc, q_s, smem + (tile % P1_STAGES) * TILE_BYTES, warp, lane);
+    qk_tile<T, G, TMA>(acc, q_s, smem + (tile % P1_STAGES) * KT, warp, lane);
     const int cbase = r0 + tile * TILE + warp * 16 + 2 * t;
 #pragma unroll
     for (int i = 0; i < G; ++i)
@@ -224,10 +261,14 @@ __device__ __forceinline__ float slot_weight(int selector, int W, int w) {
 // SM, latency bound at 3 us per tile; without that table a CTA needs 69 KB and three are resident.
 constexpr int P2_CHUNK = 512;
 
-template <typename T, int G>
-__global__ void __launch_bounds__(NTHREADS, 3) window_pass2_mma(const WinArgs a) {
-  extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* q_s = smem + P2_STAGES * TILE_BYTES;                             // [G*16][PITCH]
+template <typename T, int G, bool TMA>
+__global__ void __launch_bounds__(NTHREADS, 3) window_pass2_mma(const WinArgs a, const __grid_constant__ CUtensorMap tm_k) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[P2_STAGES];
+  constexpr int KT = TMA ? TMA_TILE_BYTES : TILE_BYTES;
+  unsigned char* smem = TMA ? reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023)
+                            : smem_raw;
+  unsigned char* q_s = smem + P2_STAGES * KT;                                     // [G*16][PITCH]
   float* st_s = reinterpret_cast<float*>(q_s + (size_t)G * WPAD * PITCH);         // [G*16][2]
   const int kvh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -239,25 +280,43 @@ __global__ void __launch_bounds__(NTHREADS, 3) window_pass2_mma(const WinArgs a)
   const T* kb = static_cast<const T*>(a.k) + (size_t)b * a.k_sb + (size_t)kvh * a.k_sh;
   const T* qb = static_cast<const T*>(a.qw) + (size_t)b * a.H * a.W * kHeadDim;
 
+  if constexpr (TMA) {
+    if (tid == 0) {
 #pragma unroll
-  for (int s = 0; s < P2_STAGES - 1; ++s) {
-    if (s < ntiles) issue_k_tile<T>(smem + s * TILE_BYTES, kb, a.k_sr, r0 + s * TILE, r1, tid);
-    cp_async_commit();
+      for (int s = 0; s < P2_STAGES; ++s) mbar_init(&full_bar[s], 1);
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+#pragma unroll
+      for (int s = 0; s < P2_STAGES - 1; ++s)
+        if (s < ntiles) issue_k_tile_tma(smem + s * KT, &tm_k, r0 + s * TILE, kvh, b, &full_bar[s]);
+    }
+  } else {
+#pragma unroll
+    for (int s = 0; s < P2_STAGES - 1; ++s) {
+      if (s < ntiles) issue_k_tile<T>(smem + s * KT, kb, a.k_sr, r0 + s * TILE, r1, tid);
+      cp_async_commit();
+    }
   }
   load_q<T>(q_s, qb, kvh * G, G, a.W, tid);
   for (int i = tid; i < G * WPAD * 2; i += NTHREADS) st_s[i] = a.stats[((size_t)b * a.H + kvh * G) * WPAD * 2 + i];
   int* plane0 = reinterpret_cast<int*>(a.planes) + (size_t)b * a.W * a.plane_stride;
 
   for (int tile = 0; tile < ntiles; ++tile) {
-    cp_async_wait<P2_STAGES - 2>();
-    __syncthreads();  // the tile has landed (and, the first time, the queries and statistics are in place)
     {
       const int nt = tile + P2_STAGES - 1;
-      if (nt < ntiles) issue_k_tile<T>(smem + (nt % P2_STAGES) * TILE_BYTES, kb, a.k_sr, r0 + nt * TILE, r1, tid);
-      cp_async_commit();
+      if constexpr (TMA) {
+        __syncthreads();  // slot of tile - 1 is free (and, the first time, queries and statistics are in place)
+        if (tid == 0 && nt < ntiles)
+          issue_k_tile_tma(smem + (nt % P2_STAGES) * KT, &tm_k, r0 + nt * TILE, kvh, b, &full_bar[nt % P2_STAGES]);
+        if (!mbar_wait(&full_bar[tile % P2_STAGES], (tile / P2_STAGES) & 1) && a.status) atomicExch(a.status, 5);
+      } else {
+        cp_async_wait<P2_STAGES - 2>();
+        __syncthreads();  // the tile has landed (and, the first time, the queries and statistics are in place)
+        if (nt < ntiles) issue_k_tile<T>(smem + (nt % P2_STAGES) * KT, kb, a.k_sr, r0 + nt * TILE, r1, tid);
+        cp_async_commit();
+      }
     }
     float acc[G][2][4];
-    qk_tile<T, G>(acc, q_s, smem + (tile % P2_STAGES) * TILE_BYTES, warp, lane);
+    qk_tile<T, G, TMA>(acc, q_s, smem + (tile % P2_STAGES) * KT, warp, lane);
     const int cbase = r0 + tile * TILE + warp * 16 + 2 * t;
     float hm[2][4];
 #pragma unroll
@@ -421,21 +480,21 @@ __global__ void __launch_bounds__(NTHREADS) window_pass2_f32(const WinArgs a) {
   }
 }
 
-template <typename T, int G>
-int launch_mma(const WinArgs& a, int n_chunks2, int max_len, cudaStream_t st) {
-  const int smem1 = P1_STAGES * TILE_BYTES + G * WPAD * PITCH;
-  const int smem2 = P2_STAGES * TILE_BYTES + G * WPAD * PITCH + G * WPAD * 2 * (int)sizeof(float);
-  (void)n_chunks2;
-  OMNIKV_CUDA_OK(cudaFuncSetAttribute(window_pass1_mma<T, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1));
-  OMNIKV_CUDA_OK(cudaFuncSetAttribute(window_pass2_mma<T, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
+template <typename T, int G, bool TMA>
+int launch_mma_copy(const WinArgs& a, const CUtensorMap& tm_k, int max_len, cudaStream_t st) {
+  constexpr int KT = TMA ? TMA_TILE_BYTES : TILE_BYTES;
+  const int smem1 = P1_STAGES * KT + G * WPAD * PITCH + (TMA ? 1024 : 0);
+  const int smem2 = P2_STAGES * KT + G * WPAD * PITCH + G * WPAD * 2 * (int)sizeof(float) + (TMA ? 1024 : 0);
+  OMNIKV_CUDA_OK(cudaFuncSetAttribute(window_pass1_mma<T, G, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1));
+  OMNIKV_CUDA_OK(cudaFuncSetAttribute(window_pass2_mma<T, G, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
   // the planes receive atomic maxima: clear the part pass 2 may touch
   OMNIKV_CUDA_OK(cudaMemsetAsync(a.planes, 0, (size_t)a.B * a.W * a.plane_stride * sizeof(float), st));
-  window_pass1_mma<T, G><<<dim3(a.S, a.KVH, a.B), NTHREADS, smem1, st>>>(a);
+  window_pass1_mma<T, G, TMA><<<dim3(a.S, a.KVH, a.B), NTHREADS, smem1, st>>>(a, tm_k);
   OMNIKV_CUDA_OK(cudaGetLastError());
   const int rows = a.B * a.H * WPAD;
   window_stats_merge<<<ceil_div(rows, 128), 128, 0, st>>>(a.part, a.stats, rows, a.S);
   OMNIKV_CUDA_OK(cudaGetLastError());
-  window_pass2_mma<T, G><<<dim3(ceil_div(max_len, P2_CHUNK), a.KVH, a.B), NTHREADS, smem2, st>>>(a);
+  window_pass2_mma<T, G, TMA><<<dim3(ceil_div(max_len, P2_CHUNK), a.KVH, a.B), NTHREADS, smem2, st>>>(a, tm_k);
   OMNIKV_CUDA_OK(cudaGetLastError());
   if (a.score_out) {
     window_fold_planes<<<dim3(min(1184, ceil_div(max_len, 256)), a.B), 256, 0, st>>>(
@@ -443,6 +502,22 @@ int launch_mma(const WinArgs& a, int n_chunks2, int max_len, cudaStream_t st) {
     OMNIKV_CUDA_OK(cudaGetLastError());
   }
   return OMNIKV_OK;
+}
+
+// K tiles travel through a TMA tensor map over rows [0, max_len) of the cache (rows past it read as zero and are
+// masked anyway); when the map cannot be built, through 16-byte cp.async copies.
+template <typename T, int G>
+int launch_mma(const WinArgs& a, int n_chunks2, int max_len, cudaStream_t st) {
+  (void)n_chunks2;
+  CUtensorMap tm_k = {};
+  constexpr bool is_bf16 = !std::is_same<T, __half>::value;
+  static const bool tma_on = [] {
+    const char* e = getenv("OMNIKV_WINDOW_TMA");
+    return !(e && e[0] == '0');
+  }();
+  if (tma_on && make_kv_tensor_map(&tm_k, is_bf16, a.k, max_len, a.KVH, a.B, a.k_sr, a.k_sh, a.k_sb))
+    return launch_mma_copy<T, G, true>(a, tm_k, max_len, st);
+  return launch_mma_copy<T, G, false>(a, tm_k, max_len, st);
 }
 
 template <typename T>
@@ -514,7 +589,7 @@ extern "C" int omnikv_score_window(const omnikv_window_params* p, void* stream) 
     a.planes = a.stats + stats_floats(p->B, p->H); a.plane_stride = (int64_t)plane_stride_of(p->max_len);
   }
   a.B = p->B; a.H = p->H; a.KVH = p->KVH; a.G = p->H / p->KVH; a.W = p->W; a.S = kPass1Splits;
-  a.selector = p->selector; a.scale = p->scale;
+  a.selector = p->selector; a.scale = p->scale; a.status = p->status;
   // pass 2: chunks of whole tiles, about two CTAs' worth of chunks per SM over the batch
   int chunks = ceil_div(296, p->B);
   a.chunk2 = ceil_div(ceil_div(p->max_len, chunks), TILE) * TILE;

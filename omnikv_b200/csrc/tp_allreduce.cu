@@ -9,7 +9,7 @@
 // stores, never on a peer, so there is no cycle).  The grid is small enough to be resident at once.
 //
 // Exchange buffer layout and flag values are those of omnikv_tp_exchange (two alternating slots, flag =
-// step * 256 + exchange number + 1, nothing is ever reset).  No TMA, no multicast: plain loads and stores.
+// step * 256 + exchange number + 1, nothing is ever reset).  Plain peer loads and stores only.
 #include "common.cuh"
 
 namespace omnikv {

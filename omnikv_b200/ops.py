@@ -104,13 +104,15 @@ def decode_attn(
     scale: Optional[float] = None,
     ws: Optional[torch.Tensor] = None,
     scores_only: bool = False,
+    state_capacity: bool = True,
 ) -> Optional[torch.Tensor]:
     """``omnikv_decode_attn``.  q ``[B,H,d]``; k, v ``[B,KVH,rows,d]``; ``len_a`` int32 ``[B]`` on
     the device; ``idx`` int32 ``[B, >=len_a]`` selects rows of (k, v) (with ``idx_row`` int32 ``[B]``, batch
     entry b reads row ``idx_row[b]`` of ``idx`` -- a request table over a paged pool); the tail is
     ``tail_len[b]`` rows of (k_tail, v_tail) from ``tail_start[b]``.  ``score_out``
     ``[KVH,B,stride]`` fp32 receives the per-KV-head selector-``last`` scores of positions
-    ``< score_len[b]``.  Returns ``out`` ``[B,H,d]`` (None when ``scores_only``)."""
+    ``< score_len[b]``.  ``state_capacity=False`` withholds the cache's row capacity from the kernel (it then
+    uses its cp.async variant on dense layers).  Returns ``out`` ``[B,H,d]`` (None when ``scores_only``)."""
     _need_cuda(q, k, v, len_a, idx, idx_row, k_tail, v_tail, out, score_out)
     B, H, d = q.shape
     KVH = k.shape[1]
@@ -161,7 +163,8 @@ def decode_attn(
             ws = workspace(q.device, need, "attn")
         p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
     p.status = status_word(q.device).data_ptr()
-    p.a_rows = k.shape[2]
+    # the row capacity lets a dense 16-bit layer fetch its tiles through a TMA tensor map
+    p.a_rows = k.shape[2] if state_capacity else 0
     abi.check(abi.lib().omnikv_decode_attn(C.byref(p), _stream()), "omnikv_decode_attn")
     _count(1)  # one kernel: the last CTA of every (sequence, KV head) merges the splits
     return out
@@ -239,6 +242,7 @@ def score_window(qw: torch.Tensor, k: torch.Tensor, consider_len: torch.Tensor, 
     if ws is None:
         ws = workspace(qw.device, need, "window")
     p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
+    p.status = status_word(qw.device).data_ptr()
     abi.check(abi.lib().omnikv_score_window(C.byref(p), _stream()), "omnikv_score_window")
     _count(3)  # pass 1, statistics merge, pass 2
     return score_out if planes_out is None else planes_out

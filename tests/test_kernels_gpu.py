@@ -623,3 +623,30 @@ def test_ragged_batch_splits_cover_every_row():
         for b in range(B):
             ref = oracle.dense_attention(q[b:b + 1].cpu(), k[b:b + 1, :, :lens[b]].cpu(), v[b:b + 1, :, :lens[b]].cpu())
             assert (o[b:b + 1].float().cpu() - ref).abs().max().item() < 2e-2, (s, b)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,L,cap", [(1, 5000, 5000), (1, 4097, 6000), (3, 700, 1024), (2, 64, 64)])
+def test_dense_attn_tensor_map_tiles_equal_cp_async(dtype, B, L, cap):
+    """The two ways a dense layer's tiles reach shared memory -- TMA tensor-map boxes with a 128-byte swizzle when the
+    cache's capacity is stated, 16-byte cp.async copies into padded rows otherwise -- feed the same arithmetic:
+    outputs and score planes are bit-identical, also with garbage (NaN) in the cache rows past the sequence."""
+    g = torch.Generator(device="cuda").manual_seed(31)
+    H, KVH, d = 8, 2, 128
+    kv = torch.randn(B, KVH, cap, 2, d, generator=g, device="cuda").to(dtype)
+    lens = [L - 3 * b for b in range(B)]
+    for b in range(B):
+        kv[b, :, lens[b]:] = float("nan")   # rows the kernel may fetch but must not use
+    kc, vc = kv[:, :, :, 0, :], kv[:, :, :, 1, :]
+    q = torch.randn(B, H, d, generator=g, device="cuda").to(dtype)
+    n = dev_i32(lens)
+    outs = []
+    for cap_known in (True, False):
+        planes = torch.zeros(KVH, B, cap, dtype=torch.float32, device="cuda")
+        o = ops().decode_attn(q, kc, vc, n, score_out=planes, score_len=n, state_capacity=cap_known, n_splits=3)
+        outs.append((o, planes))
+    ops().check_status("cuda")
+    assert torch.isfinite(outs[0][0].float()).all()
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    ref = oracle.dense_attention(q[:1].cpu(), kc[:1, :, :lens[0]].cpu(), vc[:1, :, :lens[0]].cpu())
+    assert (outs[0][0][:1].float().cpu() - ref).abs().max().item() < 2e-2
