@@ -7,6 +7,8 @@
 // the cluster through distributed shared memory.  Integer atomics only: the result is deterministic.
 #include <cooperative_groups.h>
 
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -16,7 +18,7 @@ namespace {
 
 constexpr int TK_THREADS = 1024;
 constexpr int TK_WARPS = TK_THREADS / 32;
-constexpr int TK_MAX_CLUSTER = 8;
+constexpr int TK_MAX_CLUSTER = 16;  // 16 needs the non-portable cluster size attribute; 8 is the portable limit
 constexpr int TK_RESIDENT_KEYS = 49152;  // 192 KiB of keys per CTA
 
 struct TopkArgs {
@@ -270,27 +272,44 @@ extern "C" int omnikv_topk(const float* scores, int n_planes, int64_t plane_stri
             (n_planes == 1 || plane_stride % 4 == 0) && (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15) == 0) &&
             max_len % 4 == 0) ? 1 : 0;
 
-  int csize = 1;
-  while (csize < TK_MAX_CLUSTER && ceil_div(max_len, csize) > 8192) csize *= 2;
-  const int slice = ceil_div(ceil_div(max_len, csize), 4) * 4;
-  const bool resident = slice <= TK_RESIDENT_KEYS;
-  if (!resident && (!workspace || workspace_bytes < omnikv_topk_workspace_bytes(B, max_len))) return OMNIKV_E_WORKSPACE;
-  const size_t smem = ((sizeof(TkShared) + 15) / 16) * 16 + (resident ? (size_t)slice * sizeof(unsigned) : 0);
-
-  auto kern = resident ? topk_kernel<true> : topk_kernel<false>;
-  OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  // Slices of at most 8192 keys per CTA; a cluster of 16 (above the portable limit of 8) when the device can
+  // co-schedule one, since the load of the score planes and every histogram pass scale with the CTA count.
+  static const int max_cluster = [] {
+    const char* e = getenv("OMNIKV_TOPK_CLUSTER");
+    const int v = e ? atoi(e) : TK_MAX_CLUSTER;
+    return v >= 1 && v <= TK_MAX_CLUSTER ? v : TK_MAX_CLUSTER;
+  }();
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(csize, B, 1);
-  cfg.blockDim = dim3(TK_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = static_cast<cudaStream_t>(stream);
   cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = csize;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  decltype(&topk_kernel<true>) kern = nullptr;
+  int csize = 1;
+  for (int limit = max_cluster;; limit = 8) {
+    csize = 1;
+    while (csize < limit && ceil_div(max_len, csize) > 8192) csize *= 2;
+    const int slice = ceil_div(ceil_div(max_len, csize), 4) * 4;
+    const bool resident = slice <= TK_RESIDENT_KEYS;
+    if (!resident && (!workspace || workspace_bytes < omnikv_topk_workspace_bytes(B, max_len))) return OMNIKV_E_WORKSPACE;
+    const size_t smem = ((sizeof(TkShared) + 15) / 16) * 16 + (resident ? (size_t)slice * sizeof(unsigned) : 0);
+    kern = resident ? topk_kernel<true> : topk_kernel<false>;
+    OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (csize > 8) OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    cfg = {};
+    cfg.gridDim = dim3(csize, B, 1);
+    cfg.blockDim = dim3(TK_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = csize;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (csize <= 8) break;
+    // a cluster of 16 CTAs of this size must be schedulable at once on this device; else the portable 8
+    int n_clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&n_clusters, kern, &cfg) == cudaSuccess && n_clusters >= 1) break;
+    (void)cudaGetLastError();
+  }
   OMNIKV_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, a));
   return OMNIKV_OK;
 }
