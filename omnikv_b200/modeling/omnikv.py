@@ -84,6 +84,18 @@ class OmniKVRotaryEmbedding(nn.Module):
         return emb.cos().to(x.dtype), emb.sin().to(x.dtype)
 
 
+class _LazyRotary:
+    """(cos, sin) computed when first unpacked; ``cos, sin = obj`` works as with the tuple."""
+
+    def __init__(self, make):
+        self._make, self._value = make, None
+
+    def __iter__(self):
+        if self._value is None:
+            self._value = self._make()
+        return iter(self._value)
+
+
 def rotate_half(x):
     h = x.shape[-1] // 2
     return torch.cat((-x[..., h:], x[..., :h]), dim=-1)
@@ -198,7 +210,6 @@ class OmniKVAttention(nn.Module):
 
     def forward(self, hidden_states, position_embeddings, past_key_value, score_out=None, score_len=None):
         B, n, _ = hidden_states.shape
-        cos, sin = position_embeddings
         rope_pos = getattr(past_key_value, "rope_pos_dev", None)
         if n == 1 and rope_pos is not None and hidden_states.is_cuda and self.head_dim == 128:
             # decode: rotate q and k and append k, v to the cache in one kernel, straight from the fused projection
@@ -210,6 +221,7 @@ class OmniKVAttention(nn.Module):
             o = past_key_value.attend(q, self.layer_idx, score_out=score_out, score_len=score_len)
             o = F.linear(o.view(B, 1, self.num_heads * self.head_dim), self.o_weight)
             return self.tp.all_reduce_sum(o) if self.tp is not None else o
+        cos, sin = position_embeddings
         q, k, v = self.qkv(hidden_states, cos, sin)
         if n > 1:  # prefill: full causal attention over the fresh keys (what cache.update returns)
             k, v = past_key_value.update(k, v, self.layer_idx)
@@ -544,7 +556,8 @@ class OmniKVMulModel(nn.Module):
                 cache.rope_pos_dev = position_ids.reshape(-1).to(torch.int32).contiguous()
         elif position_ids is None:
             position_ids = torch.arange(n, device=h.device)[None, :].expand(B, n)
-        pos_emb = self.rotary_emb(h, position_ids)
+        # the fused batch-1 kernels rotate inside the QKV kernel and never read the table: build it on first use
+        pos_emb = _LazyRotary(lambda: self.rotary_emb(h, position_ids))
         for layer in self.layers:
             h = layer(h, attention_mask=attention_mask, position_ids=position_ids, past_key_value=cache,
                       use_cache=use_cache, cache_position=cache_position, position_embeddings=pos_emb)[0]

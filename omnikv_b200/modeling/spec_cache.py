@@ -139,10 +139,10 @@ class OmniKVMultiStageCache:
         self.prefill_len = int(max(prefill_lens))
         i32 = dict(dtype=torch.int32, device=device)
         self.prefill_len_dev = torch.tensor(list(prefill_lens), **i32)
-        self.cur_len_dev = self.prefill_len_dev.clone()
-        self.tail_len_dev = torch.zeros(B, **i32)
-        self.pos_dev = self.prefill_len_dev - 1
-        self.tail_pos_dev = torch.full((B,), -1, **i32)
+        # the four counters a decode step advances live in ONE tensor, so one in-place add moves them all
+        self._step_counters = torch.stack([self.prefill_len_dev, torch.zeros(B, **i32), self.prefill_len_dev - 1,
+                                           torch.full((B,), -1, **i32)]).contiguous()
+        self.cur_len_dev, self.tail_len_dev, self.pos_dev, self.tail_pos_dev = self._step_counters.unbind(0)
         self.zero_dev = torch.zeros(B, **i32)
 
     def _alloc_layer(self, layer_idx: int, B: int, KVH: int, d: int, dtype, device) -> None:
@@ -255,10 +255,7 @@ class OmniKVMultiStageCache:
         step before layer 0 appends (the reference bumps ``_seen_tokens`` at layer 0, :315-316):
         ``update`` does it for layer 0; callers of ``append_kv`` do it themselves."""
         self.check_room(1)
-        self.cur_len_dev.add_(1)
-        self.tail_len_dev.add_(1)
-        self.pos_dev.add_(1)
-        self.tail_pos_dev.add_(1)
+        self._step_counters.add_(1)  # cur_len, tail_len, pos, tail_pos
         self._seen_tokens += 1
 
     def check_room(self, n_tokens: int) -> None:
