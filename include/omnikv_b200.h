@@ -329,7 +329,11 @@ int omnikv_decode_gemv_residual(int dtype, const void* w, int N, int K, const vo
                                 void* out, const omnikv_tp_exchange* tp_out, int32_t* status, void* stream);
 int omnikv_decode_gate_up(int dtype, const void* h, const void* norm_w, float eps, const void* w_gate_up,
                           int hidden, int inter, void* act_out, const omnikv_tp_exchange* tp_in, void* h_inout,
-                          int32_t* status, void* stream);
+                          int32_t* sched, int32_t* status, void* stream);
+/* sched (optional): four device int32, zero before the first use (the kernel leaves them zero).  With it the last
+ * chunks of the gate/up matrix are handed to whichever SM is ready instead of by a fixed round-robin, which evens
+ * out the end of the kernel (SMs do not all stream at the same rate).  Calls sharing one sched buffer must be
+ * issued on one stream.  NULL: fixed assignment. */
 int omnikv_decode_logits(int dtype, const void* h, const void* norm_w, float eps, const void* w_head,
                          int hidden, int vocab_rows, int row_offset, float* logits,
                          unsigned long long* best_scratch, int64_t* token_out, const omnikv_tp_exchange* tp_in,

@@ -71,6 +71,8 @@ struct GemvArgs {
   const unsigned* tp_epoch;         // device word bumped once per decode step
   unsigned tp_seq;                  // flag value = epoch * 256 + seq + 1
   int trace_slot;                   // profiling build: which slot of the stamp array this launch writes
+  int tail_pool;                    // chunks at the end of the matrix handed out dynamically (0: all static)
+  int* tail_next;                   // [2] device: next index of the pool, finished producers (self-resetting)
 };
 
 #ifdef OMNIKV_GEMV_TRACE
@@ -165,6 +167,7 @@ __device__ __forceinline__ bool produce_phase(const GemvArgs& a, const Ring& rin
   constexpr unsigned PIECE_BYTES = HALF * K * 2;
   const T* W = static_cast<const T*>(a.W);
   int i = 0;
+  int grab = -2;  // index taken from the tail pool and not used yet (-2: none)
   for (;; ++it) {
     const int slot = it % GV_STAGES;
     if (it >= GV_STAGES && !mbar_wait(&ring.empty_bar[slot], ((it / GV_STAGES) - 1) & 1)) {
@@ -184,6 +187,20 @@ __device__ __forceinline__ bool produce_phase(const GemvArgs& a, const Ring& rin
     int c;
     if (a.next_chunk) {
       c = atomicAdd(a.next_chunk, 1);
+    } else if (a.tail_pool > 0) {
+      // static share first; the LAST tail_pool chunks of the matrix go to whoever gets there first, one at a
+      // time, the next grab already requested while the current chunk is being fetched
+      const int n_static = a.n_chunks - a.tail_pool;
+      c = (int)blockIdx.x + i * (int)gridDim.x;
+      if (c < n_static) {
+        ++i;
+        if (grab == -2 && (int)blockIdx.x + (i + 1) * (int)gridDim.x >= n_static) grab = atomicAdd(a.tail_next, 1);
+      } else {
+        if (grab == -2) grab = atomicAdd(a.tail_next, 1);
+        c = n_static + grab;
+        grab = -2;
+        if (c < a.n_chunks) grab = atomicAdd(a.tail_next, 1);
+      }
     } else {
       c = (int)blockIdx.x + i * (int)gridDim.x;
       ++i;
@@ -192,6 +209,10 @@ __device__ __forceinline__ bool produce_phase(const GemvArgs& a, const Ring& rin
       ring.slot_chunk[slot] = -1;
       mbar_arrive(&ring.full_bar[slot]);
       ++it;
+      if (a.tail_pool > 0 && atomicAdd(a.tail_next + 1, 1) == (int)gridDim.x - 1) {  // last producer: reset
+        a.tail_next[0] = 0;
+        a.tail_next[1] = 0;
+      }
       return true;
     }
     ring.slot_chunk[slot] = c;
@@ -672,12 +693,27 @@ int launch_one(const GemvArgs& a, int n_sms, cudaStream_t st) {
   auto kern = decode_gemv_kernel<T, KV, WK, EPI>;
   OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int grid = a.n_chunks < n_sms ? a.n_chunks : n_sms;
+  GemvArgs aa = a;
+  if (aa.tail_next) {
+    // The last chunks of a long matrix are handed out dynamically (two per CTA on average): SMs that stream a
+    // little faster take more of them, which evens out the end of the kernel.  Worth it only when a CTA has
+    // many chunks; calls alternate between the two counter pairs of the caller's buffer, so that a launch
+    // that starts early (programmatic dependent launch) never shares a pair with the one before it.
+    static unsigned toggle = 0;
+    const int pool = 2 * grid;
+    if (aa.tp_world <= 1 && aa.n_chunks >= 8 * grid) {
+      aa.tail_pool = pool;
+      aa.tail_next += 2 * (toggle++ & 1u);
+    } else {
+      aa.tail_next = nullptr;
+    }
+  }
 #ifdef OMNIKV_GEMV_TRACE
-  GemvArgs b = a;
+  GemvArgs b = aa;
   b.trace_slot = g_trace_launch++ % 64;
   OMNIKV_CUDA_OK(launch_pdl(kern, dim3(grid), dim3(GV_THREADS), smem, st, b));
 #else
-  OMNIKV_CUDA_OK(launch_pdl(kern, dim3(grid), dim3(GV_THREADS), smem, st, a));
+  OMNIKV_CUDA_OK(launch_pdl(kern, dim3(grid), dim3(GV_THREADS), smem, st, aa));
 #endif
   return OMNIKV_OK;
 }
@@ -809,7 +845,7 @@ extern "C" int omnikv_decode_gemv_residual(int dtype, const void* w, int N, int 
 
 extern "C" int omnikv_decode_gate_up(int dtype, const void* h, const void* norm_w, float eps, const void* w_gate_up,
                                      int hidden, int inter, void* act_out, const omnikv_tp_exchange* tp_in,
-                                     void* h_inout, int32_t* status, void* stream) {
+                                     void* h_inout, int32_t* sched, int32_t* status, void* stream) {
   using namespace omnikv;
   if (!h || !norm_w || !w_gate_up || !act_out || !status || inter <= 0) return OMNIKV_E_BADARG;
   if (!al16(h) || !al16(norm_w) || !al16(w_gate_up)) return OMNIKV_E_BADARG;
@@ -817,7 +853,7 @@ extern "C" int omnikv_decode_gate_up(int dtype, const void* h, const void* norm_
   if (inter % half) return OMNIKV_E_UNSUPPORTED;
   GemvArgs a = {};
   a.W = w_gate_up; a.x = h; a.norm_w = norm_w; a.eps = eps; a.N = 2 * inter; a.K = hidden;
-  a.n_chunks = inter / half; a.partner_rows = inter; a.out = act_out; a.status = status;
+  a.n_chunks = inter / half; a.partner_rows = inter; a.out = act_out; a.status = status; a.tail_next = sched;
   if (const int rc = tp_fill_consumer(a, tp_in, hidden, h_inout)) return rc;
   return dispatch<EPI_GATEUP>(dtype, a, static_cast<cudaStream_t>(stream));
 }

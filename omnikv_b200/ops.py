@@ -377,6 +377,17 @@ FUSED_K = (512, 1024, 1792, 2048, 3584, 4096, 7168, 8192, 14336)
 _status = {}
 
 
+_sched = {}
+
+
+def sched_words(device) -> torch.Tensor:
+    """Four zeroed int32 per device: the dynamic-tail counters of ``omnikv_decode_gate_up`` (self-resetting)."""
+    key = torch.device(device).index
+    if key not in _sched:
+        _sched[key] = torch.zeros(4, dtype=torch.int32, device=device)
+    return _sched[key]
+
+
 def status_word(device) -> torch.Tensor:
     """The device int32 the kernels report bounded-wait failures into (stays 0)."""
     key = torch.device(device).index
@@ -436,7 +447,8 @@ def decode_gate_up(h, norm_w, eps, w_gate_up, act_out, tp_in=None, h_out=None):
     abi.check(abi.lib().omnikv_decode_gate_up(_DT[h.dtype], h.data_ptr(), norm_w.data_ptr(), float(eps),
                                               w_gate_up.data_ptr(), w_gate_up.shape[1], w_gate_up.shape[0] // 2,
                                               act_out.data_ptr(), _xref(tp_in), _ptr(h_out),
-                                              status_word(h.device).data_ptr(), _stream()), "omnikv_decode_gate_up")
+                                              sched_words(h.device).data_ptr(), status_word(h.device).data_ptr(),
+                                              _stream()), "omnikv_decode_gate_up")
     _count(1)
 
 
