@@ -303,10 +303,29 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
     if (cs.fail) return false;
   }
   {
+    // Every global load of this prologue is issued BEFORE the first store to shared memory: written as one
+    // loop (load, store, load, store ...) the compiler keeps the order, since it cannot rule out that the two
+    // generic pointers alias, and each iteration then costs a full round trip (seven in a row for K = 14336).
+    constexpr int NT = GV_CONSUMER_WARPS * 32;
+    constexpr int NV = (K / 8 + NT - 1) / NT;  // 16-byte vectors per thread
     const uint4* xg = reinterpret_cast<const uint4*>(a.x);
     const uint4* ng = reinterpret_cast<const uint4*>(a.norm_w);
-    for (int v = tid; v < K / 8; v += GV_CONSUMER_WARPS * 32) {
-      uint4 raw = (COHERENT || tp_consume) ? __ldcg(xg + v) : xg[v];
+    uint4 xr_[NV], nr_[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = tid + i * NT;
+      xr_[i] = make_uint4(0, 0, 0, 0);
+      nr_[i] = xr_[i];
+      if (v < K / 8) {
+        xr_[i] = (COHERENT || tp_consume) ? __ldcg(xg + v) : xg[v];
+        if (ng) nr_[i] = ng[v];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = tid + i * NT;
+      if (v >= K / 8) continue;
+      uint4 raw = xr_[i];
       if (tp_consume) {  // residual + the ranks' partials (fp32), rounded once to the storage type
         float f[8];
         unpack8<T>(raw, f);
@@ -324,7 +343,7 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
       }
       xs[v] = raw;
       if (ng) {
-        ns[v] = ng[v];
+        ns[v] = nr_[i];
         float f[8];
         unpack8<T>(raw, f);
 #pragma unroll
