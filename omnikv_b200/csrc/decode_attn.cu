@@ -360,16 +360,22 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
     if (a.pdl_trigger) pdl_trigger();
   }
   ATTN_STAMP(1);
-  // Q tile: 16 rows x 128, rows >= G are zero.
+  // Q tile: 16 rows x 128, rows >= G are zero.  Both loads first, then the stores (one round trip, not two: the
+  // compiler keeps a load behind an earlier store through a generic pointer).
+  uint4 qv[2];
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
     const int i = tid + j * NTHREADS, r = i >> 4, c = i & 15;
-    uint4 qv = make_uint4(0, 0, 0, 0);
+    qv[j] = make_uint4(0, 0, 0, 0);
     if (r < G) {
       const T* qp = static_cast<const T*>(a.q) + (size_t)b * a.q_sb + (size_t)(kvh * G + r) * a.q_sh;
-      qv = *reinterpret_cast<const uint4*>(qp + c * 8);
+      qv[j] = *reinterpret_cast<const uint4*>(qp + c * 8);
     }
-    *reinterpret_cast<uint4*>(q_s + r * PITCH + c * 16) = qv;
+  }
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int i = tid + j * NTHREADS, r = i >> 4, c = i & 15;
+    *reinterpret_cast<uint4*>(q_s + r * PITCH + c * 16) = qv[j];
   }
   __syncthreads();
   unsigned qf[8][4];

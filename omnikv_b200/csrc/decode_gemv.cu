@@ -361,7 +361,20 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
       (size_t)K * 2 + (size_t)a.N * 2 <= ring.stage_bytes &&
       (reinterpret_cast<uintptr_t>(a.resid) & 15) == 0) {
     const uint4* rg = reinterpret_cast<const uint4*>(a.resid);
-    for (int v = tid; v < a.N / 8; v += GV_CONSUMER_WARPS * 32) ns[v] = COHERENT ? __ldcg(rg + v) : rg[v];
+    constexpr int NT = GV_CONSUMER_WARPS * 32;
+    uint4 rr[4];  // loads first, stores after (see above); 4 x 256 vectors cover N <= 8192
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int v = tid + i * NT;
+      rr[i] = make_uint4(0, 0, 0, 0);
+      if (v < a.N / 8) rr[i] = COHERENT ? __ldcg(rg + v) : rg[v];
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int v = tid + i * NT;
+      if (v < a.N / 8) ns[v] = rr[i];
+    }
+    for (int v = tid + 4 * NT; v < a.N / 8; v += NT) ns[v] = COHERENT ? __ldcg(rg + v) : rg[v];
     rs_s = reinterpret_cast<const T*>(ns);
   }
   int rope_pos_r = 0, cache_pos_r = 0;

@@ -82,12 +82,24 @@ __device__ __forceinline__ void issue_k_tile_tma(unsigned char* dst, const CUten
 // Query rows of `nheads` heads starting at head h0 -> shared memory [nheads*16][PITCH], slots >= W zero.
 template <typename T>
 __device__ __forceinline__ void load_q(unsigned char* q_s, const T* qw_b, int h0, int nheads, int W, int tid) {
-  for (int i = tid; i < nheads * WPAD * 16; i += NTHREADS) {
-    const int c = i & 15, r = i >> 4;
-    const int hl = r / WPAD, w = r % WPAD;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (w < W) v = *reinterpret_cast<const uint4*>(qw_b + ((size_t)(h0 + hl) * W + w) * kHeadDim + c * 8);
-    *reinterpret_cast<uint4*>(q_s + r * PITCH + c * 16) = v;
+  // batches of eight loads, then their stores: written as load, store, load, store ... every iteration would
+  // cost a round trip (the compiler keeps a load behind an earlier store through a generic pointer)
+  const int total = nheads * WPAD * 16;
+  for (int base = 0; base < total; base += 8 * NTHREADS) {
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + tid + u * NTHREADS;
+      const int c = i & 15, r = i >> 4;
+      const int hl = r / WPAD, w = r % WPAD;
+      v[u] = make_uint4(0, 0, 0, 0);
+      if (i < total && w < W) v[u] = *reinterpret_cast<const uint4*>(qw_b + ((size_t)(h0 + hl) * W + w) * kHeadDim + c * 8);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + tid + u * NTHREADS;
+      if (i < total) *reinterpret_cast<uint4*>(q_s + (i >> 4) * PITCH + (i & 15) * 16) = v[u];
+    }
   }
 }
 
