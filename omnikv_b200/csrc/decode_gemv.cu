@@ -321,26 +321,31 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
         if (ng) nr_[i] = ng[v];
       }
     }
+    if (tp_consume) {  // residual + the ranks' partials (fp32), rounded once to the storage type; still no store
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int v = tid + i * NT;
-      if (v >= K / 8) continue;
-      uint4 raw = xr_[i];
-      if (tp_consume) {  // residual + the ranks' partials (fp32), rounded once to the storage type
+      for (int i = 0; i < NV; ++i) {
+        const int v = tid + i * NT;
+        if (v >= K / 8) continue;
         float f[8];
-        unpack8<T>(raw, f);
+        unpack8<T>(xr_[i], f);
         for (int r = 0; r < a.tp_world; ++r) {
           const float4* pp = reinterpret_cast<const float4*>(a.tp_my_partials + (size_t)r * K) + 2 * v;
           const float4 p0 = __ldcg(pp), p1 = __ldcg(pp + 1);
           f[0] += p0.x; f[1] += p0.y; f[2] += p0.z; f[3] += p0.w;
           f[4] += p1.x; f[5] += p1.y; f[6] += p1.z; f[7] += p1.w;
         }
-        raw.x = pack2<T>(f[0], f[1]);
-        raw.y = pack2<T>(f[2], f[3]);
-        raw.z = pack2<T>(f[4], f[5]);
-        raw.w = pack2<T>(f[6], f[7]);
-        if (blockIdx.x == 0 && a.tp_h_out) reinterpret_cast<uint4*>(a.tp_h_out)[v] = raw;
+        xr_[i].x = pack2<T>(f[0], f[1]);
+        xr_[i].y = pack2<T>(f[2], f[3]);
+        xr_[i].z = pack2<T>(f[4], f[5]);
+        xr_[i].w = pack2<T>(f[6], f[7]);
       }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = tid + i * NT;
+      if (v >= K / 8) continue;
+      const uint4 raw = xr_[i];
+      if (tp_consume && blockIdx.x == 0 && a.tp_h_out) reinterpret_cast<uint4*>(a.tp_h_out)[v] = raw;
       xs[v] = raw;
       if (ng) {
         ns[v] = nr_[i];
