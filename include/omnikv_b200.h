@@ -17,6 +17,11 @@
  *   - return value: 0 or a negative omnikv_status after host-side validation;
  *     nothing throws or aborts across the boundary;
  *   - head_dim is 128 (Llama-3 8B / 70B); other values return OMNIKV_E_UNSUPPORTED.
+ *   - process-wide switches, read ONCE from the environment on first use (the only global state besides the
+ *     built-in scratch of omnikv_decode_attn_no_alloc): OMNIKV_PDL=0 launches every kernel without programmatic
+ *     dependent launch; OMNIKV_ATTN_TMA=0 keeps dense decode attention on its cp.async variant;
+ *     OMNIKV_WINDOW_TMA=0 does the same for the window selector; OMNIKV_TOPK_CLUSTER=8 limits omnikv_topk to
+ *     the portable cluster size.  They exist for measurements and fault isolation; results are the same.
  */
 #ifndef OMNIKV_B200_H_
 #define OMNIKV_B200_H_
@@ -28,7 +33,7 @@
 extern "C" {
 #endif
 
-#define OMNIKV_ABI_VERSION 3
+#define OMNIKV_ABI_VERSION 4
 
 typedef enum {
   OMNIKV_OK = 0,
@@ -141,14 +146,18 @@ int omnikv_decode_attn(const omnikv_attn_params* p, void* stream);
  * the process exits.  p->workspace and p->workspace_bytes are ignored; inputs and outputs are the caller's.
  *
  * Limit: omnikv_decode_attn_workspace_bytes(B, H, n_splits) must not exceed OMNIKV_NO_ALLOC_SCRATCH_BYTES
- * (B * H * n_splits <= 8034, e.g. batch 1, 32 heads, 251 splits); larger problems return OMNIKV_E_WORKSPACE
- * and launch nothing.  Nothing is allocated or freed, here or in any routine it calls.
+ * (B * H * n_splits <= 8034, e.g. batch 1, 32 heads, 251 splits); larger problems return OMNIKV_E_WORKSPACE.
+ * A call that is refused -- for its size or for any argument omnikv_decode_attn would refuse -- puts nothing on
+ * the stream and does not touch the array.  Nothing is allocated or freed, here or in any routine it calls.
  *
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
  * current); make that first call outside stream capture.  All calls on a device share the one array: it
  * keeps the previous call's contents (the counters are cleared at the start of every call, on the given
  * stream), and two calls that overlap on the GPU -- different streams, or graphs replayed concurrently --
- * race on it.  Keep them on one stream, or order them with events.
+ * race on it.  Keep them on one stream, or order them with events.  The first call may come from several host
+ * threads at once (the address look-up is idempotent and its cache is atomic).  The clearing of the counters is a
+ * memset node in front of the kernel, so unlike omnikv_decode_attn this call does not start early behind a
+ * preceding weight-streaming call (no programmatic overlap).
  * ------------------------------------------------------------------------------------------ */
 #define OMNIKV_NO_ALLOC_SCRATCH_BYTES (4 * 1024 * 1024)
 int omnikv_decode_attn_no_alloc(const omnikv_attn_params* p, void* stream);
@@ -295,13 +304,16 @@ int omnikv_silu_mul(int dtype, const void* gate_up, int64_t gate_up_stride_b, vo
  *             DIFFERENT buffer than h: other CTAs of the same launch are still reading h.
  * peer_base[r]: rank r's exchange buffer (omnikv_tp_exchange_bytes(hidden) bytes, zero before first use) as
  * mapped into THIS process (peer_base[rank] = the local one).  Exchanges alternate between two slots
- * (seq & 1); seq numbers the exchanges of a decode step 0, 1, 2, ... (< 256) and must follow program order;
- * *epoch is a local device word that every rank bumps once per decode step.  All ranks must issue the same
- * sequence of calls.  world <= 8.  NULL or world <= 1: no exchange. */
+ * (seq & 1); seq numbers the exchanges of a decode step 0, 1, 2, ... (< 256) and must follow program order, and a
+ * step must hold an EVEN number of them (a decoder layer has two), so that the last exchange of a step and the
+ * first of the next never share a slot; *epoch is a local device word that every rank bumps once per decode
+ * step.  All ranks must issue the same sequence of calls.  world <= 8.  NULL or world <= 1: no exchange.
+ * The wait for the peers' flags gives up after two seconds (status 4). */
 typedef struct {
   int32_t world, rank;
   void* peer_base[8];
-  uint32_t* done_counter; /* local device word, zero before first use (producers) */
+  uint32_t* done_counter; /* TWO local device words, zero before first use: [0] CTAs that have finished (producers),
+                             [1] calls made so far on this object (omnikv_tp_allreduce_sum) */
   const uint32_t* epoch;
   int32_t seq;
   int32_t hidden;
@@ -316,8 +328,10 @@ size_t omnikv_tp_exchange_bytes(int hidden);
  * MLP of the reference's tensor-parallel fork (lightllm/common/basemodel/layer_infer/template/
  * transformer_layer_infer_template.py:119-120, :128-129).  The exchange describes a buffer of
  * omnikv_tp_exchange_bytes(hidden) bytes per rank; n * element size must not exceed hidden * 4 bytes and must be
- * a multiple of 16; seq < 256 numbers the calls of a step on THIS exchange object in program order, identically
- * on every rank; *epoch is bumped once per step.  The wait for the peers' flags is bounded (status 4). */
+ * a multiple of 16.  The two slots alternate by a device-side count of the calls made on THIS exchange object
+ * (done_counter[1]; seq and epoch are not used), so any number of calls per step -- odd ones too, and replays of a
+ * captured step -- is safe as long as every rank issues the same sequence of calls on one stream.  The wait for
+ * the peers' flags gives up after two seconds (status 4). */
 int omnikv_tp_allreduce_sum(int dtype, void* x, int64_t n, const omnikv_tp_exchange* t, int32_t* status,
                             void* stream);
 int omnikv_decode_qkv(int dtype, const void* h, const void* norm_w, float eps, const void* w_qkv, int hidden,
@@ -386,9 +400,6 @@ typedef struct {
   const void* next_w;      /* optional: the weights the NEXT launch will read first (next layer's w_o); the kernel asks
                               for next_w_bytes of them to be brought into L2 when its own copies are issued */
   size_t next_w_bytes;
-  void* trace;             /* optional profiling aid: device uint64 [n_SMs][32] of %globaltimer stamps per CTA
-                              ([0] start; [1+3p..3+3p] phase p: barrier passed, activations ready, rows done;
-                              [16+p] producer issued all copies of phase p); NULL: nothing is recorded */
 } omnikv_chain_params;
 
 int omnikv_decode_chain(const omnikv_chain_params* p, void* stream);

@@ -10,7 +10,7 @@ from pathlib import Path
 _LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libomnikv_b200.so"
 _lib = None
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 F32, BF16, F16 = 0, 1, 2
 SEL_SOFTMAX_LAST, SEL_UNIFORM, SEL_EXP = 0, 1, 2
 NO_ALLOC_SCRATCH_BYTES = 4 * 1024 * 1024
@@ -74,7 +74,8 @@ class ChainParams(C.Structure):
         ("kv_stride_h", C.c_int64), ("kv_stride_row", C.c_int64), ("cache_pos", C.c_void_p),
         ("final_norm_w", C.c_void_p), ("w_head", C.c_void_p), ("vocab_rows", C.c_int32),
         ("logits", C.c_void_p), ("best_scratch", C.c_void_p), ("token_out", C.c_void_p),
-        ("grid_sync", C.c_void_p), ("chunk_counters", C.c_void_p), ("status", C.c_void_p), ("next_w", C.c_void_p), ("next_w_bytes", C.c_size_t), ("trace", C.c_void_p),
+        ("grid_sync", C.c_void_p), ("chunk_counters", C.c_void_p), ("status", C.c_void_p),
+        ("next_w", C.c_void_p), ("next_w_bytes", C.c_size_t),
     ]
 
 

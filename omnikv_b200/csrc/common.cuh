@@ -51,9 +51,23 @@ inline cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cud
   return cudaLaunchKernelEx(&cfg, kern, a);
 }
 
+__device__ __forceinline__ unsigned ld_volatile_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.volatile.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
+  return t;
+}
+
 // ---- mbarrier + bulk copies (TMA, untiled) -------------------------------------------------------------
-// Every wait in these kernels is bounded: after kSpinLimit polls the waiter gives up and reports it.
+// Every wait in these kernels is bounded, by TIME (a poll of an mbarrier may itself block for a while, so a poll
+// count bounds nothing): a waiter that has not been served after kWaitNs gives up and reports it.  kSpinLimit
+// bounds the few remaining plain spin loops (grid barrier).
 constexpr unsigned kSpinLimit = 1u << 24;
+constexpr unsigned long long kWaitNs = 2000000000ull;  // 2 s
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
 
@@ -66,23 +80,32 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
-// Bounded wait for the phase with the given parity; false if the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
+__device__ __forceinline__ bool mbar_try_wait(unsigned addr, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(addr), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Wait for the phase with the given parity; false if it has not completed within kWaitNs.  `abort` (optional):
+// a shared-memory flag another thread of the CTA raises when it has given up; the wait then ends at once.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, const volatile int* abort = nullptr) {
   const unsigned addr = smem_u32(bar);
-  for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
-    unsigned ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (ok) return true;
+  if (mbar_try_wait(addr, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 8; ++i)
+      if (mbar_try_wait(addr, parity)) return true;
+    if (abort && *abort) return false;
+    if (globaltimer_ns() - t0 > kWaitNs) return false;
   }
-  return false;
 }
 __device__ __forceinline__ void tma_bulk_g2s(void* smem_dst, const void* gmem_src, unsigned bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
@@ -91,6 +114,22 @@ __device__ __forceinline__ void tma_bulk_g2s(void* smem_dst, const void* gmem_sr
                : "memory");
 }
 
+
+// ---- waits on words another GPU (or another CTA) writes ------------------------------------------------
+// Waits until *flag has reached `want` (flags only grow; compared as a signed difference so that a wrap of the
+// 32-bit counter is harmless).  Bounded by TIME: a peer that never arrives costs kPeerWaitNs, after which the
+// caller records a status code and returns, leaving the context usable.
+constexpr unsigned long long kPeerWaitNs = kWaitNs;
+__device__ __forceinline__ bool wait_flag_reached(const unsigned* flag, unsigned want) {
+  if ((int)(ld_volatile_u32(flag) - want) >= 0) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if ((int)(ld_volatile_u32(flag) - want) >= 0) return true;
+    if (globaltimer_ns() - t0 > kPeerWaitNs) return false;
+  }
+}
 
 // ---- TMA tensor-map tiles of a K or V cache ----------------------------------------------------------------
 // A tile of 64 rows x 256 bytes (head_dim 128, 16-bit) is two boxes of 64 rows x 128 bytes; the map's 128-byte

@@ -12,6 +12,7 @@
 // KV head) merges that group's splits into the output, so an attention call is a single launch.
 #include <stdlib.h>
 
+#include <atomic>
 #include <type_traits>
 
 #include "common.cuh"
@@ -764,7 +765,8 @@ extern "C" size_t omnikv_decode_attn_workspace_bytes(int B, int H, int n_splits)
          (omnikv::attn_ws_o_floats(B, H, n_splits) + omnikv::attn_ws_ml_floats(B, H, n_splits)) * sizeof(float);
 }
 
-extern "C" int omnikv_decode_attn(const omnikv_attn_params* p, void* stream) {
+// Host-side validation of a call (everything except the workspace).  OMNIKV_OK or the status to return.
+static int validate_attn_params(const omnikv_attn_params* p) {
   using namespace omnikv;
   if (!p || !p->q || !p->kA || !p->lenA) return OMNIKV_E_BADARG;
   if (p->B <= 0 || p->H <= 0 || p->KVH <= 0 || p->n_splits <= 0) return OMNIKV_E_BADARG;
@@ -790,6 +792,16 @@ extern "C" int omnikv_decode_attn(const omnikv_attn_params* p, void* stream) {
   if (p->lenB && (p->b_stride_b % vec || p->b_stride_h % vec || p->b_stride_row % vec || p->b_stride_row < kHeadDim))
     return OMNIKV_E_BADARG;
   if (p->dtype == OMNIKV_F32 ? (G != 1 && G != 2 && G != 4 && G != 8) : (G > 16)) return OMNIKV_E_UNSUPPORTED;
+  if (with_v && (p->n_splits > 512 || (size_t)p->B * p->KVH * 4 > kAttnCntBytes)) return OMNIKV_E_UNSUPPORTED;
+  return OMNIKV_OK;
+}
+
+extern "C" int omnikv_decode_attn(const omnikv_attn_params* p, void* stream) {
+  using namespace omnikv;
+  if (const int rc = validate_attn_params(p)) return rc;
+  const int G = p->H / p->KVH;
+  const bool with_v = p->out != nullptr;
+  const bool with_score = p->score_out != nullptr;
   if (with_v) {
     if (!p->workspace || p->workspace_bytes < omnikv_decode_attn_workspace_bytes(p->B, p->H, p->n_splits))
       return OMNIKV_E_WORKSPACE;
@@ -806,7 +818,6 @@ extern "C" int omnikv_decode_attn(const omnikv_attn_params* p, void* stream) {
   a.ws_cnt = static_cast<unsigned*>(p->workspace);
   a.ws_o = with_v ? reinterpret_cast<float*>(static_cast<unsigned char*>(p->workspace) + kAttnCntBytes) : nullptr;
   a.ws_ml = with_v ? a.ws_o + attn_ws_o_floats(p->B, p->H, p->n_splits) : nullptr;
-  if (with_v && (p->n_splits > 512 || (size_t)p->B * p->KVH * 4 > kAttnCntBytes)) return OMNIKV_E_UNSUPPORTED;
   a.B = p->B; a.H = p->H; a.KVH = p->KVH; a.G = G; a.S = p->n_splits;
   a.scale = p->scale;
   a.pdl_trigger = 0;
@@ -834,7 +845,9 @@ namespace {
 static __device__ __align__(256) unsigned char g_no_alloc_scratch[OMNIKV_NO_ALLOC_SCRATCH_BYTES];
 
 constexpr int kMaxDevices = 64;
-void* g_no_alloc_ptr[kMaxDevices] = {};  // device address of the array, per device ordinal
+// device address of the array, per device ordinal; filled on a device's first call.  Several host threads may
+// make that first call at once: they all look up the same address, and the slot is read and written atomically.
+std::atomic<void*> g_no_alloc_ptr[kMaxDevices];
 
 // The array's name is only a handle on the host; the device address has to be asked for, once per
 // device and with that device current.
@@ -842,13 +855,13 @@ int no_alloc_scratch(void** out) {
   int dev = 0;
   OMNIKV_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return OMNIKV_E_UNSUPPORTED;
-  if (!g_no_alloc_ptr[dev]) {
-    void* ptr = nullptr;
+  void* ptr = g_no_alloc_ptr[dev].load(std::memory_order_acquire);
+  if (!ptr) {
     OMNIKV_CUDA_OK(cudaGetSymbolAddress(&ptr, g_no_alloc_scratch));
     if (!ptr) return OMNIKV_E_CUDA;
-    g_no_alloc_ptr[dev] = ptr;
+    g_no_alloc_ptr[dev].store(ptr, std::memory_order_release);
   }
-  *out = g_no_alloc_ptr[dev];
+  *out = ptr;
   return OMNIKV_OK;
 }
 
@@ -857,8 +870,8 @@ int no_alloc_scratch(void** out) {
 
 extern "C" int omnikv_decode_attn_no_alloc(const omnikv_attn_params* p, void* stream) {
   using namespace omnikv;
-  if (!p) return OMNIKV_E_BADARG;
-  if (p->B <= 0 || p->H <= 0 || p->n_splits <= 0) return OMNIKV_E_BADARG;
+  // every argument check comes first: a refused call puts nothing on the stream and leaves the shared array alone
+  if (const int bad = validate_attn_params(p)) return bad;
   if (p->out && omnikv_decode_attn_workspace_bytes(p->B, p->H, p->n_splits) > (size_t)OMNIKV_NO_ALLOC_SCRATCH_BYTES)
     return OMNIKV_E_WORKSPACE;  // B * H * n_splits is more than the built-in scratch can hold
   void* scratch = nullptr;

@@ -117,18 +117,6 @@ __device__ __forceinline__ void unpack8<__half>(const uint4& v, float (&f)[8]) {
   }
 }
 
-__device__ __forceinline__ unsigned ld_volatile_u32(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.volatile.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
-  return t;
-}
-
 // Shared-memory ring shared by the producer thread and the consumer warps of a CTA.
 struct Ring {
   unsigned char* smem;      // GV_STAGES slots of slot_bytes
@@ -138,6 +126,7 @@ struct Ring {
   int* slot_chunk;          // chunk held by each slot, -1 = the phase has no more chunks for this CTA
   unsigned char* stage_x;   // staging area for the phase's activations (and norm weights), 16-byte aligned
   unsigned stage_bytes;     // its size
+  const volatile int* abort;  // ConsumerShared::fail
 };
 
 // First row of the two pieces of chunk c.
@@ -162,6 +151,7 @@ __device__ __forceinline__ void piece_rows(const GemvArgs& a, int c, int& row0, 
 // Producer side of one phase: called by ONE thread.  `it` is the CTA's running chunk number (ring position).
 template <typename T, int KV, int WK, int EPI>
 __device__ __forceinline__ bool produce_phase(const GemvArgs& a, const Ring& ring, int& it) {
+  const volatile int* abort = ring.abort;  // raised by the consumers when they give up: stop producing
   constexpr int HALF = GV_CONSUMER_WARPS / WK / 2;
   constexpr int K = WK * KV * 256;
   constexpr unsigned PIECE_BYTES = HALF * K * 2;
@@ -170,16 +160,16 @@ __device__ __forceinline__ bool produce_phase(const GemvArgs& a, const Ring& rin
   int grab = -2;  // index taken from the tail pool and not used yet (-2: none)
   for (;; ++it) {
     const int slot = it % GV_STAGES;
-    if (it >= GV_STAGES && !mbar_wait(&ring.empty_bar[slot], ((it / GV_STAGES) - 1) & 1)) {
-      atomicExch(a.status, 1);
+    if (it >= GV_STAGES && !mbar_wait(&ring.empty_bar[slot], ((it / GV_STAGES) - 1) & 1, abort)) {
+      if (!*abort) atomicExch(a.status, 1);
       return false;
     }
     // The first fill of the ring is paced: a chunk is asked for when the one before it has landed.  One
     // chunk per SM in flight already saturates HBM; three per SM at once (28 MB) only build a queue that the
     // consumers' loads of the activations -- issued a little later, and on the critical path of the whole
     // kernel -- would have to wait behind (measured: 3.5 us instead of about 1).
-    if (GV_PACED_FILL && it > 0 && it < GV_STAGES && !mbar_wait(&ring.full_bar[it - 1], 0)) {
-      atomicExch(a.status, 1);
+    if (GV_PACED_FILL && it > 0 && it < GV_STAGES && !mbar_wait(&ring.full_bar[it - 1], 0, abort)) {
+      if (!*abort) atomicExch(a.status, 1);
       return false;
     }
     // next chunk: from the shared counter (whoever is ready takes the next one, so slow SMs take fewer),
@@ -263,8 +253,7 @@ __device__ __forceinline__ void consumer_bar() {
 // Consumer side of one phase: called by the 256 consumer threads.  COHERENT: x and resid were written by
 // other CTAs of this same launch, so they are read through L2 (ld.global.cg), never from a stale L1 line.
 template <typename T, int KV, int WK, int EPI, bool COHERENT>
-__device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& ring, ConsumerShared& cs, int& it,
-                                              unsigned long long* stamp = nullptr) {
+__device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& ring, ConsumerShared& cs, int& it) {
   constexpr int RPS = GV_CONSUMER_WARPS / WK;
   constexpr int HALF = RPS / 2;
   constexpr int K = WK * KV * 256;
@@ -288,13 +277,10 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
     if (tid == 0) {
       const unsigned want = __ldcg(a.tp_epoch) * 256u + a.tp_seq + 1u;
       for (int r = 0; r < a.tp_world; ++r) {
-        unsigned spin = 0;
-        while ((int)(ld_volatile_u32(a.tp_my_flags + r) - want) < 0) {
-          if (++spin > GV_SPIN_LIMIT) {
-            cs.fail = 1;
-            atomicExch(a.status, 4);
-            break;
-          }
+        if (!wait_flag_reached(a.tp_my_flags + r, want)) {  // a rank that never arrived: give up after 2 s
+          cs.fail = 1;
+          atomicExch(a.status, 4);
+          break;
         }
       }
       __threadfence_system();
@@ -413,7 +399,6 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
       for (int e = 0; e < 8; ++e) xr[j][e] *= nw[e];
     }
   }
-  if (stamp && threadIdx.x == 0) *stamp = globaltimer_ns();  // activations loaded, norm known
   if (threadIdx.x == 0) GEMV_STAMP(a, 2);
 #ifdef OMNIKV_GEMV_TRACE
   bool first_stage = true;
@@ -582,7 +567,7 @@ __global__ void __launch_bounds__(GV_THREADS, 1) decode_gemv_kernel(const GemvAr
   __shared__ int slot_chunk[GV_STAGES];
   ring_init(full_bar, empty_bar, cs);
   constexpr unsigned SLOT = GV_CONSUMER_WARPS / WK * K * 2;
-  Ring ring{smem, full_bar, empty_bar, SLOT, slot_chunk, smem + GV_STAGES * SLOT, (unsigned)K * 4u};
+  Ring ring{smem, full_bar, empty_bar, SLOT, slot_chunk, smem + GV_STAGES * SLOT, (unsigned)K * 4u, &cs.fail};
   int it = 0;
   // Programmatic dependent launch: the grid is one CTA per SM, all resident, so the next kernel may be
   // scheduled behind it right away.  The producer starts streaming weights at once (they depend on nothing);
@@ -612,7 +597,6 @@ struct ChainArgs {
   GemvArgs ph[4];
   int kind[4];          // ChainKind, or -1 when the phase is skipped
   unsigned* grid_sync;  // one word: arrivals | generation << 16; zero before the first launch, self-resetting
-  unsigned long long* trace;  // optional [gridDim.x][32] globaltimer stamps (profiling), or nullptr
   const void* next_w;         // optional: weights the next launch reads first, prefetched into L2 at the end
   size_t next_w_bytes;
 };
@@ -645,13 +629,11 @@ __global__ void __launch_bounds__(GV_THREADS, 1) decode_chain_kernel(const Chain
   __shared__ ConsumerShared cs;
   constexpr unsigned SLOT_H = GV_CONSUMER_WARPS / WKH_ * (WKH_ * KVH_ * 256) * 2;
   constexpr unsigned SLOT_I = GV_CONSUMER_WARPS / WKI_ * (WKI_ * KVI_ * 256) * 2;
-  unsigned long long* tr = c.trace ? c.trace + (size_t)blockIdx.x * 32 : nullptr;
-  if (tr && threadIdx.x == 0) tr[0] = globaltimer_ns();
   __shared__ int slot_chunk[GV_STAGES];
   ring_init(full_bar, empty_bar, cs);
   constexpr unsigned CHAIN_STAGE_BYTES = 4u * (WKH_ * KVH_ * 256) > 2u * (WKI_ * KVI_ * 256) ? 4u * (WKH_ * KVH_ * 256) : 2u * (WKI_ * KVI_ * 256);
   constexpr unsigned SLOT = SLOT_H > SLOT_I ? SLOT_H : SLOT_I;
-  Ring ring{smem, full_bar, empty_bar, SLOT, slot_chunk, smem + GV_STAGES * SLOT, CHAIN_STAGE_BYTES};
+  Ring ring{smem, full_bar, empty_bar, SLOT, slot_chunk, smem + GV_STAGES * SLOT, CHAIN_STAGE_BYTES, &cs.fail};
   int it = 0;
   if ((threadIdx.x >> 5) == GV_CONSUMER_WARPS) {
     if ((threadIdx.x & 31) == 0) {
@@ -665,7 +647,6 @@ __global__ void __launch_bounds__(GV_THREADS, 1) decode_chain_kernel(const Chain
           case CK_LOGITS: ok = produce_phase<T, KVH_, WKH_, EPI_LOGITS>(c.ph[p], ring, it); break;
           default: break;
         }
-        if (tr) tr[16 + p] = globaltimer_ns();  // all copies of phase p issued
         if (!ok) break;
         int nx = p + 1;
         while (nx < 4 && c.kind[nx] < 0) ++nx;
@@ -691,7 +672,6 @@ __global__ void __launch_bounds__(GV_THREADS, 1) decode_chain_kernel(const Chain
   bool first = true;
   for (int p = 0; p < 4; ++p) {
     if (c.kind[p] < 0) continue;
-    unsigned long long* st = tr ? tr + 1 + 3 * p : nullptr;  // [barrier passed, activations ready, rows done]
     if (!first) {
       // every CTA's outputs of the previous phase must be visible before this phase reads them
       consumer_bar();
@@ -703,18 +683,16 @@ __global__ void __launch_bounds__(GV_THREADS, 1) decode_chain_kernel(const Chain
       if (cs.fail) return;
     }
     first = false;
-    if (st && threadIdx.x == 0) st[0] = globaltimer_ns();
     bool ok = true;
     switch (c.kind[p]) {
-      case CK_O: ok = consume_phase<T, KVH_, WKH_, EPI_RESID, true>(c.ph[p], ring, cs, it, st ? st + 1 : nullptr); break;
-      case CK_GATEUP: ok = consume_phase<T, KVH_, WKH_, EPI_GATEUP, true>(c.ph[p], ring, cs, it, st ? st + 1 : nullptr); break;
-      case CK_DOWN: ok = consume_phase<T, KVI_, WKI_, EPI_RESID, true>(c.ph[p], ring, cs, it, st ? st + 1 : nullptr); break;
-      case CK_QKV: ok = consume_phase<T, KVH_, WKH_, EPI_QKV, true>(c.ph[p], ring, cs, it, st ? st + 1 : nullptr); break;
-      case CK_LOGITS: ok = consume_phase<T, KVH_, WKH_, EPI_LOGITS, true>(c.ph[p], ring, cs, it, st ? st + 1 : nullptr); break;
+      case CK_O: ok = consume_phase<T, KVH_, WKH_, EPI_RESID, true>(c.ph[p], ring, cs, it); break;
+      case CK_GATEUP: ok = consume_phase<T, KVH_, WKH_, EPI_GATEUP, true>(c.ph[p], ring, cs, it); break;
+      case CK_DOWN: ok = consume_phase<T, KVI_, WKI_, EPI_RESID, true>(c.ph[p], ring, cs, it); break;
+      case CK_QKV: ok = consume_phase<T, KVH_, WKH_, EPI_QKV, true>(c.ph[p], ring, cs, it); break;
+      case CK_LOGITS: ok = consume_phase<T, KVH_, WKH_, EPI_LOGITS, true>(c.ph[p], ring, cs, it); break;
       default: break;
     }
     if (!ok) return;
-    if (st && threadIdx.x == 0) st[2] = globaltimer_ns();
   }
 }
 
@@ -929,7 +907,6 @@ extern "C" int omnikv_decode_chain(const omnikv_chain_params* p, void* stream) {
   ChainArgs c = {};
   for (int i = 0; i < 4; ++i) c.kind[i] = -1;
   c.grid_sync = p->grid_sync;
-  c.trace = static_cast<unsigned long long*>(p->trace);
   int* counters = p->chunk_counters;  // 4 ints, zero at launch (dynamic scheduling), or NULL (static)
   c.next_w = p->next_w;
   c.next_w_bytes = p->next_w ? p->next_w_bytes : 0;

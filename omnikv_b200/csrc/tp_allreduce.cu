@@ -8,8 +8,12 @@
 // GPUs wait for one another's flags with a bounded spin (a rank's flag depends only on that rank's own
 // stores, never on a peer, so there is no cycle).  The grid is small enough to be resident at once.
 //
-// Exchange buffer layout and flag values are those of omnikv_tp_exchange (two alternating slots, flag =
-// step * 256 + exchange number + 1, nothing is ever reset).  Plain peer loads and stores only.
+// Exchange buffer layout is that of omnikv_tp_exchange (two alternating slots).  Slot and flag value come from
+// a DEVICE-side counter of the calls made on this exchange object (slot = calls & 1, flag = calls + 1), which
+// every rank advances identically: consecutive calls therefore always alternate slots, whatever the number of
+// calls per decode step and also when a captured step is replayed.  (A rank can only be two calls ahead of a
+// peer after that peer has raised the flag of the call in between, i.e. has finished reading the older slot.)
+// Nothing is ever reset.  Plain peer loads and stores only.
 #include "common.cuh"
 
 namespace omnikv {
@@ -22,22 +26,14 @@ struct ArArgs {
   void* x;                 // [n_vec] 16-byte vectors, reduced in place
   int n_vec;
   int world, rank;
-  uint4* peer_slot[8];     // rank p's slot region for MY vector
-  unsigned* peer_flag[8];  // rank p's flag word for (slot, me)
-  const uint4* my_slots;   // local: [8][slot_stride_vec]
+  uint4* peer_slot[8];     // rank p's region for MY vector in slot 0 (slot 1: + 8 * slot_stride_vec)
+  unsigned* peer_flag[8];  // rank p's flag word for (slot 0, me) (slot 1: + 8)
+  const uint4* my_slots;   // local: [2 slots][8][slot_stride_vec]
   size_t slot_stride_vec;
-  const unsigned* my_flags;  // local [8]
-  unsigned* done;          // local counter of finished CTAs (self-resetting)
-  const unsigned* epoch;
-  unsigned seq;
+  const unsigned* my_flags;  // local [2 slots][8]
+  unsigned* done;          // local: [0] counter of finished CTAs (self-resetting), [1] calls made so far
   int* status;
 };
-
-__device__ __forceinline__ unsigned ld_volatile_u32(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.volatile.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 
 template <typename T>
 __device__ __forceinline__ void add8(const uint4& v, float (&acc)[8]);
@@ -77,37 +73,42 @@ __device__ __forceinline__ uint4 pack8<float>(const float (&acc)[8]) {
 template <typename T>
 __global__ void __launch_bounds__(AR_THREADS) tp_allreduce_kernel(const ArArgs a) {
   __shared__ int fail;
+  __shared__ unsigned call_s;
   const int tid = threadIdx.x;
   const int stride = gridDim.x * AR_THREADS;
   uint4* x = static_cast<uint4*>(a.x);
-  if (tid == 0) fail = 0;
+  if (tid == 0) {
+    fail = 0;
+    // the number of this call: read before this CTA counts itself in, so before the last CTA can bump it
+    call_s = ld_volatile_u32(a.done + 1);
+  }
+  __syncthreads();
+  const unsigned call = call_s;
+  const unsigned slot = call & 1u;
   // 1. my vector into my slot on every rank (the local one included)
   for (int v = blockIdx.x * AR_THREADS + tid; v < a.n_vec; v += stride) {
     const uint4 val = x[v];
-    for (int p = 0; p < a.world; ++p) a.peer_slot[p][v] = val;
+    for (int p = 0; p < a.world; ++p) (a.peer_slot[p] + (size_t)slot * 8 * a.slot_stride_vec)[v] = val;
   }
   __threadfence_system();
   __syncthreads();
   if (tid == 0) {
     // all of this CTA's stores are ordered before its count; the CTA that completes the count raises this
-    // rank's flag on every rank
+    // rank's flag on every rank and advances the call counter for the next launch
+    const unsigned val = call + 1u;
     if (atomicAdd(a.done, 1u) == gridDim.x - 1) {
       atomicExch(a.done, 0u);
+      atomicExch(a.done + 1, val);
       __threadfence_system();
-      const unsigned val = __ldcg(a.epoch) * 256u + a.seq + 1u;
       for (int p = 0; p < a.world; ++p)
-        asm volatile("st.volatile.global.u32 [%0], %1;\n" ::"l"(a.peer_flag[p]), "r"(val) : "memory");
+        asm volatile("st.volatile.global.u32 [%0], %1;\n" ::"l"(a.peer_flag[p] + slot * 8), "r"(val) : "memory");
     }
-    // 2. every rank's vector must have landed here (bounded wait)
-    const unsigned want = __ldcg(a.epoch) * 256u + a.seq + 1u;
+    // 2. every rank's vector must have landed here (wait bounded by time)
     for (int r = 0; r < a.world; ++r) {
-      unsigned spin = 0;
-      while ((int)(ld_volatile_u32(a.my_flags + r) - want) < 0) {
-        if (++spin > kSpinLimit) {
-          fail = 1;
-          atomicExch(a.status, 4);
-          break;
-        }
+      if (!wait_flag_reached(a.my_flags + slot * 8 + r, val)) {
+        fail = 1;
+        atomicExch(a.status, 4);
+        break;
       }
     }
     __threadfence_system();
@@ -115,9 +116,10 @@ __global__ void __launch_bounds__(AR_THREADS) tp_allreduce_kernel(const ArArgs a
   __syncthreads();
   if (fail) return;
   // 3. sum in rank order, fp32, rounded once
+  const uint4* mine = a.my_slots + (size_t)slot * 8 * a.slot_stride_vec;
   for (int v = blockIdx.x * AR_THREADS + tid; v < a.n_vec; v += stride) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int r = 0; r < a.world; ++r) add8<T>(__ldcg(a.my_slots + (size_t)r * a.slot_stride_vec + v), acc);
+    for (int r = 0; r < a.world; ++r) add8<T>(__ldcg(mine + (size_t)r * a.slot_stride_vec + v), acc);
     x[v] = pack8<T>(acc);
   }
 }
@@ -130,9 +132,8 @@ extern "C" int omnikv_tp_allreduce_sum(int dtype, void* x, int64_t n, const omni
   using namespace omnikv;
   if (!x || n <= 0 || !t || !status) return OMNIKV_E_BADARG;
   if (t->world <= 1) return OMNIKV_OK;
-  if (t->world > 8 || t->rank < 0 || t->rank >= t->world || !t->done_counter || !t->epoch || t->hidden <= 0)
+  if (t->world > 8 || t->rank < 0 || t->rank >= t->world || !t->done_counter || t->hidden <= 0)
     return OMNIKV_E_BADARG;
-  if (t->seq < 0 || t->seq >= 256) return OMNIKV_E_UNSUPPORTED;
   const int esz = dtype == OMNIKV_F32 ? 4 : 2;
   if (dtype != OMNIKV_F32 && dtype != OMNIKV_BF16 && dtype != OMNIKV_F16) return OMNIKV_E_UNSUPPORTED;
   const size_t bytes = (size_t)n * esz;
@@ -141,19 +142,18 @@ extern "C" int omnikv_tp_allreduce_sum(int dtype, void* x, int64_t n, const omni
   if (bytes > slot_bytes) return OMNIKV_E_WORKSPACE;
   ArArgs a = {};
   a.x = x; a.n_vec = (int)(bytes / 16); a.world = t->world; a.rank = t->rank;
-  const int slot = t->seq & 1;
   const size_t flags_off = (size_t)2 * 8 * slot_bytes;
   for (int p = 0; p < t->world; ++p) {
     if (!t->peer_base[p]) return OMNIKV_E_BADARG;
     unsigned char* base = static_cast<unsigned char*>(t->peer_base[p]);
-    a.peer_slot[p] = reinterpret_cast<uint4*>(base + ((size_t)slot * 8 + t->rank) * slot_bytes);
-    a.peer_flag[p] = reinterpret_cast<unsigned*>(base + flags_off) + slot * 8 + t->rank;
+    a.peer_slot[p] = reinterpret_cast<uint4*>(base + (size_t)t->rank * slot_bytes);
+    a.peer_flag[p] = reinterpret_cast<unsigned*>(base + flags_off) + t->rank;
   }
   unsigned char* mine = static_cast<unsigned char*>(t->peer_base[t->rank]);
-  a.my_slots = reinterpret_cast<const uint4*>(mine + (size_t)slot * 8 * slot_bytes);
+  a.my_slots = reinterpret_cast<const uint4*>(mine);
   a.slot_stride_vec = slot_bytes / 16;
-  a.my_flags = reinterpret_cast<const unsigned*>(mine + flags_off) + slot * 8;
-  a.done = t->done_counter; a.epoch = t->epoch; a.seq = (unsigned)t->seq; a.status = status;
+  a.my_flags = reinterpret_cast<const unsigned*>(mine + flags_off);
+  a.done = t->done_counter; a.status = status;
   int grid = ceil_div(a.n_vec, AR_THREADS);
   if (grid > AR_MAX_CTAS) grid = AR_MAX_CTAS;
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -46,42 +46,135 @@ def time_analyze() -> float:
 # rotary embedding (cos/sin generation is the boundary to the HF Llama patch,
 # modeling/patch_of_llama3_1.py: default, linear, dynamic-NTK and llama3 frequency rules)
 # ----------------------------------------------------------------------------------------------
-def _inv_freq(config, seq_len: Optional[int] = None) -> Tuple[torch.Tensor, float]:
-    d = config.head_dim
+def _dynamic_ntk_inv_freq(theta: float, d: int, factor: float, max_pos: int, seq_len: torch.Tensor) -> torch.Tensor:
+    """Dynamic-NTK frequencies for the current sequence length (a 0-dim integer tensor on any device), with the
+    arithmetic of modeling/patch_of_llama3_1.py:137-142 in the same order and precision (fp32 tensor maths):
+    ``seq_len`` counts only above ``max_pos``, the base grows with it, ``inv_freq = base ** -(2i/d)``."""
+    seq = torch.clamp(seq_len, min=max_pos)
+    base = theta * ((factor * seq / max_pos) - (factor - 1)) ** (d / (d - 2))
+    expo = torch.arange(0, d, 2, dtype=torch.int64, device=seq_len.device).float() / d
+    return 1.0 / (base ** expo)
+
+
+def rope_parameters(config, seq_len: Optional[int] = None) -> Tuple[torch.Tensor, float]:
+    """(inv_freq fp32 ``[d/2]``, attention scaling) for the ``rope_scaling`` of ``config``: the rules of
+    ``ROPE_INIT_FUNCTIONS`` in modeling/patch_of_llama3_1.py -- default :12-51, linear :54-93, dynamic NTK
+    :96-143, yarn :146-222, longrope :225-287, llama3 :290-330.  ``rope_type`` may also be spelled ``type``."""
+    d = int(config.head_dim * getattr(config, "partial_rotary_factor", 1.0))
     base = float(config.rope_theta)
     scaling = getattr(config, "rope_scaling", None) or {}
-    kind = scaling.get("rope_type", scaling.get("type", "default"))
-    factor = float(scaling.get("factor", 1.0))
-    if kind == "dynamic" and seq_len is not None and seq_len > config.max_position_embeddings:
-        base = base * ((factor * seq_len / config.max_position_embeddings) - (factor - 1)) ** (d / (d - 2))
-    inv = 1.0 / (base ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    kind = scaling.get("rope_type", scaling.get("type", "default")) or "default"
+    expo = torch.arange(0, d, 2, dtype=torch.int64).float() / d
+    if kind == "default":
+        return 1.0 / (base ** expo), 1.0
     if kind == "linear":
-        inv = inv / factor
-    elif kind == "llama3":
-        lo, hi = float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
-        old = float(scaling["original_max_position_embeddings"])
+        return (1.0 / (base ** expo)) / float(scaling["factor"]), 1.0
+    if kind == "dynamic":
+        n = torch.tensor(int(seq_len) if seq_len is not None else 0, dtype=torch.int64)
+        return _dynamic_ntk_inv_freq(base, d, float(scaling["factor"]), int(config.max_position_embeddings), n), 1.0
+    if kind == "llama3":
+        inv = 1.0 / (base ** expo)
+        factor = scaling["factor"]
+        lo, hi = scaling["low_freq_factor"], scaling["high_freq_factor"]
+        old = scaling["original_max_position_embeddings"]
+        low_wavelen, high_wavelen = old / lo, old / hi
         wavelen = 2 * math.pi / inv
-        smooth = ((old / wavelen) - lo) / (hi - lo)
-        mid = (1 - smooth) * inv / factor + smooth * inv
-        inv = torch.where(wavelen > old / lo, inv / factor, torch.where(wavelen < old / hi, inv, mid))
-    elif kind not in ("default", "dynamic"):
-        raise NotImplementedError(f"rope_scaling type {kind!r}")
-    return inv, 1.0
+        out = torch.where(wavelen > low_wavelen, inv / factor, inv)
+        smooth = (old / wavelen - lo) / (hi - lo)
+        mid = (1 - smooth) * out / factor + smooth * out
+        is_mid = ~(wavelen < high_wavelen) * ~(wavelen > low_wavelen)
+        return torch.where(is_mid, mid, out), 1.0
+    if kind == "yarn":
+        factor = scaling["factor"]
+        max_pos = config.max_position_embeddings
+        att = scaling.get("attention_factor")
+        if att is None:
+            att = 0.1 * math.log(factor) + 1.0
+        beta_fast = scaling.get("beta_fast") or 32
+        beta_slow = scaling.get("beta_slow") or 1
+
+        def correction_dim(n_rot):  # the dimension that makes n_rot rotations over max_pos positions
+            return (d * math.log(max_pos / (n_rot * 2 * math.pi))) / (2 * math.log(base))
+
+        low = max(math.floor(correction_dim(beta_fast)), 0)
+        high = min(math.ceil(correction_dim(beta_slow)), d - 1)
+        if low == high:
+            high += 0.001
+        pos_freqs = base ** (torch.arange(0, d, 2).float() / d)
+        extrapolation, interpolation = 1.0 / pos_freqs, 1.0 / (factor * pos_freqs)
+        ramp = torch.clamp((torch.arange(d // 2, dtype=torch.float32) - low) / (high - low), 0, 1)
+        keep = 1 - ramp
+        return interpolation * (1 - keep) + extrapolation * keep, float(att)
+    if kind == "longrope":
+        factor = scaling.get("factor")
+        att = scaling.get("attention_factor")
+        if hasattr(config, "original_max_position_embeddings"):
+            max_pos = config.original_max_position_embeddings
+            expanded = config.max_position_embeddings
+            factor = expanded / max_pos
+        else:
+            max_pos = config.max_position_embeddings
+            expanded = max_pos * factor
+        if att is None:
+            att = 1.0 if factor <= 1.0 else math.sqrt(1 + math.log(factor) / math.log(max_pos))
+        ext = torch.tensor(scaling["long_factor"] if expanded > max_pos else scaling["short_factor"], dtype=torch.float32)
+        return 1.0 / (ext * base ** expo), float(att)
+    raise NotImplementedError(f"rope_scaling type {kind!r}")
 
 
 class OmniKVRotaryEmbedding(nn.Module):
+    """cos / sin generation of the Llama patch (modeling/patch_of_llama3_1.py:545-629).  One instance serves every
+    layer of a model (the reference holds an identical copy per layer).  ``inv_freq`` is a device buffer that the
+    fused decode kernels read directly; for dynamic-NTK scaling it is rewritten IN PLACE, on the device, whenever
+    the sequence outgrows the length it was last computed for (``advance``), so a captured decode step keeps
+    following the rule when replayed."""
+
     def __init__(self, config):
         super().__init__()
         self.config = config
-        inv, _ = _inv_freq(config)
+        scaling = getattr(config, "rope_scaling", None) or {}
+        self.rope_type = scaling.get("rope_type", scaling.get("type", "default")) or "default"
+        inv, att = rope_parameters(config)
+        self.attention_scaling = float(att)
         self.register_buffer("inv_freq", inv, persistent=False)
+        self.original_inv_freq = inv.clone()
+        self.original_max_seq_len = int(config.max_position_embeddings)
+        self.dynamic = "dynamic" in self.rope_type
+        # length inv_freq was last computed for (the reference's max_seq_len_cached), on the device
+        self.register_buffer("seq_cached", torch.tensor(self.original_max_seq_len, dtype=torch.int64), persistent=False)
+
+    @torch.no_grad()
+    def advance(self, position_ids: torch.Tensor, prefill: bool = False) -> None:
+        """The reference's ``_dynamic_frequency_update`` (:589-606), called once per forward before anything reads
+        ``inv_freq``: growth recomputes the frequencies for ``max(position_ids) + 1``; a prefill that is back inside
+        the original range after a longer sequence restores the original ones.  Decode steps run entirely on the
+        device (no synchronisation); a prefill reads the cached length back once."""
+        if not self.dynamic:
+            return
+        s = getattr(self.config, "rope_scaling")
+        seq = position_ids.max().to(torch.int64) + 1
+        if prefill:
+            n, cached = int(seq.item()), int(self.seq_cached.item())
+            if n < self.original_max_seq_len and cached > self.original_max_seq_len and n <= cached:
+                self.inv_freq.copy_(self.original_inv_freq.to(self.inv_freq.device))
+                self.seq_cached.fill_(self.original_max_seq_len)
+                return
+            if n <= cached:
+                return
+        torch.maximum(self.seq_cached, seq.to(self.seq_cached.device), out=self.seq_cached)
+        self.inv_freq.copy_(_dynamic_ntk_inv_freq(float(self.config.rope_theta), self.inv_freq.numel() * 2,
+                                                  float(s["factor"]), self.original_max_seq_len, self.seq_cached))
 
     @torch.no_grad()
     def forward(self, x: torch.Tensor, position_ids: torch.Tensor):
-        """cos, sin ``[B, q, d]`` in x's dtype for integer positions ``[B, q]`` (computed in fp32)."""
+        """cos, sin ``[B, q, d]`` in x's dtype for integer positions ``[B, q]`` (computed in fp32), times the
+        attention scaling of yarn / longrope (:623-624)."""
         freqs = position_ids.to(torch.float32)[:, :, None] * self.inv_freq.to(x.device)[None, None, :]
         emb = torch.cat((freqs, freqs), dim=-1)
-        return emb.cos().to(x.dtype), emb.sin().to(x.dtype)
+        cos, sin = emb.cos(), emb.sin()
+        if self.attention_scaling != 1.0:
+            cos, sin = cos * self.attention_scaling, sin * self.attention_scaling
+        return cos.to(x.dtype), sin.to(x.dtype)
 
 
 class _LazyRotary:
@@ -175,7 +268,7 @@ class OmniKVAttention(nn.Module):
     """The ``self_attn`` object of a layer: Llama attention with fused QKV weights whose decode path
     runs in ``omnikv_decode_attn`` through the cache."""
 
-    def __init__(self, config, layer_idx: int, tp=None):
+    def __init__(self, config, layer_idx: int, tp=None, rotary_emb=None):
         super().__init__()
         self.config = config
         self.layer_idx = layer_idx
@@ -196,7 +289,8 @@ class OmniKVAttention(nn.Module):
         self.k_proj = _ProjView(self, "qkv_weight", nq, nq + nkv)
         self.v_proj = _ProjView(self, "qkv_weight", nq + nkv, nq + 2 * nkv)
         self.o_proj = _ProjView(self, "o_weight", 0, self.hidden_size)
-        self.rotary_emb = OmniKVRotaryEmbedding(config)
+        # every layer reads the model's one rotary module (same frequencies everywhere, one dynamic update per step)
+        self.rotary_emb = rotary_emb if rotary_emb is not None else OmniKVRotaryEmbedding(config)
 
     def qkv(self, x, cos, sin):
         """x ``[B, n, hidden]`` -> rotated q ``[B,H,n,d]``, rotated k and v ``[B,KVH,n,d]``."""
@@ -211,7 +305,8 @@ class OmniKVAttention(nn.Module):
     def forward(self, hidden_states, position_embeddings, past_key_value, score_out=None, score_len=None):
         B, n, _ = hidden_states.shape
         rope_pos = getattr(past_key_value, "rope_pos_dev", None)
-        if n == 1 and rope_pos is not None and hidden_states.is_cuda and self.head_dim == 128:
+        if (n == 1 and rope_pos is not None and hidden_states.is_cuda and self.head_dim == 128
+                and self.rotary_emb.attention_scaling == 1.0):
             # decode: rotate q and k and append k, v to the cache in one kernel, straight from the fused projection
             qkv = F.linear(hidden_states.view(B, -1), self.qkv_weight)
             q = torch.empty(B, self.num_heads, self.head_dim, dtype=qkv.dtype, device=qkv.device)
@@ -261,12 +356,12 @@ class OmniKVMLP(nn.Module):
 class OmniKVMulLayer(nn.Module):
     """Decoder layer with the filter-layer hook of modeling/omnikv.py:113-246."""
 
-    def __init__(self, config, layer_idx, tp=None):
+    def __init__(self, config, layer_idx, tp=None, rotary_emb=None):
         super().__init__()
         self.config = config
         self.layer_idx = layer_idx
         self.tp = tp
-        self.self_attn = OmniKVAttention(config, layer_idx, tp)
+        self.self_attn = OmniKVAttention(config, layer_idx, tp, rotary_emb)
         self.mlp = OmniKVMLP(config, tp)
         self.input_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps)
         self.post_attention_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps)
@@ -368,7 +463,8 @@ class OmniKVMulLayer(nn.Module):
         ok = self._fused_cache.get(key)
         if ok is None:
             a = self.self_attn
-            ok = self.config.get("fused_decode", True) and ops.fused_decode_supported(
+            # the fused QKV kernel rotates with cos/sin of pos * inv_freq: no attention scaling (yarn, longrope)
+            ok = self.config.get("fused_decode", True) and a.rotary_emb.attention_scaling == 1.0 and ops.fused_decode_supported(
                 key, self.config.hidden_size, self.mlp.intermediate_size, a.num_heads * a.head_dim, 8)
             self._fused_cache[key] = ok
         return ok
@@ -535,9 +631,9 @@ class OmniKVMulModel(nn.Module):
         self.padding_idx = config.pad_token_id
         self.vocab_size = config.vocab_size
         self.embed_tokens = nn.Embedding(config.vocab_size, config.hidden_size, self.padding_idx)
-        self.layers = nn.ModuleList([OmniKVMulLayer(config, i, tp) for i in range(config.num_hidden_layers)])
-        self.norm = RMSNorm(config.hidden_size, config.rms_norm_eps)
         self.rotary_emb = OmniKVRotaryEmbedding(config)
+        self.layers = nn.ModuleList([OmniKVMulLayer(config, i, tp, self.rotary_emb) for i in range(config.num_hidden_layers)])
+        self.norm = RMSNorm(config.hidden_size, config.rms_norm_eps)
 
     def forward(self, input_ids=None, attention_mask=None, position_ids=None, past_key_values=None,
                 inputs_embeds=None, use_cache=None, output_attentions=None, output_hidden_states=None,
@@ -556,6 +652,7 @@ class OmniKVMulModel(nn.Module):
                 cache.rope_pos_dev = position_ids.reshape(-1).to(torch.int32).contiguous()
         elif position_ids is None:
             position_ids = torch.arange(n, device=h.device)[None, :].expand(B, n)
+        self.rotary_emb.advance(position_ids, prefill=n > 1)  # dynamic-NTK scaling follows the sequence length
         # the fused batch-1 kernels rotate inside the QKV kernel and never read the table: build it on first use
         pos_emb = _LazyRotary(lambda: self.rotary_emb(h, position_ids))
         for layer in self.layers:
@@ -594,20 +691,45 @@ class OmniKVMulLM(nn.Module):
     # -- construction ----------------------------------------------------------------------------
     @torch.no_grad()
     def init_random_(self, seed: int = 0, std: float = 0.02):
-        """Seeded N(0, std) weights, norm weights 1 (benchmarks run on random-init weights)."""
+        """Seeded N(0, std) weights, norm weights 1 (benchmarks run on random-init weights).
+
+        The random stream is that of the UNSHARDED model: every matrix is drawn at its full Hugging Face shape
+        (q, k, v, o, gate, up, down per layer, then the embedding and the head, in that order, in blocks of rows)
+        and each rank keeps its slice -- the same slices ``load_hf_state_dict`` takes.  A tensor-parallel group
+        built from one seed is therefore the same model as the single-GPU one, which is what lets a multi-GPU
+        run be checked against it."""
         dev = self.lm_head.weight.device
-        rank = self.tp.rank if self.tp is not None else 0
-        g_shared = torch.Generator(device=dev).manual_seed(seed)             # replicated tensors
-        g_shard = torch.Generator(device=dev).manual_seed(seed + 1000 * (rank + 1))  # this rank's shards
-        for name, p in self.named_parameters():
-            g = g_shared if "embed_tokens" in name else g_shard
-            if p.dim() == 1:
-                p.fill_(1.0)
-            else:
-                step = max(1, (1 << 28) // max(1, p.shape[1]))
-                for s in range(0, p.shape[0], step):
-                    blk = p[s:s + step]
-                    blk.copy_(torch.randn(blk.shape, generator=g, device=p.device, dtype=torch.float32) * std)
+        g = torch.Generator(device=dev).manual_seed(seed)
+        tp, cfg = self.tp, self.config
+
+        def draw(dst, rows, cols, dim=None):
+            """dst: this rank's ``[rows_local, cols_local]`` slice (dimension ``dim`` sharded) of a rows x cols matrix."""
+            lo_r, hi_r = tp.shard(rows) if (tp is not None and dim == 0) else (0, rows)
+            lo_c, hi_c = tp.shard(cols) if (tp is not None and dim == 1) else (0, cols)
+            step = max(1, (1 << 26) // cols)
+            for s0 in range(0, rows, step):
+                e0 = min(rows, s0 + step)
+                blk = torch.randn(e0 - s0, cols, generator=g, device=dev, dtype=torch.float32)
+                a, b = max(s0, lo_r), min(e0, hi_r)
+                if a < b:
+                    dst[a - lo_r:b - lo_r].copy_(blk[a - s0:b - s0, lo_c:hi_c] * std)
+
+        hid, inter, d = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+        nq, nkv = cfg.num_attention_heads * d, cfg.num_key_value_heads * d
+        for layer in self.model.layers:
+            a, mlp = layer.self_attn, layer.mlp
+            draw(a.q_proj.weight, nq, hid, 0)
+            draw(a.k_proj.weight, nkv, hid, 0)
+            draw(a.v_proj.weight, nkv, hid, 0)
+            draw(a.o_proj.weight, hid, nq, 1)
+            draw(mlp.gate_proj.weight, inter, hid, 0)
+            draw(mlp.up_proj.weight, inter, hid, 0)
+            draw(mlp.down_proj.weight, hid, inter, 1)
+            layer.input_layernorm.weight.fill_(1.0)
+            layer.post_attention_layernorm.weight.fill_(1.0)
+        draw(self.model.embed_tokens.weight, cfg.vocab_size, hid)
+        draw(self.lm_head.weight, cfg.vocab_size, hid, 0)
+        self.model.norm.weight.fill_(1.0)
         return self
 
     @classmethod
@@ -744,7 +866,7 @@ class OmniKVMulLM(nn.Module):
         lm_head and the arg-max run in one fused weight-streaming kernel."""
         layer0 = self.model.layers[0]
         fused = tokens.shape[0] == 1 and layer0._fused_ok(self.model.embed_tokens.weight[:1].view(1, 1, -1))
-        if fused and self.tp is None and self.config.get("chained_decode", True) and ops.decode_chain_supported(
+        if fused and self.tp is None and self.config.get("chained_decode", False) and ops.decode_chain_supported(
                 self.lm_head.weight.dtype, self.config.hidden_size, layer0.mlp.intermediate_size,
                 layer0.self_attn.num_heads) and self.lm_head.weight.shape[0] % 8 == 0:
             return self._decode_step_chained(tokens, cache)
@@ -790,6 +912,7 @@ class OmniKVMulLM(nn.Module):
         layers = self.model.layers
         cfg = self.config
         cache.begin_decode_step()
+        self.model.rotary_emb.advance(cache.pos_dev[:, None])
         h = self.model.embed_tokens(tokens).view(-1)
         fb = layers[0]._fused_bufs(cache, h.device, h.dtype)
         if getattr(fb, "logits", None) is None:
@@ -837,7 +960,7 @@ class OmniKVMulLM(nn.Module):
         runner = DecodeRunner(self, input_ids, cache=cache, first_token=first_token, max_new_tokens=max_new_tokens,
                               use_cuda_graph=use_cuda_graph, warmup_steps=warmup_steps)
         runner.run(max_new_tokens - 1 - runner.steps_done)
-        return runner.tokens()
+        return runner.tokens(check=True)
 
 
 class DecodeRunner:
@@ -909,5 +1032,10 @@ class DecodeRunner:
                 self._step()
         self.steps_done += n_steps
 
-    def tokens(self) -> torch.Tensor:
+    def tokens(self, check: bool = False) -> torch.Tensor:
+        """The ids generated so far ``[B, steps_done + 1]``.  ``check`` synchronises and raises if any kernel of
+        the steps reported that one of its bounded waits ran out (an absent rank, a copy that never landed):
+        tokens produced after that are not to be trusted."""
+        if check:
+            ops.check_status(self.out.device)
         return self.out[:, : self.steps_done + 1]

@@ -19,6 +19,7 @@ _SEL = {"softmax_before_last": abi.SEL_SOFTMAX_LAST, "uniform": abi.SEL_UNIFORM,
 
 _sm_count = {}
 _workspaces = {}
+_retired_workspaces = []
 _launches = 0
 
 
@@ -57,11 +58,15 @@ def _need_cuda(*ts):
 
 def workspace(device, nbytes: int, tag: str = "default") -> torch.Tensor:
     """A cached per-device scratch tensor of at least ``nbytes`` bytes (the caller of the C ABI
-    owns the workspace; this cache is that caller).  Grows on demand; never call it with a larger
-    size for the first time while a CUDA graph is being captured."""
+    owns the workspace; this cache is that caller).  Grows on demand, and a buffer that has been handed out is
+    never freed: a CUDA graph captured earlier has its address baked in and keeps replaying into it, so the
+    outgrown buffer stays alive beside the larger one (a few MB per growth).  Never call it with a larger size
+    for the first time while a CUDA graph is being captured."""
     key = (torch.device(device).index, tag)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
+        if ws is not None:
+            _retired_workspaces.append(ws)
         # zero-filled: the decode-attention workspace starts with arrival counters that must be zero
         ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
@@ -401,7 +406,9 @@ def check_status(device) -> None:
     code = int(status_word(device).item())
     if code:
         status_word(device).zero_()
-        raise abi.OmniKVError(f"a decode kernel gave up waiting for a shared-memory copy (code {code})")
+        what = {1: "a weight copy's ring slot (producer)", 2: "a weight copy (consumer)", 3: "the grid barrier",
+                4: "another rank's exchange flag", 5: "a K/V tile copy"}.get(code, "an unknown wait")
+        raise abi.OmniKVError(f"a decode kernel gave up waiting for {what} (status {code}); its results are incomplete")
 
 
 def rows_per_stage(K: int) -> int:
@@ -478,7 +485,7 @@ def decode_chain_supported(dtype, hidden: int, inter: int, H: int) -> bool:
 def decode_chain(h, *, eps, H, KVH, inter, w_o=None, attn_out=None, post_norm_w=None, w_gate_up=None, w_down=None,
                  act=None, in_norm_w=None, w_qkv=None, inv_freq=None, rope_pos=None, q_out=None, k_cache_seq=None,
                  v_cache_seq=None, cache_pos=None, final_norm_w=None, w_head=None, logits=None, best=None,
-                 token_out=None, trace=None, chunk_counters=None, next_w=None):
+                 token_out=None, chunk_counters=None, next_w=None):
     """``omnikv_decode_chain``: the weight-streaming phases between two attention calls in one cooperative
     launch.  h ``[hidden]`` is updated in place."""
     p = abi.ChainParams()
@@ -495,7 +502,6 @@ def decode_chain(h, *, eps, H, KVH, inter, w_o=None, attn_out=None, post_norm_w=
     p.vocab_rows = 0 if w_head is None else w_head.shape[0]
     p.logits, p.best_scratch, p.token_out = _ptr(logits), _ptr(best), _ptr(token_out)
     p.grid_sync, p.status = grid_sync_words(h.device).data_ptr(), status_word(h.device).data_ptr()
-    p.trace = _ptr(trace)
     p.chunk_counters = _ptr(chunk_counters)
     if next_w is not None:
         p.next_w, p.next_w_bytes = next_w.data_ptr(), next_w.numel() * next_w.element_size()

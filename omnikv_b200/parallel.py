@@ -48,7 +48,7 @@ class PeerExchange:
             symm.enable_symm_mem_for_group(grp.group_name)
             self.handle = symm.rendezvous(self.buf, grp)
         self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
-        self.done = torch.zeros(1, dtype=torch.int32, device=device)
+        self.done = torch.zeros(2, dtype=torch.int32, device=device)  # [finished CTAs, calls made]
         self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
         self._structs = {}
         dist.barrier(group=group)  # every rank's buffer is zeroed and mapped before anyone stores into it
@@ -76,7 +76,7 @@ class TPGroup:
         self.world, self.rank, self.group = world, rank, group
         self.exchange: Optional[PeerExchange] = None   # fused projection + all-reduce (batch-1 decode kernels)
         self.reducer: Optional[PeerExchange] = None    # standalone small all-reduce (batched decode)
-        self._reduce_seq = 0
+        self.peer_reduce_calls = 0                     # all_reduce_sum calls served by the peer-memory kernel
 
     def enable_peer_exchange(self, hidden: int, device: torch.device) -> bool:
         """Set up the peer-mapped buffers for the fused projection + all-reduce kernels.  Returns False (and
@@ -111,15 +111,11 @@ class TPGroup:
         dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
         if int(ok.item()) == 0:
             self.reducer = None
-        self._reduce_seq = 0
         return self.reducer is not None
 
     def begin_step(self) -> None:
-        """Once per model forward on every rank: the peer all-reduce numbers its calls from zero again and its
-        flags carry the new step number (a device counter, so a captured step can be replayed)."""
-        if self.reducer is not None:
-            self.reducer.begin_step()
-            self._reduce_seq = 0
+        """Once per model forward on every rank.  The peer all-reduce numbers its calls on the device, so it has
+        nothing to reset here; this is the hook where per-step state of the group would go."""
 
     def shard(self, n: int) -> Tuple[int, int]:
         """[lo, hi) of this rank's contiguous share of ``n`` items (``n`` divisible by the world size)."""
@@ -135,10 +131,10 @@ class TPGroup:
         nbytes = t.numel() * t.element_size()
         # every condition depends on shapes and call order only, so all ranks take the same branch
         if (r is not None and t.is_cuda and t.is_contiguous() and nbytes % 16 == 0 and nbytes <= r.hidden * 4
-                and self._reduce_seq < 256 and t.dtype in (torch.bfloat16, torch.float16, torch.float32)):
+                and t.dtype in (torch.bfloat16, torch.float16, torch.float32)):
             from . import ops
-            ops.tp_allreduce_sum(t, r.at(self._reduce_seq))
-            self._reduce_seq += 1
+            ops.tp_allreduce_sum(t, r.at(0))
+            self.peer_reduce_calls += 1
             return t
         dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
         return t

@@ -39,10 +39,12 @@ def _rms(x, w, eps):
 
 
 class OracleLM:
-    def __init__(self, cfg: Dict, weights: Dict[str, torch.Tensor]):
-        """cfg: plain dict with the Llama fields and the OmniKV keys; weights: HF-named fp32 tensors."""
+    def __init__(self, cfg: Dict, weights: Dict[str, torch.Tensor], device="cpu"):
+        """cfg: plain dict with the Llama fields and the OmniKV keys; weights: HF-named tensors (held as fp32 on
+        ``device``: the CPU, or a GPU when a test checks a model too large for a CPU run -- still this fp32 code)."""
         self.cfg = cfg
-        self.w = {k: v.detach().float().cpu() for k, v in weights.items()}
+        self.device = torch.device(device)
+        self.w = {k: v.detach().to(self.device, torch.float32) for k, v in weights.items()}
         self.n_layers = cfg["num_hidden_layers"]
         self.H, self.KVH = cfg["num_attention_heads"], cfg["num_key_value_heads"]
         self.d = cfg.get("head_dim") or cfg["hidden_size"] // self.H
@@ -51,6 +53,7 @@ class OracleLM:
         self.window = cfg.get("window_size", 16)
         self.state = [dict(prefill_len=None, window=None, decode_step=0) for _ in range(self.n_layers)]
         self.selected = {}  # (decode forward number, layer) -> idx, for the tests
+        self.scores = {}    # (decode forward number, layer) -> (scores [B, consider_len], k) behind that selection
 
     def new_cache(self):
         name = self.cfg.get("cache_cls", "multi")
@@ -86,8 +89,9 @@ class OracleLM:
                 k_sel = max(1, k_sel - nptw)
             idx = oo.select_tokens_by_attn_universal(attn, window_hs, position_ids, cache, k_sel, consider_len, i,
                                                      self.selector)
+            self.scores[(fwd_no, i)] = (oo.select_tokens_by_attn_universal.last_scores, k_sel)
             if "last" not in self.selector:
-                extra = torch.arange(st["prefill_len"] - nptw, st["prefill_len"])[None, :].repeat(idx.shape[0], 1)
+                extra = torch.arange(st["prefill_len"] - nptw, st["prefill_len"], device=idx.device)[None, :].repeat(idx.shape[0], 1)
                 idx = torch.cat([idx, extra], dim=1)
             self.selected[(fwd_no, i)] = idx
             cache.set_idx_on_gpu(idx, i)
@@ -105,7 +109,7 @@ class OracleLM:
             kr = kk[:, :, None].expand(B, self.KVH, g, n, self.d).reshape(B, self.H, n, self.d)
             vr = vv[:, :, None].expand(B, self.KVH, g, n, self.d).reshape(B, self.H, n, self.d)
             s = torch.matmul(q, kr.transpose(2, 3)) / math.sqrt(self.d)
-            s = s + torch.full((n, n), float("-inf")).triu(1)
+            s = s + torch.full((n, n), float("-inf"), device=s.device).triu(1)
             o = torch.matmul(torch.softmax(s, dim=-1), vr)
         else:
             o = oo.dense_attention(q[:, :, 0], kk, vv)[:, :, None, :]
@@ -124,10 +128,25 @@ class OracleLM:
         cache.stage = "decoding" if n == 1 else "prefill"
         if position_ids is None:
             start = cache._seen_tokens
-            position_ids = torch.arange(start, start + n)[None, :].expand(B, n)
-        h = F.embedding(input_ids, self.w["model.embed_tokens.weight"])
+            position_ids = torch.arange(start, start + n, device=self.device)[None, :].expand(B, n)
+        h = F.embedding(input_ids.to(self.device), self.w["model.embed_tokens.weight"])
         for i in range(self.n_layers):
             h = self._layer(i, h, position_ids, cache, fwd_no)
         h = _rms(h, self.w["model.norm.weight"], self.cfg["rms_norm_eps"])
         logits = F.linear(h[:, -1:], self.w["lm_head.weight"]).float()
         return logits, cache
+
+    @torch.no_grad()
+    def forward_hidden(self, x: torch.Tensor, cache=None, fwd_no=0):
+        """The decoder stack alone on input hidden states ``[B, n, hidden]`` (no embedding, no final norm):
+        what the layer-hook fixture drives through the reference's ``OmniKVMulLayer.forward``."""
+        B, n, _ = x.shape
+        if cache is None:
+            cache = self.new_cache()
+        cache.stage = "decoding" if n == 1 else "prefill"
+        start = cache._seen_tokens
+        position_ids = torch.arange(start, start + n, device=self.device)[None, :].expand(B, n)
+        h = x.to(self.device, torch.float32)
+        for i in range(self.n_layers):
+            h = self._layer(i, h, position_ids, cache, fwd_no)
+        return h, cache

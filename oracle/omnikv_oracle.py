@@ -24,7 +24,7 @@ def rope_cos_sin(position_ids: torch.Tensor, head_dim: int, theta: float = 50000
     forward of PatchLlamaRotaryEmbedding :599-629 (fp32, cat(freqs, freqs)).
     """
     inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
-    freqs = position_ids.to(torch.float32)[:, :, None] * inv_freq[None, None, :]
+    freqs = position_ids.to(torch.float32)[:, :, None] * inv_freq.to(position_ids.device)[None, None, :]
     emb = torch.cat((freqs, freqs), dim=-1)
     return emb.cos(), emb.sin()
 
@@ -145,6 +145,7 @@ def select_tokens_by_attn_universal(
         s = score_window(q, k_cache, consider_len, selector_cls)
     else:
         raise NotImplementedError(selector_cls)
+    select_tokens_by_attn_universal.last_scores = s  # for tests that check a selection up to a score band
     return topk_ascending(s, num_selected_tokens)
 
 

@@ -1,7 +1,7 @@
 """Small stand-alone launches of each kernel at the benchmark's shapes, for profilers:
 
-    python -m omnikv_b200.profile_cases dense_attn [--reps 3] [--ctx 131072]
-    ncu --set full --clock-control none -k regex:decode_attn_mma -c 3 python -m omnikv_b200.profile_cases dense_attn
+    python profile_cases.py dense_attn [--reps 3] [--ctx 131072]
+    ncu --set full --clock-control none -k regex:decode_attn_mma -c 3 python profile_cases.py dense_attn
 
 Cases: dense_attn (filter layer: K and V of 8 KV heads x ctx rows, fused scores), sparse_attn
 (8781 selected rows + tail), topk (ctx scores, 8 planes), score_window (16-slot window, exp),
@@ -13,7 +13,12 @@ import argparse
 
 import torch
 
-from . import ops
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parent))
+
+from omnikv_b200 import ops  # noqa: E402
 
 
 def gemv_cases(reps: int, n_sets: int = 8):

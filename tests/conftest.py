@@ -7,6 +7,7 @@ import pytest
 ROOT = Path(__file__).resolve().parent.parent
 sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(ROOT / "tests" / "golden"))
+sys.path.insert(0, str(ROOT / "tests"))
 
 
 def pytest_configure(config):

@@ -46,8 +46,20 @@ def selector_inputs(case):
 CACHE_FLOW = dict(n_layers=6, sel=[1, 3], wait=1, kvh=2, d=16, P=40, steps=3, n_idx=9, seed=7)
 
 
-def cache_flow_inputs():
-    c = CACHE_FLOW
+# the same flow at the head size the CUDA kernels are built for; its fixture stores signatures, not tensors
+CACHE_FLOW_D128 = dict(n_layers=6, sel=[1, 3], wait=1, kvh=2, d=128, P=300, steps=4, n_idx=41, seed=17)
+
+
+def signature(a) -> list:
+    """[shape..., sum, sum of magnitudes, position-weighted sum] in float64: equal for equal arrays, and changed by
+    any swapped, missing or altered element (the cache returns copies of its inputs, never new values)."""
+    f = np.ascontiguousarray(a).astype(np.float64).ravel()
+    w = np.arange(1, f.size + 1, dtype=np.float64)
+    return [*a.shape, float(f.sum()), float(np.abs(f).sum()), float((f * w).sum())]
+
+
+def cache_flow_inputs(c=None):
+    c = c or CACHE_FLOW
     rng = np.random.default_rng(c["seed"])
     n, kvh, d, P, steps = c["n_layers"], c["kvh"], c["d"], c["P"], c["steps"]
     k_pre = [rng.standard_normal((1, kvh, P, d), dtype=np.float32) for _ in range(n)]
@@ -101,3 +113,62 @@ def operator_inputs(seed: int = 2024, L: int = 16384, H: int = 32, KVH: int = 8,
     hot = np.sort(rng.choice(L, size=int(round(0.02 * L)), replace=False))
     k[:, :, hot, :] += 4.0 * u
     return dict(q=q, k=k, k2=k2, v2=v2, k_new=k_new, v_new=v_new, hot=hot)
+
+
+LAYER_HOOK = dict(seed=31, n_layers=6, sel=[1, 3], wait=0, hidden=512, H=4, KVH=2, d=128, inter=768, P=200, steps=20,
+                  window=16, frac=0.25, theta=500000.0, eps=1e-5, qk_gain=3.0)
+
+
+def layer_hook_inputs():
+    """A 6-layer decoder stack for the filter-layer hook: per layer the Hugging Face named weights (fp32; q/k
+    scaled up so that attention is peaked and the selection matters), the prompt's input hidden states
+    ``x_pre [1, P, hidden]`` and one input hidden state per decode step ``x_dec [steps][1, 1, hidden]``."""
+    c = LAYER_HOOK
+    rng = np.random.default_rng(c["seed"])
+    hid, d, H, KVH, inter = c["hidden"], c["d"], c["H"], c["KVH"], c["inter"]
+    n = lambda *s: rng.standard_normal(s, dtype=np.float32)  # noqa: E731
+    layers = []
+    for _ in range(c["n_layers"]):
+        layers.append({
+            "self_attn.q_proj.weight": n(H * d, hid) * (c["qk_gain"] / math.sqrt(hid)),
+            "self_attn.k_proj.weight": n(KVH * d, hid) * (c["qk_gain"] / math.sqrt(hid)),
+            "self_attn.v_proj.weight": n(KVH * d, hid) / math.sqrt(hid),
+            "self_attn.o_proj.weight": n(hid, H * d) / math.sqrt(H * d),
+            "mlp.gate_proj.weight": n(inter, hid) / math.sqrt(hid),
+            "mlp.up_proj.weight": n(inter, hid) / math.sqrt(hid),
+            "mlp.down_proj.weight": n(hid, inter) / math.sqrt(inter),
+            "input_layernorm.weight": (1.0 + 0.1 * n(hid)).astype(np.float32),
+            "post_attention_layernorm.weight": (1.0 + 0.1 * n(hid)).astype(np.float32),
+        })
+    x_pre = n(1, c["P"], hid)
+    x_dec = [n(1, 1, hid) for _ in range(c["steps"])]
+    return dict(layers=layers, x_pre=x_pre, x_dec=x_dec)
+
+
+ROPE_CASES = [
+    dict(name="default", head_dim=128, rope_theta=500000.0, max_position_embeddings=8192, rope_scaling=None),
+    dict(name="linear", head_dim=128, rope_theta=10000.0, max_position_embeddings=4096,
+         rope_scaling={"rope_type": "linear", "factor": 4.0}),
+    dict(name="dynamic_init", head_dim=128, rope_theta=500000.0, max_position_embeddings=8192,
+         rope_scaling={"type": "dynamic", "factor": 4}),
+    dict(name="llama3", head_dim=128, rope_theta=500000.0, max_position_embeddings=131072,
+         rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                       "original_max_position_embeddings": 8192}),
+    dict(name="yarn", head_dim=128, rope_theta=10000.0, max_position_embeddings=4096,
+         rope_scaling={"rope_type": "yarn", "factor": 16.0}),
+    dict(name="yarn_betas", head_dim=64, rope_theta=1000000.0, max_position_embeddings=32768,
+         rope_scaling={"rope_type": "yarn", "factor": 4.0, "beta_fast": 16, "beta_slow": 2, "attention_factor": 1.25}),
+    dict(name="longrope_long", head_dim=96, rope_theta=10000.0, max_position_embeddings=4096,
+         rope_scaling={"rope_type": "longrope", "factor": 8.0,
+                       "long_factor": [1.0 + 0.25 * i for i in range(48)], "short_factor": [1.0 + 0.01 * i for i in range(48)]}),
+    dict(name="longrope_phi3", head_dim=96, rope_theta=10000.0, max_position_embeddings=131072,
+         original_max_position_embeddings=4096,
+         rope_scaling={"rope_type": "longrope", "long_factor": [1.0 + 0.5 * i for i in range(48)],
+                       "short_factor": [1.0 + 0.02 * i for i in range(48)]}),
+]
+
+# dynamic NTK followed over a conversation: forwards given as (first position, number of positions)
+ROPE_DYNAMIC_SEQ = dict(head_dim=128, rope_theta=500000.0, max_position_embeddings=1024,
+                        rope_scaling={"type": "dynamic", "factor": 4.0},
+                        forwards=[(0, 600), (600, 1), (0, 1500), (1500, 1), (1501, 1), (1502, 1), (0, 1200), (1200, 1),
+                                  (0, 300), (300, 1), (0, 2000), (2000, 1)])

@@ -175,6 +175,35 @@ def make_cache_flow_fixture(ref_cache):
     print("cache flow arrays:", len(arrays))
 
 
+def make_cache_flow_d128_fixture(ref_cache):
+    """The same flow at head size 128 (what the CUDA kernels are built for), four decode steps; per returned
+    tensor a signature (shape, sums) instead of the tensor itself, since the returns are pure copies of inputs."""
+    from inputs import CACHE_FLOW_D128, signature
+    c = CACHE_FLOW_D128
+    x = cache_flow_inputs(c)
+    n_layers, sel, wait, steps = c["n_layers"], c["sel"], c["wait"], c["steps"]
+    full = list(range(0, sel[0])) + sel + [n_layers]
+    t = lambda a: torch.from_numpy(a)  # noqa: E731
+    sigs = {}
+    for cls in (ref_cache.OmniKVMultiStageCache, ref_cache.WOPackCache):
+        dyn = types.SimpleNamespace(key_cache=[], value_cache=[], _seen_tokens=0)
+        cache = cls.from_dynamic_cache(dyn, full, n_layers, wait, False)
+        cache.stage = "prefill"
+        for i in range(n_layers):
+            cache.update(t(x["k_pre"][i]), t(x["v_pre"][i]), i)
+        for s in range(steps):
+            cache.stage = "decoding"
+            for i in range(n_layers):
+                if i in sel:
+                    cache.set_idx_on_gpu(t(x["idx"][(s, i)]), i)
+                kk, vv = cache.update(t(x["k_new"][s][i]), t(x["v_new"][s][i]), i)
+                sigs[f"{cls.__name__}/{s}/{i}"] = [signature(kk.numpy()), signature(vv.numpy())]
+        sigs[f"{cls.__name__}/seen"] = int(cache._seen_tokens)
+    flat = x["k_pre"] + x["v_pre"] + [a for r in x["k_new"] for a in r] + [a for r in x["v_new"] for a in r]
+    (HERE / "cache_flow_d128.json").write_text(json.dumps(dict(c, full=full, input_checksum=checksum(flat), returns=sigs)))
+    print("cache flow d128 returns:", len(sigs))
+
+
 def make_operator_fixture(ref_omnikv, ref_cache):
     """The single-layer operator case through the reference: selector ``last`` (k = 1098), gather of the
     second layer's rows by OmniKVMultiStageCache, then fp32 attention over what ``update`` returns."""
@@ -237,6 +266,174 @@ def make_lazy_rule_fixture(ref_cache):
     print("lazy rule:", {k: sum(v["applied"]) for k, v in res.items()}, "re-gathers of", c["steps"])
 
 
+class _StubAttention(torch.nn.Module):
+    """Stand-in for the third-party attention module the reference's layer calls (transformers 4.41.2
+    ``LlamaAttention``, absent from the reference tree): projections, rotation, ``past_key_value.update`` and plain
+    softmax attention, with that version's call signature and 3-tuple return.  Everything the FILTER HOOK does --
+    window capture, k / consider_len / nptw bookkeeping, the selector call, the appended window positions,
+    ``set_idx_on_gpu`` -- is the reference's own ``OmniKVMulLayer.forward`` running around it."""
+
+    def __init__(self, w, c, layer_idx):
+        super().__init__()
+        self.config = _Cfg()
+        self.layer_idx = layer_idx
+        self.num_heads, self.num_key_value_heads, self.head_dim = c["H"], c["KVH"], c["d"]
+        self.num_key_value_groups = c["H"] // c["KVH"]
+        self._theta = c["theta"]
+        for name in ("q_proj", "k_proj", "v_proj", "o_proj"):
+            lin = torch.nn.Linear(1, 1, bias=False)
+            lin.weight = torch.nn.Parameter(torch.from_numpy(w[f"self_attn.{name}.weight"]), requires_grad=False)
+            setattr(self, name, lin)
+
+    def rotary_emb(self, x, position_ids):
+        inv_freq = 1.0 / (self._theta ** (torch.arange(0, self.head_dim, 2, dtype=torch.float32) / self.head_dim))
+        freqs = position_ids.float()[:, :, None] * inv_freq[None, None, :]
+        emb = torch.cat((freqs, freqs), dim=-1)
+        return emb.cos(), emb.sin()
+
+    def forward(self, hidden_states, attention_mask=None, position_ids=None, past_key_value=None,
+                output_attentions=False, use_cache=False, cache_position=None):
+        B, n, _ = hidden_states.shape
+        H, KVH, d = self.num_heads, self.num_key_value_heads, self.head_dim
+        q = self.q_proj(hidden_states).view(B, n, H, d).transpose(1, 2)
+        k = self.k_proj(hidden_states).view(B, n, KVH, d).transpose(1, 2)
+        v = self.v_proj(hidden_states).view(B, n, KVH, d).transpose(1, 2)
+        cos, sin = self.rotary_emb(v, position_ids)
+
+        def rot(x):
+            h = x.shape[-1] // 2
+            return x * cos.unsqueeze(1) + torch.cat((-x[..., h:], x[..., :h]), dim=-1) * sin.unsqueeze(1)
+
+        q, k = rot(q), rot(k)
+        k, v = past_key_value.update(k, v, self.layer_idx)
+        m = k.shape[2]
+        k = k[:, :, None].expand(B, KVH, H // KVH, m, d).reshape(B, H, m, d)
+        v = v[:, :, None].expand(B, KVH, H // KVH, m, d).reshape(B, H, m, d)
+        s = torch.matmul(q, k.transpose(2, 3)) / math.sqrt(d)
+        if n > 1:
+            s = s + torch.full((n, m), float("-inf")).triu(1 + m - n)
+        o = torch.matmul(torch.softmax(s, dim=-1), v).transpose(1, 2).reshape(B, n, H * d)
+        return self.o_proj(o), None, past_key_value
+
+
+def make_layer_hook_fixture(ref_omnikv, ref_cache):
+    """The reference's ``OmniKVMulLayer.forward`` (modeling/omnikv.py:143-246) on a six-layer stack: a prefill of
+    P hidden states, then 20 decode forwards, for the selectors ``last``, ``uniform`` and ``exp``.  The layer objects
+    are created without transformers' constructor (whose signature changed after 4.41.2) and given exactly the
+    attributes the reference's ``__init__`` sets (:114-141).  Stored: every filter layer's index list at every
+    decode forward and the stack's output hidden state of every forward."""
+    from inputs import LAYER_HOOK, layer_hook_inputs
+    c = LAYER_HOOK
+    x = layer_hook_inputs()
+    # transformers 4.41.2's DynamicCache.__len__ is the number of layers held, which is what makes the reference's
+    # `if past_key_value:` true; 5.x returns 0 for this subclass.  Restore that meaning on the reference classes.
+    for cls in (ref_cache.OmniKVMultiStageCache, ref_cache.WOPackCache):
+        cls.__len__ = lambda self: len(self.key_cache)
+
+    class Cfg:
+        def __init__(self, **kw):
+            self.__dict__.update(kw)
+
+        def get(self, key, default=None):
+            return self.__dict__.get(key, default)
+
+    class Norm(torch.nn.Module):
+        def __init__(self, w):
+            super().__init__()
+            self.w = torch.from_numpy(w)
+
+        def forward(self, h):
+            return h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + c["eps"]) * self.w
+
+    class MLP(torch.nn.Module):
+        def __init__(self, w):
+            super().__init__()
+            self.g, self.u, self.d = (torch.from_numpy(w[f"mlp.{n}_proj.weight"]) for n in ("gate", "up", "down"))
+
+        def forward(self, h):
+            return torch.nn.functional.linear(torch.nn.functional.silu(torch.nn.functional.linear(h, self.g)) *
+                                              torch.nn.functional.linear(h, self.u), self.d)
+
+    arrays = {}
+    full = list(range(0, c["sel"][0])) + c["sel"] + [c["n_layers"]]
+    for selector in ("last", "uniform", "exp"):
+        cfg = Cfg(cache_cls="multi", do_select_layers=",".join(map(str, c["sel"])), selector_cls=selector,
+                  window_size=c["window"], num_of_selected_tokens=c["frac"], dense_more=True)
+        layers = []
+        for i, w in enumerate(x["layers"]):
+            layer = object.__new__(ref_omnikv.OmniKVMulLayer)
+            torch.nn.Module.__init__(layer)
+            layer.self_attn = _StubAttention(w, c, i)
+            layer.mlp = MLP(w)
+            layer.input_layernorm = Norm(w["input_layernorm.weight"])
+            layer.post_attention_layernorm = Norm(w["post_attention_layernorm.weight"])
+            layer.config, layer.layer_idx, layer.prefill_len = cfg, i, None
+            layer.cache_cls = ref_cache.get_cache_cls(cfg)
+            layer.do_select_layers = list(c["sel"])
+            layer.hidden_state_window, layer.selector_cls = None, selector
+            layer.window_size, layer.decode_step = c["window"], 0
+            layers.append(layer)
+        dyn = types.SimpleNamespace(key_cache=[], value_cache=[], _seen_tokens=0)
+        cache = ref_cache.OmniKVMultiStageCache.from_dynamic_cache(dyn, full, c["n_layers"], c["wait"], False)
+        seen = {}
+        orig_set = cache.set_idx_on_gpu
+
+        def spy(idx, layer_idx, _orig=orig_set, _seen=seen):
+            _seen[layer_idx] = idx.clone()
+            return _orig(idx, layer_idx)
+
+        cache.set_idx_on_gpu = spy
+        P = c["P"]
+        with torch.no_grad():
+            cache.stage = "prefill"   # modeling/omnikv.py:343-346: the LM sets the stage from the number of tokens
+            h = torch.from_numpy(x["x_pre"])
+            pos = torch.arange(P)[None, :]
+            for layer in layers:
+                h = layer(h, position_ids=pos, past_key_value=cache, use_cache=True)[0]
+            arrays[f"{selector}/h/prefill"] = h[:, -1].numpy().copy()
+            for s in range(c["steps"]):
+                cache.stage = "decoding"
+                h = torch.from_numpy(x["x_dec"][s])
+                pos = torch.tensor([[P + s]])
+                for layer in layers:
+                    h = layer(h, position_ids=pos, past_key_value=cache, use_cache=True)[0]
+                arrays[f"{selector}/h/{s}"] = h[:, -1].numpy().copy()
+                for f in c["sel"]:
+                    arrays[f"{selector}/idx/{s}/{f}"] = seen[f].numpy().astype(np.int32)
+    np.savez_compressed(HERE / "layer_hook.npz", **arrays)
+    flat = [a for w in x["layers"] for a in w.values()] + [x["x_pre"]] + x["x_dec"]
+    (HERE / "layer_hook.json").write_text(json.dumps(dict(c, full=full, input_checksum=checksum(flat))))
+    print("layer hook arrays:", len(arrays))
+
+
+def make_rope_fixture(ref_root):
+    """inv_freq and attention scaling of every ``rope_type`` from the reference's ROPE_INIT_FUNCTIONS
+    (modeling/patch_of_llama3_1.py:336-343), and the dynamic-NTK frequencies its PatchLlamaRotaryEmbedding
+    (:545-629) holds after each forward of a conversation that grows past, and falls back under, the trained length."""
+    import modeling.patch_of_llama3_1 as ref_rope
+    from inputs import ROPE_CASES, ROPE_DYNAMIC_SEQ
+    arrays, meta = {}, []
+    for case in ROPE_CASES:
+        cfg = types.SimpleNamespace(**{k: v for k, v in case.items() if k != "name"})
+        cfg.hidden_size, cfg.num_attention_heads = case["head_dim"] * 4, 4
+        kind = "default" if case["rope_scaling"] is None else case["rope_scaling"].get("rope_type", case["rope_scaling"].get("type"))
+        inv, att = ref_rope.ROPE_INIT_FUNCTIONS[kind](cfg, "cpu")
+        arrays[f"{case['name']}/inv_freq"] = inv.numpy().astype(np.float32)
+        meta.append(dict(name=case["name"], attention_scaling=float(att)))
+    d = ROPE_DYNAMIC_SEQ
+    cfg = types.SimpleNamespace(**{k: v for k, v in d.items() if k != "forwards"})
+    cfg.hidden_size, cfg.num_attention_heads = d["head_dim"] * 4, 4
+    emb = ref_rope.PatchLlamaRotaryEmbedding(config=cfg)
+    for i, (first, n) in enumerate(d["forwards"]):
+        pos = torch.arange(first, first + n)[None, :]
+        cos, sin = emb(torch.zeros(1, 1, dtype=torch.float32), pos)
+        arrays[f"dynamic_seq/{i}/inv_freq"] = emb.inv_freq.numpy().astype(np.float32).copy()
+        arrays[f"dynamic_seq/{i}/cos_last"] = cos[0, -1].numpy().copy()
+    np.savez_compressed(HERE / "rope.npz", **arrays)
+    (HERE / "rope.json").write_text(json.dumps(dict(cases=meta)))
+    print("rope arrays:", len(arrays))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the OmniKV checkout")
@@ -246,8 +443,11 @@ def main():
     make_selector_fixture(ref_omnikv)
     make_plan_fixture(ref_cache)
     make_cache_flow_fixture(ref_cache)
+    make_cache_flow_d128_fixture(ref_cache)
     make_operator_fixture(ref_omnikv, ref_cache)
     make_lazy_rule_fixture(ref_cache)
+    make_layer_hook_fixture(ref_omnikv, ref_cache)
+    make_rope_fixture(os.path.abspath(args.reference))
 
 
 if __name__ == "__main__":

@@ -166,3 +166,31 @@ def test_index_tracer_roundtrip(tmp_path):
     assert idx[0][0]["idx"].tolist() == [3] and prefill_res[0]["idx"].tolist() == [[4]]
     prev = tt.set_tracer(tr)
     assert tt.idx_tracer is tr and tt.set_tracer(prev) is tr and tt.idx_tracer is prev
+
+
+def test_rope_parameters_match_reference():
+    """inv_freq and attention scaling of every rope_type against what the reference's ROPE_INIT_FUNCTIONS returned
+    (fixture), and dynamic-NTK scaling followed through a conversation that outgrows the trained length, falls
+    back under it and grows again, against the reference's rotary module after each forward."""
+    import numpy as np
+    import torch
+
+    import inputs as gi
+    from omnikv_b200.modeling import LlamaCompressorConfig
+    from omnikv_b200.modeling.omnikv import OmniKVRotaryEmbedding, rope_parameters
+    gold = np.load(G / "rope.npz")
+    meta = {m["name"]: m for m in json.loads((G / "rope.json").read_text())["cases"]}
+    for case in gi.ROPE_CASES:
+        cfg = LlamaCompressorConfig(**{k: v for k, v in case.items() if k != "name"})
+        inv, att = rope_parameters(cfg)
+        np.testing.assert_allclose(inv.numpy(), gold[f"{case['name']}/inv_freq"], rtol=2e-6, atol=0, err_msg=case["name"])
+        assert att == pytest.approx(meta[case["name"]]["attention_scaling"], rel=1e-12), case["name"]
+    d = gi.ROPE_DYNAMIC_SEQ
+    cfg = LlamaCompressorConfig(**{k: v for k, v in d.items() if k != "forwards"})
+    emb = OmniKVRotaryEmbedding(cfg)
+    for i, (first, n) in enumerate(d["forwards"]):
+        pos = torch.arange(first, first + n)[None, :]
+        emb.advance(pos, prefill=n > 1)
+        np.testing.assert_allclose(emb.inv_freq.numpy(), gold[f"dynamic_seq/{i}/inv_freq"], rtol=2e-6, atol=0, err_msg=str(i))
+        cos, _ = emb(torch.zeros(1, dtype=torch.float32), pos)
+        np.testing.assert_allclose(cos[0, -1].numpy(), gold[f"dynamic_seq/{i}/cos_last"], atol=2e-4, rtol=0)

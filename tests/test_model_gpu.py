@@ -14,6 +14,7 @@ import torch
 
 import inputs as gi
 from oracle.llama_oracle import OracleLM
+from parity import band_check
 
 pytestmark = pytest.mark.gpu
 G = Path(__file__).resolve().parent / "golden"
@@ -72,14 +73,14 @@ def test_fp32_logits_and_selection_match_oracle(selector, nsel, cache_cls, offlo
     got, want, cache = run_both(lm, oracle, ids, steps=20)
     for i, (a, b) in enumerate(zip(got, want)):
         assert (a - b).abs().max().item() <= 1e-4, (i, (a - b).abs().max().item())
-    # the index list the last filter layer produced at the last step
+    # the index list the last filter layer produced at the last step: the oracle's, up to positions whose score
+    # lies within 1e-4 of the k-th score
     sel_layer = 3
     idx, count = cache._idx[sel_layer]
     mine = idx[0, : count.item()].cpu().long()
     ref = oracle.selected[(19, sel_layer)][0]
-    assert mine.shape == ref.shape
-    if not torch.equal(mine, ref):
-        assert len(set(mine.tolist()) ^ set(ref.tolist())) <= 2  # threshold-band swaps only
+    scores, k_sel = oracle.scores[(19, sel_layer)]
+    band_check(scores[0], k_sel, mine, ref, 1e-4)
 
 
 @pytest.mark.parametrize("thr", [0.0, 0.5, 0.8, 1.0])
@@ -266,8 +267,10 @@ def test_selector_function_matches_reference_fixture():
         idx = select_tokens_by_attn_universal(Attn, window, pos, cache, k, L, 0, sel)
         assert idx.dtype == torch.int64 and idx.shape == (1, k)
         want = gold[key].astype(np.int64)
-        diff = set(idx[0].tolist()) ^ set(want[0].tolist())
-        assert len(diff) <= 2, (sel, len(diff))
+        import oracle as orc
+        qt, kt = torch.from_numpy(x["q"]), torch.from_numpy(x["k"])
+        s_ref = (orc.score_last(qt[:, :, -1], kt, L) if sel == "last" else orc.score_window(qt, kt, L, sel))[0]
+        band_check(s_ref, k, idx[0].tolist(), want[0].tolist(), 1e-4 if sel == "last" else 1e-6, sel)
 
 
 def test_chat_api_factory_with_a_checkpoint_on_disk(tmp_path):
@@ -333,9 +336,244 @@ def test_selected_index_tracer_records_what_was_selected(tmp_path):
         for s, r in enumerate(recs):
             ref = oracle.selected[(s, layer)]
             assert r["prefill_len"] == 200 and r["idx"].dtype == torch.int64 and r["idx"].shape == ref.shape
-            assert len(set(r["idx"][0].tolist()) ^ set(ref[0].tolist())) <= 2
+            scores, k_sel = oracle.scores[(s, layer)]
+            band_check(scores[0], k_sel, r["idx"][0].tolist(), ref[0].tolist(), 1e-4, (s, layer))
             assert r["value"].shape == r["idx"].shape and r["value"].dtype == torch.float32
             # recorded scores are those of the selected positions: all >= every unselected score is implied by
             # top-k; here: finite and sorted positions
             assert torch.isfinite(r["value"]).all()
             assert torch.equal(r["idx"][0], torch.sort(r["idx"][0]).values)
+
+
+# ------------------------------------------------------------------------------------------
+# the filter-layer hook against the reference's own OmniKVMulLayer.forward (fixture)
+# ------------------------------------------------------------------------------------------
+def _hook_model(selector, dtype=torch.float32):
+    from test_oracle_golden import hook_model_inputs
+    from omnikv_b200.modeling import LlamaCompressorConfig, OmniKVMulLM
+    c, cfgd, weights, x = hook_model_inputs()
+    cfg = LlamaCompressorConfig(**{k: cfgd[k] for k in ("num_hidden_layers", "hidden_size", "intermediate_size",
+                                                        "num_attention_heads", "num_key_value_heads", "head_dim",
+                                                        "rope_theta", "rms_norm_eps")}, vocab_size=64)
+    cfg.set_config_of_compressor(model_cls="multi", cache_cls="multi", do_select_layers=cfgd["do_select_layers"],
+                                 num_wait_load_layers=cfgd["num_wait_load_layers"], real_offload=False, dense_more=True,
+                                 num_of_selected_tokens=cfgd["num_of_selected_tokens"], selector_cls=selector,
+                                 window_size=cfgd["window_size"])
+    lm = OmniKVMulLM.from_config(cfg, dtype=dtype, device="cuda", seed=None)
+    sd = dict(weights)
+    sd["model.embed_tokens.weight"] = torch.zeros(64, c["hidden"])
+    sd["model.norm.weight"] = torch.ones(c["hidden"])
+    sd["lm_head.weight"] = torch.zeros(64, c["hidden"])
+    lm.load_hf_state_dict({k: v.cuda() for k, v in sd.items()})
+    return c, lm, x
+
+
+@pytest.mark.parametrize("selector", ["last", "uniform", "exp"])
+def test_layer_hook_matches_reference_fixture(selector):
+    """The decoder stack of this package (CUDA kernels, device-side window bookkeeping) against the fixture the
+    reference's own ``OmniKVMulLayer.forward`` produced on the same weights and hidden states: per decode
+    forward the index list of both filter layers (window positions appended as the reference does) and the
+    stack's output."""
+    import oracle as orc
+    from test_oracle_golden import hook_model_inputs
+    c, lm, x = _hook_model(selector)
+    gold = np.load(G / "layer_hook.npz")
+    # reference scores behind every selection, for the tolerance band at the k-th score
+    _, cfgd, weights, _ = hook_model_inputs()
+    ref = OracleLM(dict(cfgd, selector_cls=selector), weights)
+    _, ocache = ref.forward_hidden(torch.from_numpy(x["x_pre"]))
+    cache = lm.new_cache()
+    cache.stage = "prefill"
+    out = lm.model(inputs_embeds=torch.from_numpy(x["x_pre"]).cuda(), past_key_values=cache, apply_final_norm=False)
+    assert np.abs(out.last_hidden_state[:, -1].cpu().numpy() - gold[f"{selector}/h/prefill"]).max() <= 1e-4
+    for s in range(c["steps"]):
+        cache.stage = "decoding"
+        out = lm.model(inputs_embeds=torch.from_numpy(x["x_dec"][s]).cuda(), past_key_values=cache, apply_final_norm=False)
+        ref.forward_hidden(torch.from_numpy(x["x_dec"][s]), ocache, fwd_no=s)
+        for f in c["sel"]:
+            idx, count = cache._idx[f]
+            mine = idx[0, : count.item()].cpu().tolist()
+            want = gold[f"{selector}/idx/{s}/{f}"][0].tolist()
+            scores, k_sel = ref.scores[(s, f)]
+            band_check(scores[0], k_sel, mine, want, 1e-4 if selector == "last" else 1e-6, (selector, s, f))
+        err = np.abs(out.last_hidden_state[:, -1].cpu().numpy() - gold[f"{selector}/h/{s}"]).max()
+        assert err <= 1e-4, (s, err)
+
+
+# ------------------------------------------------------------------------------------------
+# the caches' reference-signature API on CUDA tensors (fixture from the reference's classes)
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("cls_name", ["OmniKVMultiStageCache", "WOPackCache"])
+@pytest.mark.parametrize("offload", [False, True])
+def test_cache_reference_api_matches_fixture(cls_name, offload):
+    """``from_dynamic_cache`` -> prefill ``update`` of every layer -> per decode forward ``set_idx_on_gpu`` on the
+    filter layers and ``update`` on every layer, with the reference's signatures on CUDA tensors: what ``update``
+    returns (the whole cache of a dense layer, ``cat([selected rows, tail])`` of a sparse one) must be the
+    reference's tensors element for element (signatures of the reference's returns are the fixture)."""
+    from omnikv_b200.modeling import spec_cache
+    c = json.loads((G / "cache_flow_d128.json").read_text())
+    x = gi.cache_flow_inputs(gi.CACHE_FLOW_D128)
+    t = lambda a: torch.from_numpy(a).cuda()  # noqa: E731
+    cls = getattr(spec_cache, cls_name)
+    dyn = SimpleNamespace(key_cache=[], value_cache=[], _seen_tokens=0)
+    cache = cls.from_dynamic_cache(dyn, c["full"], c["n_layers"], c["wait"], offload)
+    cache.stage = "prefill"
+    for i in range(c["n_layers"]):
+        kk, vv = cache.update(t(x["k_pre"][i]), t(x["v_pre"][i]), i)
+        assert torch.equal(kk.cpu(), torch.from_numpy(x["k_pre"][i]))  # prefill attention sees the fresh rows
+    for s in range(c["steps"]):
+        cache.stage = "decoding"
+        for i in range(c["n_layers"]):
+            if i in c["sel"]:
+                cache.set_idx_on_gpu(t(x["idx"][(s, i)]), i)
+            kk, vv = cache.update(t(x["k_new"][s][i]), t(x["v_new"][s][i]), i)
+            want_k, want_v = c["returns"][f"{cls_name}/{s}/{i}"]
+            assert gi.signature(kk.cpu().numpy()) == want_k, (s, i)
+            assert gi.signature(vv.cpu().numpy()) == want_v, (s, i)
+    assert cache._seen_tokens == c["returns"][f"{cls_name}/seen"]
+
+
+# ------------------------------------------------------------------------------------------
+# batched decode with a window selector: ragged batch, every sequence against its own oracle run
+# ------------------------------------------------------------------------------------------
+def test_batched_window_selector_matches_per_sequence_oracle():
+    """Batch 4 with ragged contexts, selector ``exp``, window 16, integer k, 20 decode steps in fp32 (the shape of
+    the batched benchmark configuration at reduced size).  The reference flattens the index list over the batch
+    (modeling/spec_cache.py:292), so its semantics exist at batch 1 only; the oracle is its batch-1 flow
+    (modeling/omnikv.py:168-210) applied to every sequence by itself, starting from the same cache rows and the
+    same observation window."""
+    dt = torch.float32
+    cfg = small_config(selector_cls="exp", num_of_selected_tokens=48, window_size=16)
+    lm, oracle = build(cfg, dt)
+    lens, B, steps = [700, 333, 512, 97], 4, 20
+    cache = lm.new_cache().init_synthetic(B, 1, 128, lens, dt, "cuda", seed=5, reserve=64)
+    lm.prepare_synthetic_decode(B, seed=2)
+    refs = []
+    for b, n in enumerate(lens):  # a batch-1 oracle per sequence, its cache and window taken from the batched state
+        r = OracleLM(cfg.to_dict(), lm.hf_state_dict())
+        oc = r.new_cache()
+        oc.key_cache = [cache._k[l][b:b + 1, :, :n].float().cpu().contiguous() for l in range(cfg.num_hidden_layers)]
+        oc.value_cache = [cache._v[l][b:b + 1, :, :n].float().cpu().contiguous() for l in range(cfg.num_hidden_layers)]
+        oc._seen_tokens, oc.stage = n, "decoding"
+        for i, layer in enumerate(lm.model.layers):
+            r.state[i]["prefill_len"] = n
+            if layer.is_filter:
+                r.state[i]["window"] = layer.hidden_state_window[b:b + 1].float().cpu().clone()
+                r.state[i]["decode_step"] = 1
+        refs.append((r, oc))
+    g = torch.Generator().manual_seed(9)
+    toks = torch.randint(0, 1000, (steps, B, 1), generator=g)
+    out = SimpleNamespace(past_key_values=cache)
+    cache.stage = "decoding"
+    for s in range(steps):
+        out = lm(input_ids=toks[s].cuda(), past_key_values=out.past_key_values)
+        for b in range(B):
+            r, oc = refs[b]
+            want, _ = r.forward(toks[s][b:b + 1], oc, fwd_no=s)
+            err = (out.logits[b:b + 1].cpu() - want).abs().max().item()
+            assert err <= 1e-4, (s, b, err)
+            for f in (1, 3):
+                idx, count = cache._idx[f]
+                mine = idx[b, : count[b].item()].cpu().tolist()
+                scores, k_sel = r.scores[(s, f)]
+                band_check(scores[0], k_sel, mine, r.selected[(s, f)][0].tolist(), 1e-6, (s, b, f))
+
+
+# ------------------------------------------------------------------------------------------
+# offload at a longer context, both cache classes
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("cache_cls", ["multi", "without_pack"])
+def test_offload_long_context_matches_oracle(cache_cls):
+    """``real_offload`` at a 20 000-token prompt (the offload benchmark configuration at reduced size): sparse layers'
+    prompt KV in pinned host memory, selected rows gathered over the host link every step.  fp32 against the
+    oracle (run on the GPU for the 20 000 x 20 000 prefill scores; it is the same fp32 torch code)."""
+    cfg = small_config(selector_cls="last", num_of_selected_tokens=0.067, cache_cls=cache_cls, real_offload=True)
+    lm, _ = build(cfg, torch.float32)
+    oracle = OracleLM(cfg.to_dict(), lm.hf_state_dict(), device="cuda")
+    g = torch.Generator().manual_seed(12)
+    ids = torch.randint(0, 1000, (1, 20000), generator=g)
+    out = lm(input_ids=ids.cuda())
+    cache = out.past_key_values
+    lo, ocache = oracle.forward(ids)
+    assert (out.logits - lo).abs().max().item() <= 1e-4
+    for s in range(8):
+        tok = lo[:, -1].argmax(-1, keepdim=True)
+        out = lm(input_ids=tok.cuda(), past_key_values=cache)
+        lo, ocache = oracle.forward(tok, ocache, fwd_no=s)
+        err = (out.logits - lo).abs().max().item()
+        assert err <= 1e-4, (s, err)
+        for f in (1, 3):
+            idx, count = cache._idx[f]
+            scores, k_sel = oracle.scores[(s, f)]
+            band_check(scores[0], k_sel, idx[0, : count.item()].cpu().tolist(), oracle.selected[(s, f)][0].tolist(), 1e-4, (s, f))
+    assert all(cache.key_cache[i].device.type == "cpu" for i, st in cache.layer_state.items() if st[0])
+
+
+# ------------------------------------------------------------------------------------------
+# workspace growth must not disturb a captured step
+# ------------------------------------------------------------------------------------------
+def test_captured_step_survives_workspace_growth():
+    """A decode step captured at batch 1 bakes the attention workspace's address into the graph.  A later, larger
+    call in the same process makes the cached workspace grow; the outgrown buffer must stay alive (and its arrival
+    counters zero), so replays after the growth still give the eager tokens."""
+    from omnikv_b200 import ops
+    from omnikv_b200.modeling.omnikv import DecodeRunner
+    cfg = small_config(selector_cls="last")
+    lm, _ = build(cfg, torch.bfloat16)
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, 1000, (1, 400), generator=g).cuda()
+    eager = lm.generate_greedy(ids, 20, use_cuda_graph=False)
+    runner = DecodeRunner(lm, ids, max_new_tokens=20, use_cuda_graph=True, warmup_steps=2)
+    runner.run(6)
+    before = ops.workspace(torch.device("cuda", 0), 1, "attn")
+    # a much larger attention call: batch 16, many splits -> the cached workspace is replaced by a larger one
+    B, H, KVH, d, L = 16, 32, 8, 128, 2048
+    q = torch.randn(B, H, d, device="cuda").to(torch.bfloat16)
+    kv = torch.randn(B, KVH, L, d, device="cuda").to(torch.bfloat16)
+    ops.decode_attn(q, kv, kv, torch.full((B,), L, dtype=torch.int32, device="cuda"), n_splits=16)
+    after = ops.workspace(torch.device("cuda", 0), 1, "attn")
+    assert after.data_ptr() != before.data_ptr() and after.numel() > before.numel()
+    junk = [torch.full((before.numel(),), 7, dtype=torch.uint8, device="cuda") for _ in range(4)]  # would land on freed memory
+    runner.run(20)
+    torch.cuda.synchronize()
+    assert torch.equal(runner.tokens(check=True), eager)
+    del junk
+
+
+def test_bounded_peer_wait_reports_and_returns():
+    """A consumer of the fused projection + all-reduce exchange whose peer never arrives: the kernel gives up after
+    its time limit, writes status 4 and returns; the context stays usable.  (World of 2 described over two LOCAL
+    buffers that nothing writes flags into -- no second GPU, no fault.)"""
+    import time
+    from omnikv_b200 import abi, ops
+    hidden, inter = 512, 1024
+    nbytes = abi.lib().omnikv_tp_exchange_bytes(hidden)
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(2)]
+    x = abi.TpExchange()
+    x.world, x.rank, x.seq, x.hidden = 2, 0, 0, hidden
+    x.peer_base[0], x.peer_base[1] = bufs[0].data_ptr(), bufs[1].data_ptr()
+    done = torch.zeros(2, dtype=torch.int32, device="cuda")
+    epoch = torch.ones(1, dtype=torch.int32, device="cuda")
+    x.done_counter, x.epoch = done.data_ptr(), epoch.data_ptr()
+    h = torch.randn(hidden, device="cuda").to(torch.bfloat16)
+    h_out = torch.zeros_like(h)
+    w = torch.randn(2 * inter, hidden, device="cuda").to(torch.bfloat16)
+    act = torch.zeros(inter, dtype=torch.bfloat16, device="cuda")
+    nw = torch.ones(hidden, dtype=torch.bfloat16, device="cuda")
+    ops.status_word("cuda").zero_()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    ops.decode_gate_up(h, nw, 1e-5, w, act, tp_in=x, h_out=h_out)
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    assert 1.0 <= waited <= 20.0, waited
+    with pytest.raises(abi.OmniKVError, match="status 4"):
+        ops.check_status("cuda")
+    # the context is intact: the same kernel without an exchange runs and the status stays clear
+    ops.decode_gate_up(h, nw, 1e-5, w, act)
+    torch.cuda.synchronize()
+    ops.check_status("cuda")
+    want = torch.nn.functional.rms_norm(h.float(), (hidden,), nw.float(), 1e-5)
+    gu = w.float() @ want
+    ref = torch.nn.functional.silu(gu[:inter]) * gu[inter:]
+    assert (act.float() - ref).abs().max().item() <= 0.05 * ref.abs().max().item()

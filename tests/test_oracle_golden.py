@@ -142,3 +142,60 @@ def test_lazy_rule_matches_reference(thr):
         assert abs(score - gold["scores"][s]) < 1e-9
         # fixture rows: feature 0 of token t is 4 t, so the sum identifies the list in use
         assert float(rule.live[1].sum()) * 4.0 == gold["live_sum"][s]
+
+
+def hook_model_inputs():
+    """(config dict, HF-named fp32 weights, x_pre, x_dec list) of the layer-hook fixture."""
+    c = json.loads((G / "layer_hook.json").read_text())
+    x = gi.layer_hook_inputs()
+    flat = [a for w in x["layers"] for a in w.values()] + [x["x_pre"]] + x["x_dec"]
+    assert gi.checksum(flat) == pytest.approx(c["input_checksum"], rel=1e-12)
+    weights = {f"model.layers.{i}.{k}": torch.from_numpy(v) for i, w in enumerate(x["layers"]) for k, v in w.items()}
+    cfg = dict(num_hidden_layers=c["n_layers"], hidden_size=c["hidden"], intermediate_size=c["inter"],
+               num_attention_heads=c["H"], num_key_value_heads=c["KVH"], head_dim=c["d"], rope_theta=c["theta"],
+               rms_norm_eps=c["eps"], do_select_layers=",".join(map(str, c["sel"])), num_wait_load_layers=c["wait"],
+               num_of_selected_tokens=c["frac"], window_size=c["window"], cache_cls="multi", real_offload=False,
+               dense_more=True)
+    return c, cfg, weights, x
+
+
+@pytest.mark.parametrize("selector", ["last", "uniform", "exp"])
+def test_layer_hook_matches_reference(selector):
+    """The restated filter-layer hook (oracle.llama_oracle.OracleLM._layer) against the reference's own
+    OmniKVMulLayer.forward: same index lists at every decode forward of both filter layers, same hidden states."""
+    from oracle.llama_oracle import OracleLM
+    c, cfg, weights, x = hook_model_inputs()
+    gold = np.load(G / "layer_hook.npz")
+    lm = OracleLM(dict(cfg, selector_cls=selector), weights)
+    h, cache = lm.forward_hidden(torch.from_numpy(x["x_pre"]))
+    np.testing.assert_allclose(h[:, -1].numpy(), gold[f"{selector}/h/prefill"], atol=2e-5, rtol=0)
+    for s in range(c["steps"]):
+        h, cache = lm.forward_hidden(torch.from_numpy(x["x_dec"][s]), cache, fwd_no=s)
+        for f in c["sel"]:
+            want = gold[f"{selector}/idx/{s}/{f}"]
+            got = lm.selected[(s, f)].numpy()
+            assert got.shape == want.shape, (s, f)
+            assert np.array_equal(got, want), (selector, s, f, len(set(got[0].tolist()) ^ set(want[0].tolist())))
+        np.testing.assert_allclose(h[:, -1].numpy(), gold[f"{selector}/h/{s}"], atol=5e-5, rtol=0)
+
+
+@pytest.mark.parametrize("cls_name", ["OmniKVMultiStageCache", "WOPackCache"])
+def test_cache_flow_d128_matches_reference(cls_name):
+    """The flow at head size 128 (the fixture the CUDA caches are checked against), by signature."""
+    c = json.loads((G / "cache_flow_d128.json").read_text())
+    x = gi.cache_flow_inputs(gi.CACHE_FLOW_D128)
+    flat = x["k_pre"] + x["v_pre"] + [a for r in x["k_new"] for a in r] + [a for r in x["v_new"] for a in r]
+    assert gi.checksum(flat) == pytest.approx(c["input_checksum"], rel=1e-12)
+    t = torch.from_numpy
+    cls = oracle.OracleMultiStageCache if cls_name == "OmniKVMultiStageCache" else oracle.OracleWOPackCache
+    cache = cls(c["full"], c["n_layers"], c["wait"], False)
+    for i in range(c["n_layers"]):
+        cache.update(t(x["k_pre"][i]), t(x["v_pre"][i]), i)
+    for s in range(c["steps"]):
+        cache.stage = "decoding"
+        for i in range(c["n_layers"]):
+            if i in c["sel"]:
+                cache.set_idx_on_gpu(t(x["idx"][(s, i)]), i)
+            kk, vv = cache.update(t(x["k_new"][s][i]), t(x["v_new"][s][i]), i)
+            assert [gi.signature(kk.numpy()), gi.signature(vv.numpy())] == c["returns"][f"{cls_name}/{s}/{i}"]
+    assert cache._seen_tokens == c["returns"][f"{cls_name}/seen"]

@@ -144,18 +144,21 @@ def _worker_reduce(rank, world, port, ret):
                 want = torch.zeros(n, dtype=torch.float32, device=dev)
                 for p in parts:  # rank order, fp32, rounded once: what the kernel computes
                     want += p.float()
-                seq0 = tp._reduce_seq
+                seq0 = tp.peer_reduce_calls
                 tp.all_reduce_sum(x)
-                used += tp._reduce_seq - seq0
+                used += tp.peer_reduce_calls - seq0
                 exact = exact and torch.equal(x, want.to(dtype))
         # a tensor above the buffer's capacity goes through NCCL (same numbers up to summation order)
         tp.begin_step()
         big = torch.ones(1 << 20, device=dev)
-        seq0 = tp._reduce_seq
+        seq0 = tp.peer_reduce_calls
         tp.all_reduce_sum(big)
-        fell_back = tp._reduce_seq == seq0 and bool((big == world).all())
-        # a captured step replays: begin_step bumps the device-side step counter inside the graph
-        xs = [torch.full((4096,), float(rank + 1), device=dev, dtype=torch.bfloat16) for _ in range(3)]
+        fell_back = tp.peer_reduce_calls == seq0 and bool((big == world).all())
+        # A captured step with an ODD number of calls, replayed back to back with data that differs per replay and
+        # per rank: the two slots must keep alternating across the replays (the slot comes from a device-side call
+        # counter), or the first call of a replay would overwrite what a peer still reads from the last call of
+        # the replay before it.
+        xs = [torch.zeros(4096 * (i + 1), device=dev, dtype=torch.bfloat16) for i in range(3)]
         gr = torch.cuda.CUDAGraph()
         tp.begin_step(); [tp.all_reduce_sum(t.clone()) for t in xs]  # warm-up outside the capture
         torch.cuda.synchronize()
@@ -166,10 +169,28 @@ def _worker_reduce(rank, world, port, ret):
                 o.copy_(t)
                 tp.all_reduce_sum(o)
         graph_ok = True
-        for _ in range(4):
+        n_rep = 6
+        feeds = [[torch.randn(t.shape, generator=g, device=dev).to(t.dtype) for t in xs] for _ in range(n_rep)]
+        wants = []
+        for feed in feeds:  # expected sums first (NCCL), so that the replays below run back to back
+            row = []
+            for x in feed:
+                parts = [torch.empty_like(x) for _ in range(world)]
+                dist.all_gather(parts, x)
+                acc = torch.zeros(x.shape, dtype=torch.float32, device=dev)
+                for p in parts:
+                    acc += p.float()
+                row.append(acc.to(x.dtype))
+            wants.append(row)
+        got = []
+        for feed in feeds:
+            for t, x in zip(xs, feed):
+                t.copy_(x)
             gr.replay()
-            torch.cuda.synchronize()
-            graph_ok = graph_ok and all(bool((o.float() == sum(range(1, world + 1))).all()) for o in outs)
+            got.append([o.clone() for o in outs])
+        torch.cuda.synchronize()
+        for grow, wrow in zip(got, wants):
+            graph_ok = graph_ok and all(torch.equal(a, b) for a, b in zip(grow, wrow))
         ops.check_status(dev)
 
         # batched decode of a sharded model with the peer all-reduce against the full model on one GPU
@@ -190,18 +211,19 @@ def _worker_reduce(rank, world, port, ret):
         err = (o1.logits - o2.logits).abs().max().item()
         for t in toks:
             o1 = full(input_ids=t, past_key_values=o1.past_key_values)
-            seq0 = tp._reduce_seq
+            seq0 = tp.peer_reduce_calls
             o2 = shard(input_ids=t, past_key_values=o2.past_key_values)
             err = max(err, (o1.logits - o2.logits).abs().max().item())
         ops.check_status(dev)
-        ret[rank] = (bool(has), bool(exact), used, bool(fell_back), bool(graph_ok), err, tp._reduce_seq)
+        ret[rank] = (bool(has), bool(exact), used, bool(fell_back), bool(graph_ok), err, tp.peer_reduce_calls - seq0)
     finally:
         torch.distributed.destroy_process_group()
 
 
 def test_tp2_peer_allreduce():
     """omnikv_tp_allreduce_sum on 2 GPUs: bit-exact rank-ordered fp32 sums for all dtypes and sizes over several
-    steps (slot reuse, step counter), NCCL fallback above the capacity, CUDA-graph replay, and a batch-3 decode
+    steps (slot reuse), NCCL fallback above the capacity, CUDA-graph replays of an odd number of calls on changing
+    data, and a batch-3 decode
     of a sharded model equal to the single-GPU model."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")

@@ -58,3 +58,29 @@ def test_no_alloc_refuses_what_does_not_fit():
     p.dtype, p.B, p.H, p.KVH, p.head_dim, p.n_splits = abi.BF16, B, H, KVH, d, 64
     p.q, p.out, p.kA, p.vA, p.lenA = q.data_ptr(), out.data_ptr(), kc.data_ptr(), kc.data_ptr(), _i32([64] * B).data_ptr()
     assert abi.lib().omnikv_decode_attn_no_alloc(ctypes.byref(p), None) == -3
+
+
+def test_no_alloc_first_call_then_graph_replay():
+    """The documented order of use: the first call on a device (which looks up the built-in array's address) is made
+    outside stream capture; after that the entry point is captured and replayed like any other launch, and the
+    replays -- over changing inputs -- equal the regular entry point."""
+    from omnikv_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(5)
+    B, H, KVH, d, L, splits = 1, 32, 8, 128, 4096, 8
+    kc = torch.randn(B, KVH, L, d, generator=g, device="cuda").to(torch.bfloat16)
+    vc = torch.randn(B, KVH, L, d, generator=g, device="cuda").to(torch.bfloat16)
+    q = torch.randn(B, H, d, generator=g, device="cuda").to(torch.bfloat16)
+    n = _i32([L])
+    out = torch.empty_like(q)
+    ops.decode_attn_no_alloc(q, kc, vc, n, out, n_splits=splits)  # first call: outside capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ops.decode_attn_no_alloc(q, kc, vc, n, out, n_splits=splits)
+    for rep in range(3):
+        q.copy_(torch.randn(B, H, d, generator=g, device="cuda").to(torch.bfloat16))
+        n.fill_(L - 100 * rep)
+        graph.replay()
+        want = ops.decode_attn(q, kc, vc, n, n_splits=splits)
+        torch.cuda.synchronize()
+        assert torch.equal(out, want), rep
