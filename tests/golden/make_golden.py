@@ -7,19 +7,11 @@ Run where the reference checkout is available (it is not needed to run the tests
 It imports ``modeling.omnikv.select_tokens_by_attn_universal`` and
 ``modeling.spec_cache.{OmniKVMultiStageCache, WOPackCache}`` unchanged, feeds them
 seeded inputs, and stores their outputs as small ``.npz`` / ``.json`` files.
-Nothing of the reference is copied; the import needs a few shims because the
-reference targets transformers 4.41.2:
-
-* its logger wants a git work tree with a ``debug_logs/`` folder as the current
-  directory (tiny_tools/get_code_id.py:5-28, tiny_tools/log.py:46-49) -> a scratch
-  repository under the temp dir is used as cwd while importing;
-* ``from transformers.models.llama.modeling_llama import *`` is expected to leak
-  ``torch, math, nn, F, Cache, DynamicCache, ...`` -> those names are set on that
-  module and its ``__all__`` widened before the import;
-* the 5.x ``DynamicCache`` has no ``key_cache`` list -> caches are built through
-  ``from_dynamic_cache`` on a namespace carrying the three attributes it copies;
-* ``Tensor.cuda`` is made the identity on this GPU-less host
-  (modeling/spec_cache.py:298-303 calls it on the gathered rows).
+Nothing of the reference is copied; the import goes through ``oracle/ref_shim.py`` (the
+reference targets transformers 4.41.2: the shims it needs under a newer one are listed
+there).  One more adaptation lives here: the 5.x ``DynamicCache`` has no ``key_cache`` list,
+so caches are built through ``from_dynamic_cache`` on a namespace carrying the three
+attributes it copies.
 
 Only the reference's OUTPUTS are stored; the inputs are rebuilt from the seeded
 functions of ``inputs.py`` (a checksum of them is stored beside each fixture).
@@ -47,37 +39,8 @@ from inputs import (CACHE_FLOW, OPERATOR, cache_flow_inputs, checksum, operator_
                     selector_case_list, selector_inputs)
 
 
-def import_reference(ref_root: str):
-    scratch = tempfile.mkdtemp(prefix="omnikv_ref_cwd_")
-    os.makedirs(os.path.join(scratch, "debug_logs"))
-    env = dict(os.environ, GIT_AUTHOR_NAME="g", GIT_AUTHOR_EMAIL="g@g", GIT_COMMITTER_NAME="g", GIT_COMMITTER_EMAIL="g@g")
-    subprocess.check_call(["git", "init", "-q"], cwd=scratch)
-    subprocess.check_call(["git", "commit", "-q", "--allow-empty", "-m", "scratch"], cwd=scratch, env=env)
-    os.chdir(scratch)
-    sys.path.insert(0, ref_root)
-
-    import transformers  # noqa: F401
-    import transformers.models.llama.modeling_llama as ml
-    from typing import List, Optional, Tuple, Union
-    from transformers.cache_utils import Cache, DynamicCache
-    from transformers.modeling_outputs import CausalLMOutputWithPast
-    from transformers.models.llama.configuration_llama import LlamaConfig
-
-    leak = dict(
-        LlamaConfig=LlamaConfig, math=math, F=torch.nn.functional, nn=torch.nn, torch=torch, Cache=Cache,
-        DynamicCache=DynamicCache, CausalLMOutputWithPast=CausalLMOutputWithPast, Optional=Optional,
-        Tuple=Tuple, Union=Union, List=List, CrossEntropyLoss=torch.nn.CrossEntropyLoss,
-        LLAMA_ATTENTION_CLASSES={},
-    )
-    for k, v in leak.items():
-        setattr(ml, k, v)
-    ml.__all__ = [n for n in dir(ml) if not n.startswith("_")]
-    torch.Tensor.cuda = lambda self, *a, **k: self  # GPU-less host
-
-    import modeling.omnikv as ref_omnikv
-    import modeling.spec_cache as ref_cache
-
-    return ref_omnikv, ref_cache
+sys.path.insert(0, str(HERE.parent.parent))
+from oracle.ref_shim import import_reference  # noqa: E402  (the import shims live there)
 
 
 class _Cfg:
