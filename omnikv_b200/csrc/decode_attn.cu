@@ -870,10 +870,12 @@ int no_alloc_scratch(void** out) {
 
 extern "C" int omnikv_decode_attn_no_alloc(const omnikv_attn_params* p, void* stream) {
   using namespace omnikv;
-  // every argument check comes first: a refused call puts nothing on the stream and leaves the shared array alone
-  if (const int bad = validate_attn_params(p)) return bad;
+  // every check comes first: a refused call puts nothing on the stream and leaves the shared array alone
+  if (!p) return OMNIKV_E_BADARG;
+  if (p->B <= 0 || p->H <= 0 || p->n_splits <= 0) return OMNIKV_E_BADARG;
   if (p->out && omnikv_decode_attn_workspace_bytes(p->B, p->H, p->n_splits) > (size_t)OMNIKV_NO_ALLOC_SCRATCH_BYTES)
     return OMNIKV_E_WORKSPACE;  // B * H * n_splits is more than the built-in scratch can hold
+  if (const int bad = validate_attn_params(p)) return bad;
   void* scratch = nullptr;
   const int rc = no_alloc_scratch(&scratch);
   if (rc != OMNIKV_OK) return rc;

@@ -104,17 +104,32 @@ class OmniKVMultiStageCache:
     @staticmethod
     def from_dynamic_cache(cache, full_attn_layers: List, num_hidden_layers, num_wait_load_layers=2,
                            real_offload=True):
-        """modeling/spec_cache.py:371-385.  ``cache`` may be None or any object with (empty)
-        ``key_cache`` / ``value_cache`` lists: the decode path always starts from a fresh prefill."""
+        """modeling/spec_cache.py:371-385.  ``cache`` may be None, an object with empty ``key_cache`` /
+        ``value_cache`` lists (the usual case: the prefill then runs through this cache), or one that already holds
+        a prompt -- CUDA tensors ``[B, KVH, P, d]`` for every layer: they are taken over as if that prompt had just
+        been prefilled (copied into the preallocated layout; with ``real_offload`` the sparse layers' rows go to
+        pinned host memory), and decoding continues from there."""
         c = OmniKVMultiStageCache(full_attn_layers, num_hidden_layers, num_wait_load_layers, real_offload)
         c._adopt(cache)
         return c
 
     def _adopt(self, cache):
-        if cache is not None and len(getattr(cache, "key_cache", [])) > 0:
-            raise NotImplementedError("wrapping a non-empty cache is not supported: prefill through this cache")
-        if cache is not None:
+        if cache is None:
+            return
+        keys = list(getattr(cache, "key_cache", None) or [])
+        if not keys:
             self._seen_tokens = int(getattr(cache, "_seen_tokens", 0))
+            return
+        vals = list(cache.value_cache)
+        if len(keys) != self.num_hidden_layers or len(vals) != self.num_hidden_layers:
+            raise ValueError(f"a cache to take over must hold all {self.num_hidden_layers} layers, got {len(keys)}")
+        self.stage = "prefill"
+        for i, (k, v) in enumerate(zip(keys, vals)):
+            if not (k.is_cuda and v.is_cuda and k.dim() == 4 and k.shape == v.shape):
+                raise ValueError("a cache to take over must hold CUDA tensors [B, KVH, P, d] per layer")
+            self._store_prefill(k, v, i)
+        if self.real_offload:
+            torch.cuda.current_stream().synchronize()  # the host copies of the sparse layers have landed
 
     def get_seq_length(self, layer_idx: int = 0) -> int:
         return self._seen_tokens

@@ -33,10 +33,14 @@ def _count(n: int) -> None:
     _launches += n
 
 
+def _dev_index(device) -> int:
+    """Ordinal of a CUDA device given as a tensor's device, a torch.device, a string or an int ("cuda" = current)."""
+    idx = torch.device(device).index if not isinstance(device, int) else device
+    return torch.cuda.current_device() if idx is None else idx
+
+
 def sm_count(device) -> int:
-    idx = torch.device(device).index
-    if idx is None:
-        idx = torch.cuda.current_device()
+    idx = _dev_index(device)
     if idx not in _sm_count:
         _sm_count[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
     return _sm_count[idx]
@@ -62,7 +66,7 @@ def workspace(device, nbytes: int, tag: str = "default") -> torch.Tensor:
     never freed: a CUDA graph captured earlier has its address baked in and keeps replaying into it, so the
     outgrown buffer stays alive beside the larger one (a few MB per growth).  Never call it with a larger size
     for the first time while a CUDA graph is being captured."""
-    key = (torch.device(device).index, tag)
+    key = (_dev_index(device), tag)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         if ws is not None:
@@ -387,7 +391,7 @@ _sched = {}
 
 def sched_words(device) -> torch.Tensor:
     """Four zeroed int32 per device: the dynamic-tail counters of ``omnikv_decode_gate_up`` (self-resetting)."""
-    key = torch.device(device).index
+    key = _dev_index(device)
     if key not in _sched:
         _sched[key] = torch.zeros(4, dtype=torch.int32, device=device)
     return _sched[key]
@@ -395,7 +399,7 @@ def sched_words(device) -> torch.Tensor:
 
 def status_word(device) -> torch.Tensor:
     """The device int32 the kernels report bounded-wait failures into (stays 0)."""
-    key = torch.device(device).index
+    key = _dev_index(device)
     if key not in _status:
         _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _status[key]
@@ -472,7 +476,7 @@ _grid_sync = {}
 
 def grid_sync_words(device) -> torch.Tensor:
     """Two zeroed uint32 words per device for the grid-wide barrier of ``omnikv_decode_chain``."""
-    key = torch.device(device).index
+    key = _dev_index(device)
     if key not in _grid_sync:
         _grid_sync[key] = torch.zeros(2, dtype=torch.int32, device=device)
     return _grid_sync[key]

@@ -130,8 +130,11 @@ class OracleLM:
             start = cache._seen_tokens
             position_ids = torch.arange(start, start + n, device=self.device)[None, :].expand(B, n)
         h = F.embedding(input_ids.to(self.device), self.w["model.embed_tokens.weight"])
+        trace = [h]  # residual stream entering every layer, then leaving the last one (kept for per-layer checks)
         for i in range(self.n_layers):
             h = self._layer(i, h, position_ids, cache, fwd_no)
+            trace.append(h)
+        self.hidden_trace = trace
         h = _rms(h, self.w["model.norm.weight"], self.cfg["rms_norm_eps"])
         logits = F.linear(h[:, -1:], self.w["lm_head.weight"]).float()
         return logits, cache
