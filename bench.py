@@ -255,31 +255,45 @@ def gpu_torch_baseline(cache, q, dev, reps: int = 3):
 # multi-GPU self-check: the sharded model against the unsharded one built on rank 0
 # ------------------------------------------------------------------------------------------------
 def tp_parity_check(lm, cfg_factory, tp, dev, rank, ctx: int = 8192, steps: int = 4):
-    """Before the timed region of a multi-GPU run: prefill ``ctx`` tokens and run ``steps`` teacher-forced decode
-    steps through the sharded model (the fused peer-exchange path when it is on) on every rank, and through the
-    UNSHARDED model (same seed: the shards are slices of its weights) on rank 0; the tokens fed are the unsharded
-    model's greedy ones.  Returns, on rank 0, the largest logit difference and whether every filter layer selected
-    the same index list."""
+    """Before the timed region of a multi-GPU run: the sharded model (the fused peer-exchange path when it is on)
+    against the UNSHARDED model (same seed: the shards are slices of its weights) built on rank 0.
+
+    Rank 0 prefills ``ctx`` tokens through the unsharded model and broadcasts the prompt's K/V; every rank's cache
+    takes over its KV heads of it, so both models decode from identical prompts (a sharded prefill rounds its
+    partial sums to 16 bits before the all-reduce, which by itself moves 16-bit logits by tenths after 32 layers).
+    Then ``steps`` teacher-forced decode steps (the unsharded model's greedy tokens) through both.  Returns, on
+    rank 0, the largest logit difference and whether every filter layer selected the same index list."""
+    from types import SimpleNamespace
     import torch.distributed as dist
     from omnikv_b200 import ops
     from omnikv_b200.modeling import OmniKVMulLM
+    cfg = lm.config
     gen = torch.Generator(device=dev).manual_seed(11)
-    vocab = lm.config.vocab_size
-    ids = torch.randint(0, vocab, (1, ctx), generator=gen, device=dev)
-    out_s = lm(input_ids=ids)
-    cache_s = out_s.past_key_values
-    cache_s.stage = "decoding"
+    ids = torch.randint(0, cfg.vocab_size, (1, ctx), generator=gen, device=dev)
     full = cache_f = None
     tok = torch.zeros(1, 1, dtype=torch.int64, device=dev)
-    diff, same, overlap = 0.0, True, 1.0
     if rank == 0:
         full = OmniKVMulLM.from_config(cfg_factory(), dtype=torch.bfloat16, device=dev, seed=0, tp=None)
         out_f = full(input_ids=ids)
         cache_f = out_f.past_key_values
         cache_f.stage = "decoding"
-        diff = (out_s.logits - out_f.logits).abs().max().item()
         tok = out_f.logits[:, -1].argmax(-1, keepdim=True)
+        del out_f
     dist.broadcast(tok, src=0)
+    lo, hi = tp.shard(cfg.num_key_value_heads)
+    keys, vals = [], []
+    buf = torch.empty(2, 1, cfg.num_key_value_heads, ctx, cfg.head_dim, dtype=torch.bfloat16, device=dev)
+    for layer in range(cfg.num_hidden_layers):
+        if rank == 0:
+            buf[0].copy_(cache_f._k[layer][:, :, :ctx])
+            buf[1].copy_(cache_f._v[layer][:, :, :ctx])
+        dist.broadcast(buf, src=0)
+        keys.append(buf[0, :, lo:hi].clone())
+        vals.append(buf[1, :, lo:hi].clone())
+    cache_s = lm.new_cache(SimpleNamespace(key_cache=keys, value_cache=vals, _seen_tokens=ctx))
+    cache_s.stage = "decoding"
+    del keys, vals, buf
+    diff, same, overlap = 0.0, True, 1.0
     for _ in range(steps):
         logits_s, _ = lm._decode_step(tok, cache_s)
         logits_s = logits_s.clone()
@@ -299,7 +313,8 @@ def tp_parity_check(lm, cfg_factory, tp, dev, rank, ctx: int = 8192, steps: int 
     torch.cuda.empty_cache()
     dist.barrier()
     return {"max_abs_logit_diff": diff, "index_sets_equal": bool(same), "min_index_set_overlap": overlap, "ctx": ctx,
-            "steps": steps, "against": "the unsharded model (same seed) on rank 0, teacher-forced with its greedy tokens"}
+            "steps": steps, "against": "the unsharded model (same seed) on rank 0, decoding from the same prompt K/V, "
+                                       "teacher-forced with its greedy tokens"}
 
 
 # ------------------------------------------------------------------------------------------------
