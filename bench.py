@@ -259,10 +259,16 @@ def tp_parity_check(lm, cfg_factory, tp, dev, rank, ctx: int = 8192, steps: int 
     against the UNSHARDED model (same seed: the shards are slices of its weights) built on rank 0.
 
     Rank 0 prefills ``ctx`` tokens through the unsharded model and broadcasts the prompt's K/V; every rank's cache
-    takes over its KV heads of it, so both models decode from identical prompts (a sharded prefill rounds its
-    partial sums to 16 bits before the all-reduce, which by itself moves 16-bit logits by tenths after 32 layers).
-    Then ``steps`` teacher-forced decode steps (the unsharded model's greedy tokens) through both.  Returns, on
-    rank 0, the largest logit difference and whether every filter layer selected the same index list."""
+    takes over its KV heads of it, so both models decode from identical prompts.  Then ``steps`` teacher-forced
+    decode steps (the unsharded model's greedy tokens) through both.  Two depths:
+
+    * ``depth2``: both models cut to their first two layers.  The exchange arithmetic is exercised at full width
+      and the bound is the 16-bit one, 2e-2.
+    * ``full_depth``: all layers.  Sums taken in another order differ in the last fp32 bit; each 16-bit rounding
+      that such a difference flips is a 0.4 % change of that element, which flips more roundings downstream, so
+      within a few layers two 16-bit runs that differ ONLY in summation order carry independent rounding noise.
+      The figure is therefore reported next to a noise floor measured the same way on ONE GPU: the unsharded
+      model against itself with the attention split count changed (nothing else)."""
     from types import SimpleNamespace
     import torch.distributed as dist
     from omnikv_b200 import ops
@@ -270,51 +276,101 @@ def tp_parity_check(lm, cfg_factory, tp, dev, rank, ctx: int = 8192, steps: int 
     cfg = lm.config
     gen = torch.Generator(device=dev).manual_seed(11)
     ids = torch.randint(0, cfg.vocab_size, (1, ctx), generator=gen, device=dev)
-    full = cache_f = None
-    tok = torch.zeros(1, 1, dtype=torch.int64, device=dev)
-    if rank == 0:
-        full = OmniKVMulLM.from_config(cfg_factory(), dtype=torch.bfloat16, device=dev, seed=0, tp=None)
-        out_f = full(input_ids=ids)
-        cache_f = out_f.past_key_values
-        cache_f.stage = "decoding"
-        tok = out_f.logits[:, -1].argmax(-1, keepdim=True)
-        del out_f
-    dist.broadcast(tok, src=0)
     lo, hi = tp.shard(cfg.num_key_value_heads)
-    keys, vals = [], []
-    buf = torch.empty(2, 1, cfg.num_key_value_heads, ctx, cfg.head_dim, dtype=torch.bfloat16, device=dev)
-    for layer in range(cfg.num_hidden_layers):
+    full = OmniKVMulLM.from_config(cfg_factory(), dtype=torch.bfloat16, device=dev, seed=0, tp=None) if rank == 0 else None
+
+    def filters_of(cache):
+        return [f for f in cache.groups]
+
+    def compare(model_s, model_f, n_layers, floor=False):
+        """Teacher-forced decode of (sharded or second unsharded) model_s against model_f on rank 0."""
+        tok = torch.zeros(1, 1, dtype=torch.int64, device=dev)
+        cache_f = None
         if rank == 0:
-            buf[0].copy_(cache_f._k[layer][:, :, :ctx])
-            buf[1].copy_(cache_f._v[layer][:, :, :ctx])
-        dist.broadcast(buf, src=0)
-        keys.append(buf[0, :, lo:hi].clone())
-        vals.append(buf[1, :, lo:hi].clone())
-    cache_s = lm.new_cache(SimpleNamespace(key_cache=keys, value_cache=vals, _seen_tokens=ctx))
-    cache_s.stage = "decoding"
-    del keys, vals, buf
-    diff, same, overlap = 0.0, True, 1.0
-    for _ in range(steps):
-        logits_s, _ = lm._decode_step(tok, cache_s)
-        logits_s = logits_s.clone()
-        if rank == 0:
-            logits_f, nxt = full._decode_step(tok, cache_f)
-            diff = max(diff, (logits_s.view(-1) - logits_f.view(-1)).abs().max().item())
-            for f in cache_f.groups:
-                a, ca = cache_s._idx[f]
-                b, cb = cache_f._idx[f]
-                sa, sb = set(a[0, : int(ca[0])].tolist()), set(b[0, : int(cb[0])].tolist())
-                same = same and sa == sb
-                overlap = min(overlap, len(sa & sb) / max(1, len(sb)))
-            tok = nxt.clone().view(1, 1)
+            out_f = model_f(input_ids=ids)
+            cache_f = out_f.past_key_values
+            cache_f.stage = "decoding"
+            tok = out_f.logits[:, -1].argmax(-1, keepdim=True)
+            del out_f
         dist.broadcast(tok, src=0)
+        buf = torch.empty(2, 1, cfg.num_key_value_heads, ctx, cfg.head_dim, dtype=torch.bfloat16, device=dev)
+        keys, vals = [], []
+        for layer in range(n_layers):
+            if rank == 0:
+                buf[0].copy_(cache_f._k[layer][:, :, :ctx])
+                buf[1].copy_(cache_f._v[layer][:, :, :ctx])
+            if not floor:
+                dist.broadcast(buf, src=0)
+                keys.append(buf[0, :, lo:hi].clone())
+                vals.append(buf[1, :, lo:hi].clone())
+            elif rank == 0:
+                keys.append(buf[0].clone())
+                vals.append(buf[1].clone())
+        diff, same, overlap = 0.0, True, 1.0
+        if floor and rank != 0:
+            return None
+        cache_s = model_s.new_cache(SimpleNamespace(key_cache=keys, value_cache=vals, _seen_tokens=ctx))
+        cache_s.stage = "decoding"
+        del keys, vals, buf
+        for _ in range(steps):
+            if floor:
+                real = ops.default_splits
+                ops.default_splits = lambda *a, **k: real(*a, **k) + 3   # the only change: attention split count
+                try:
+                    logits_s, _ = model_s._decode_step(tok, cache_s)
+                finally:
+                    ops.default_splits = real
+            else:
+                logits_s, _ = model_s._decode_step(tok, cache_s)
+            logits_s = logits_s.clone()
+            if rank == 0:
+                logits_f, nxt = model_f._decode_step(tok, cache_f)
+                diff = max(diff, (logits_s.view(-1) - logits_f.view(-1)).abs().max().item())
+                for f in filters_of(cache_f):
+                    a_, ca = cache_s._idx[f]
+                    b_, cb = cache_f._idx[f]
+                    sa, sb = set(a_[0, : int(ca[0])].tolist()), set(b_[0, : int(cb[0])].tolist())
+                    same = same and sa == sb
+                    overlap = min(overlap, len(sa & sb) / max(1, len(sb)))
+                tok = nxt.clone().view(1, 1)
+            if not floor:
+                dist.broadcast(tok, src=0)
+        return {"max_abs_logit_diff": diff, "index_sets_equal": bool(same), "min_index_set_overlap": overlap}
+
+    def cut(model, n):
+        """The model reduced to its first n layers (shares the weights)."""
+        keep = model.model.layers
+        model.model.layers = torch.nn.ModuleList(list(keep)[:n])
+        model.config.num_hidden_layers = n
+        return keep
+
+    res = {"ctx": ctx, "steps": steps, "against": "the unsharded model (same seed) on rank 0, decoding from the same prompt "
+                                                 "K/V, teacher-forced with its greedy tokens"}
+    n_all = cfg.num_hidden_layers
+    res["full_depth"] = compare(lm, full, n_all)
+    if rank == 0:
+        res["full_depth"]["noise_floor"] = dict(compare(full, full, n_all, floor=True),
+                                                what="the unsharded model against itself with the attention split count changed")
+    # reduced depth: the first two layers of both models
+    keep_s = cut(lm, 2)
+    keep_f = cut(full, 2) if rank == 0 else None
+    sel = cfg.get("do_select_layers")
+    cfg.do_select_layers = "1"
+    for model in ([lm, full] if rank == 0 else [lm]):
+        for i, layer in enumerate(model.model.layers):
+            layer.do_select_layers, layer.is_filter = [1], i == 1
+    try:
+        res["depth2"] = compare(lm, full, 2)
+    finally:
+        lm.model.layers, cfg.num_hidden_layers, cfg.do_select_layers = keep_s, n_all, sel
+        filt = [int(i) for i in sel.split(",")]
+        for i, layer in enumerate(lm.model.layers):
+            layer.do_select_layers, layer.is_filter = filt, i in filt
     ops.check_status(dev)
-    del full, cache_f, cache_s
+    del full
     torch.cuda.empty_cache()
     dist.barrier()
-    return {"max_abs_logit_diff": diff, "index_sets_equal": bool(same), "min_index_set_overlap": overlap, "ctx": ctx,
-            "steps": steps, "against": "the unsharded model (same seed) on rank 0, decoding from the same prompt K/V, "
-                                       "teacher-forced with its greedy tokens"}
+    return res
 
 
 # ------------------------------------------------------------------------------------------------
@@ -329,6 +385,10 @@ def build_workload(args, world, rank, dev, tp):
         if wl == "tp70b":
             cfg = LlamaCompressorConfig(num_hidden_layers=args.layers, hidden_size=8192, intermediate_size=28672,
                                         num_attention_heads=64, num_key_value_heads=8)
+        elif args.rank_shape_of > 1:
+            n = args.rank_shape_of
+            cfg = LlamaCompressorConfig(num_hidden_layers=args.layers, num_attention_heads=32 // n, num_key_value_heads=8 // n,
+                                        intermediate_size=14336 // n, vocab_size=128256 // n, head_dim=128)
         else:
             cfg = LlamaCompressorConfig(num_hidden_layers=args.layers)
         omni = dict(OMNI)
@@ -376,6 +436,10 @@ def main():
     ap.add_argument("--nccl-allreduce", action="store_true", help="multi-GPU: NCCL all-reduce after the row-parallel "
                     "projections instead of the peer-memory exchange")
     ap.add_argument("--skip-threshold", type=float, default=None, help="offload: cache_cls lazy with this threshold")
+    ap.add_argument("--rank-shape-of", type=int, default=0, metavar="N",
+                    help="decode128k on ONE GPU with the shapes one rank of an N-way tensor-parallel run holds (1/N of the "
+                         "heads, the MLP and the vocabulary) and no exchange: the per-rank floor a multi-GPU step is "
+                         "compared with.  The line is marked and is not a benchmark value")
     ap.add_argument("--profile-step", action="store_true",
                     help="after the warm-up, run ONE step between cudaProfilerStart/Stop and exit (for ncu "
                          "--profile-from-start off); prints no benchmark line")
@@ -586,6 +650,8 @@ def main():
         "whole_step": {"algorithmic_bytes": step_bytes, "kv_bytes": kv_bytes, "weight_bytes": w_bytes,
                        "achieved_gbs_per_gpu": step_gbs, "frac_of_peak": step_gbs / peak},
     }
+    if args.rank_shape_of > 1:
+        line["metric"] = f"NOT A BENCHMARK VALUE: one rank's share of a {args.rank_shape_of}-way tensor-parallel step, no exchange"
     if link_bytes:
         line["host_link"] = {"bytes_per_step": link_bytes, "achieved_gbs": link_bytes / (ms_step * 1e-3) / 1e9}
     if tp_parity is not None:

@@ -296,19 +296,28 @@ int omnikv_silu_mul(int dtype, const void* gate_up, int64_t gate_up_stride_b, vo
  * transformer_layer_infer_template.py:119-120, :128-129 in the reference's fork) is fused into the kernels on
  * both sides of it, over peer-mapped memory:
  *   producer  omnikv_decode_gemv_residual(tp_out = x): every rank stores its fp32 partial sums straight into
- *             EVERY rank's exchange buffer (plain peer stores over NVLink); the CTA that finishes last raises
- *             this rank's flag word on every rank.  `resid` and `out` are then unused (may be NULL).
- *   consumer  omnikv_decode_gate_up / _qkv / _logits(tp_in = x): once all ranks' flags of that exchange have
- *             arrived (bounded wait), the activations are h + sum over ranks of the partials, rounded once to the
- *             storage type; they are also written to h_inout (the updated residual stream), which must be a
- *             DIFFERENT buffer than h: other CTAs of the same launch are still reading h.
+ *             EVERY rank's exchange buffer (plain peer stores over NVLink) as 8-byte entries {value, tag}, one
+ *             store per entry, tag = *epoch * 256 + seq + 1: an entry is the old one or the new one, never a mix,
+ *             so there is no flag, no fence and nothing after the last row.  `resid` and `out` are unused (may be
+ *             NULL).
+ *   consumer  omnikv_decode_gate_up / _qkv / _logits(tp_in = x): every thread reads its entries of all ranks until
+ *             they carry this exchange's tag (bounded wait), then the activations are h + sum over ranks of the
+ *             partials (rank order, the same on every rank), rounded once to the storage type; they are also
+ *             written to h_inout (the updated residual stream), which must be a DIFFERENT buffer than h: other
+ *             CTAs of the same launch are still reading h.  A consumer does not wait for the completion of the
+ *             call before it on the stream (it is launched as a programmatic dependent launch): the only thing it
+ *             may need from that call are the local partials, which arrive through the entries.  So the call right
+ *             before a consumer must be the producer of its exchange (or any call whose outputs the consumer does
+ *             not read), and what else the consumer reads (h, the norm weights) must come from calls at least two
+ *             back.
  * peer_base[r]: rank r's exchange buffer (omnikv_tp_exchange_bytes(hidden) bytes, zero before first use) as
  * mapped into THIS process (peer_base[rank] = the local one).  Exchanges alternate between two slots
  * (seq & 1); seq numbers the exchanges of a decode step 0, 1, 2, ... (< 256) and must follow program order, and a
  * step must hold an EVEN number of them (a decoder layer has two), so that the last exchange of a step and the
  * first of the next never share a slot; *epoch is a local device word that every rank bumps once per decode
- * step.  All ranks must issue the same sequence of calls.  world <= 8.  NULL or world <= 1: no exchange.
- * The wait for the peers' flags gives up after two seconds (status 4). */
+ * step (it must never repeat: tags identify an exchange for good).  All ranks must issue the same sequence of
+ * calls.  world <= 8.  NULL or world <= 1: no exchange.  The wait for the peers' entries gives up after two
+ * seconds (status 4). */
 typedef struct {
   int32_t world, rank;
   void* peer_base[8];

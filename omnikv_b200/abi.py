@@ -5,9 +5,11 @@ There is no fallback: if the library is missing, ``lib()`` raises with the build
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
-_LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libomnikv_b200.so"
+# OMNIKV_B200_LIB selects another build of the same library (the profiling build of ``build.py --trace``)
+_LIB_PATH = Path(os.environ.get("OMNIKV_B200_LIB") or Path(__file__).resolve().parent / "_lib" / "libomnikv_b200.so")
 _lib = None
 
 ABI_VERSION = 4

@@ -36,6 +36,13 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\
 
 bool pdl_enabled();  // OMNIKV_PDL=0 in the environment turns it off
 
+#ifdef OMNIKV_TRACE
+// Profiling build only (-DOMNIKV_TRACE, `python -m omnikv_b200.build --trace`): the weight-streaming and attention
+// kernels stamp %globaltimer at their stages into per-launch slots; the host numbers the launches in issue order.
+constexpr int kTraceSlots = 256;
+int trace_next_slot();   // slot of the launch being issued (wraps at kTraceSlots)
+#endif
+
 template <typename Kern, typename Args>
 inline cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, const Args& a) {
   cudaLaunchConfig_t cfg = {};

@@ -42,23 +42,27 @@ struct AttnArgs {
   float* ws_ml;
   unsigned* ws_cnt;   // [B*KVH] arrival counters of the splits, zero between launches
   int pdl_trigger;    // 1: the grid is fully resident, the next kernel may be scheduled early
+  int trace_slot;     // profiling build: slot of the stamp array this launch writes
   int* status;        // device word for bounded-wait failures, or nullptr
   int B, H, KVH, G, S;
   float scale;
 };
 
-#ifdef OMNIKV_ATTN_TRACE
-// Profiling build only (-DOMNIKV_ATTN_TRACE): per-CTA %globaltimer stamps of the mma kernel's stages.
-__device__ unsigned long long g_attn_trace[4096 * 8];
-__device__ __forceinline__ void attn_stamp(int slot) {
+#ifdef OMNIKV_TRACE
+// Profiling build only: per-CTA %globaltimer stamps of the mma kernel's stages, one slot per launch.
+// [0] CTA start, [1] previous kernel complete, [2] prologue done, [3] tiles consumed, [4] partials written,
+// [5] counted in (the last CTA of a group: merged), [6] 2000 + (sparse ? 1 : 0).
+constexpr int kAttnTraceCtas = 320, kAttnTraceWords = 8;
+__device__ unsigned long long g_attn_trace[kTraceSlots * kAttnTraceCtas * kAttnTraceWords];
+__device__ __forceinline__ void attn_stamp(int launch, int word) {
   if (threadIdx.x == 0) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
     const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-    if (cta < 4096) g_attn_trace[cta * 8 + slot] = t;
+    if (cta < kAttnTraceCtas) g_attn_trace[(launch * kAttnTraceCtas + cta) * kAttnTraceWords + word] = t;
   }
 }
-#define ATTN_STAMP(i) attn_stamp(i)
+#define ATTN_STAMP(i) attn_stamp(a.trace_slot, i)
 #else
 #define ATTN_STAMP(i)
 #endif
@@ -207,6 +211,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
   // tiles already reach the last row waits first.  The successor may be scheduled early only when this grid is
   // fully resident (a.pdl_trigger, decided by the host from the grid size).
   ATTN_STAMP(0);
+#ifdef OMNIKV_TRACE
+  if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
+    g_attn_trace[(a.trace_slot * kAttnTraceCtas) * kAttnTraceWords + 6] = 2000ull + (a.idxA ? 1 : 0);
+#endif
   const int nA = a.lenA[b];
   const int nB = a.lenB ? a.lenB[b] : 0;
   const int startB = a.startB ? a.startB[b] : 0;
@@ -700,6 +708,9 @@ int launch_mma(AttnArgs a, bool with_v, bool with_score, int64_t a_rows, cudaStr
   OMNIKV_CUDA_OK(cudaGetDevice(&dev));
   OMNIKV_CUDA_OK(cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev));
   a.pdl_trigger = ((long long)a.S * a.KVH * a.B <= 2ll * n_sms) ? 1 : 0;  // two CTAs of this kernel fit per SM
+#ifdef OMNIKV_TRACE
+  a.trace_slot = trace_next_slot();
+#endif
   // scattered rows: one bulk copy per row; a contiguous cache of known capacity: tensor-map tiles; else cp.async
   int mode = a.idxA != nullptr ? kCopyBulkRows : kCopyCpAsync;
   CUtensorMap tm_k = {}, tm_v = {};
@@ -821,6 +832,7 @@ extern "C" int omnikv_decode_attn(const omnikv_attn_params* p, void* stream) {
   a.B = p->B; a.H = p->H; a.KVH = p->KVH; a.G = G; a.S = p->n_splits;
   a.scale = p->scale;
   a.pdl_trigger = 0;
+  a.trace_slot = 0;
   a.status = p->status;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (p->dtype) {
@@ -889,7 +901,7 @@ extern "C" int omnikv_decode_attn_no_alloc(const omnikv_attn_params* p, void* st
   return omnikv_decode_attn(&q, stream);
 }
 
-#ifdef OMNIKV_ATTN_TRACE
+#ifdef OMNIKV_TRACE
 extern "C" int omnikv_debug_attn_trace(unsigned long long* host_out, int n_words) {
   return (int)cudaMemcpyFromSymbol(host_out, omnikv::g_attn_trace, (size_t)n_words * 8);
 }

@@ -61,30 +61,32 @@ struct GemvArgs {
   // producer side (EPI_RESID): this rank's partial outputs are stored straight into every rank's exchange
   // buffer; when the whole grid is done, a flag word is stored on every rank
   int tp_world;                     // 0/1: off
-  float* tp_peer_partial[8];        // rank p's slot for MY partials: [N] fp32
-  unsigned* tp_peer_flag[8];        // rank p's flag word for (slot, me)
-  unsigned* tp_done;                // local counter of finished CTAs (self-resetting)
-  // consumer side (phases with a norm): x = resid + sum over ranks of their partials, once the flags arrived
-  const float* tp_my_partials;      // local [8][K] fp32 of the slot to consume, or nullptr
-  const unsigned* tp_my_flags;      // local [8]
+  uint2* tp_peer_ll[8];             // rank p's slot for MY partials: [N] x {fp32 bits, tag}
+  // consumer side (phases with a norm): x = resid + sum over ranks of their partials, once every entry carries
+  // this exchange's tag
+  const uint2* tp_my_ll;            // local [8][K] x {fp32 bits, tag} of the slot to consume, or nullptr
   void* tp_h_out;                   // local [K]: CTA 0 stores the summed residual stream here
   const unsigned* tp_epoch;         // device word bumped once per decode step
-  unsigned tp_seq;                  // flag value = epoch * 256 + seq + 1
+  unsigned tp_seq;                  // tag = epoch * 256 + seq + 1
   int trace_slot;                   // profiling build: which slot of the stamp array this launch writes
   int tail_pool;                    // chunks at the end of the matrix handed out dynamically (0: all static)
   int* tail_next;                   // [2] device: next index of the pool, finished producers (self-resetting)
 };
 
-#ifdef OMNIKV_GEMV_TRACE
-// Profiling build only (-DOMNIKV_GEMV_TRACE): per-CTA %globaltimer stamps of the single-phase kernel, one
-// slot per launch (the host numbers the launches 0..63 round-robin).
-__device__ unsigned long long g_gemv_trace[64 * 160 * 8];
-int g_trace_launch = 0;  // host: launches so far
-#define GEMV_STAMP(a, i)                                                                            \
-  do {                                                                                              \
-    unsigned long long t_;                                                                          \
-    asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t_));                                         \
-    if (blockIdx.x < 160) g_gemv_trace[((a).trace_slot * 160 + blockIdx.x) * 8 + (i)] = t_;         \
+#ifdef OMNIKV_TRACE
+// Profiling build only: per-CTA %globaltimer stamps of the single-phase kernel, one slot per launch.
+// [0] CTA start, [1] previous kernel complete (dependent-launch wait passed), [6] staging area free, [7] activations
+// staged (after the wait for the peers' flags, when there is an exchange), [2] activations in registers, [3] first
+// chunk landed, [8] rows done, [4] consumers done (after the exchange tail: fence, count, flags), [5] last copy
+// issued (producer thread), [9] flags raised (the CTA that finished last), [10] epilogue kind.
+constexpr int kGemvTraceCtas = 160, kGemvTraceWords = 12;
+__device__ unsigned long long g_gemv_trace[kTraceSlots * kGemvTraceCtas * kGemvTraceWords];
+#define GEMV_STAMP(a, i)                                                                                       \
+  do {                                                                                                         \
+    unsigned long long t_;                                                                                     \
+    asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t_));                                                    \
+    if (blockIdx.x < kGemvTraceCtas)                                                                           \
+      g_gemv_trace[((a).trace_slot * kGemvTraceCtas + blockIdx.x) * kGemvTraceWords + (i)] = t_;               \
   } while (0)
 #else
 #define GEMV_STAMP(a, i)
@@ -270,20 +272,50 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
   float sq = 0.f;
   consumer_bar();  // the previous phase no longer reads the staging area
   if (threadIdx.x == 0) GEMV_STAMP(a, 6);
-  const bool tp_consume = a.tp_world > 1 && a.tp_my_partials != nullptr;
+  const bool tp_consume = a.tp_world > 1 && a.tp_my_ll != nullptr;
+  constexpr int NT_ = GV_CONSUMER_WARPS * 32;
+  constexpr int NV_ = (K / 8 + NT_ - 1) / NT_;  // 16-byte vectors of activations per thread
+  float psum[NV_][8];
   if (tp_consume) {
-    // every rank's partial sums of the previous projection must have landed in this GPU's memory: each rank
-    // stores a flag here after its last store.  Bounded wait, one poller per CTA.
-    if (tid == 0) {
-      const unsigned want = __ldcg(a.tp_epoch) * 256u + a.tp_seq + 1u;
+    // Every rank's partial sums of the previous projection arrive in this GPU's memory as 8-byte entries
+    // {value, tag}, each written by ONE 8-byte store, so an entry is either the old one or the new one, never
+    // a mix, and the tag says which: no flag, no fence and no completion of the producing kernel is waited for
+    // -- a thread reads its entries until all of them carry this exchange's tag (a few microseconds after the
+    // slowest rank has computed them).  The ranks' values are added in rank order (the same sums on every rank).
+    // This kernel does NOT wait for its predecessor's completion either (see decode_gemv_kernel): everything it
+    // needs from that kernel -- the local rank's partials -- comes through the tagged entries, and whatever else
+    // it reads was written by kernels that had completed before the predecessor computed a single row.
+    const unsigned want = __ldcg(a.tp_epoch) * 256u + a.tp_seq + 1u;
+#pragma unroll
+    for (int i = 0; i < NV_; ++i) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) psum[i][e] = 0.f;
+      const int v = tid + i * NT_;
+      if (v >= K / 8) continue;
       for (int r = 0; r < a.tp_world; ++r) {
-        if (!wait_flag_reached(a.tp_my_flags + r, want)) {  // a rank that never arrived: give up after 2 s
-          cs.fail = 1;
-          atomicExch(a.status, 4);
-          break;
+        const uint4* src = reinterpret_cast<const uint4*>(a.tp_my_ll + (size_t)r * K + (size_t)v * 8);
+        uint4 e0, e1, e2, e3;
+        unsigned long long t0 = 0ull;
+        for (unsigned spin = 0;; ++spin) {
+          e0 = __ldcv(src); e1 = __ldcv(src + 1); e2 = __ldcv(src + 2); e3 = __ldcv(src + 3);
+          const bool ok = e0.y == want && e0.w == want && e1.y == want && e1.w == want && e2.y == want &&
+                          e2.w == want && e3.y == want && e3.w == want;
+          if (ok) break;
+          if ((spin & 63u) == 63u) {  // bounded by time: an absent rank costs kWaitNs, then the kernel reports and returns
+            const unsigned long long now = globaltimer_ns();
+            if (t0 == 0ull) t0 = now;
+            if (now - t0 > kWaitNs || cs.fail) {
+              cs.fail = 1;
+              atomicExch(a.status, 4);
+              break;
+            }
+          }
         }
+        psum[i][0] += __uint_as_float(e0.x); psum[i][1] += __uint_as_float(e0.z);
+        psum[i][2] += __uint_as_float(e1.x); psum[i][3] += __uint_as_float(e1.z);
+        psum[i][4] += __uint_as_float(e2.x); psum[i][5] += __uint_as_float(e2.z);
+        psum[i][6] += __uint_as_float(e3.x); psum[i][7] += __uint_as_float(e3.z);
       }
-      __threadfence_system();
     }
     consumer_bar();
     if (cs.fail) return false;
@@ -314,12 +346,8 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
         if (v >= K / 8) continue;
         float f[8];
         unpack8<T>(xr_[i], f);
-        for (int r = 0; r < a.tp_world; ++r) {
-          const float4* pp = reinterpret_cast<const float4*>(a.tp_my_partials + (size_t)r * K) + 2 * v;
-          const float4 p0 = __ldcg(pp), p1 = __ldcg(pp + 1);
-          f[0] += p0.x; f[1] += p0.y; f[2] += p0.z; f[3] += p0.w;
-          f[4] += p1.x; f[5] += p1.y; f[6] += p1.z; f[7] += p1.w;
-        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] += psum[i][e];
         xr_[i].x = pack2<T>(f[0], f[1]);
         xr_[i].y = pack2<T>(f[2], f[3]);
         xr_[i].z = pack2<T>(f[4], f[5]);
@@ -400,14 +428,16 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
     }
   }
   if (threadIdx.x == 0) GEMV_STAMP(a, 2);
-#ifdef OMNIKV_GEMV_TRACE
+#ifdef OMNIKV_TRACE
   bool first_stage = true;
 #endif
   unsigned long long my_best = 0ull;
+  unsigned tp_tag = 0u;
+  if (EPI == EPI_RESID && a.tp_world > 1) tp_tag = __ldcg(a.tp_epoch) * 256u + a.tp_seq + 1u;
   for (;; ++it) {
     const int slot = it % GV_STAGES;
     const bool ok = mbar_wait(&ring.full_bar[slot], (it / GV_STAGES) & 1);
-#ifdef OMNIKV_GEMV_TRACE
+#ifdef OMNIKV_TRACE
     if (first_stage && threadIdx.x == 0) GEMV_STAMP(a, 3);  // first chunk has landed
     first_stage = false;
 #endif
@@ -459,9 +489,11 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
       row0 += p;
       row1 += p;
       if (EPI == EPI_RESID && a.tp_world > 1) {
+        // {value, tag} in one 8-byte store per entry, straight into every rank's buffer (the local one included)
+        const uint2 v0 = make_uint2(__float_as_uint(r0), tp_tag), v1 = make_uint2(__float_as_uint(r1), tp_tag);
         for (int pr = 0; pr < a.tp_world; ++pr) {
-          a.tp_peer_partial[pr][row0] = r0;
-          a.tp_peer_partial[pr][row1] = r1;
+          __stcg(a.tp_peer_ll[pr] + row0, v0);
+          __stcg(a.tp_peer_ll[pr] + row1, v1);
         }
       } else if (EPI == EPI_RESID) {
         const T* rs = static_cast<const T*>(a.resid);
@@ -514,21 +546,7 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
       }
     }
   }
-  if (EPI == EPI_RESID && a.tp_world > 1) {
-    // all of this CTA's stores (to every rank) are ordered before its count; the CTA that completes the count
-    // raises this rank's flag on every rank
-    consumer_bar();
-    if (tid == 0) {
-      __threadfence_system();
-      if (atomicAdd(a.tp_done, 1u) == gridDim.x - 1) {
-        atomicExch(a.tp_done, 0u);
-        __threadfence_system();
-        const unsigned val = __ldcg(a.tp_epoch) * 256u + a.tp_seq + 1u;
-        for (int pr = 0; pr < a.tp_world; ++pr)
-          asm volatile("st.volatile.global.u32 [%0], %1;\n" ::"l"(a.tp_peer_flag[pr]), "r"(val) : "memory");
-      }
-    }
-  }
+  if (threadIdx.x == 0) GEMV_STAMP(a, 8);
   if (EPI == EPI_LOGITS) {
     consumer_bar();
     if (tid < HALF) cs.best[tid] = my_best;
@@ -573,7 +591,13 @@ __global__ void __launch_bounds__(GV_THREADS, 1) decode_gemv_kernel(const GemvAr
   // scheduled behind it right away.  The producer starts streaming weights at once (they depend on nothing);
   // the consumers wait for the previous kernel before they touch activations or write any output.
   pdl_trigger();
-  if (threadIdx.x == 0) GEMV_STAMP(a, 0);
+  if (threadIdx.x == 0) {
+    GEMV_STAMP(a, 0);
+#ifdef OMNIKV_TRACE
+    if (blockIdx.x < kGemvTraceCtas)
+      g_gemv_trace[(a.trace_slot * kGemvTraceCtas + blockIdx.x) * kGemvTraceWords + 10] = 1000ull + EPI * 10 + (a.tp_world > 1 ? (a.tp_my_ll ? 2 : (EPI == EPI_RESID ? 1 : 0)) : 0);
+#endif
+  }
   if ((threadIdx.x >> 5) == GV_CONSUMER_WARPS) {
     if ((threadIdx.x & 31) == 0) {
       produce_phase<T, KV, WK, EPI>(a, ring, it);
@@ -581,7 +605,9 @@ __global__ void __launch_bounds__(GV_THREADS, 1) decode_gemv_kernel(const GemvAr
     }
     return;
   }
-  pdl_wait();
+  // A consumer of a tensor-parallel exchange does not wait for its predecessor to complete: what it needs from it
+  // arrives as tagged entries (consume_phase).  Every other kernel reads plain memory and waits.
+  if (!(a.tp_world > 1 && a.tp_my_ll != nullptr)) pdl_wait();
   if (threadIdx.x == 0) GEMV_STAMP(a, 1);
   consume_phase<T, KV, WK, EPI, false>(a, ring, cs, it);
   if (threadIdx.x == 0) GEMV_STAMP(a, 4);
@@ -723,9 +749,9 @@ int launch_one(const GemvArgs& a, int n_sms, cudaStream_t st) {
       aa.tail_next = nullptr;
     }
   }
-#ifdef OMNIKV_GEMV_TRACE
+#ifdef OMNIKV_TRACE
   GemvArgs b = aa;
-  b.trace_slot = g_trace_launch++ % 64;
+  b.trace_slot = trace_next_slot();
   OMNIKV_CUDA_OK(launch_pdl(kern, dim3(grid), dim3(GV_THREADS), smem, st, b));
 #else
   OMNIKV_CUDA_OK(launch_pdl(kern, dim3(grid), dim3(GV_THREADS), smem, st, aa));
@@ -776,23 +802,21 @@ int launch_chain(const ChainArgs& c, int n_sms, cudaStream_t st) {
   return OMNIKV_OK;
 }
 
-// Exchange buffer of one rank: [2 slots][8 ranks][hidden] fp32 partials, then [2][8] flag words.
-size_t tp_partials_bytes(int hidden) { return (size_t)2 * 8 * hidden * sizeof(float); }
+// Exchange buffer of one rank: [2 slots][8 ranks][hidden] entries of {fp32 partial, tag} (the fused projection +
+// all-reduce kernels), then [2][8] flag words (used by omnikv_tp_allreduce_sum, which lays fp32/16-bit vectors over
+// the first half of the entry area).
+size_t tp_partials_bytes(int hidden) { return (size_t)2 * 8 * hidden * sizeof(uint2); }
 
 // Producer fields: where MY partials of exchange `seq` go on every rank.
 int tp_fill_producer(GemvArgs& a, const omnikv_tp_exchange* t, int n_rows) {
   if (!t || t->world <= 1) return OMNIKV_OK;
-  if (t->world > 8 || t->rank < 0 || t->rank >= t->world || !t->done_counter || !t->epoch || t->hidden != n_rows)
-    return OMNIKV_E_BADARG;
+  if (t->world > 8 || t->rank < 0 || t->rank >= t->world || !t->epoch || t->hidden != n_rows) return OMNIKV_E_BADARG;
   const int slot = t->seq & 1;
   a.tp_world = t->world;
   for (int p = 0; p < t->world; ++p) {
     if (!t->peer_base[p]) return OMNIKV_E_BADARG;
-    unsigned char* base = static_cast<unsigned char*>(t->peer_base[p]);
-    a.tp_peer_partial[p] = reinterpret_cast<float*>(base) + ((size_t)slot * 8 + t->rank) * t->hidden;
-    a.tp_peer_flag[p] = reinterpret_cast<unsigned*>(base + tp_partials_bytes(t->hidden)) + slot * 8 + t->rank;
+    a.tp_peer_ll[p] = static_cast<uint2*>(t->peer_base[p]) + ((size_t)slot * 8 + t->rank) * t->hidden;
   }
-  a.tp_done = t->done_counter;
   a.tp_epoch = t->epoch;
   a.tp_seq = (unsigned)t->seq;
   return OMNIKV_OK;
@@ -806,8 +830,7 @@ int tp_fill_consumer(GemvArgs& a, const omnikv_tp_exchange* t, int k, void* h_ou
   const int slot = t->seq & 1;
   unsigned char* base = static_cast<unsigned char*>(t->peer_base[t->rank]);
   a.tp_world = t->world;
-  a.tp_my_partials = reinterpret_cast<const float*>(base) + (size_t)slot * 8 * t->hidden;
-  a.tp_my_flags = reinterpret_cast<const unsigned*>(base + tp_partials_bytes(t->hidden)) + slot * 8;
+  a.tp_my_ll = reinterpret_cast<const uint2*>(base) + (size_t)slot * 8 * t->hidden;
   a.tp_h_out = h_out;
   a.tp_epoch = t->epoch;
   a.tp_seq = (unsigned)t->seq;
@@ -985,7 +1008,7 @@ extern "C" size_t omnikv_tp_exchange_bytes(int hidden) {
   return omnikv::tp_partials_bytes(hidden) + 2 * 8 * sizeof(unsigned) + 192;  // padded to a multiple of 256
 }
 
-#ifdef OMNIKV_GEMV_TRACE
+#ifdef OMNIKV_TRACE
 extern "C" int omnikv_debug_gemv_trace(unsigned long long* host_out, int n_words) {
   return (int)cudaMemcpyFromSymbol(host_out, omnikv::g_gemv_trace, (size_t)n_words * 8);
 }

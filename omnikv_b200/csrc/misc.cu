@@ -56,6 +56,11 @@ int record_cuda_error(cudaError_t e, const char* where) {
   return OMNIKV_E_CUDA;
 }
 
+#ifdef OMNIKV_TRACE
+static int g_trace_slot = 0;
+int trace_next_slot() { return g_trace_slot++ % kTraceSlots; }
+#endif
+
 bool pdl_enabled() {
   static const int on = [] {
     const char* e = getenv("OMNIKV_PDL");
@@ -374,3 +379,7 @@ extern "C" int omnikv_window_fold(const float* planes, float* score_out, int B, 
   OMNIKV_CUDA_OK(cudaGetLastError());
   return OMNIKV_OK;
 }
+
+#ifdef OMNIKV_TRACE
+extern "C" void omnikv_debug_trace_reset(void) { omnikv::g_trace_slot = 0; }
+#endif

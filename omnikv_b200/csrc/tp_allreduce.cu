@@ -142,7 +142,7 @@ extern "C" int omnikv_tp_allreduce_sum(int dtype, void* x, int64_t n, const omni
   if (bytes > slot_bytes) return OMNIKV_E_WORKSPACE;
   ArArgs a = {};
   a.x = x; a.n_vec = (int)(bytes / 16); a.world = t->world; a.rank = t->rank;
-  const size_t flags_off = (size_t)2 * 8 * slot_bytes;
+  const size_t flags_off = (size_t)2 * 8 * slot_bytes * 2;  // behind the entry area (8 bytes per element of `hidden`)
   for (int p = 0; p < t->world; ++p) {
     if (!t->peer_base[p]) return OMNIKV_E_BADARG;
     unsigned char* base = static_cast<unsigned char*>(t->peer_base[p]);

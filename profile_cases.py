@@ -3,7 +3,12 @@
     python profile_cases.py dense_attn [--reps 3] [--ctx 131072]
     ncu --set full --clock-control none -k regex:decode_attn_mma -c 3 python profile_cases.py dense_attn
 
-Cases: dense_attn (filter layer: K and V of 8 KV heads x ctx rows, fused scores), sparse_attn
+    python -m omnikv_b200.build --trace     # once: the profiling build of the library
+    OMNIKV_B200_LIB=omnikv_b200/_lib/libomnikv_b200_trace.so python -m torch.distributed.run --nnodes=1 \
+        --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29533 profile_cases.py tp_timeline
+
+Cases: tp_timeline (one graph-replayed decode step of the benchmark on N GPUs, or on one: per-kernel %globaltimer
+stamps of the profiling build, with the wait for the peers' flags separated from the streaming time), dense_attn (filter layer: K and V of 8 KV heads x ctx rows, fused scores), sparse_attn
 (8781 selected rows + tail), topk (ctx scores, 8 planes), score_window (16-slot window, exp),
 offload_gather (30150 tokens x 12 layers from pinned host memory).  Each prints the CUDA-event time per launch.
 """
@@ -83,13 +88,141 @@ def gemv_cases(reps: int, n_sets: int = 8):
     ops.check_status(dev)
 
 
+def tp_timeline(ctx: int, replays: int = 6):
+    """One decode step of the benchmark (Llama-3-8B shape, batch 1, ``ctx`` tokens of synthetic KV, fused kernels,
+    peer-memory exchange, CUDA graph) on the ranks of this torchrun job, with the profiling build of the library:
+    every weight-streaming and attention launch of the LAST replay reports, from its own %globaltimer stamps, when
+    it started, when the previous kernel had completed, how long it waited for the peers' flags, when its first
+    weights landed and when it ended.  Timers of different GPUs are not comparable: every figure is a difference
+    on one GPU.  Rank 0 prints its table and a summary by kind; every rank prints its totals."""
+    import ctypes
+    import os
+
+    import numpy as np
+
+    from omnikv_b200 import abi, parallel
+    from omnikv_b200.modeling import LlamaCompressorConfig, OmniKVMulLM
+    from omnikv_b200.modeling.omnikv import DecodeRunner
+    lib = abi.lib()
+    if not hasattr(lib, "omnikv_debug_gemv_trace"):
+        raise SystemExit("tp_timeline needs the profiling build: python -m omnikv_b200.build --trace and "
+                         "OMNIKV_B200_LIB=omnikv_b200/_lib/libomnikv_b200_trace.so")
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    tp = parallel.init(world, rank, dev) if world > 1 else None
+    if tp is not None:
+        tp.enable_peer_exchange(4096, dev)
+    cfg = LlamaCompressorConfig()
+    cfg.set_config_of_compressor(model_cls="multi", cache_cls="multi", do_select_layers="2,8,18", num_wait_load_layers=1,
+                                 real_offload=False, dense_more=True, num_of_selected_tokens=0.067, selector_cls="last",
+                                 window_size=16, fused_decode=True, chained_decode=False)
+    lm = OmniKVMulLM.from_config(cfg, dtype=torch.bfloat16, device=dev, seed=0, tp=tp)
+    cache = lm.new_cache().init_synthetic(1, cfg.num_key_value_heads // world, cfg.head_dim, [ctx], torch.bfloat16, dev,
+                                          seed=1 + rank, reserve=64)
+    runner = DecodeRunner(lm, None, cache=cache, first_token=torch.ones(1, 1, dtype=torch.int64, device=dev),
+                          max_new_tokens=40, use_cuda_graph=False)
+    runner.run(2)
+    torch.cuda.synchronize()
+    lib.omnikv_debug_trace_reset()
+    runner._capture()          # the capture issues the step's launches once: slots 0 .. launches-1
+    n_launch = runner.launches_per_step
+    if tp is not None:
+        torch.distributed.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    runner.run(2)
+    e0.record()
+    runner.run(replays)
+    e1.record()
+    torch.cuda.synchronize()
+    step_us = e0.elapsed_time(e1) * 1e3 / replays
+    GS, GC, GW, AC, AW = 256, 160, 12, 320, 8
+    gbuf = (ctypes.c_uint64 * (GS * GC * GW))()
+    abuf = (ctypes.c_uint64 * (GS * AC * AW))()
+    lib.omnikv_debug_gemv_trace.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    lib.omnikv_debug_attn_trace.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    assert lib.omnikv_debug_gemv_trace(gbuf, GS * GC * GW) == 0 and lib.omnikv_debug_attn_trace(abuf, GS * AC * AW) == 0
+    g = np.frombuffer(gbuf, dtype=np.uint64).astype(np.int64).reshape(GS, GC, GW)
+    a = np.frombuffer(abuf, dtype=np.uint64).astype(np.int64).reshape(GS, AC, AW)
+    names = {1000: "qkv", 1002: "qkv<-x", 1010: "resid", 1011: "resid->x", 1020: "gate_up", 1022: "gate_up<-x",
+             1030: "logits", 1032: "logits<-x", 2000: "attn dense", 2001: "attn sparse"}
+    rows = []
+    for slot in range(GS):
+        if 1000 <= g[slot, 0, 10] < 2000:
+            t = g[slot]
+            live = t[:, 0] > 0
+            n_cta = int(live.sum())
+            t = t[live]
+            flags = t[:, 9][t[:, 9] > 0]
+            rows.append(dict(slot=slot, kind=names.get(int(t[0, 10]), str(t[0, 10])), ctas=n_cta, start=t[:, 0].min(),
+                             prev_done=np.median(t[:, 1]), wait=np.median(t[:, 7] - t[:, 6]), first=np.median(t[:, 3]),
+                             rows_done=t[:, 8].max(), end=t[:, 4].max(), flags=int(flags.max()) if flags.size else 0))
+        elif 2000 <= a[slot, 0, 6] < 3000:
+            t = a[slot]
+            kind = names[int(t[0, 6])]
+            live = t[:, 0] > 0
+            t = t[live]
+            rows.append(dict(slot=slot, kind=kind, ctas=int(live.sum()), start=t[:, 0].min(), prev_done=np.median(t[:, 1]),
+                             wait=0.0, first=np.median(t[:, 2]), rows_done=t[:, 3].max(), end=t[:, 5].max(), flags=0))
+    rows.sort(key=lambda r: r["start"])
+    rows = rows[-n_launch:] if len(rows) > n_launch else rows
+    t0 = rows[0]["start"]
+    out = [f"rank {rank} of {world}: step {step_us:.0f} us by CUDA events over {replays} replays; {len(rows)} stamped launches "
+           f"(top-k, NCCL and element-wise kernels between them are not stamped and show as gaps)"]
+    if rank == 0:
+        out.append("  # kind          ctas  start   gap-to-prev-end  prev-complete  flag-wait+staging  first-data  rows-done  tail   end   duration (us)")
+    agg = {}
+    prev_end = None
+    for i, r in enumerate(rows):
+        us = lambda x: (x - t0) / 1e3  # noqa: E731
+        gap = (r["start"] - prev_end) / 1e3 if prev_end is not None else 0.0
+        dur = (r["end"] - r["start"]) / 1e3
+        tail = (r["end"] - r["rows_done"]) / 1e3
+        if rank == 0 and i < 40:
+            out.append(f"{i:3d} {r['kind']:13s} {r['ctas']:4d} {us(r['start']):7.1f} {gap:10.1f} {us(r['prev_done']) - us(r['start']):14.1f} "
+                       f"{r['wait'] / 1e3:14.1f} {us(r['first']) - us(r['start']):14.1f} {us(r['rows_done']) - us(r['start']):10.1f} {tail:6.1f} "
+                       f"{us(r['end']):7.1f} {dur:7.1f}")
+        k = agg.setdefault(r["kind"], dict(n=0, dur=0.0, gap=0.0, wait=0.0, tail=0.0, first=0.0, prev=0.0))
+        k["n"] += 1
+        k["dur"] += dur
+        k["gap"] += max(gap, 0.0)
+        k["wait"] += r["wait"] / 1e3
+        k["tail"] += tail
+        k["first"] += (r["first"] - r["start"]) / 1e3
+        k["prev"] += (r["prev_done"] - r["start"]) / 1e3
+        prev_end = r["end"]
+    span = (rows[-1]["end"] - t0) / 1e3
+    out.append(f"rank {rank} summary: first start to last end {span:.0f} us; per kind: launches, mean duration, mean gap after the "
+               "previous stamped kernel's end (negative gaps, i.e. overlap by dependent launch, counted as 0), mean time from start "
+               "until the previous kernel had completed, mean flag-wait+staging, mean time to first data, mean tail after the rows")
+    for kind, k in sorted(agg.items()):
+        n = k["n"]
+        out.append(f"  {kind:13s} n={n:3d} dur {k['dur'] / n:6.1f}  gap {k['gap'] / n:6.1f}  prev-complete {k['prev'] / n:6.1f}  "
+                   f"wait+staging {k['wait'] / n:6.1f}  first-data {k['first'] / n:6.1f}  tail {k['tail'] / n:5.1f}  (sum dur {k['dur']:.0f}, sum gap {k['gap']:.0f}, sum wait {k['wait']:.0f})")
+    text = "\n".join(out)
+    if tp is not None:
+        for r_ in range(world):
+            if r_ == rank:
+                print(text, flush=True)
+            torch.distributed.barrier()
+        runner.graph = None
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+        os._exit(0)
+    print(text)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["dense_attn", "sparse_attn", "topk", "score_window", "offload_gather", "gemv", "operator"])
+    ap.add_argument("case", choices=["dense_attn", "sparse_attn", "topk", "score_window", "offload_gather", "gemv", "operator",
+                                     "tp_timeline"])
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--ctx", type=int, default=131072)
     ap.add_argument("--splits", type=int, default=0)
     args = ap.parse_args()
+    if args.case == "tp_timeline":
+        return tp_timeline(args.ctx)
     dev = "cuda"
     B, H, KVH, d, L = 1, 32, 8, 128, args.ctx
     k_sel = int(0.067 * L)
