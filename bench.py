@@ -279,9 +279,6 @@ def tp_parity_check(lm, cfg_factory, tp, dev, rank, ctx: int = 8192, steps: int 
     lo, hi = tp.shard(cfg.num_key_value_heads)
     full = OmniKVMulLM.from_config(cfg_factory(), dtype=torch.bfloat16, device=dev, seed=0, tp=None) if rank == 0 else None
 
-    def filters_of(cache):
-        return [f for f in cache.groups]
-
     def compare(model_s, model_f, n_layers, floor=False):
         """Teacher-forced decode of (sharded or second unsharded) model_s against model_f on rank 0."""
         tok = torch.zeros(1, 1, dtype=torch.int64, device=dev)
@@ -292,7 +289,8 @@ def tp_parity_check(lm, cfg_factory, tp, dev, rank, ctx: int = 8192, steps: int 
             cache_f.stage = "decoding"
             tok = out_f.logits[:, -1].argmax(-1, keepdim=True)
             del out_f
-        dist.broadcast(tok, src=0)
+        if not floor:  # the noise floor runs on rank 0 alone: no collective in that mode
+            dist.broadcast(tok, src=0)
         buf = torch.empty(2, 1, cfg.num_key_value_heads, ctx, cfg.head_dim, dtype=torch.bfloat16, device=dev)
         keys, vals = [], []
         for layer in range(n_layers):
@@ -315,7 +313,7 @@ def tp_parity_check(lm, cfg_factory, tp, dev, rank, ctx: int = 8192, steps: int 
         for _ in range(steps):
             if floor:
                 real = ops.default_splits
-                ops.default_splits = lambda *a, **k: real(*a, **k) + 3   # the only change: attention split count
+                ops.default_splits = lambda *a, **k: 2 * real(*a, **k)   # the only change: twice the attention splits
                 try:
                     logits_s, _ = model_s._decode_step(tok, cache_s)
                 finally:
@@ -326,7 +324,7 @@ def tp_parity_check(lm, cfg_factory, tp, dev, rank, ctx: int = 8192, steps: int 
             if rank == 0:
                 logits_f, nxt = model_f._decode_step(tok, cache_f)
                 diff = max(diff, (logits_s.view(-1) - logits_f.view(-1)).abs().max().item())
-                for f in filters_of(cache_f):
+                for f in cache_f._idx:
                     a_, ca = cache_s._idx[f]
                     b_, cb = cache_f._idx[f]
                     sa, sb = set(a_[0, : int(ca[0])].tolist()), set(b_[0, : int(cb[0])].tolist())
@@ -355,8 +353,8 @@ def tp_parity_check(lm, cfg_factory, tp, dev, rank, ctx: int = 8192, steps: int 
     keep_s = cut(lm, 2)
     keep_f = cut(full, 2) if rank == 0 else None
     sel = cfg.get("do_select_layers")
-    cfg.do_select_layers = "1"
     for model in ([lm, full] if rank == 0 else [lm]):
+        model.config.do_select_layers = "1"
         for i, layer in enumerate(model.model.layers):
             layer.do_select_layers, layer.is_filter = [1], i == 1
     try:
