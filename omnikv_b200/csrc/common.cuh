@@ -159,10 +159,10 @@ __device__ __forceinline__ const unsigned char* swz128(const unsigned char* tile
 }
 
 // Host: 4-D map [B, KVH, rows, d = 128] of 16-bit elements over a cache given by element strides; box 64 elements
-// x 64 rows, 128-byte swizzle, out-of-range rows read as zero.  False when the driver entry point is missing or
-// the layout cannot be described (callers then use their cp.async variant).
+// x box_rows rows (at most 256), 128-byte swizzle, out-of-range rows read as zero.  False when the driver entry point
+// is missing or the layout cannot be described (callers then use their cp.async variant).
 bool make_kv_tensor_map(CUtensorMap* map, bool is_bf16, const void* base, int64_t rows, int KVH, int B, int64_t sr,
-                        int64_t sh, int64_t sb);
+                        int64_t sh, int64_t sb, int box_rows = 64);
 
 // ---- cp.async (16-byte, L1-bypassing) with zero fill when !valid ---------------------------
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, bool valid) {

@@ -27,10 +27,10 @@ PFN_encodeTiled encode_tiled_fn() {
 
 }  // namespace
 
-// 4-D map [B, KVH, rows, d] of 16-bit elements over a K or V cache given by element strides; box 64 x 64 rows,
+// 4-D map [B, KVH, rows, d] of 16-bit elements over a K or V cache given by element strides; box 64 x box_rows rows,
 // 128-byte swizzle.  False when the layout cannot be described (the caller then uses the cp.async variant).
 bool make_kv_tensor_map(CUtensorMap* map, bool is_bf16, const void* base, int64_t rows, int KVH, int B, int64_t sr,
-                        int64_t sh, int64_t sb) {
+                        int64_t sh, int64_t sb, int box_rows) {
   PFN_encodeTiled enc = encode_tiled_fn();
   if (!enc || rows <= 0 || rows > 0x7fffffffll) return false;
   // a dimension of extent 1 still needs a legal stride
@@ -39,7 +39,7 @@ bool make_kv_tensor_map(CUtensorMap* map, bool is_bf16, const void* base, int64_
   if (sr % 8 || sh % 8 || sb % 8 || sr <= 0 || sh <= 0 || sb <= 0) return false;
   const cuuint64_t dims[4] = {(cuuint64_t)kHeadDim, (cuuint64_t)rows, (cuuint64_t)KVH, (cuuint64_t)B};
   const cuuint64_t strides[3] = {(cuuint64_t)sr * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};  // bytes, dims 1..3
-  const cuuint32_t box[4] = {64, 64, 1, 1};
+  const cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   return enc(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
              const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,

@@ -20,6 +20,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "score_window_tc.cuh"
 
 namespace omnikv {
 namespace {
@@ -523,6 +524,24 @@ int launch_mma(const WinArgs& a, int n_chunks2, int max_len, cudaStream_t st) {
   (void)n_chunks2;
   CUtensorMap tm_k = {};
   constexpr bool is_bf16 = !std::is_same<T, __half>::value;
+  // The Blackwell tensor path (tcgen05.mma, accumulators in tensor memory) when it covers the shape and the K
+  // cache can be described by a tensor map with 128-row boxes; OMNIKV_WINDOW_TC=0 keeps the mma.sync kernels.
+  static const bool tc_on = [] {
+    const char* e = getenv("OMNIKV_WINDOW_TC");
+    return !(e && e[0] == '0');
+  }();
+  if (tc_on && window_tc_supported(G, a.KVH) &&
+      make_kv_tensor_map(&tm_k, is_bf16, a.k, max_len, a.KVH, a.B, a.k_sr, a.k_sh, a.k_sb, 128)) {
+    int dev = 0, n_sms = 0;
+    OMNIKV_CUDA_OK(cudaGetDevice(&dev));
+    OMNIKV_CUDA_OK(cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev));
+    WinTcArgs t;
+    t.qw = a.qw; t.consider_len = a.consider_len; t.part = a.part; t.c2 = a.stats;
+    t.score_out = a.score_out; t.planes_out = a.planes_out; t.score_stride = a.score_stride;
+    t.B = a.B; t.H = a.H; t.KVH = a.KVH; t.G = G; t.W = a.W; t.S = window_tc_splits(a.B, a.KVH, n_sms);
+    t.selector = a.selector; t.n_sms = n_sms; t.scale = a.scale; t.status = a.status;
+    return window_tc_launch(is_bf16 ? OMNIKV_BF16 : OMNIKV_F16, t, tm_k, max_len, st);
+  }
   static const bool tma_on = [] {
     const char* e = getenv("OMNIKV_WINDOW_TMA");
     return !(e && e[0] == '0');
@@ -559,6 +578,7 @@ int launch_f32(const WinArgs& a, int max_len, cudaStream_t st) {
 }
 
 constexpr int kPass1Splits = 55;  // 8 KV heads x 55 = 440 CTAs = 3 per SM on 148 SMs
+static_assert(kWindowTcMaxSplits >= kPass1Splits, "the partials are sized for the larger split count");
 
 size_t part_floats(int B, int H, int S) { return (size_t)B * H * WPAD * S * 2; }
 size_t stats_floats(int B, int H) { return (size_t)B * H * WPAD * 2; }
@@ -572,7 +592,7 @@ extern "C" size_t omnikv_score_window_workspace_bytes(int B, int H, int W, int m
   using namespace omnikv;
   if (B <= 0 || H <= 0 || W <= 0 || max_len <= 0) return 0;
   // pass-1 partials, merged statistics, and the per-slot planes of pass 2 (used when the caller gives none)
-  return (part_floats(B, H, kPass1Splits) + stats_floats(B, H) + plane_floats(B, W, max_len)) * sizeof(float);
+  return (part_floats(B, H, kWindowTcMaxSplits) + stats_floats(B, H) + plane_floats(B, W, max_len)) * sizeof(float);
 }
 
 extern "C" int omnikv_score_window(const omnikv_window_params* p, void* stream) {
@@ -593,7 +613,7 @@ extern "C" int omnikv_score_window(const omnikv_window_params* p, void* stream) 
   a.qw = p->qw; a.k = p->k; a.k_sb = p->k_stride_b; a.k_sh = p->k_stride_h; a.k_sr = p->k_stride_row;
   a.consider_len = p->consider_len;
   a.part = static_cast<float*>(p->workspace);
-  a.stats = a.part + part_floats(p->B, p->H, kPass1Splits);
+  a.stats = a.part + part_floats(p->B, p->H, kWindowTcMaxSplits);
   a.score_out = p->score_out; a.planes_out = p->planes_out; a.score_stride = p->score_stride;
   if (p->planes_out) {  // the caller's planes (tensor parallelism: they are MAX-reduced over ranks, then folded)
     a.planes = p->planes_out; a.plane_stride = p->score_stride;
