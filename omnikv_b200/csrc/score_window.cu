@@ -34,6 +34,12 @@ constexpr int WPAD = 16;  // window slots per head after padding
 constexpr int P1_STAGES = 3;
 constexpr int P2_STAGES = 3;
 
+// workspace layout: [pass-1 partials][merged statistics][per-slot planes]
+size_t part_floats(int B, int H, int S) { return (size_t)B * H * WPAD * S * 2; }
+size_t stats_floats(int B, int H) { return (size_t)B * H * WPAD * 2; }
+size_t plane_stride_of(int max_len) { return (size_t)ceil_div(max_len, 4) * 4; }
+size_t plane_floats(int B, int W, int max_len) { return (size_t)B * W * plane_stride_of(max_len); }
+
 struct WinArgs {
   const void* qw;
   const void* k;
@@ -536,7 +542,8 @@ int launch_mma(const WinArgs& a, int n_chunks2, int max_len, cudaStream_t st) {
     OMNIKV_CUDA_OK(cudaGetDevice(&dev));
     OMNIKV_CUDA_OK(cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev));
     WinTcArgs t;
-    t.qw = a.qw; t.consider_len = a.consider_len; t.part = a.part; t.c2 = a.stats;
+    t.qw = a.qw; t.consider_len = a.consider_len; t.part = a.part;
+    t.tplane = a.stats + stats_floats(a.B, a.H); t.tplane_stride = (int64_t)plane_stride_of(max_len);
     t.score_out = a.score_out; t.planes_out = a.planes_out; t.score_stride = a.score_stride;
     t.B = a.B; t.H = a.H; t.KVH = a.KVH; t.G = G; t.W = a.W; t.S = window_tc_splits(a.B, a.KVH, n_sms);
     t.selector = a.selector; t.n_sms = n_sms; t.scale = a.scale; t.status = a.status;
@@ -580,10 +587,6 @@ int launch_f32(const WinArgs& a, int max_len, cudaStream_t st) {
 constexpr int kPass1Splits = 55;  // 8 KV heads x 55 = 440 CTAs = 3 per SM on 148 SMs
 static_assert(kWindowTcMaxSplits >= kPass1Splits, "the partials are sized for the larger split count");
 
-size_t part_floats(int B, int H, int S) { return (size_t)B * H * WPAD * S * 2; }
-size_t stats_floats(int B, int H) { return (size_t)B * H * WPAD * 2; }
-size_t plane_stride_of(int max_len) { return (size_t)ceil_div(max_len, 4) * 4; }
-size_t plane_floats(int B, int W, int max_len) { return (size_t)B * W * plane_stride_of(max_len); }
 
 }  // namespace
 }  // namespace omnikv
@@ -592,7 +595,8 @@ extern "C" size_t omnikv_score_window_workspace_bytes(int B, int H, int W, int m
   using namespace omnikv;
   if (B <= 0 || H <= 0 || W <= 0 || max_len <= 0) return 0;
   // pass-1 partials, merged statistics, and the per-slot planes of pass 2 (used when the caller gives none)
-  return (part_floats(B, H, kWindowTcMaxSplits) + stats_floats(B, H) + plane_floats(B, W, max_len)) * sizeof(float);
+  (void)W;  // the planes are sized for the padded window: the tensor-memory path keeps 16 per-slot maxima per key there
+  return (part_floats(B, H, kWindowTcMaxSplits) + stats_floats(B, H) + plane_floats(B, WPAD, max_len)) * sizeof(float);
 }
 
 extern "C" int omnikv_score_window(const omnikv_window_params* p, void* stream) {

@@ -95,42 +95,45 @@ __device__ __forceinline__ unsigned instr_desc(int N) {
   return (1u << 4) | (fmt << 7) | (fmt << 10) | ((unsigned)(N >> 3) << 17) | ((unsigned)(TC_TILE >> 4) << 24);
 }
 
-__device__ __forceinline__ unsigned bar_or_128(bool pred) {  // OR over the 128 epilogue threads (named barrier 1)
-  unsigned r;
-  asm volatile(
-      "{\n"
-      ".reg .pred p, q;\n"
-      "setp.ne.b32 p, %1, 0;\n"
-      "barrier.cta.red.or.pred q, 1, 128, p;\n"
-      "selp.u32 %0, 1, 0, q;\n"
-      "}\n"
-      : "=r"(r)
-      : "r"((unsigned)pred)
-      : "memory");
-  return r;
-}
-__device__ __forceinline__ void bar_epi() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
-
 // Query block of KV head `kvh` -> shared memory as the B operand: N = 16 G rows (head-major, window padded to 16
 // slots, rows >= W zero) x 128, two boxes of [N rows x 128 bytes], 16-byte chunk c of row r at chunk c ^ (r & 7).
+// Loads go out in batches of eight before their stores: written as load, store, load, store ... every iteration
+// would cost a memory round trip (the compiler keeps a load behind an earlier store through a generic pointer).
 template <typename T>
 __device__ __forceinline__ void stage_q_block(unsigned char* dst, const T* qw_b, int h0, int G, int W, int tid, int nthreads) {
   const int N = G * TC_WPAD;
-  for (int i = tid; i < N * 16; i += nthreads) {
-    const int r = i >> 4, c = i & 15;  // row, 16-byte chunk of the 256-byte row
-    const int hl = r / TC_WPAD, w = r % TC_WPAD;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (w < W) v = *reinterpret_cast<const uint4*>(qw_b + ((size_t)(h0 + hl) * W + w) * kHeadDim + c * 8);
-    unsigned char* box = dst + (c >> 3) * (N * 128);
-    *reinterpret_cast<uint4*>(box + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+  const int total = N * 16;  // 16-byte chunks
+  for (int base = 0; base < total; base += 8 * nthreads) {
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + tid + u * nthreads;
+      const int r = i >> 4, c = i & 15;  // row, 16-byte chunk of the 256-byte row
+      const int hl = r / TC_WPAD, w = r % TC_WPAD;
+      v[u] = make_uint4(0, 0, 0, 0);
+      if (i < total && w < W) v[u] = *reinterpret_cast<const uint4*>(qw_b + ((size_t)(h0 + hl) * W + w) * kHeadDim + c * 8);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + tid + u * nthreads;
+      const int r = i >> 4, c = i & 15;
+      if (i < total) {
+        unsigned char* box = dst + (c >> 3) * (N * 128);
+        *reinterpret_cast<uint4*>(box + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v[u];
+      }
+    }
   }
 }
+
+// Accumulators in flight: the MMAs of a tile, their completion signal and the epilogue's read of tensor memory are a
+// chain of latencies; four buffers of N <= 64 columns (half of the 512 columns at most) keep it from pacing the stream.
+constexpr int kAccBufs = 4;
 
 struct TcShared {
   uint64_t full[4];
   uint64_t empty[4];
-  uint64_t acc_full[2];
-  uint64_t acc_empty[2];
+  uint64_t acc_full[4];
+  uint64_t acc_empty[4];
   unsigned tmem_base;
   int fail;
   int issued;  // K tiles the producer has asked for (read at teardown after a failure)
@@ -163,9 +166,9 @@ __device__ __forceinline__ void issue_mmas(TcShared& sh, unsigned char* ring, un
                                            int* status) {
   const unsigned idesc = instr_desc<T>(N);
   for (int j = 0; j < n_sub; ++j) {
-    const int s = j % STAGES, buf = j & 1;
+    const int s = j % STAGES, buf = j % kAccBufs;
     if (!mbar_wait(&sh.full[s], (j / STAGES) & 1, &sh.fail) ||
-        !mbar_wait(&sh.acc_empty[buf], ((j >> 1) & 1) ^ 1, &sh.fail)) {
+        !mbar_wait(&sh.acc_empty[buf], ((j / kAccBufs) & 1) ^ 1, &sh.fail)) {
       if (!sh.fail && status) atomicExch(status, 5);
       sh.fail = 1;
       return;
@@ -175,7 +178,7 @@ __device__ __forceinline__ void issue_mmas(TcShared& sh, unsigned char* ring, un
     sub(j, row0, kvh_slot);  // kvh_slot: which resident query block this sub-tile meets
     const unsigned a_base = smem_u32(ring + (size_t)s * TC_KTILE_BYTES);
     const unsigned b_base = smem_u32(q_s + (size_t)kvh_slot * N * 256);
-    const unsigned d_tmem = sh.tmem_base + (unsigned)(buf * N);
+    const unsigned d_tmem = sh.tmem_base + (unsigned)(buf * N);  // accumulator buf: columns [buf * N, +N)
 #pragma unroll
     for (int k = 0; k < 8; ++k) {  // 8 steps of 16 elements along head_dim: 4 per 128-byte box row, then the other box
       const uint64_t a_desc = smem_desc_sw128(a_base + (k >> 2) * TC_BOX_BYTES + (k & 3) * 32);
@@ -187,19 +190,22 @@ __device__ __forceinline__ void issue_mmas(TcShared& sh, unsigned char* ring, un
   }
 }
 
-// Epilogue side: wait for accumulator `j`, read this thread's N logits into v (N <= 128), hand the buffer back.
-template <int N>
-__device__ __forceinline__ bool take_accumulator(TcShared& sh, int j, float (&v)[N], int warp, int* status) {
-  const int buf = j & 1;
-  if (!mbar_wait(&sh.acc_full[buf], (j >> 1) & 1, &sh.fail)) {
+// Epilogue side: wait for accumulator `j`, read NC of this thread's logits (columns col0 .. col0 + NC of its TMEM
+// lane) into v, hand the buffer back.  lane_quarter = warp & 3 (a warp reaches the 32 lanes of its quarter only).
+template <int NC>
+__device__ __forceinline__ bool take_accumulator(TcShared& sh, int j, float (&v)[NC], int lane_quarter, int acc_col0,
+                                                 int* status) {
+  static_assert(NC % 16 == 0, "columns are read 16 at a time");
+  const int buf = j % kAccBufs;
+  if (!mbar_wait(&sh.acc_full[buf], (j / kAccBufs) & 1, &sh.fail)) {
     if (!sh.fail && status) atomicExch(status, 5);
     sh.fail = 1;
     return false;
   }
   tc_fence_after();
-  const unsigned taddr = sh.tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)(buf * N);
+  const unsigned taddr = sh.tmem_base + ((unsigned)(lane_quarter * 32) << 16) + (unsigned)acc_col0;
 #pragma unroll
-  for (int c = 0; c < N; c += 16) tmem_ld16(taddr + c, *reinterpret_cast<float(*)[16]>(&v[c]));
+  for (int c = 0; c < NC; c += 16) tmem_ld16(taddr + c, *reinterpret_cast<float(*)[16]>(&v[c]));
   tmem_ld_wait();
   tc_fence_before();
   mbar_arrive(&sh.acc_empty[buf]);
@@ -207,7 +213,7 @@ __device__ __forceinline__ bool take_accumulator(TcShared& sh, int j, float (&v)
 }
 
 template <int STAGES>
-__device__ __forceinline__ void tc_setup(TcShared& sh, unsigned ncols, int warp) {
+__device__ __forceinline__ void tc_setup(TcShared& sh, unsigned ncols, int warp, int n_epilogue_threads) {
   if (threadIdx.x == 0) {
     sh.fail = 0;
     sh.issued = 0;
@@ -216,9 +222,9 @@ __device__ __forceinline__ void tc_setup(TcShared& sh, unsigned ncols, int warp)
       mbar_init(&sh.full[s], 1);
       mbar_init(&sh.empty[s], 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kAccBufs; ++i) {
       mbar_init(&sh.acc_full[i], 1);
-      mbar_init(&sh.acc_empty[i], 128);
+      mbar_init(&sh.acc_empty[i], n_epilogue_threads);
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -235,13 +241,13 @@ __device__ __forceinline__ void tc_setup(TcShared& sh, unsigned ncols, int warp)
 }
 
 template <int STAGES>
-__device__ __forceinline__ void tc_teardown(TcShared& sh, unsigned ncols, int warp) {
+__device__ __forceinline__ void tc_teardown(TcShared& sh, unsigned ncols, int warp, int producer_tid) {
   tc_fence_before();
   __syncthreads();  // every role is out of its loop: no MMA, copy or TMEM read of this CTA is still wanted
   if (sh.fail) {
     // a wait ran out: copies that were asked for may still be on their way into this CTA's shared memory.  Wait
     // (bounded) for each stage's last requested tile before the memory is given up.
-    if (threadIdx.x == 128) {
+    if ((int)threadIdx.x == producer_tid) {
       for (int s = 0; s < STAGES; ++s) {
         const int last = sh.issued - 1 - ((sh.issued - 1 - s) % STAGES + STAGES) % STAGES;  // last j < issued with j % STAGES == s
         if (sh.issued > s && last >= 0) mbar_wait(&sh.full[s], (last / STAGES) & 1);
@@ -255,17 +261,56 @@ __device__ __forceinline__ void tc_teardown(TcShared& sh, unsigned ncols, int wa
   }
 }
 
-__host__ __device__ constexpr unsigned tmem_cols(int N) { return 2 * N <= 32 ? 32u : (2 * N <= 64 ? 64u : (2 * N <= 128 ? 128u : 256u)); }
+__host__ __device__ constexpr unsigned tmem_cols(int N) {  // kAccBufs accumulators of N columns, a power of two >= 32
+  return kAccBufs * N <= 32 ? 32u : (kAccBufs * N <= 64 ? 64u : (kAccBufs * N <= 128 ? 128u : (kAccBufs * N <= 256 ? 256u : 512u)));
+}
+
+// 2^x on the special-function unit (x <= 16 here, -inf gives 0; relative error about 2^-22)
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
 
 // ---- pass 1 ------------------------------------------------------------------------------------------------------
+// 16 G accumulator columns per key.  With 32 columns or more two warps share a TMEM lane quarter and split the
+// columns (eight epilogue warps, two per scheduler: one warp alone cannot hide its own latencies, and the exp2 and
+// add per (key, column) of this pass made a four-warp epilogue the limit, not the K stream).
 constexpr int P1_STAGES = 4;
+template <int G>
+struct P1Shape {
+  static constexpr int N = G * TC_WPAD;
+  static constexpr int HALVES = N >= 32 ? 2 : 1;
+  static constexpr int NC = N / HALVES;        // columns per epilogue thread
+  static constexpr int EPI = 128 * HALVES;     // epilogue threads
+  static constexpr int THREADS = EPI + 64;     // + TMA producer warp + MMA warp
+};
+
+template <int EPI>
+__device__ __forceinline__ unsigned bar_or_epi(bool pred) {  // OR over the epilogue threads (named barrier 1)
+  unsigned r;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.b32 p, %1, 0;\n"
+      "barrier.cta.red.or.pred q, 1, %2, p;\n"
+      "selp.u32 %0, 1, 0, q;\n"
+      "}\n"
+      : "=r"(r)
+      : "r"((unsigned)pred), "n"(EPI)
+      : "memory");
+  return r;
+}
+template <int EPI>
+__device__ __forceinline__ void bar_sync_epi() { asm volatile("bar.sync 1, %0;\n" ::"n"(EPI) : "memory"); }
 
 template <typename T, int G>
-__global__ void __launch_bounds__(TC_THREADS, 1) window_tc_pass1(const WinTcArgs a, const __grid_constant__ CUtensorMap tm_k) {
-  constexpr int N = G * TC_WPAD;
+__global__ void __launch_bounds__(P1Shape<G>::THREADS, 1) window_tc_pass1(const WinTcArgs a, const __grid_constant__ CUtensorMap tm_k) {
+  using S_ = P1Shape<G>;
+  constexpr int N = S_::N, NC = S_::NC, EPI = S_::EPI, THREADS = S_::THREADS;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ TcShared sh;
-  __shared__ float off_s[N];    // per-column offset b (log2 domain) shared by the CTA
+  __shared__ float off_s[N];    // per-column offset (log2 domain) shared by the CTA
   __shared__ float shift_s[N];
   __shared__ float cmax_s[4][N];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -279,51 +324,55 @@ __global__ void __launch_bounds__(TC_THREADS, 1) window_tc_pass1(const WinTcArgs
   const int n_sub = r1 > r0 ? ceil_div(r1 - r0, TC_TILE) : 0;
   float* part = a.part + ((((size_t)b * a.H + kvh * G) * TC_WPAD) * a.S + split) * 2;  // + (hl*16 + w) * S * 2
   if (n_sub == 0) {
-    for (int c = tid; c < N; c += TC_THREADS) {
+    for (int c = tid; c < N; c += THREADS) {
       part[(size_t)c * a.S * 2 + 0] = -INFINITY;
       part[(size_t)c * a.S * 2 + 1] = 0.f;
     }
     return;
   }
-  stage_q_block<T>(q_s, static_cast<const T*>(a.qw) + (size_t)b * a.H * a.W * kHeadDim, kvh * G, G, a.W, tid, TC_THREADS);
-  tc_setup<P1_STAGES>(sh, tmem_cols(N), warp);
-  auto sub = [&](int j, int& row0, int& slot) { row0 = r0 + j * TC_TILE; slot = 0; };
-  if (warp == 4) {
+  stage_q_block<T>(q_s, static_cast<const T*>(a.qw) + (size_t)b * a.H * a.W * kHeadDim, kvh * G, G, a.W, tid, THREADS);
+  tc_setup<P1_STAGES>(sh, tmem_cols(N), warp, EPI);
+  if (warp == EPI / 32) {
     if (lane == 0) {
       auto psub = [&](int j, int& row0, int& kv) { row0 = r0 + j * TC_TILE; kv = kvh; };
       produce_tiles<P1_STAGES>(sh, ring, &tm_k, n_sub, b, psub, a.status);
     }
-  } else if (warp == 5) {
-    if (lane == 0) issue_mmas<T, P1_STAGES>(sh, ring, q_s, N, n_sub, sub, a.status);
+  } else if (warp == EPI / 32 + 1) {
+    if (lane == 0) {
+      auto sub = [&](int j, int& row0, int& slot) { row0 = r0 + j * TC_TILE; slot = 0; };
+      issue_mmas<T, P1_STAGES>(sh, ring, q_s, N, n_sub, sub, a.status);
+    }
   } else {
+    const int quarter = warp & 3, half = warp >> 2;   // key = quarter * 32 + lane of the tile, columns [half * NC, +NC)
+    const int key = quarter * 32 + lane, col0 = half * NC;
     const float k2 = a.scale * kLog2e;
-    float l[N];
+    float l[NC];
 #pragma unroll
-    for (int c = 0; c < N; ++c) l[c] = 0.f;
+    for (int c = 0; c < NC; ++c) l[c] = 0.f;
     if (tid < N) off_s[tid] = 0.f;
-    bar_epi();
+    bar_sync_epi<EPI>();
     for (int j = 0; j < n_sub; ++j) {
-      float x[N];
-      const bool ok = take_accumulator<N>(sh, j, x, warp, a.status);
-      const bool valid = ok && r0 + j * TC_TILE + tid < r1;
+      float x[NC];
+      const bool ok = take_accumulator<NC>(sh, j, x, quarter, (j % kAccBufs) * N + col0, a.status);
+      const bool valid = ok && r0 + j * TC_TILE + key < r1;
       float tmax = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < N; ++c) {
-        x[c] = valid ? fmaf(x[c], k2, -off_s[c]) : -INFINITY;
+      for (int c = 0; c < NC; ++c) {
+        x[c] = valid ? fmaf(x[c], k2, -off_s[col0 + c]) : -INFINITY;
         tmax = fmaxf(tmax, x[c]);
       }
       // The shared offsets are set from the first tile and raised when some logit has outgrown them by more than
       // 2^16 (a sum of 2^16-sized terms cannot overflow fp32, and smaller terms lose nothing that matters).
-      if (bar_or_128(!ok || j == 0 || tmax > 16.f)) {
-        if (bar_or_128(!ok)) break;  // a wait ran out somewhere: all 128 threads leave together
+      if (bar_or_epi<EPI>(!ok || j == 0 || tmax > 16.f)) {
+        if (bar_or_epi<EPI>(!ok)) break;  // a wait ran out somewhere: all epilogue threads leave together
 #pragma unroll
-        for (int c = 0; c < N; ++c) {
+        for (int c = 0; c < NC; ++c) {
           float m = x[c];
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-          if (lane == 0) cmax_s[warp][c] = m;
+          if (lane == 0) cmax_s[quarter][col0 + c] = m;
         }
-        bar_epi();
+        bar_sync_epi<EPI>();
         if (tid < N) {
           float m = fmaxf(fmaxf(cmax_s[0][tid], cmax_s[1][tid]), fmaxf(cmax_s[2][tid], cmax_s[3][tid]));
           // first tile: the column's maximum becomes the offset (whatever its sign); later: only ever raise it
@@ -331,28 +380,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1) window_tc_pass1(const WinTcArgs
           shift_s[tid] = s;
           off_s[tid] += s;
         }
-        bar_epi();
+        bar_sync_epi<EPI>();
 #pragma unroll
-        for (int c = 0; c < N; ++c) {
-          const float s = shift_s[c];
-          if (j > 0) l[c] *= exp2f(-s);
+        for (int c = 0; c < NC; ++c) {
+          const float s = shift_s[col0 + c];
+          if (j > 0) l[c] *= ex2_fast(-s);
           x[c] -= s;
         }
-        bar_epi();  // shift_s is free again before anybody could rewrite it
+        bar_sync_epi<EPI>();  // shift_s is free again before anybody could rewrite it
       }
       if (valid) {
 #pragma unroll
-        for (int c = 0; c < N; ++c) l[c] += exp2f(x[c]);
+        for (int c = 0; c < NC; ++c) l[c] += ex2_fast(x[c]);
       }
     }
     // add the 128 private sums of every column (through shared memory: the ring is idle by now)
-    bar_epi();
-    float* red = reinterpret_cast<float*>(ring);  // [128][N + 1]
+    bar_sync_epi<EPI>();
+    float* red = reinterpret_cast<float*>(ring);  // [128 keys][N + 1]
     if (!sh.fail) {
 #pragma unroll
-      for (int c = 0; c < N; ++c) red[tid * (N + 1) + c] = l[c];
+      for (int c = 0; c < NC; ++c) red[key * (N + 1) + col0 + c] = l[c];
     }
-    bar_epi();
+    bar_sync_epi<EPI>();
     if (tid < N && !sh.fail) {
       float tot = 0.f;
       for (int t = 0; t < 128; ++t) tot += red[t * (N + 1) + tid];
@@ -360,57 +409,72 @@ __global__ void __launch_bounds__(TC_THREADS, 1) window_tc_pass1(const WinTcArgs
       part[(size_t)tid * a.S * 2 + 1] = tot;
     }
   }
-  tc_teardown<P1_STAGES>(sh, tmem_cols(N), warp);
-}
-
-// splits -> c = m + log2(l) per (b, h, slot) row.  One thread per row; (m, l) pairs are in the log2 domain.
-__global__ void window_tc_merge(const float* __restrict__ part, float* __restrict__ c2, int rows, int S) {
-  const int r = blockIdx.x * blockDim.x + threadIdx.x;
-  if (r >= rows) return;
-  float M = -INFINITY;
-  for (int s = 0; s < S; ++s)
-    if (part[((size_t)r * S + s) * 2 + 1] > 0.f) M = fmaxf(M, part[((size_t)r * S + s) * 2]);
-  float L = 0.f;
-  for (int s = 0; s < S; ++s) {
-    const float l = part[((size_t)r * S + s) * 2 + 1];
-    if (l > 0.f) L += l * exp2f(part[((size_t)r * S + s) * 2] - M);
-  }
-  c2[r] = L > 0.f ? M + log2f(L) : INFINITY;  // an empty row (padded window slot) normalises everything to 0
+  tc_teardown<P1_STAGES>(sh, tmem_cols(N), warp, EPI);
 }
 
 // ---- pass 2 ------------------------------------------------------------------------------------------------------
-constexpr int P2_STAGES = 2;
+// One launch per GROUP of KV heads whose query blocks fit in shared memory beside a four-tile K ring (64 KB of
+// queries: four KV heads of a group of four query heads).  A launch walks its KV heads for every key tile and keeps
+// the running max over heads per window slot in registers; between launches the 16 per-slot maxima of every key
+// (log domain, 64 bytes per key against the 2 KB of K that a KV-head group streams for it) go through a plane in the
+// workspace.  The last launch turns them into the score.  With a two-tile ring -- all that fits beside eight
+// resident query blocks -- the stream ran at half the rate: the ring depth is the memory parallelism of an SM.
+constexpr int P2_STAGES = 4;
 
 template <typename T, int G>
-__global__ void __launch_bounds__(TC_THREADS, 1) window_tc_pass2(const WinTcArgs a, const __grid_constant__ CUtensorMap tm_k) {
+__global__ void __launch_bounds__(TC_THREADS, 1) window_tc_pass2(const WinTcArgs a, const __grid_constant__ CUtensorMap tm_k,
+                                                                 const int kvh0, const int n_kvh, const int first, const int last) {
   constexpr int N = G * TC_WPAD;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ TcShared sh;
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* ring = smem;
-  unsigned char* q_s = smem + P2_STAGES * TC_KTILE_BYTES;                   // [KVH][N rows x 256 bytes]
-  float* c2_s = reinterpret_cast<float*>(q_s + (size_t)a.KVH * N * 256);  // [KVH * N]
+  unsigned char* q_s = smem + P2_STAGES * TC_KTILE_BYTES;                 // [n_kvh][N rows x 256 bytes]
+  float* c2_s = reinterpret_cast<float*>(q_s + (size_t)n_kvh * N * 256);  // [n_kvh * N]
   const int b = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n = a.consider_len[b];
   const int n_tiles = ceil_div(n, TC_TILE);
   const int my_tiles = (int)blockIdx.x < n_tiles ? ceil_div(n_tiles - (int)blockIdx.x, (int)gridDim.x) : 0;
   if (my_tiles == 0) return;
-  const int n_sub = my_tiles * a.KVH;
+  const int n_sub = my_tiles * n_kvh;
   const T* qb = static_cast<const T*>(a.qw) + (size_t)b * a.H * a.W * kHeadDim;
-  for (int kv = 0; kv < a.KVH; ++kv) stage_q_block<T>(q_s + (size_t)kv * N * 256, qb, kv * G, G, a.W, tid, TC_THREADS);
-  for (int i = tid; i < a.KVH * N; i += TC_THREADS) c2_s[i] = a.c2[(size_t)b * a.H * TC_WPAD + i];
-  tc_setup<P2_STAGES>(sh, tmem_cols(N), warp);
-  const int KVH = a.KVH;
+  for (int kv = 0; kv < n_kvh; ++kv)
+    stage_q_block<T>(q_s + (size_t)kv * N * 256, qb, (kvh0 + kv) * G, G, a.W, tid, TC_THREADS);
+  tc_setup<P2_STAGES>(sh, tmem_cols(N), warp, 128);
   auto sub = [&](int j, int& row0, int& kv) {
-    row0 = ((int)blockIdx.x + (j / KVH) * (int)gridDim.x) * TC_TILE;
-    kv = j % KVH;
+    row0 = ((int)blockIdx.x + (j / n_kvh) * (int)gridDim.x) * TC_TILE;
+    kv = j % n_kvh;
   };
   if (warp == 4) {
-    if (lane == 0) produce_tiles<P2_STAGES>(sh, ring, &tm_k, n_sub, b, sub, a.status);
+    if (lane == 0) {
+      auto psub = [&](int j, int& row0, int& kv) { sub(j, row0, kv); kv += kvh0; };
+      produce_tiles<P2_STAGES>(sh, ring, &tm_k, n_sub, b, psub, a.status);
+    }
   } else if (warp == 5) {
     if (lane == 0) issue_mmas<T, P2_STAGES>(sh, ring, q_s, N, n_sub, sub, a.status);
   } else {
+    // log2 of the softmax normaliser of this launch's (head, slot) rows, from the splits of pass 1 (what a separate
+    // merge kernel would do; here it runs while the first K tiles are on their way)
+    for (int i = tid; i < n_kvh * N; i += 128) {
+      const float2* pr = reinterpret_cast<const float2*>(a.part) + (((size_t)b * a.H + kvh0 * G) * TC_WPAD + i) * a.S;
+      float M = -INFINITY, L = 0.f;
+      for (int s0 = 0; s0 < a.S; s0 += 16) {  // sixteen (offset, sum) pairs per round trip
+        float2 ml[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) ml[u] = s0 + u < a.S ? pr[s0 + u] : make_float2(-INFINITY, 0.f);
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          if (ml[u].y > 0.f) {
+            const float Mn = fmaxf(M, ml[u].x);
+            L = L * exp2f(M - Mn) + ml[u].y * exp2f(ml[u].x - Mn);
+            M = Mn;
+          }
+        }
+      }
+      c2_s[i] = L > 0.f ? M + log2f(L) : INFINITY;  // an empty row normalises everything to 0
+    }
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");
     const float k2 = a.scale * kLog2e;
     float wgt[TC_WPAD];
 #pragma unroll
@@ -420,70 +484,82 @@ __global__ void __launch_bounds__(TC_THREADS, 1) window_tc_pass2(const WinTcArgs
       wgt[w] = v;
     }
     float t[TC_WPAD];
+    float* tplane = a.tplane + (size_t)b * TC_WPAD * a.tplane_stride;  // [16][tplane_stride] per sequence
     for (int j = 0; j < n_sub; ++j) {
       float x[N];
-      if (!take_accumulator<N>(sh, j, x, warp, a.status)) break;
-      const int kv = j % KVH;
+      if (!take_accumulator<N>(sh, j, x, warp, (j % kAccBufs) * N, a.status)) break;
+      const int kv = j % n_kvh;
+      const int p = ((int)blockIdx.x + (j / n_kvh) * (int)gridDim.x) * TC_TILE + tid;
       if (kv == 0) {
 #pragma unroll
-        for (int w = 0; w < TC_WPAD; ++w) t[w] = -INFINITY;
+        for (int w = 0; w < TC_WPAD; ++w) t[w] = (first || p >= n) ? -INFINITY : tplane[(size_t)w * a.tplane_stride + p];
       }
       const float* c2 = c2_s + kv * N;
 #pragma unroll
       for (int c = 0; c < N; ++c) t[c % TC_WPAD] = fmaxf(t[c % TC_WPAD], fmaf(x[c], k2, -c2[c]));
-      if (kv == KVH - 1) {
-        const int p = ((int)blockIdx.x + (j / KVH) * (int)gridDim.x) * TC_TILE + tid;
-        if (p < n) {
+      if (kv == n_kvh - 1 && p < n) {
+        if (!last) {
+#pragma unroll
+          for (int w = 0; w < TC_WPAD; ++w) tplane[(size_t)w * a.tplane_stride + p] = t[w];
+        } else {
           if (a.planes_out) {
 #pragma unroll
             for (int w = 0; w < TC_WPAD; ++w)
-              if (w < a.W) a.planes_out[((size_t)b * a.W + w) * a.score_stride + p] = exp2f(t[w]);
+              if (w < a.W) a.planes_out[((size_t)b * a.W + w) * a.score_stride + p] = ex2_fast(t[w]);
           }
           if (a.score_out) {
             float s = 0.f;
 #pragma unroll
-            for (int w = 0; w < TC_WPAD; ++w) s = fmaf(wgt[w], exp2f(t[w]), s);
+            for (int w = 0; w < TC_WPAD; ++w) s = fmaf(wgt[w], ex2_fast(t[w]), s);
             a.score_out[(size_t)b * a.score_stride + p] = s;
           }
         }
       }
     }
   }
-  tc_teardown<P2_STAGES>(sh, tmem_cols(N), warp);
+  tc_teardown<P2_STAGES>(sh, tmem_cols(N), warp, 128);
 }
+
+constexpr int kP2QueryBytes = 64 * 1024;  // query blocks resident per pass-2 launch
 
 template <typename T, int G>
 int launch_tc(const WinTcArgs& a, const CUtensorMap& tm_k, int max_len, cudaStream_t st) {
   constexpr int N = G * TC_WPAD;
+  const int group = kP2QueryBytes / (N * 256) < a.KVH ? kP2QueryBytes / (N * 256) : a.KVH;  // KV heads per pass-2 launch
   const int smem1 = P1_STAGES * TC_KTILE_BYTES + N * 256 + 1024;
-  const int smem2 = P2_STAGES * TC_KTILE_BYTES + a.KVH * N * 256 + a.KVH * N * (int)sizeof(float) + 1024;
+  const int smem2 = P2_STAGES * TC_KTILE_BYTES + group * N * 256 + group * N * (int)sizeof(float) + 1024;
   OMNIKV_CUDA_OK(cudaFuncSetAttribute(window_tc_pass1<T, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1));
   OMNIKV_CUDA_OK(cudaFuncSetAttribute(window_tc_pass2<T, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
-  window_tc_pass1<T, G><<<dim3(a.S, a.KVH, a.B), TC_THREADS, smem1, st>>>(a, tm_k);
-  OMNIKV_CUDA_OK(cudaGetLastError());
-  const int rows = a.B * a.H * TC_WPAD;
-  window_tc_merge<<<ceil_div(rows, 128), 128, 0, st>>>(a.part, a.c2, rows, a.S);
+  window_tc_pass1<T, G><<<dim3(a.S, a.KVH, a.B), P1Shape<G>::THREADS, smem1, st>>>(a, tm_k);
   OMNIKV_CUDA_OK(cudaGetLastError());
   const int max_tiles = ceil_div(max_len, TC_TILE);
   int per_seq = ceil_div(a.n_sms, a.B);
   if (per_seq > max_tiles) per_seq = max_tiles;
-  window_tc_pass2<T, G><<<dim3(per_seq, a.B), TC_THREADS, smem2, st>>>(a, tm_k);
-  OMNIKV_CUDA_OK(cudaGetLastError());
+  for (int kvh0 = 0; kvh0 < a.KVH; kvh0 += group) {
+    const int n_kvh = a.KVH - kvh0 < group ? a.KVH - kvh0 : group;
+    window_tc_pass2<T, G><<<dim3(per_seq, a.B), TC_THREADS, smem2, st>>>(a, tm_k, kvh0, n_kvh, kvh0 == 0 ? 1 : 0,
+                                                                        kvh0 + n_kvh >= a.KVH ? 1 : 0);
+    OMNIKV_CUDA_OK(cudaGetLastError());
+  }
   return OMNIKV_OK;
 }
 
 }  // namespace
 
 bool window_tc_supported(int G, int KVH) {
-  if (G != 1 && G != 2 && G != 4) return false;  // 16 G accumulator columns and as many running sums per thread
-  const int N = G * TC_WPAD;
-  // pass 2 keeps every KV head's query block resident beside a two-tile ring
-  return P2_STAGES * TC_KTILE_BYTES + KVH * N * 256 + KVH * N * 4 + 1024 <= 200 * 1024;
+  (void)KVH;
+  return G == 1 || G == 2 || G == 4;  // 16 G accumulator columns and as many running sums per key
 }
 
 int window_tc_splits(int B, int KVH, int n_sms) {
-  int s = n_sms / (B * KVH > 0 ? B * KVH : 1);  // one wave of one CTA per SM (a thread holds 128 fp32 values)
+  int s = n_sms / (B * KVH > 0 ? B * KVH : 1);  // one wave of one CTA per SM
   return s < 1 ? 1 : (s > kWindowTcMaxSplits ? kWindowTcMaxSplits : s);
+}
+
+int window_tc_launches(int G, int KVH) {
+  const int N = G * TC_WPAD;
+  const int group = kP2QueryBytes / (N * 256) < KVH ? kP2QueryBytes / (N * 256) : KVH;
+  return 1 + ceil_div(KVH, group);
 }
 
 int window_tc_launch(int dtype, const WinTcArgs& a, const CUtensorMap& tm_k, int max_len, cudaStream_t st) {

@@ -11,7 +11,9 @@ struct WinTcArgs {
   const void* qw;              // [B, H, W, d]
   const int* consider_len;     // device [B]
   float* part;                 // [B][H][16][S][2]  pass-1 partials (offset, sum), log2 domain
-  float* c2;                   // [B][H][16]        log2 of the softmax normaliser per (head, window slot)
+  float* tplane;               // [B][16][tplane_stride] running max over heads per window slot (log domain), between
+                               // the launches of pass 2
+  int64_t tplane_stride;
   float* score_out;            // [B, score_stride] or nullptr
   float* planes_out;           // [B, W, score_stride] or nullptr (max over the local heads per slot)
   int64_t score_stride;
@@ -24,6 +26,7 @@ struct WinTcArgs {
 // memory beside the K ring; a thread holds one accumulator row of 16 G columns in registers).
 bool window_tc_supported(int G, int KVH);
 int window_tc_splits(int B, int KVH, int n_sms);
+int window_tc_launches(int G, int KVH);  // kernels one call launches
 // tm_k: tensor map over the K cache [B, KVH, rows, 128] with boxes of 64 elements x 128 rows, 128-byte swizzle.
 int window_tc_launch(int dtype, const WinTcArgs& a, const CUtensorMap& tm_k, int max_len, cudaStream_t st);
 

@@ -220,6 +220,8 @@ def main():
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--ctx", type=int, default=131072)
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--kv-layout", default="interleaved", choices=["interleaved", "planes"],
+                    help="dense_attn / score_window: K|V rows of a head interleaved, or in two separate runs of rows")
     args = ap.parse_args()
     if args.case == "tp_timeline":
         return tp_timeline(args.ctx)
@@ -258,8 +260,12 @@ def main():
     # K and V share one buffer as in the package's cache: head-major with K|V rows interleaved for a dense layer,
     # token-major for a sparse layer
     if args.case in ("dense_attn", "score_window"):
-        kv = rnd(B, KVH, L + 64, 2, d)
-        kc, vc, q = kv[:, :, :, 0, :], kv[:, :, :, 1, :], rnd(B, H, d)
+        if args.kv_layout == "planes":  # K and V of a head in separate runs of rows (a filter layer under a window selector)
+            kv = rnd(B, KVH, 2, L + 64, d)
+            kc, vc, q = kv[:, :, 0], kv[:, :, 1], rnd(B, H, d)
+        else:                            # K and V rows of a head interleaved (every other dense layer)
+            kv = rnd(B, KVH, L + 64, 2, d)
+            kc, vc, q = kv[:, :, :, 0, :], kv[:, :, :, 1, :], rnd(B, H, d)
     if args.case == "sparse_attn":
         kv = rnd(B, L + 64, KVH, 2, d)
         kc, vc, q = kv[:, :, :, 0, :].permute(0, 2, 1, 3), kv[:, :, :, 1, :].permute(0, 2, 1, 3), rnd(B, H, d)
