@@ -130,8 +130,8 @@ __device__ __forceinline__ void stage_q_block(unsigned char* dst, const T* qw_b,
 constexpr int kAccBufs = 4;
 
 struct TcShared {
-  uint64_t full[4];
-  uint64_t empty[4];
+  uint64_t full[6];
+  uint64_t empty[6];
   uint64_t acc_full[4];
   uint64_t acc_empty[4];
   unsigned tmem_base;
@@ -276,7 +276,7 @@ __device__ __forceinline__ float ex2_fast(float x) {
 // 16 G accumulator columns per key.  With 32 columns or more two warps share a TMEM lane quarter and split the
 // columns (eight epilogue warps, two per scheduler: one warp alone cannot hide its own latencies, and the exp2 and
 // add per (key, column) of this pass made a four-warp epilogue the limit, not the K stream).
-constexpr int P1_STAGES = 4;
+constexpr int P1_STAGES = 2;  // two CTAs per SM (see window_tc_pass1): 128 KB of K in flight per SM
 template <int G>
 struct P1Shape {
   static constexpr int N = G * TC_WPAD;
@@ -305,7 +305,7 @@ template <int EPI>
 __device__ __forceinline__ void bar_sync_epi() { asm volatile("bar.sync 1, %0;\n" ::"n"(EPI) : "memory"); }
 
 template <typename T, int G>
-__global__ void __launch_bounds__(P1Shape<G>::THREADS, 1) window_tc_pass1(const WinTcArgs a, const __grid_constant__ CUtensorMap tm_k) {
+__global__ void __launch_bounds__(P1Shape<G>::THREADS, 2) window_tc_pass1(const WinTcArgs a, const __grid_constant__ CUtensorMap tm_k) {
   using S_ = P1Shape<G>;
   constexpr int N = S_::N, NC = S_::NC, EPI = S_::EPI, THREADS = S_::THREADS;
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -520,7 +520,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) window_tc_pass2(const WinTcArgs
   tc_teardown<P2_STAGES>(sh, tmem_cols(N), warp, 128);
 }
 
-constexpr int kP2QueryBytes = 64 * 1024;  // query blocks resident per pass-2 launch
+constexpr int kP2QueryBytes = 64 * 1024;  // query blocks resident per pass-2 launch (four KV heads of four query heads)
 
 template <typename T, int G>
 int launch_tc(const WinTcArgs& a, const CUtensorMap& tm_k, int max_len, cudaStream_t st) {
@@ -552,7 +552,7 @@ bool window_tc_supported(int G, int KVH) {
 }
 
 int window_tc_splits(int B, int KVH, int n_sms) {
-  int s = n_sms / (B * KVH > 0 ? B * KVH : 1);  // one wave of one CTA per SM
+  int s = 2 * (n_sms / (B * KVH > 0 ? B * KVH : 1));  // one wave of two CTAs per SM
   return s < 1 ? 1 : (s > kWindowTcMaxSplits ? kWindowTcMaxSplits : s);
 }
 
