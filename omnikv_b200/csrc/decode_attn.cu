@@ -127,15 +127,34 @@ __device__ __forceinline__ void finish_group(const AttnArgs& a, int b, int kvh, 
   for (int r = warp; r < G; r += NWARPS) {
     const int h = kvh * G + r;
     const size_t base = (size_t)(b * a.H + h) * S;
-    float M = -INFINITY;
-    for (int s = lane; s < S; s += 32) M = fmaxf(M, __ldcg(a.ws_ml + (base + s) * 2));
+    // Everything that does not depend on the weights is asked for at once: the (m, l) pairs of all splits (two
+    // per lane cover 64 splits, the rest in a loop) AND the first sixteen partial outputs -- the merge is a chain
+    // of L2 round trips on the critical path of every attention call, so it should be as short as possible.
+    const float4* op = reinterpret_cast<const float4*>(a.ws_o + base * kHeadDim) + lane;
+    const float2* mlp = reinterpret_cast<const float2*>(a.ws_ml + base * 2);
+    float2 ml0 = make_float2(-INFINITY, 0.f), ml1 = ml0;
+    if (lane < S) ml0 = __ldcg(mlp + lane);
+    if (lane + 32 < S) ml1 = __ldcg(mlp + lane + 32);
+    constexpr int PRE = 16;
+    float4 o_pre[PRE];
+#pragma unroll
+    for (int s = 0; s < PRE; ++s) o_pre[s] = s < S ? __ldcg(op + (size_t)s * (kHeadDim / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float M = fmaxf(ml0.x, ml1.x);
+    for (int s = lane + 64; s < S; s += 32) M = fmaxf(M, __ldcg(a.ws_ml + (base + s) * 2));
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
     const float Mu = (M == -INFINITY) ? 0.f : M;
     float l = 0.f;
     __syncwarp();
-    for (int s = lane; s < S; s += 32) {
-      const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.ws_ml + (base + s) * 2));
+    {
+      const float w0 = (ml0.x == -INFINITY) ? 0.f : exp2f((ml0.x - Mu) * kLog2e);
+      const float w1 = (ml1.x == -INFINITY) ? 0.f : exp2f((ml1.x - Mu) * kLog2e);
+      if (lane < S) w[lane] = w0;
+      if (lane + 32 < S) w[lane + 32] = w1;
+      l = fmaf(ml0.y, w0, ml1.y * w1);
+    }
+    for (int s = lane + 64; s < S; s += 32) {
+      const float2 ml = __ldcg(mlp + s);
       const float wt = (ml.x == -INFINITY) ? 0.f : exp2f((ml.x - Mu) * kLog2e);
       w[s] = wt;
       l = fmaf(ml.y, wt, l);
@@ -144,9 +163,18 @@ __device__ __forceinline__ void finish_group(const AttnArgs& a, int b, int kvh, 
     for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
     __syncwarp();
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4* op = reinterpret_cast<const float4*>(a.ws_o + base * kHeadDim) + lane;
+#pragma unroll
+    for (int s = 0; s < PRE; ++s) {
+      if (s < S) {
+        const float wt = w[s];
+        acc.x = fmaf(o_pre[s].x, wt, acc.x);
+        acc.y = fmaf(o_pre[s].y, wt, acc.y);
+        acc.z = fmaf(o_pre[s].z, wt, acc.z);
+        acc.w = fmaf(o_pre[s].w, wt, acc.w);
+      }
+    }
 #pragma unroll 16
-    for (int s = 0; s < S; ++s) {
+    for (int s = PRE; s < S; ++s) {
       const float4 o = __ldcg(op + (size_t)s * (kHeadDim / 4));
       const float wt = w[s];
       acc.x = fmaf(o.x, wt, acc.x);
