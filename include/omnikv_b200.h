@@ -20,8 +20,8 @@
  *   - process-wide switches, read ONCE from the environment on first use (the only global state besides the
  *     built-in scratch of omnikv_decode_attn_no_alloc): OMNIKV_PDL=0 launches every kernel without programmatic
  *     dependent launch; OMNIKV_ATTN_TMA=0 keeps dense decode attention on its cp.async variant;
- *     OMNIKV_WINDOW_TMA=0 does the same for the window selector; OMNIKV_TOPK_CLUSTER=8 limits omnikv_topk to
- *     the portable cluster size.  They exist for measurements and fault isolation; results are the same.
+ *     OMNIKV_WINDOW_TMA=0 does the same for the window selector's mma.sync kernels; OMNIKV_WINDOW_TC=0 keeps the
+ *     window selector off its tcgen05 kernels; OMNIKV_TOPK_CLUSTER=8 limits omnikv_topk to the portable cluster size.  They exist for measurements and fault isolation; results are the same.
  */
 #ifndef OMNIKV_B200_H_
 #define OMNIKV_B200_H_
