@@ -399,7 +399,7 @@ def build_workload(args, world, rank, dev, tp):
         elif wl == "tp70b":
             omni.update(do_select_layers="5,20,45")
         cfg.set_config_of_compressor(**omni)
-        cfg.set_config_of_compressor(fused_decode=True, chained_decode=args.chain)
+        cfg.set_config_of_compressor(fused_decode=True, chained_decode=args.chain, prefill_kernel=args.prefill_kernel)
         return cfg
 
     cfg = make_cfg()
@@ -438,6 +438,11 @@ def main():
                     help="decode128k on ONE GPU with the shapes one rank of an N-way tensor-parallel run holds (1/N of the "
                          "heads, the MLP and the vocabulary) and no exchange: the per-rank floor a multi-GPU step is "
                          "compared with.  The line is marked and is not a benchmark value")
+    ap.add_argument("--real-prefill", action="store_true",
+                    help="offload: run the prompt through the model (this package's prefill attention kernel, K/V handed "
+                         "to pinned host memory layer by layer) instead of filling the cache with seeded values")
+    ap.add_argument("--prefill-kernel", default="tcgen05", choices=["tcgen05", "sdpa"],
+                    help="prompt attention: this package's kernel, or PyTorch's fused attention")
     ap.add_argument("--profile-step", action="store_true",
                     help="after the warm-up, run ONE step between cudaProfilerStart/Stop and exit (for ncu "
                          "--profile-from-start off); prints no benchmark line")
@@ -476,7 +481,7 @@ def main():
     reserve = total + 16
     kvh_local = cfg.num_key_value_heads // (world if tp else 1)
     prefill_s, fill_s = None, None
-    if wl == "decode128k" and not args.synthetic_kv:
+    if (wl == "decode128k" and not args.synthetic_kv) or (args.real_prefill and B == 1):
         cache = lm.new_cache()
         cache.reserve = reserve
         gen = torch.Generator(device=dev).manual_seed(3)  # the same prompt on every rank
@@ -637,7 +642,7 @@ def main():
         "config": config_block(args, world),
         "run": {"exchange": par if world > 1 else None, "cuda_graph": not args.no_graph,
                 "context_lengths": lens if B > 1 else lens[0],
-                "kv_fill": (f"real prefill of {args.ctx} uniform-random token ids ({prefill_s:.1f} s)" if prefill_s
+                "kv_fill": (f"real prefill of {args.ctx} uniform-random token ids ({prefill_s:.1f} s, attention: {args.prefill_kernel})" if prefill_s
                             else f"seeded N(0,1), no prefill run ({fill_s:.1f} s)")},
         "clocks": clocks,
         "e2e": {"value": B * args.steps / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 8 * B,

@@ -21,7 +21,8 @@
  *     built-in scratch of omnikv_decode_attn_no_alloc): OMNIKV_PDL=0 launches every kernel without programmatic
  *     dependent launch; OMNIKV_ATTN_TMA=0 keeps dense decode attention on its cp.async variant;
  *     OMNIKV_WINDOW_TMA=0 does the same for the window selector's mma.sync kernels; OMNIKV_WINDOW_TC=0 keeps the
- *     window selector off its tcgen05 kernels; OMNIKV_TOPK_CLUSTER=8 limits omnikv_topk to the portable cluster size.  They exist for measurements and fault isolation; results are the same.
+ *     window selector off its tcgen05 kernels; OMNIKV_TOPK_CLUSTER=8 limits omnikv_topk to the portable cluster size.
+ *     They exist for measurements and fault isolation; results are the same.
  */
 #ifndef OMNIKV_B200_H_
 #define OMNIKV_B200_H_
@@ -258,6 +259,37 @@ int omnikv_kv_append(int dtype, const void* k_new, const void* v_new, void* k_ca
                      int B, int KVH, int head_dim, int64_t new_stride_b, int64_t new_stride_h,
                      int64_t cache_stride_b, int64_t cache_stride_h, int64_t cache_stride_row,
                      const int32_t* pos, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Causal prefill attention: the attention of the prompt pass that fills the cache before the first decode step
+ * (the reference reaches flash-attn there through transformers' decoder layer, modeling/omnikv.py:219-227, after
+ * cache.update has returned the fresh keys, modeling/spec_cache.py:318-336).
+ *
+ *   out[b, i, h, :] = softmax over keys j <= q_pos0 + i of (q[b,h,i,:] . k[b,h/G,j,:] * scale) . v[b,h/G,j,:]
+ *
+ * q [B, H, Sq, d], k and v [B, KVH, Skv, d] (Skv >= q_pos0 + Sq; a chunk of queries against a longer cache passes its
+ * first position as q_pos0), out [B, Sq, H, d]; all 16-bit of one dtype, element strides given (multiples of 8,
+ * rows of d contiguous elements, bases 16-byte aligned), so k and v may be views of a cache or of a fused
+ * projection.  tcgen05 kernel: 128 queries of a head per CTA, tiles by TMA, accumulators in tensor memory.
+ * status (optional device word) is set to 6 if a bounded wait ran out.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+  int32_t dtype; /* OMNIKV_BF16 or OMNIKV_F16 */
+  int32_t B, H, KVH, head_dim;
+  int32_t Sq, Skv, q_pos0;
+  float scale;
+  const void* q;
+  int64_t q_stride_b, q_stride_h, q_stride_row;
+  const void* k;
+  int64_t k_stride_b, k_stride_h, k_stride_row;
+  const void* v;
+  int64_t v_stride_b, v_stride_h, v_stride_row;
+  void* out;
+  int64_t o_stride_b, o_stride_row, o_stride_h;
+  int32_t* status;
+} omnikv_prefill_params;
+
+int omnikv_prefill_attn(const omnikv_prefill_params* p, void* stream);
 
 /* The current token of every sequence straight from a fused QKV projection (batched decode):
  * qkv[b] = [H query heads | KVH key heads | KVH value heads] x head_dim.  q and k are rotated (pairs (i, i+64) of

@@ -56,6 +56,20 @@ class WindowParams(C.Structure):
     ]
 
 
+class PrefillParams(C.Structure):
+    """Mirror of ``omnikv_prefill_params``."""
+
+    _fields_ = [
+        ("dtype", C.c_int32), ("B", C.c_int32), ("H", C.c_int32), ("KVH", C.c_int32), ("head_dim", C.c_int32),
+        ("Sq", C.c_int32), ("Skv", C.c_int32), ("q_pos0", C.c_int32), ("scale", C.c_float),
+        ("q", C.c_void_p), ("q_stride_b", C.c_int64), ("q_stride_h", C.c_int64), ("q_stride_row", C.c_int64),
+        ("k", C.c_void_p), ("k_stride_b", C.c_int64), ("k_stride_h", C.c_int64), ("k_stride_row", C.c_int64),
+        ("v", C.c_void_p), ("v_stride_b", C.c_int64), ("v_stride_h", C.c_int64), ("v_stride_row", C.c_int64),
+        ("out", C.c_void_p), ("o_stride_b", C.c_int64), ("o_stride_row", C.c_int64), ("o_stride_h", C.c_int64),
+        ("status", C.c_void_p),
+    ]
+
+
 class TpExchange(C.Structure):
     """Mirror of ``omnikv_tp_exchange``."""
 
@@ -91,6 +105,7 @@ SIGNATURES = {
     "omnikv_decode_attn_no_alloc": (C.c_int, [C.POINTER(AttnParams), C.c_void_p]),
     "omnikv_score_window_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "omnikv_score_window": (C.c_int, [C.POINTER(WindowParams), C.c_void_p]),
+    "omnikv_prefill_attn": (C.c_int, [C.POINTER(PrefillParams), C.c_void_p]),
     "omnikv_window_fold": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_void_p, C.c_int,
                                      C.c_int, C.c_void_p]),
     "omnikv_topk_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int]),

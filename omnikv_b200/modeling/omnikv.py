@@ -320,8 +320,12 @@ class OmniKVAttention(nn.Module):
         q, k, v = self.qkv(hidden_states, cos, sin)
         if n > 1:  # prefill: full causal attention over the fresh keys (what cache.update returns)
             k, v = past_key_value.update(k, v, self.layer_idx)
-            o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.num_key_value_groups > 1)
-            o = o.transpose(1, 2).reshape(B, n, self.num_heads * self.head_dim)
+            if (q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and self.head_dim == 128
+                    and self.config.get("prefill_kernel", "tcgen05") == "tcgen05"):
+                o = ops.prefill_attn(q, k, v).view(B, n, self.num_heads * self.head_dim)  # this package's kernel
+            else:  # fp32 (parity runs) or prefill_kernel="sdpa": the library path
+                o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.num_key_value_groups > 1)
+                o = o.transpose(1, 2).reshape(B, n, self.num_heads * self.head_dim)
         else:
             past_key_value.append_kv(k[:, :, 0].contiguous(), v[:, :, 0].contiguous(), self.layer_idx)
             o = past_key_value.attend(q[:, :, 0].contiguous(), self.layer_idx, score_out=score_out,

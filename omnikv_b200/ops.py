@@ -257,6 +257,34 @@ def score_window(qw: torch.Tensor, k: torch.Tensor, consider_len: torch.Tensor, 
     return score_out if planes_out is None else planes_out
 
 
+def prefill_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, q_pos0: int = 0,
+                 scale: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``omnikv_prefill_attn``: causal attention of a block of prompt queries.  q ``[B,H,Sq,d]``, k and v
+    ``[B,KVH,Skv,d]`` with ``Skv >= q_pos0 + Sq`` (any strides that are multiples of 8 elements, rows contiguous),
+    16-bit.  Query ``i`` sees keys ``j <= q_pos0 + i``.  Returns ``[B, Sq, H, d]``."""
+    _need_cuda(q, k, v, out)
+    B, H, Sq, d = q.shape
+    KVH, Skv = k.shape[1], k.shape[2]
+    if q.stride(3) != 1 or k.stride(3) != 1 or v.stride(3) != 1 or k.shape != v.shape or q.dtype != k.dtype:
+        raise abi.OmniKVError("prefill_attn: rows of q, k, v must be contiguous and k, v of one shape and dtype")
+    if out is None:
+        out = torch.empty(B, Sq, H, d, dtype=q.dtype, device=q.device)
+    p = abi.PrefillParams()
+    p.dtype = _DT[q.dtype]
+    p.B, p.H, p.KVH, p.head_dim = B, H, KVH, d
+    p.Sq, p.Skv, p.q_pos0 = Sq, Skv, int(q_pos0)
+    p.scale = float(scale if scale is not None else 1.0 / math.sqrt(d))
+    p.q, p.k, p.v, p.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    p.q_stride_b, p.q_stride_h, p.q_stride_row = q.stride(0), q.stride(1), q.stride(2)
+    p.k_stride_b, p.k_stride_h, p.k_stride_row = k.stride(0), k.stride(1), k.stride(2)
+    p.v_stride_b, p.v_stride_h, p.v_stride_row = v.stride(0), v.stride(1), v.stride(2)
+    p.o_stride_b, p.o_stride_row, p.o_stride_h = out.stride(0), out.stride(1), out.stride(2)
+    p.status = status_word(q.device).data_ptr()
+    abi.check(abi.lib().omnikv_prefill_attn(C.byref(p), _stream()), "omnikv_prefill_attn")
+    _count(1)
+    return out
+
+
 def window_fold(planes: torch.Tensor, consider_len: torch.Tensor, selector: str, *, max_len: int,
                 score_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _need_cuda(planes, consider_len, score_out)

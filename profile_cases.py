@@ -213,13 +213,44 @@ def tp_timeline(ctx: int, replays: int = 6):
     print(text)
 
 
+def prefill_case(ctx: int, reps: int, library: bool):
+    """Causal prefill attention of one Llama-3-8B layer (32 query heads, 8 KV heads) over ``ctx`` tokens: this
+    package's tcgen05 kernel (and, with --library, PyTorch's fused attention on the same tensors)."""
+    import torch.nn.functional as F
+    dev, H, KVH, d = "cuda", 32, 8, 128
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *s: torch.randn(*s, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)  # noqa: E731
+    q, k, v = rnd(1, H, ctx, d), rnd(1, KVH, ctx, d), rnd(1, KVH, ctx, d)
+    flops = 4.0 * H * d * ctx * (ctx + 1) / 2  # two products over the causal triangle
+    legs = [("tcgen05 kernel", lambda: ops.prefill_attn(q, k, v))]
+    if library:
+        legs.append(("torch sdpa", lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)))
+    outs = {}
+    for name, fn in legs:
+        outs[name] = fn()
+        torch.cuda.synchronize()
+        for r in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            print(f"prefill_attn {name} ctx {ctx} rep {r}: {ms:.3f} ms, {flops / ms / 1e9:.0f} TFLOP/s")
+    ops.check_status(q.device)
+    if library:
+        a, b = outs["tcgen05 kernel"].float(), outs["torch sdpa"].transpose(1, 2).float()
+        print(f"max |kernel - sdpa| = {(a - b).abs().max().item():.4f}")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["dense_attn", "sparse_attn", "topk", "score_window", "offload_gather", "gemv", "operator",
-                                     "tp_timeline"])
+                                     "tp_timeline", "prefill_attn"])
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--ctx", type=int, default=131072)
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--library", action="store_true", help="prefill_attn: also time PyTorch's fused attention")
     ap.add_argument("--kv-layout", default="interleaved", choices=["interleaved", "planes"],
                     help="dense_attn / score_window: K|V rows of a head interleaved, or in two separate runs of rows")
     args = ap.parse_args()
@@ -236,6 +267,8 @@ def main():
 
     if args.case == "gemv":
         return gemv_cases(args.reps)
+    if args.case == "prefill_attn":
+        return prefill_case(args.ctx if args.ctx != 131072 else 16384, args.reps, args.library)
     if args.case == "operator":
         # the single-layer operator in fp32: context 16384, selector `last` on a filter layer's K, 1098 selected rows,
         # decode attention over a second layer's K/V at those rows -- three launches

@@ -650,3 +650,63 @@ def test_dense_attn_tensor_map_tiles_equal_cp_async(dtype, B, L, cap):
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
     ref = oracle.dense_attention(q[:1].cpu(), kc[:1, :, :lens[0]].cpu(), vc[:1, :, :lens[0]].cpu())
     assert (outs[0][0][:1].float().cpu() - ref).abs().max().item() < 2e-2
+
+
+def _causal_reference(q, k, v, q_pos0, scale):
+    """fp32 definition: query i sees keys j <= q_pos0 + i.  q [B,H,Sq,d], k/v [B,KVH,Skv,d] -> [B,Sq,H,d]."""
+    B, H, Sq, d = q.shape
+    KVH, Skv = k.shape[1], k.shape[2]
+    G = H // KVH
+    qf, kf, vf = q.float(), k.float().repeat_interleave(G, dim=1), v.float().repeat_interleave(G, dim=1)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    pos = q_pos0 + torch.arange(Sq, device=q.device)[:, None]
+    s = s.masked_fill(torch.arange(Skv, device=q.device)[None, :] > pos, float("-inf"))
+    return torch.matmul(torch.softmax(s, dim=-1), vf).transpose(1, 2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,H,KVH,Sq,Skv,q_pos0", [
+    (1, 8, 2, 128, 128, 0),      # one tile, diagonal mask only
+    (1, 8, 2, 300, 300, 0),      # ragged last query block and key tile
+    (2, 4, 1, 1000, 1000, 0),    # batch, eight key tiles, one KV head for four query heads
+    (1, 4, 4, 200, 520, 320),    # a chunk of queries behind 320 cached keys
+    (1, 32, 8, 2048, 2048, 0),   # Llama-3-8B head counts
+])
+def test_prefill_attention_matches_definition(dtype, B, H, KVH, Sq, Skv, q_pos0):
+    """tcgen05 prefill attention through the C ABI against the fp32 definition (2e-2 absolute for 16-bit inputs:
+    P is rounded to 16 bits before the second product, as in flash attention)."""
+    g = torch.Generator().manual_seed(Sq * 7 + H)
+    q = torch.randn(B, H, Sq, 128, generator=g).to(dtype).cuda()
+    k = torch.randn(B, KVH, Skv, 128, generator=g).to(dtype).cuda()
+    v = torch.randn(B, KVH, Skv, 128, generator=g).to(dtype).cuda()
+    scale = 1.0 / math.sqrt(128)
+    out = ops().prefill_attn(q, k, v, q_pos0=q_pos0)
+    ops().check_status(q.device)
+    ref = _causal_reference(q, k, v, q_pos0, scale)
+    assert out.shape == (B, Sq, H, 128)
+    err = (out.float() - ref).abs().max().item()
+    assert err <= 2e-2, err
+
+
+def test_prefill_attention_reads_strided_views():
+    """k and v as views of one fused projection output (row stride of the whole projection), peaked logits."""
+    B, H, KVH, S = 1, 8, 2, 700
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn(B, S, (H + 2 * KVH) * 128, generator=g).to(torch.bfloat16).cuda()
+    q = (qkv[..., :H * 128].view(B, S, H, 128).transpose(1, 2) * 3).contiguous()
+    k = qkv[..., H * 128:(H + KVH) * 128].view(B, S, KVH, 128).transpose(1, 2)
+    v = qkv[..., (H + KVH) * 128:].view(B, S, KVH, 128).transpose(1, 2)
+    out = ops().prefill_attn(q, k, v)
+    ops().check_status(q.device)
+    ref = _causal_reference(q, k, v, 0, 1.0 / math.sqrt(128))
+    assert (out.float() - ref).abs().max().item() <= 2e-2
+
+
+def test_prefill_attention_rejects_bad_arguments():
+    q = torch.zeros(1, 4, 64, 128, dtype=torch.bfloat16, device="cuda")
+    k = torch.zeros(1, 2, 32, 128, dtype=torch.bfloat16, device="cuda")
+    from omnikv_b200.abi import OmniKVError
+    with pytest.raises(OmniKVError):
+        ops().prefill_attn(q, k, k)  # fewer keys than queries
+    with pytest.raises(OmniKVError):
+        ops().prefill_attn(q.float(), k.float().repeat(1, 1, 2, 1), k.float().repeat(1, 1, 2, 1))  # fp32
