@@ -778,7 +778,126 @@ int launch_mma(AttnArgs a, bool with_v, bool with_score, int64_t a_rows, cudaStr
   return OMNIKV_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// fp32 selector-`last` scores of a contiguous cache, as a stream: the rows of one (sequence, KV head) are
+// consecutive in memory, so a tile of 64 rows is ONE 32 KB bulk copy into a three-stage ring (a producer thread,
+// mbarrier transaction counts), which keeps ~190 KB per SM in flight -- the register-staged kernel above holds 8 KB
+// per CTA and is bound by the memory latency.  Eight consumer warps take eight rows of a tile each (lane L holds
+// dims 4L..4L+3 of the row and of the G queries), the eight scores of a warp leave as one 32-byte store.
+// ---------------------------------------------------------------------------------------------
+constexpr int SL_ROWS = 64, SL_STAGES = 3, SL_WARPS = 8, SL_THREADS = (SL_WARPS + 1) * 32;
+constexpr int SL_TILE_BYTES = SL_ROWS * kHeadDim * 4;
+constexpr int SL_SMEM_BYTES = SL_STAGES * SL_TILE_BYTES + 128;
+
+template <int G>
+__global__ void __launch_bounds__(SL_THREADS) score_last_f32_stream_kernel(const AttnArgs a) {
+  extern __shared__ __align__(128) unsigned char sl_smem_raw[];
+  __shared__ uint64_t full[SL_STAGES], empty[SL_STAGES];
+  __shared__ int fail;
+  float* ring = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(sl_smem_raw) + 127) & ~(uintptr_t)127);
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n = min(a.score_len[b], a.lenA[b]);  // rows that get a score
+  int r0, r1;
+  split_range(n, n, a.S, split, r0, r1);
+  const int n_tiles = r1 > r0 ? ceil_div(r1 - r0, SL_ROWS) : 0;
+  const float* k = static_cast<const float*>(a.kA) + (size_t)b * a.a_sb + (size_t)kvh * a.a_sh;
+  float* score_row = a.score_out + ((size_t)kvh * a.B + b) * a.score_stride;
+  if (tid == 0) {
+    fail = 0;
+    for (int s = 0; s < SL_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], SL_WARPS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == SL_WARPS) {
+    if (lane == 0) {
+      for (int t = 0; t < n_tiles; ++t) {
+        const int s = t % SL_STAGES;
+        if (!mbar_wait(&empty[s], ((t / SL_STAGES) & 1) ^ 1, &fail)) {
+          if (!fail && a.status) atomicExch(a.status, 5);
+          fail = 1;
+          break;
+        }
+        const int row = r0 + t * SL_ROWS;
+        const unsigned bytes = (unsigned)min(SL_ROWS, r1 - row) * kHeadDim * 4;
+        mbar_expect_tx(&full[s], bytes);
+        tma_bulk_g2s(ring + (size_t)s * SL_ROWS * kHeadDim, k + (size_t)row * kHeadDim, bytes, &full[s]);
+      }
+    }
+    return;  // copies in flight are waited for by the consumers (a consumer that gives up leaves them to the 2 s bound)
+  }
+  float4 qv[G];
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    const float* qp = static_cast<const float*>(a.q) + (size_t)b * a.q_sb + (size_t)(kvh * G + h) * a.q_sh;
+    qv[h] = *reinterpret_cast<const float4*>(qp + lane * 4);
+  }
+  for (int t = 0; t < n_tiles; ++t) {
+    const int s = t % SL_STAGES;
+    if (!mbar_wait(&full[s], (t / SL_STAGES) & 1, &fail)) {
+      if (!fail && a.status) atomicExch(a.status, 5);
+      fail = 1;
+      break;
+    }
+    const int row0 = r0 + t * SL_ROWS + warp * 8;  // this warp's eight rows
+    const float4* tile = reinterpret_cast<const float4*>(ring + (size_t)s * SL_ROWS * kHeadDim) + warp * 8 * 32;
+    float4 kx[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) kx[i] = tile[i * 32 + lane];
+    float mine = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float best = -INFINITY;
+#pragma unroll
+      for (int h = 0; h < G; ++h) {
+        float d = qv[h].x * kx[i].x;
+        d = fmaf(qv[h].y, kx[i].y, d);
+        d = fmaf(qv[h].z, kx[i].z, d);
+        d = fmaf(qv[h].w, kx[i].w, d);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+        best = fmaxf(best, d * a.scale);
+      }
+      if (lane == i) mine = best;
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[s]);  // the tile's rows are in registers: the stage may be refilled
+    if (lane < 8 && row0 + lane < r1) score_row[row0 + lane] = mine;
+  }
+  if (fail) {
+    // a wait ran out: let every copy that was asked for land (bounded) before the shared memory is given up
+    for (int s = 0; s < SL_STAGES; ++s) mbar_wait(&full[s], 0);
+  }
+}
+
+template <int G>
+int launch_score_stream(const AttnArgs& a, cudaStream_t st) {
+  auto kern = score_last_f32_stream_kernel<G>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SL_SMEM_BYTES));
+    attr_set = true;
+  }
+  kern<<<dim3(a.S, a.KVH, a.B), SL_THREADS, SL_SMEM_BYTES, st>>>(a);
+  OMNIKV_CUDA_OK(cudaGetLastError());
+  return OMNIKV_OK;
+}
+
 int launch_f32(const AttnArgs& a, bool with_v, bool with_score, cudaStream_t st) {
+  // scores only over a cache whose rows lie back to back: the streaming kernel
+  if (!with_v && with_score && !a.idxA && !a.kB && a.a_sr == kHeadDim && a.a_sb % 4 == 0 && a.a_sh % 4 == 0 &&
+      (reinterpret_cast<uintptr_t>(a.kA) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.q) & 15) == 0) {
+    switch (a.G) {
+      case 1: return launch_score_stream<1>(a, st);
+      case 2: return launch_score_stream<2>(a, st);
+      case 4: return launch_score_stream<4>(a, st);
+      case 8: return launch_score_stream<8>(a, st);
+      default: break;
+    }
+  }
   dim3 grid(a.S, a.KVH, a.B), block(NTHREADS);
   switch (a.G) {
     case 1: decode_attn_f32_kernel<1><<<grid, block, 0, st>>>(a, with_v, with_score); break;
