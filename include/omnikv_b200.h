@@ -291,6 +291,53 @@ typedef struct {
 
 int omnikv_prefill_attn(const omnikv_prefill_params* p, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * A projection of a batched decode step (1..16 tokens) as a stream of its weight matrix on tcgen05:
+ *
+ *   y[b, n] = sum_k w[n, k] * x'[b, k]      x' = x, or RMSNorm(x, eps) * norm_w when norm_w is given
+ *
+ *   OMNIKV_EPI_STORE      out[b, n] = y                       (fused QKV projection; out is 16-bit)
+ *   OMNIKV_EPI_STORE_F32  out[b, n] = y in fp32               (lm_head logits)
+ *   OMNIKV_EPI_RESIDUAL   out[b, n] = residual[b, n] + y      (output and down projection; out may alias residual)
+ *   OMNIKV_EPI_SWIGLU     w = [gate rows | up rows] (w_rows = 2 * inter, inter % 64 == 0),
+ *                         out[b, j] = silu(y[b, j]) * y[b, inter + j]     for j < inter
+ *
+ * the third-party decoder modules the reference calls around its selection path (modeling/omnikv.py:156, :219-236,
+ * :361-373) when several sequences decode together.  w [w_rows, K] row-major 16-bit (K % 8 == 0, 16-byte aligned),
+ * x [n_tokens, K].  The workspace (omnikv_batched_linear_workspace_bytes) starts with 16 KiB of counters that must be
+ * ZERO before the first call that uses it; every call leaves them zero; calls that share it must be stream-ordered.
+ * Sums over K are taken in a fixed order (results do not depend on scheduling).  status (optional) is set to 7 if a
+ * bounded wait ran out.
+ * ------------------------------------------------------------------------------------------ */
+typedef enum {
+  OMNIKV_EPI_STORE = 0,
+  OMNIKV_EPI_STORE_F32 = 1,
+  OMNIKV_EPI_RESIDUAL = 2,
+  OMNIKV_EPI_SWIGLU = 3
+} omnikv_epilogue;
+
+typedef struct {
+  int32_t dtype; /* OMNIKV_BF16 or OMNIKV_F16: w, x, norm_w, residual, out (except STORE_F32) */
+  int32_t n_tokens, w_rows, K;
+  const void* w;
+  int64_t w_stride_row;
+  const void* x;
+  int64_t x_stride_tok;
+  const void* norm_w; /* [K] or NULL */
+  float eps;
+  int32_t epilogue; /* omnikv_epilogue */
+  const void* residual;
+  int64_t residual_stride_tok;
+  void* out;
+  int64_t out_stride_tok;
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t* status;
+} omnikv_batched_linear_params;
+
+size_t omnikv_batched_linear_workspace_bytes(int n_tokens, int w_rows, int K, int epilogue);
+int omnikv_batched_linear(const omnikv_batched_linear_params* p, void* stream);
+
 /* The current token of every sequence straight from a fused QKV projection (batched decode):
  * qkv[b] = [H query heads | KVH key heads | KVH value heads] x head_dim.  q and k are rotated (pairs (i, i+64) of
  * a head by rope_pos[b] * inv_freq[i], the rotate_half convention of the reference's decoder; fp32 arithmetic,

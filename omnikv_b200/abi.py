@@ -70,6 +70,22 @@ class PrefillParams(C.Structure):
     ]
 
 
+class BatchedLinearParams(C.Structure):
+    """Mirror of ``omnikv_batched_linear_params``."""
+
+    _fields_ = [
+        ("dtype", C.c_int32), ("n_tokens", C.c_int32), ("w_rows", C.c_int32), ("K", C.c_int32),
+        ("w", C.c_void_p), ("w_stride_row", C.c_int64), ("x", C.c_void_p), ("x_stride_tok", C.c_int64),
+        ("norm_w", C.c_void_p), ("eps", C.c_float), ("epilogue", C.c_int32),
+        ("residual", C.c_void_p), ("residual_stride_tok", C.c_int64), ("out", C.c_void_p),
+        ("out_stride_tok", C.c_int64), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("status", C.c_void_p),
+    ]
+
+
+EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
+
+
 class TpExchange(C.Structure):
     """Mirror of ``omnikv_tp_exchange``."""
 
@@ -106,6 +122,8 @@ SIGNATURES = {
     "omnikv_score_window_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "omnikv_score_window": (C.c_int, [C.POINTER(WindowParams), C.c_void_p]),
     "omnikv_prefill_attn": (C.c_int, [C.POINTER(PrefillParams), C.c_void_p]),
+    "omnikv_batched_linear_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int]),
+    "omnikv_batched_linear": (C.c_int, [C.POINTER(BatchedLinearParams), C.c_void_p]),
     "omnikv_window_fold": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_void_p, C.c_int,
                                      C.c_int, C.c_void_p]),
     "omnikv_topk_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int]),

@@ -164,6 +164,18 @@ __device__ __forceinline__ const unsigned char* swz128(const unsigned char* tile
 bool make_kv_tensor_map(CUtensorMap* map, bool is_bf16, const void* base, int64_t rows, int KVH, int B, int64_t sr,
                         int64_t sh, int64_t sb, int box_rows = 64);
 
+// 2-D tiles of a row-major 16-bit matrix [rows, cols] (a weight): box 64 columns x box_rows rows, 128-byte swizzle,
+// rows and columns past the end read as zero.
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int col, int row, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::
+          "r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(col), "r"(row), "r"(smem_u32(bar))
+      : "memory");
+}
+bool make_matrix_tensor_map(CUtensorMap* map, bool is_bf16, const void* base, int64_t rows, int64_t cols, int64_t ld,
+                            int box_rows);
+
 // ---- cp.async (16-byte, L1-bypassing) with zero fill when !valid ---------------------------
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, bool valid) {
   unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));

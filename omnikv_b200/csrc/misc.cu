@@ -48,6 +48,20 @@ bool make_kv_tensor_map(CUtensorMap* map, bool is_bf16, const void* base, int64_
 }
 
 
+bool make_matrix_tensor_map(CUtensorMap* map, bool is_bf16, const void* base, int64_t rows, int64_t cols, int64_t ld,
+                            int box_rows) {
+  PFN_encodeTiled enc = encode_tiled_fn();
+  if (!enc || rows <= 0 || cols <= 0 || ld % 8 || ld < cols || (reinterpret_cast<uintptr_t>(base) & 15)) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return enc(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 static thread_local char g_last_error[256] = "";
 
 int record_cuda_error(cudaError_t e, const char* where) {

@@ -285,6 +285,41 @@ def prefill_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, q_pos0: i
     return out
 
 
+_EPI = {"store": abi.EPI_STORE, "store_f32": abi.EPI_STORE_F32, "residual": abi.EPI_RESIDUAL, "swiglu": abi.EPI_SWIGLU}
+
+
+def batched_linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: str = "store", norm_w: Optional[torch.Tensor] = None,
+                   eps: float = 1e-5, residual: Optional[torch.Tensor] = None,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``omnikv_batched_linear``: x ``[n_tokens <= 16, K]`` times w ``[rows, K]`` transposed as a weight stream on
+    tcgen05, with an optional RMSNorm of x in front and the epilogue ``store`` | ``store_f32`` | ``residual`` (adds
+    ``residual``; ``out`` may be the same tensor) | ``swiglu`` (w = gate rows then up rows; returns
+    ``[n_tokens, rows / 2]``)."""
+    _need_cuda(x, w, norm_w, residual, out)
+    n, K = x.shape
+    rows = w.shape[0]
+    if x.stride(1) != 1 or w.stride(1) != 1 or w.shape[1] != K or w.dtype != x.dtype:
+        raise abi.OmniKVError("batched_linear: x [n, K] and w [rows, K] need contiguous rows and one dtype")
+    epi = _EPI[epilogue]
+    cols = rows // 2 if epilogue == "swiglu" else rows
+    if out is None:
+        out = torch.empty(n, cols, dtype=torch.float32 if epilogue == "store_f32" else x.dtype, device=x.device)
+    p = abi.BatchedLinearParams()
+    p.dtype, p.n_tokens, p.w_rows, p.K = _DT[x.dtype], n, rows, K
+    p.w, p.w_stride_row, p.x, p.x_stride_tok = w.data_ptr(), w.stride(0), x.data_ptr(), x.stride(0)
+    p.norm_w, p.eps, p.epilogue = _ptr(norm_w), float(eps), epi
+    if residual is not None:
+        p.residual, p.residual_stride_tok = residual.data_ptr(), residual.stride(0)
+    p.out, p.out_stride_tok = out.data_ptr(), out.stride(0)
+    need = abi.lib().omnikv_batched_linear_workspace_bytes(n, rows, K, epi)
+    ws = workspace(x.device, need, "batched_linear")
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
+    p.status = status_word(x.device).data_ptr()
+    abi.check(abi.lib().omnikv_batched_linear(C.byref(p), _stream()), "omnikv_batched_linear")
+    _count(1)
+    return out
+
+
 def window_fold(planes: torch.Tensor, consider_len: torch.Tensor, selector: str, *, max_len: int,
                 score_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _need_cuda(planes, consider_len, score_out)

@@ -88,6 +88,55 @@ def gemv_cases(reps: int, n_sets: int = 8):
     ops.check_status(dev)
 
 
+def batched_linear_cases(reps: int, n_tokens: int = 16, n_sets: int = 8):
+    """The projections of a Llama-3-8B decoder layer for ``n_tokens`` sequences decoding together: this package's
+    tcgen05 weight stream and the library GEMM (plus the separate norm / activation / residual kernels it needs), each
+    over ``n_sets`` distinct weight sets back to back inside a CUDA graph."""
+    import torch.nn.functional as F
+    dev, dt = "cuda", torch.bfloat16
+    hidden, inter, H, KVH = 4096, 14336, 32, 8
+    mk = lambda n, k: [torch.randn(n, k, device=dev, dtype=torch.float32).mul_(k ** -0.5).to(dt) for _ in range(n_sets)]  # noqa: E731
+    w_qkv, w_o, w_gu, w_d = mk((H + 2 * KVH) * 128, hidden), mk(hidden, hidden), mk(2 * inter, hidden), mk(hidden, inter)
+    x = torch.randn(n_tokens, hidden, device=dev).to(dt)
+    a_in = torch.randn(n_tokens, inter, device=dev).to(dt)
+    nw = torch.ones(hidden, device=dev, dtype=dt)
+    h = torch.zeros(n_tokens, hidden, device=dev, dtype=dt)
+
+    def lib_gate_up(i):
+        gu = F.linear(F.rms_norm(x, (hidden,), nw, 1e-5), w_gu[i])
+        return F.silu(gu[:, :inter]) * gu[:, inter:]
+
+    kinds = {
+        "qkv (norm in front)": (lambda i: ops.batched_linear(x, w_qkv[i], norm_w=nw),
+                                lambda i: F.linear(F.rms_norm(x, (hidden,), nw, 1e-5), w_qkv[i]), w_qkv[0].numel() * 2),
+        "o_proj + residual": (lambda i: ops.batched_linear(x, w_o[i], epilogue="residual", residual=h, out=h),
+                              lambda i: h.add_(F.linear(x, w_o[i])), w_o[0].numel() * 2),
+        "gate_up + silu (norm in front)": (lambda i: ops.batched_linear(x, w_gu[i], epilogue="swiglu", norm_w=nw),
+                                           lib_gate_up, w_gu[0].numel() * 2),
+        "down + residual": (lambda i: ops.batched_linear(a_in, w_d[i], epilogue="residual", residual=h, out=h),
+                            lambda i: h.add_(F.linear(a_in, w_d[i])), w_d[0].numel() * 2),
+    }
+    for name, (mine, lib, nbytes) in kinds.items():
+        for leg, fn in (("tcgen05 stream", mine), ("library GEMM + element-wise kernels", lib)):
+            fn(0)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for i in range(n_sets):
+                    fn(i)
+            g.replay()
+            torch.cuda.synchronize()
+            for r in range(reps):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                g.replay()
+                b.record()
+                torch.cuda.synchronize()
+                ms = a.elapsed_time(b) / n_sets
+                print(f"{name} [{leg}] rep {r}: {ms * 1e3:.1f} us per call, {nbytes / 1e6:.1f} MB, {nbytes / ms / 1e6:.0f} GB/s")
+    ops.check_status(dev)
+
+
 def tp_timeline(ctx: int, replays: int = 6):
     """One decode step of the benchmark (Llama-3-8B shape, batch 1, ``ctx`` tokens of synthetic KV, fused kernels,
     peer-memory exchange, CUDA graph) on the ranks of this torchrun job, with the profiling build of the library:
@@ -246,7 +295,8 @@ def prefill_case(ctx: int, reps: int, library: bool):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["dense_attn", "sparse_attn", "topk", "score_window", "offload_gather", "gemv", "operator",
-                                     "tp_timeline", "prefill_attn"])
+                                     "tp_timeline", "prefill_attn", "batched_linear"])
+    ap.add_argument("--tokens", type=int, default=16, help="batched_linear: sequences decoding together")
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--ctx", type=int, default=131072)
     ap.add_argument("--splits", type=int, default=0)
@@ -267,6 +317,8 @@ def main():
 
     if args.case == "gemv":
         return gemv_cases(args.reps)
+    if args.case == "batched_linear":
+        return batched_linear_cases(args.reps, args.tokens)
     if args.case == "prefill_attn":
         return prefill_case(args.ctx if args.ctx != 131072 else 16384, args.reps, args.library)
     if args.case == "operator":

@@ -710,3 +710,56 @@ def test_prefill_attention_rejects_bad_arguments():
         ops().prefill_attn(q, k, k)  # fewer keys than queries
     with pytest.raises(OmniKVError):
         ops().prefill_attn(q.float(), k.float().repeat(1, 1, 2, 1), k.float().repeat(1, 1, 2, 1))  # fp32
+
+
+def _linear_reference(x, w, norm_w, eps, epilogue, residual):
+    xf = x.float()
+    if norm_w is not None:
+        xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float()
+    y = xf @ w.float().t()
+    if epilogue == "residual":
+        y = y + residual.float()
+    if epilogue == "swiglu":
+        inter = w.shape[0] // 2
+        y = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
+    return y
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("n,rows,K,epilogue,norm", [
+    (16, 6144, 4096, "store", True),        # fused QKV projection of the 8B shape behind the input norm
+    (16, 4096, 4096, "residual", False),    # output projection + residual
+    (16, 28672, 4096, "swiglu", True),      # gate/up behind the post-attention norm
+    (16, 4096, 14336, "residual", False),   # down projection + residual: K in eight slices
+    (5, 1000, 1024, "store_f32", True),     # rows that do not fill the last block, fp32 logits
+    (8, 3584, 8192, "swiglu", True),        # one GPU's share of the 70B gate/up at batch 8
+    (1, 256, 64, "store", False),           # one token, one K chunk
+    (3, 520, 200, "residual", True),        # K that is not a multiple of 64
+])
+def test_batched_linear_matches_definition(dtype, n, rows, K, epilogue, norm):
+    """tcgen05 weight-streaming projection through the C ABI against fp32 torch: 2e-2 relative to max(1, |y|)."""
+    g = torch.Generator().manual_seed(rows + K + n)
+    x = torch.randn(n, K, generator=g).to(dtype).cuda()
+    w = (torch.randn(rows, K, generator=g) * K ** -0.5).to(dtype).cuda()
+    norm_w = (1 + 0.1 * torch.randn(K, generator=g)).to(dtype).cuda() if norm else None
+    cols = rows // 2 if epilogue == "swiglu" else rows
+    residual = torch.randn(n, cols, generator=g).to(dtype).cuda() if epilogue == "residual" else None
+    ref = _linear_reference(x, w, norm_w, 1e-5, epilogue, residual)
+    out = ops().batched_linear(x, w, epilogue=epilogue, norm_w=norm_w, eps=1e-5, residual=residual)
+    ops().check_status(x.device)
+    assert out.shape == (n, cols)
+    err = ((out.float() - ref).abs() / ref.abs().clamp(min=1.0)).max().item()
+    assert err <= (2e-2 if epilogue != "store_f32" else 5e-3), err
+    # the same call again: the workspace counters were left at zero, and sums do not depend on scheduling
+    out2 = ops().batched_linear(x, w, epilogue=epilogue, norm_w=norm_w, eps=1e-5, residual=residual)
+    assert torch.equal(out, out2)
+
+
+def test_batched_linear_residual_in_place():
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(16, 4096, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(4096, 4096, generator=g) / 64).to(torch.bfloat16).cuda()
+    h = torch.randn(16, 4096, generator=g).to(torch.bfloat16).cuda()
+    ref = _linear_reference(x, w, None, 0.0, "residual", h)
+    ops().batched_linear(x, w, epilogue="residual", residual=h, out=h)
+    assert ((h.float() - ref).abs() / ref.abs().clamp(min=1.0)).max().item() <= 2e-2
