@@ -399,7 +399,8 @@ def build_workload(args, world, rank, dev, tp):
         elif wl == "tp70b":
             omni.update(do_select_layers="5,20,45")
         cfg.set_config_of_compressor(**omni)
-        cfg.set_config_of_compressor(fused_decode=True, chained_decode=args.chain, prefill_kernel=args.prefill_kernel)
+        cfg.set_config_of_compressor(fused_decode=True, chained_decode=args.chain, prefill_kernel=args.prefill_kernel,
+                                     tcgen05_linear=args.tcgen05_linear, fused_small_ops=not args.no_fused_adds)
         return cfg
 
     cfg = make_cfg()
@@ -443,6 +444,11 @@ def main():
                          "to pinned host memory layer by layer) instead of filling the cache with seeded values")
     ap.add_argument("--prefill-kernel", default="tcgen05", choices=["tcgen05", "sdpa"],
                     help="prompt attention: this package's kernel, or PyTorch's fused attention")
+    ap.add_argument("--tcgen05-linear", action="store_true",
+                    help="batched workloads: projections through this package's tcgen05 weight stream instead of the "
+                         "library GEMM")
+    ap.add_argument("--no-fused-adds", action="store_true",
+                    help="batched workloads: separate residual-add and norm kernels (PyTorch) instead of one launch")
     ap.add_argument("--profile-step", action="store_true",
                     help="after the warm-up, run ONE step between cudaProfilerStart/Stop and exit (for ncu "
                          "--profile-from-start off); prints no benchmark line")

@@ -348,6 +348,12 @@ int omnikv_rope_append(int dtype, const void* qkv, int64_t qkv_stride_b, int B, 
                        const float* inv_freq, const int32_t* rope_pos, void* q_out, int64_t q_stride_b,
                        void* k_cache, void* v_cache, int64_t cache_stride_b, int64_t cache_stride_h,
                        int64_t cache_stride_row, const int32_t* cache_pos, void* stream);
+/* The residual add and the RMSNorm behind it as one launch (batched decode): h[b] += delta[b] when delta is given
+ * (rounded to the residual stream's type), out[b] = RMSNorm(h[b], eps) * norm_w.  Replaces the separate add and norm
+ * kernels between the third-party decoder modules (modeling/omnikv.py:229-232 and the next layer's :156). */
+int omnikv_add_rms_norm(int dtype, void* h, int64_t h_stride_tok, const void* delta, int64_t delta_stride_tok,
+                        const void* norm_w, float eps, void* out, int64_t out_stride_tok, int n_tokens, int hidden,
+                        void* stream);
 /* act[b][j] = silu(gate_up[b][j]) * gate_up[b][inter + j] for j < inter (SwiGLU of a fused gate/up projection). */
 int omnikv_silu_mul(int dtype, const void* gate_up, int64_t gate_up_stride_b, void* act, int64_t act_stride_b,
                     int B, int inter, void* stream);

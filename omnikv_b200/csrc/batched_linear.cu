@@ -55,6 +55,7 @@ struct BlArgs {
   int* counters;  // [R], zero between calls
   int Bt, N, K, S, R, chunks, epi, inter;
   int* status;
+  int dbg;
 };
 
 struct BlShared {
@@ -174,6 +175,7 @@ __global__ void __launch_bounds__(BL_THREADS, 1)
 batched_linear_kernel(const BlArgs a, const __grid_constant__ CUtensorMap tm_w) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ BlShared sh;
+  __shared__ float ss_all[BL_MAX_SLICES * BL_NT];
   __shared__ float ex[BL_M][BL_NT + 1];  // SiLU(gate) * up: gate rows and up rows of a tile meet here
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* ring = smem;
@@ -226,6 +228,7 @@ batched_linear_kernel(const BlArgs a, const __grid_constant__ CUtensorMap tm_w) 
             break;
           }
           unsigned char* dst = ring + (size_t)st * BL_STAGE_BYTES;
+          if (a.dbg == 2) { mbar_arrive(&sh.full[st]); sh.issued = 0; continue; }
           mbar_expect_tx(&sh.full[st], BL_STAGE_BYTES);
           const int col = (c0 + c) * BL_KC;
           if (swiglu) {  // 64 gate rows and the 64 up rows that belong to them
@@ -256,7 +259,7 @@ batched_linear_kernel(const BlArgs a, const __grid_constant__ CUtensorMap tm_w) 
           const unsigned w_base = smem_u32(ring + (size_t)st * BL_STAGE_BYTES);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            tc_mma(d_tmem, smem_desc_sw128(w_base + k * 32), smem_desc_sw128(x_base + c * BL_XBOX_BYTES + k * 32), idesc,
+            if (a.dbg != 1) tc_mma(d_tmem, smem_desc_sw128(w_base + k * 32), smem_desc_sw128(x_base + c * BL_XBOX_BYTES + k * 32), idesc,
                    (c | k) ? 1u : 0u);
           tc_commit(&sh.empty[st]);
         }
@@ -278,6 +281,7 @@ batched_linear_kernel(const BlArgs a, const __grid_constant__ CUtensorMap tm_w) 
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the tensor core reads x through the async proxy
     mbar_arrive(&sh.x_full);
     const T* resid = static_cast<const T*>(a.resid);
+    bool rstd_ready = false;
     for (int u = 0; u < n_units; ++u) {
       const int rb = g + u * nper, buf = u & 1;
       const bool got = mbar_wait(&sh.acc_full[buf], (u >> 1) & 1, &sh.fail);
@@ -311,26 +315,37 @@ batched_linear_kernel(const BlArgs a, const __grid_constant__ CUtensorMap tm_w) 
           __threadfence();
 #pragma unroll
           for (int b = 0; b < BL_NT; ++b) y[b] = 0.f;
-          for (int sl = 0; sl < S; ++sl) {  // slice order: the same sum whichever CTA arrives last
-            const float* q = a.part + ((size_t)rb * S + sl) * a.Bt * BL_M + tid;
+          // slice order: the same sum whichever CTA arrives last.  Four slices' loads go out together.
+          for (int sl0 = 0; sl0 < S; sl0 += 4) {
+            float t[4][BL_NT];
 #pragma unroll
-            for (int b = 0; b < BL_NT; ++b)
-              if (b < a.Bt) y[b] += __ldcg(q + b * BL_M);
+            for (int u = 0; u < 4; ++u) {
+              const float* q = a.part + ((size_t)rb * S + min(sl0 + u, S - 1)) * a.Bt * BL_M + tid;
+#pragma unroll
+              for (int b = 0; b < BL_NT; ++b) t[u][b] = (b < a.Bt) ? __ldcg(q + b * BL_M) : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (sl0 + u < S) {
+#pragma unroll
+                for (int b = 0; b < BL_NT; ++b) y[b] += t[u][b];
+              }
           }
         }
       }
       if (mine) {
         if (a.norm_w) {
-          if (tid < BL_NT) {
-            float tot = 0.f;
-            if (S > 1) {
-              for (int sl = 0; sl < S; ++sl) tot += __ldcg(a.ss + sl * BL_NT + tid);
-            } else {
-              tot = sh.ss_own[tid];
+          if (!rstd_ready) {  // once per CTA: every slice's sum of squares is visible to a row block's last arriver
+            for (int i = tid; i < S * BL_NT; i += 128) ss_all[i] = (S > 1) ? __ldcg(a.ss + i) : sh.ss_own[i];
+            bl_bar();
+            if (tid < BL_NT) {
+              float tot = 0.f;
+              for (int sl = 0; sl < S; ++sl) tot += ss_all[sl * BL_NT + tid];
+              sh.rstd[tid] = rsqrtf(tot / (float)a.K + a.eps);
             }
-            sh.rstd[tid] = rsqrtf(tot / (float)a.K + a.eps);
+            bl_bar();
+            rstd_ready = true;
           }
-          bl_bar();
 #pragma unroll
           for (int b = 0; b < BL_NT; ++b) y[b] *= sh.rstd[b];
         }
@@ -367,7 +382,7 @@ batched_linear_kernel(const BlArgs a, const __grid_constant__ CUtensorMap tm_w) 
           }
         }
       }
-      bl_bar();  // ex, rstd and last are reused by the next unit
+      bl_bar();  // ex and last are reused by the next unit
     }
   }
 
@@ -456,6 +471,7 @@ int launch_bl(const omnikv_batched_linear_params* p, const BlPlan& pl, cudaStrea
   a.epi = p->epilogue;
   a.inter = p->w_rows / 2;
   a.status = p->status;
+  { const char* e = getenv("OMNIKV_BL_DEBUG"); a.dbg = e ? atoi(e) : 0; }
   auto kern = batched_linear_kernel<T>;
   static bool attr_set[2] = {false, false};
   if (!attr_set[bf16 ? 1 : 0]) {

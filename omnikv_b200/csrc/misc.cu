@@ -151,6 +151,40 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gu,
   act[(size_t)b * act_sb + j] = from_float<T>(g / (1.f + expf(-g)) * u);
 }
 
+// h[b] += delta[b] (when delta is given; rounded to T, as the residual stream is stored), out[b] = RMSNorm(h[b]) * w.
+// One CTA per token, 256 threads; a thread visits the same elements in both passes.
+template <typename T>
+__global__ void __launch_bounds__(256) add_rms_norm_kernel(T* __restrict__ h, int64_t h_st, const T* __restrict__ delta,
+                                                           int64_t d_st, const T* __restrict__ w, float eps,
+                                                           T* __restrict__ out, int64_t o_st, int hidden) {
+  __shared__ float red[8];
+  pdl_wait();
+  const int b = blockIdx.x, tid = threadIdx.x;
+  T* hr = h + (size_t)b * h_st;
+  const T* dr = delta ? delta + (size_t)b * d_st : nullptr;
+  float ss = 0.f;
+  for (int i = tid; i < hidden; i += 256) {
+    float v = to_float(hr[i]);
+    if (dr) {
+      v = to_float(from_float<T>(v + to_float(dr[i])));
+      hr[i] = from_float<T>(v);
+    }
+    ss = fmaf(v, v, ss);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float rstd = rsqrtf(tot / (float)hidden + eps);
+  for (int i = tid; i < hidden; i += 256) {  // the thread re-reads what it read or wrote above (L1 / L2 hits)
+    const float v = to_float(hr[i]);
+    out[(size_t)b * o_st + i] = from_float<T>(v * rstd * to_float(w[i]));
+  }
+}
+
 // Host-link gather.  One selected token is one contiguous chunk of n_layers*2*KVH rows in pinned
 // host memory; row r of the chunk (layer l, K|V c, head h) goes to staged[l][c][h][j][:].
 // A warp copies rows with one 16-byte load per lane per step, several rows in flight.
@@ -346,6 +380,26 @@ extern "C" int omnikv_silu_mul(int dtype, const void* gate_up, int64_t gate_up_s
     default: return OMNIKV_E_UNSUPPORTED;
   }
   OMNIKV_CUDA_OK(cudaGetLastError());
+  return OMNIKV_OK;
+}
+
+extern "C" int omnikv_add_rms_norm(int dtype, void* h, int64_t h_stride_tok, const void* delta, int64_t delta_stride_tok,
+                                   const void* norm_w, float eps, void* out, int64_t out_stride_tok, int n_tokens,
+                                   int hidden, void* stream) {
+  using namespace omnikv;
+  if (!h || !norm_w || !out || n_tokens <= 0 || hidden <= 0) return OMNIKV_E_BADARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define OMNIKV_ARN_LAUNCH(T)                                                                                        \
+  OMNIKV_CUDA_OK(launch_pdl_args(add_rms_norm_kernel<T>, dim3(n_tokens), dim3(256), st, static_cast<T*>(h), h_stride_tok, \
+                                 static_cast<const T*>(delta), delta_stride_tok, static_cast<const T*>(norm_w), eps,  \
+                                 static_cast<T*>(out), out_stride_tok, hidden))
+  switch (dtype) {
+    case OMNIKV_BF16: OMNIKV_ARN_LAUNCH(__nv_bfloat16); break;
+    case OMNIKV_F16: OMNIKV_ARN_LAUNCH(__half); break;
+    case OMNIKV_F32: OMNIKV_ARN_LAUNCH(float); break;
+    default: return OMNIKV_E_UNSUPPORTED;
+  }
+#undef OMNIKV_ARN_LAUNCH
   return OMNIKV_OK;
 }
 

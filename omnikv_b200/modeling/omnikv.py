@@ -308,13 +308,18 @@ class OmniKVAttention(nn.Module):
         if (n == 1 and rope_pos is not None and hidden_states.is_cuda and self.head_dim == 128
                 and self.rotary_emb.attention_scaling == 1.0):
             # decode: rotate q and k and append k, v to the cache in one kernel, straight from the fused projection
-            qkv = F.linear(hidden_states.view(B, -1), self.qkv_weight)
+            tc = _tc_linear_ok(self.config, hidden_states)
+            x2 = hidden_states.view(B, -1)
+            qkv = ops.batched_linear(x2, self.qkv_weight) if tc else F.linear(x2, self.qkv_weight)
             q = torch.empty(B, self.num_heads, self.head_dim, dtype=qkv.dtype, device=qkv.device)
             k_buf, v_buf, pos = past_key_value.write_target_batch(self.layer_idx)
             ops.rope_append(qkv, self.num_heads, self.num_key_value_heads, self.rotary_emb.inv_freq, rope_pos, q,
                             k_buf, v_buf, pos)
             o = past_key_value.attend(q, self.layer_idx, score_out=score_out, score_len=score_len)
-            o = F.linear(o.view(B, 1, self.num_heads * self.head_dim), self.o_weight)
+            if tc:
+                o = ops.batched_linear(o.view(B, self.num_heads * self.head_dim), self.o_weight).view(B, 1, -1)
+            else:
+                o = F.linear(o.view(B, 1, self.num_heads * self.head_dim), self.o_weight)
             return self.tp.all_reduce_sum(o) if self.tp is not None else o
         cos, sin = position_embeddings
         q, k, v = self.qkv(hidden_states, cos, sin)
@@ -335,10 +340,18 @@ class OmniKVAttention(nn.Module):
         return self.tp.all_reduce_sum(o) if self.tp is not None else o
 
 
+def _tc_linear_ok(config, x, inter=64) -> bool:
+    """Decode-sized activations (at most 16 tokens, 16-bit, on the GPU) and ``tcgen05_linear`` switched on: the
+    projections go through ``omnikv_batched_linear`` instead of the library GEMM."""
+    return (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and x.shape[-2] == 1 and x.numel() // x.shape[-1] <= 16
+            and inter % 64 == 0 and x.shape[-1] % 8 == 0 and config.get("tcgen05_linear", False))
+
+
 class OmniKVMLP(nn.Module):
     def __init__(self, config, tp=None):
         super().__init__()
         self.tp = tp
+        self.config = config
         self.intermediate_size = config.intermediate_size // (tp.world if tp is not None else 1)  # local slice
         self.gate_up_weight = nn.Parameter(torch.empty(2 * self.intermediate_size, config.hidden_size))
         self.down_weight = nn.Parameter(torch.empty(config.hidden_size, self.intermediate_size))
@@ -347,6 +360,11 @@ class OmniKVMLP(nn.Module):
         self.down_proj = _ProjView(self, "down_weight", 0, config.hidden_size)
 
     def forward(self, x):
+        if _tc_linear_ok(self.config, x, self.intermediate_size):  # opt-in: this package's tcgen05 weight stream
+            x2 = x.reshape(-1, x.shape[-1])
+            act = ops.batched_linear(x2, self.gate_up_weight, epilogue="swiglu")
+            o = ops.batched_linear(act, self.down_weight).view(*x.shape[:-1], -1)
+            return self.tp.all_reduce_sum(o) if self.tp is not None else o
         gu = F.linear(x, self.gate_up_weight)
         if x.is_cuda and x.shape[-2] == 1:  # decode: one kernel for silu(gate) * up
             act = ops.silu_mul(gu.view(-1, 2 * self.intermediate_size)).view(*x.shape[:-1], self.intermediate_size)
@@ -483,7 +501,7 @@ class OmniKVMulLayer(nn.Module):
                 act=torch.empty(mlp.intermediate_size, dtype=dt, device=dev))
         return bufs
 
-    def _decode_select_begin(self, hidden_states, cache, position_embeddings):
+    def _decode_select_begin(self, hidden_states, cache, position_embeddings, normed=None):
         """Filter layer, before its attention: selector ``last`` hands the attention kernel the score planes to
         fill; the window selectors run their own scoring kernels on the observation window now.
         Returns (score_out, score_len)."""
@@ -502,7 +520,7 @@ class OmniKVMulLayer(nn.Module):
             return st.planes, cache.prefill_len_dev
         if position_embeddings is None:
             position_embeddings = self.self_attn.rotary_emb(hidden_states, cache.pos_dev[:, None])
-        self._select(self.input_layernorm(hidden_states), position_embeddings, cache)
+        self._select(self.input_layernorm(hidden_states) if normed is None else normed, position_embeddings, cache)
         return None, None
 
     def _decode_select_end(self, cache, score_out):
@@ -589,8 +607,21 @@ class OmniKVMulLayer(nn.Module):
             out = self._forward_decode_fused(hidden_states, past_key_value, position_embeddings)
             return out + ((past_key_value,) if use_cache else ())
         residual = hidden_states
-        hidden_states = self.input_layernorm(hidden_states)
         n = hidden_states.shape[1]
+        # decode through the PyTorch modules (several sequences, or the fused batch-1 kernels switched off): every
+        # residual add travels with the norm behind it in one launch, so the second add of a layer is handed to
+        # the next layer (or to the model's final norm) through the cache object
+        small = (n == 1 and hidden_states.is_cuda and hidden_states.is_contiguous() and past_key_value is not None
+                 and self.config.get("fused_small_ops", True))
+        if small:
+            B = hidden_states.shape[0]
+            stream2d = residual.view(B, -1)
+            delta = getattr(past_key_value, "pending_delta", None)
+            past_key_value.pending_delta = None
+            hidden_states = ops.add_rms_norm(stream2d, delta, self.input_layernorm.weight,
+                                             self.input_layernorm.variance_epsilon).view(B, 1, -1)
+        else:
+            hidden_states = self.input_layernorm(hidden_states)
         if n > 1:
             self.prefill_len = n
             if "last" not in self.selector_cls and self.is_filter:
@@ -604,12 +635,23 @@ class OmniKVMulLayer(nn.Module):
         selecting = n == 1 and past_key_value is not None and self.is_filter
         score_out = score_len = None
         if selecting:
-            score_out, score_len = self._decode_select_begin(residual, past_key_value, position_embeddings)
+            score_out, score_len = self._decode_select_begin(residual, past_key_value, position_embeddings,
+                                                             normed=hidden_states if small else None)
 
         hidden_states = self.self_attn(hidden_states, position_embeddings, past_key_value, score_out=score_out,
                                        score_len=score_len)
         if selecting:
             self._decode_select_end(past_key_value, score_out)
+        if small:
+            hidden_states = ops.add_rms_norm(stream2d, hidden_states.reshape(B, -1), self.post_attention_layernorm.weight,
+                                             self.post_attention_layernorm.variance_epsilon).view(B, 1, -1)
+            past_key_value.pending_delta = self.mlp(hidden_states).reshape(B, -1)
+            outputs = (residual,)
+            if output_attentions:
+                outputs += (None,)
+            if use_cache:
+                outputs += (past_key_value,)
+            return outputs
         hidden_states = residual + hidden_states
 
         residual = hidden_states
@@ -664,7 +706,14 @@ class OmniKVMulModel(nn.Module):
                       use_cache=use_cache, cache_position=cache_position, position_embeddings=pos_emb)[0]
             if n > 1:
                 h = h.contiguous()
-        if apply_final_norm:
+        delta = getattr(cache, "pending_delta", None) if cache is not None else None
+        if delta is not None:  # the last layer's second residual add, handed on by the layer (see OmniKVMulLayer.forward)
+            cache.pending_delta = None
+            if apply_final_norm:
+                h = ops.add_rms_norm(h.view(B, -1), delta, self.norm.weight, self.norm.variance_epsilon).view(B, 1, -1)
+            else:
+                h = h + delta.view_as(h)
+        elif apply_final_norm:
             h = self.norm(h)
         return SimpleNamespace(last_hidden_state=h, past_key_values=cache, hidden_states=None, attentions=None)
 

@@ -380,6 +380,23 @@ def rope_append(qkv: torch.Tensor, H: int, KVH: int, inv_freq: torch.Tensor, rop
     _count(1)
 
 
+def add_rms_norm(h: torch.Tensor, delta: Optional[torch.Tensor], norm_w: torch.Tensor, eps: float,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``omnikv_add_rms_norm``.  h ``[n, hidden]`` (updated IN PLACE: ``h += delta`` when delta is given); returns
+    ``RMSNorm(h) * norm_w``."""
+    _need_cuda(h, delta, norm_w, out)
+    if h.dim() != 2 or h.stride(1) != 1 or (delta is not None and (delta.shape != h.shape or delta.stride(1) != 1)):
+        raise abi.OmniKVError("add_rms_norm: h and delta must be [n, hidden] with contiguous rows")
+    if out is None:
+        out = torch.empty_like(h, memory_format=torch.contiguous_format)
+    abi.check(abi.lib().omnikv_add_rms_norm(_DT[h.dtype], h.data_ptr(), h.stride(0), _ptr(delta),
+                                            0 if delta is None else delta.stride(0), norm_w.data_ptr(), float(eps),
+                                            out.data_ptr(), out.stride(0), h.shape[0], h.shape[1], _stream()),
+              "omnikv_add_rms_norm")
+    _count(1)
+    return out
+
+
 def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``omnikv_silu_mul``.  gate_up ``[B, 2*inter]`` (rows contiguous) -> ``silu(gate) * up`` ``[B, inter]``."""
     _need_cuda(gate_up, out)

@@ -603,3 +603,30 @@ def test_bounded_peer_wait_reports_and_returns():
     gu = w.float() @ want
     ref = torch.nn.functional.silu(gu[:inter]) * gu[inter:]
     assert (act.float() - ref).abs().max().item() <= 0.05 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_batched_decode_tcgen05_linear_and_fused_adds_match_library_path(dtype):
+    """A batched 16-bit decode step three ways: PyTorch modules with separate add and norm kernels, the same with
+    the add + norm launches of this package, and with the projections on this package's tcgen05 weight stream.  All
+    three are the same arithmetic up to 16-bit rounding points (2e-2 on logits of a model whose selection is not
+    peaked, as in the other 16-bit model tests)."""
+    logits = []
+    for opts in (dict(fused_small_ops=False), dict(fused_small_ops=True), dict(fused_small_ops=True, tcgen05_linear=True)):
+        cfg = small_config(selector_cls="last", num_of_selected_tokens=50, **opts)
+        lm, _ = build(cfg, dtype)
+        lens = [700, 300, 512, 640]
+        cache = lm.new_cache().init_synthetic(4, 1, 128, lens, dtype, "cuda", seed=5, reserve=64)
+        tok = torch.tensor([[1], [2], [3], [4]], device="cuda")
+        steps = []
+        for _ in range(3):
+            out = lm(input_ids=tok, past_key_values=cache).logits
+            steps.append(out.float())
+            tok = out[:, -1].argmax(-1, keepdim=True) if not logits else forced[len(steps) - 1]
+        if not logits:
+            forced = [s[:, -1].argmax(-1, keepdim=True) for s in steps]
+        logits.append(torch.stack(steps))
+        from omnikv_b200 import ops
+        ops.check_status("cuda")
+    assert (logits[0] - logits[1]).abs().max().item() <= 2e-2
+    assert (logits[0] - logits[2]).abs().max().item() <= 2e-2
