@@ -132,10 +132,10 @@ __device__ __forceinline__ float stage_x(unsigned char* x_s, const BlArgs& a, in
   const T* nw = static_cast<const T*>(a.norm_w);
   const int total = nch * 8;  // 16-byte pieces of a token's slice
   float ss = 0.f;
-  for (int base = 0; base < total; base += 32) {  // four pieces per thread per round, loads before stores
-    uint4 v[4], w[4];
+  for (int base = 0; base < total; base += 64) {  // eight pieces per thread per round, loads before stores
+    uint4 v[8], w[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < 8; ++u) {
       const int q = base + t8 + 8 * u;
       const int col = c0 * BL_KC + q * 8;
       v[u] = make_uint4(0, 0, 0, 0);
@@ -146,7 +146,7 @@ __device__ __forceinline__ float stage_x(unsigned char* x_s, const BlArgs& a, in
       }
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < 8; ++u) {
       const int q = base + t8 + 8 * u;
       if (q >= total) continue;
       uint4 o = v[u];

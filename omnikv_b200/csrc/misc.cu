@@ -185,6 +185,77 @@ __global__ void __launch_bounds__(256) add_rms_norm_kernel(T* __restrict__ h, in
   }
 }
 
+// The same with 16-byte vectors, every load of a thread issued before its first store (hidden a multiple of the
+// vector width and at most 1024 vectors per token: 8192 elements in 16 bits).
+template <typename T>
+__global__ void __launch_bounds__(256) add_rms_norm_vec_kernel(T* __restrict__ h, int64_t h_st, const T* __restrict__ delta,
+                                                               int64_t d_st, const T* __restrict__ w, float eps,
+                                                               T* __restrict__ out, int64_t o_st, int hidden) {
+  constexpr int V = 16 / sizeof(T);
+  __shared__ float red[8];
+  const int b = blockIdx.x, tid = threadIdx.x, nvec = hidden / V;
+  uint4 wv[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {  // the norm weight does not depend on the kernel before
+    const int i = tid + u * 256;
+    wv[u] = i < nvec ? reinterpret_cast<const uint4*>(w)[i] : make_uint4(0, 0, 0, 0);
+  }
+  pdl_wait();
+  uint4* h4 = reinterpret_cast<uint4*>(h + (size_t)b * h_st);
+  const uint4* d4 = delta ? reinterpret_cast<const uint4*>(delta + (size_t)b * d_st) : nullptr;
+  uint4 hv[4], dv[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int i = tid + u * 256;
+    hv[u] = make_uint4(0, 0, 0, 0);
+    dv[u] = hv[u];
+    if (i < nvec) {
+      hv[u] = h4[i];
+      if (d4) dv[u] = d4[i];
+    }
+  }
+  float x[4][V];
+  float ss = 0.f;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const T* he = reinterpret_cast<const T*>(&hv[u]);
+    const T* de = reinterpret_cast<const T*>(&dv[u]);
+    T* oe = reinterpret_cast<T*>(&hv[u]);
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      float v = to_float(he[e]);
+      if (d4) {
+        oe[e] = from_float<T>(v + to_float(de[e]));
+        v = to_float(oe[e]);
+      }
+      x[u][e] = v;
+      ss = fmaf(v, v, ss);
+    }
+    const int i = tid + u * 256;
+    if (d4 && i < nvec) h4[i] = hv[u];
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float rstd = rsqrtf(tot / (float)hidden + eps);
+  uint4* o4 = reinterpret_cast<uint4*>(out + (size_t)b * o_st);
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int i = tid + u * 256;
+    if (i >= nvec) continue;
+    uint4 ov;
+    T* oe = reinterpret_cast<T*>(&ov);
+    const T* we = reinterpret_cast<const T*>(&wv[u]);
+#pragma unroll
+    for (int e = 0; e < V; ++e) oe[e] = from_float<T>(x[u][e] * rstd * to_float(we[e]));
+    o4[i] = ov;
+  }
+}
+
 // Host-link gather.  One selected token is one contiguous chunk of n_layers*2*KVH rows in pinned
 // host memory; row r of the chunk (layer l, K|V c, head h) goes to staged[l][c][h][j][:].
 // A warp copies rows with one 16-byte load per lane per step, several rows in flight.
@@ -389,14 +460,18 @@ extern "C" int omnikv_add_rms_norm(int dtype, void* h, int64_t h_stride_tok, con
   using namespace omnikv;
   if (!h || !norm_w || !out || n_tokens <= 0 || hidden <= 0) return OMNIKV_E_BADARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const auto aligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
 #define OMNIKV_ARN_LAUNCH(T)                                                                                        \
-  OMNIKV_CUDA_OK(launch_pdl_args(add_rms_norm_kernel<T>, dim3(n_tokens), dim3(256), st, static_cast<T*>(h), h_stride_tok, \
+  const int V = 16 / (int)sizeof(T);                                                                                \
+  const bool vec = hidden % V == 0 && hidden / V <= 1024 && aligned(h) && aligned(delta) && aligned(norm_w) &&      \
+                   aligned(out) && h_stride_tok % V == 0 && delta_stride_tok % V == 0 && out_stride_tok % V == 0;   \
+  OMNIKV_CUDA_OK(launch_pdl_args(vec ? add_rms_norm_vec_kernel<T> : add_rms_norm_kernel<T>, dim3(n_tokens), dim3(256), st, static_cast<T*>(h), h_stride_tok, \
                                  static_cast<const T*>(delta), delta_stride_tok, static_cast<const T*>(norm_w), eps,  \
                                  static_cast<T*>(out), out_stride_tok, hidden))
   switch (dtype) {
-    case OMNIKV_BF16: OMNIKV_ARN_LAUNCH(__nv_bfloat16); break;
-    case OMNIKV_F16: OMNIKV_ARN_LAUNCH(__half); break;
-    case OMNIKV_F32: OMNIKV_ARN_LAUNCH(float); break;
+    case OMNIKV_BF16: { OMNIKV_ARN_LAUNCH(__nv_bfloat16); break; }
+    case OMNIKV_F16: { OMNIKV_ARN_LAUNCH(__half); break; }
+    case OMNIKV_F32: { OMNIKV_ARN_LAUNCH(float); break; }
     default: return OMNIKV_E_UNSUPPORTED;
   }
 #undef OMNIKV_ARN_LAUNCH
