@@ -55,7 +55,6 @@ struct BlArgs {
   int* counters;  // [R], zero between calls
   int Bt, N, K, S, R, chunks, epi, inter;
   int* status;
-  int dbg;
 };
 
 struct BlShared {
@@ -228,7 +227,6 @@ batched_linear_kernel(const BlArgs a, const __grid_constant__ CUtensorMap tm_w) 
             break;
           }
           unsigned char* dst = ring + (size_t)st * BL_STAGE_BYTES;
-          if (a.dbg == 2) { mbar_arrive(&sh.full[st]); sh.issued = 0; continue; }
           mbar_expect_tx(&sh.full[st], BL_STAGE_BYTES);
           const int col = (c0 + c) * BL_KC;
           if (swiglu) {  // 64 gate rows and the 64 up rows that belong to them
@@ -259,7 +257,7 @@ batched_linear_kernel(const BlArgs a, const __grid_constant__ CUtensorMap tm_w) 
           const unsigned w_base = smem_u32(ring + (size_t)st * BL_STAGE_BYTES);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            if (a.dbg != 1) tc_mma(d_tmem, smem_desc_sw128(w_base + k * 32), smem_desc_sw128(x_base + c * BL_XBOX_BYTES + k * 32), idesc,
+            tc_mma(d_tmem, smem_desc_sw128(w_base + k * 32), smem_desc_sw128(x_base + c * BL_XBOX_BYTES + k * 32), idesc,
                    (c | k) ? 1u : 0u);
           tc_commit(&sh.empty[st]);
         }
@@ -471,7 +469,6 @@ int launch_bl(const omnikv_batched_linear_params* p, const BlPlan& pl, cudaStrea
   a.epi = p->epilogue;
   a.inter = p->w_rows / 2;
   a.status = p->status;
-  { const char* e = getenv("OMNIKV_BL_DEBUG"); a.dbg = e ? atoi(e) : 0; }
   auto kern = batched_linear_kernel<T>;
   static bool attr_set[2] = {false, false};
   if (!attr_set[bf16 ? 1 : 0]) {
