@@ -12,9 +12,11 @@
 //   P  = 2^(S c - m)  written by the softmax threads as 16-bit into shared memory with the same swizzle
 //   PV = P V       P = A operand (K-major over keys), the V tile as it lies in memory ([keys x 128]: rows run
 //                  along the contraction) = MN-major B operand; accumulator [128 queries x 128] in tensor memory
-//   O  = O alpha + PV   in the softmax thread's registers (one query row, 128 fp32)
+//   O  = O alpha + PV   in the softmax threads' registers (one query row: 2 x 64 fp32)
 //
-// Roles: warps 0-3 softmax (one TMEM lane quarter each), one thread issues the TMA copies, one the MMAs.  S and PV
+// Roles: eight softmax warps (two per TMEM lane quarter, so that each scheduler has two warps to overlap: both take
+// the row maximum, each exponentiates half of the keys and accumulates half of the output columns), one thread issues
+// the TMA copies, one the MMAs.  S and PV
 // are double-buffered in tensor memory (4 x 128 columns), K and V tiles in two-stage rings, so the tensor pipe
 // computes S of tile j+1 and PV of tile j-1 while the softmax threads work on tile j.
 // Every wait is bounded by time; on expiry the CTA raises a flag, every role leaves its loop, copies in flight are
@@ -29,7 +31,7 @@ constexpr int PF_TILE = 128;                  // queries per CTA = keys per tile
 constexpr int PF_TILE_BYTES = PF_TILE * 256;  // [128 rows x 128] 16-bit: two boxes of 128 rows x 128 bytes
 constexpr int PF_BOX_BYTES = PF_TILE * 128;
 constexpr int PF_STAGES = 2;
-constexpr int PF_THREADS = 192;  // warps 0-3 softmax, 4 TMA producer, 5 MMA issuer
+constexpr int PF_THREADS = 320;  // warps 0-7 softmax (two per TMEM lane quarter), 8 TMA producer, 9 MMA issuer
 constexpr unsigned PF_TMEM_COLS = 512;  // S0 | S1 | PV0 | PV1, 128 columns each
 constexpr int PF_SMEM_BYTES = PF_TILE_BYTES * (1 + 2 * PF_STAGES + 1) + 1024;  // Q, K ring, V ring, P, alignment
 
@@ -77,6 +79,7 @@ prefill_attn_kernel(const PfArgs a, const __grid_constant__ CUtensorMap tm_q, co
                     const __grid_constant__ CUtensorMap tm_v) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ PfShared sh;
+  __shared__ float l_s[2][PF_TILE];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* q_s = smem;
   unsigned char* k_ring = q_s + PF_TILE_BYTES;
@@ -102,11 +105,11 @@ prefill_attn_kernel(const PfArgs a, const __grid_constant__ CUtensorMap tm_q, co
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sh.s_full[i], 1);
-      mbar_init(&sh.s_empty[i], 128);
+      mbar_init(&sh.s_empty[i], 256);
       mbar_init(&sh.pv_full[i], 1);
-      mbar_init(&sh.pv_empty[i], 128);
+      mbar_init(&sh.pv_empty[i], 256);
     }
-    mbar_init(&sh.p_full, 128);
+    mbar_init(&sh.p_full, 256);
     mbar_init(&sh.p_empty, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -120,9 +123,9 @@ prefill_attn_kernel(const PfArgs a, const __grid_constant__ CUtensorMap tm_q, co
   tc_fence_after();
   const unsigned tmem = sh.tmem_base;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ---- TMA producer ------------------------------------------------------------------------------------
-    if (tid == 128) {
+    if (tid == 256) {
       mbar_expect_tx(&sh.q_full, PF_TILE_BYTES);
       tma_load_4d(q_s, &tm_q, 0, q0, h, b, &sh.q_full);
       tma_load_4d(q_s + PF_BOX_BYTES, &tm_q, 64, q0, h, b, &sh.q_full);
@@ -144,9 +147,9 @@ prefill_attn_kernel(const PfArgs a, const __grid_constant__ CUtensorMap tm_q, co
         sh.v_issued = j + 1;
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ---- MMA issuer ----------------------------------------------------------------------------------------
-    if (tid == 160) {
+    if (tid == 288) {
       const unsigned idesc_s = tc_instr_desc<T>(PF_TILE, PF_TILE, false, false);
       const unsigned idesc_pv = tc_instr_desc<T>(PF_TILE, kHeadDim, false, true);
       const unsigned q_base = smem_u32(q_s), p_base = smem_u32(p_s);
@@ -195,24 +198,28 @@ prefill_attn_kernel(const PfArgs a, const __grid_constant__ CUtensorMap tm_q, co
       if (!ok) pf_fail(sh, a.status);
     }
   } else {
-    // ---- softmax: thread = query row -----------------------------------------------------------------------
-    const int row = tid;  // TMEM lane; warp w reaches lanes 32 w .. 32 w + 31
-    const int pos = a.q_pos0 + q0 + row;  // last visible key of this query
-    const unsigned lane_addr = tmem + ((unsigned)(warp * 32) << 16);
+    // ---- softmax: two threads per query row (warps w and w + 4 share TMEM lane quarter w) -------------------
+    // Each takes the row maximum over all 128 logits of the tile (cheap, and it spares an exchange), but
+    // exponentiates and writes only ITS half of the key columns of P, and accumulates ITS half of the output columns.
+    const int quarter = warp & 3, hf = warp >> 2;
+    const int row = quarter * 32 + (tid & 31);  // TMEM lane
+    const int pos = a.q_pos0 + q0 + row;        // last visible key of this query
+    const unsigned lane_addr = tmem + ((unsigned)(quarter * 32) << 16);
     const float c = a.scale_log2;
+    constexpr int HC = kHeadDim / 2;  // columns per thread: 64 keys of P, 64 dims of O
     float m = -INFINITY, l = 0.f, alpha_pending = 1.f;
-    float o[kHeadDim];
+    float o[HC];
 #pragma unroll
-    for (int i = 0; i < kHeadDim; ++i) o[i] = 0.f;
+    for (int i = 0; i < HC; ++i) o[i] = 0.f;
     bool ok = true;
-    // O = O * alpha_pending + PV_i
+    // O = O * alpha_pending + PV_i (this thread's 64 output columns)
     auto take_pv = [&](int i) -> bool {
       const int buf = i & 1;
       if (!mbar_wait(&sh.pv_full[buf], (i >> 1) & 1, &sh.fail)) return false;
       tc_fence_after();
-      const unsigned t = lane_addr + 256u + (unsigned)buf * 128u;
+      const unsigned t = lane_addr + 256u + (unsigned)buf * 128u + (unsigned)hf * HC;
 #pragma unroll
-      for (int cb = 0; cb < kHeadDim; cb += 32) {
+      for (int cb = 0; cb < HC; cb += 32) {
         float v[32];
         tmem_ld16(t + cb, *reinterpret_cast<float(*)[16]>(&v[0]));
         tmem_ld16(t + cb + 16, *reinterpret_cast<float(*)[16]>(&v[16]));
@@ -231,8 +238,8 @@ prefill_attn_kernel(const PfArgs a, const __grid_constant__ CUtensorMap tm_q, co
       const unsigned t = lane_addr + (unsigned)buf * 128u;
       const int key0 = j * PF_TILE;
       const bool masked = key0 + PF_TILE - 1 > a.q_pos0 + q0;  // some query of this CTA does not see the whole tile
-      // pass A: the row's maximum
-      float mx = m;
+      // pass A: the row's maximum over the whole tile (raw logits; the scale is positive)
+      float mraw = -INFINITY;
 #pragma unroll
       for (int cb = 0; cb < PF_TILE; cb += 32) {
         float v[32];
@@ -242,13 +249,14 @@ prefill_attn_kernel(const PfArgs a, const __grid_constant__ CUtensorMap tm_q, co
         if (masked) {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (key0 + cb + i <= pos) mx = fmaxf(mx, v[i] * c);
+            if (key0 + cb + i <= pos) mraw = fmaxf(mraw, v[i]);
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i] * c);
+          for (int i = 0; i < 32; ++i) mraw = fmaxf(mraw, v[i]);
         }
       }
-      // key 0 is visible to every query, so mx is finite from the first tile on
+      // key 0 is visible to every query, so the maximum is finite from the first tile on
+      const float mx = fmaxf(m, mraw * c);
       const float alpha = ex2_fast(m - mx);
       m = mx;
       // the previous tile's PV product has read P: fold it into O before alpha_pending changes, then reuse P
@@ -257,30 +265,30 @@ prefill_attn_kernel(const PfArgs a, const __grid_constant__ CUtensorMap tm_q, co
         if (!take_pv(j - 1)) { ok = false; break; }
       }
       alpha_pending = alpha;
-      // pass B: P = 2^(S c - m) as 16-bit into shared memory, row sum
+      // pass B: this thread's 64 keys: P = 2^(S c - m) as 16-bit into box `hf` of P, partial row sum
       float sum = 0.f;
 #pragma unroll
-      for (int cb = 0; cb < PF_TILE; cb += 32) {
+      for (int cb = 0; cb < HC; cb += 32) {
         float v[32];
-        tmem_ld16(t + cb, *reinterpret_cast<float(*)[16]>(&v[0]));
-        tmem_ld16(t + cb + 16, *reinterpret_cast<float(*)[16]>(&v[16]));
+        tmem_ld16(t + hf * HC + cb, *reinterpret_cast<float(*)[16]>(&v[0]));
+        tmem_ld16(t + hf * HC + cb + 16, *reinterpret_cast<float(*)[16]>(&v[16]));
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           float p = ex2_fast(fmaf(v[i], c, -mx));
-          if (masked && key0 + cb + i > pos) p = 0.f;
+          if (masked && key0 + hf * HC + cb + i > pos) p = 0.f;
           v[i] = p;
           sum += p;
         }
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {  // 8 keys = one 16-byte chunk of the row's 128-byte line in its 64-key box
-          const int chunk = (cb >> 3) + ch;  // 0..15
+          const int chunk = (cb >> 3) + ch;  // 0..7 inside the box
           uint4 w;
           w.x = pack2<T>(v[ch * 8 + 0], v[ch * 8 + 1]);
           w.y = pack2<T>(v[ch * 8 + 2], v[ch * 8 + 3]);
           w.z = pack2<T>(v[ch * 8 + 4], v[ch * 8 + 5]);
           w.w = pack2<T>(v[ch * 8 + 6], v[ch * 8 + 7]);
-          *reinterpret_cast<uint4*>(p_s + (chunk >> 3) * PF_BOX_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4)) = w;
+          *reinterpret_cast<uint4*>(p_s + hf * PF_BOX_BYTES + row * 128 + ((chunk ^ (row & 7)) << 4)) = w;
         }
       }
       l = fmaf(l, alpha, sum);
@@ -289,12 +297,17 @@ prefill_attn_kernel(const PfArgs a, const __grid_constant__ CUtensorMap tm_q, co
       tc_fence_before();
       mbar_arrive(&sh.s_empty[buf]);
     }
-    if (ok && mbar_wait(&sh.p_empty, (n_tiles - 1) & 1, &sh.fail) && take_pv(n_tiles - 1)) {
+    ok = ok && mbar_wait(&sh.p_empty, (n_tiles - 1) & 1, &sh.fail) && take_pv(n_tiles - 1);
+    // the two halves of a row meet for the normaliser (every softmax thread reaches this barrier)
+    l_s[hf][row] = l;
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");
+    if (ok) {
       if (q0 + row < a.Sq) {
-        const float inv = 1.f / l;
-        T* dst = reinterpret_cast<T*>(a.out) + (size_t)b * a.o_sb + (size_t)(q0 + row) * a.o_sn + (size_t)h * a.o_sh;
+        const float inv = 1.f / (l + l_s[hf ^ 1][row]);
+        T* dst = reinterpret_cast<T*>(a.out) + (size_t)b * a.o_sb + (size_t)(q0 + row) * a.o_sn + (size_t)h * a.o_sh +
+                 hf * HC;
 #pragma unroll
-        for (int i = 0; i < kHeadDim; i += 8) {
+        for (int i = 0; i < HC; i += 8) {
           uint4 w;
           w.x = pack2<T>(o[i] * inv, o[i + 1] * inv);
           w.y = pack2<T>(o[i + 2] * inv, o[i + 3] * inv);
@@ -314,7 +327,7 @@ prefill_attn_kernel(const PfArgs a, const __grid_constant__ CUtensorMap tm_q, co
   if (sh.fail) {
     // copies that were asked for may still be on their way into this CTA's shared memory: wait (bounded) for the
     // last requested tile of every stage before the memory is given up
-    if (tid == 128) {
+    if (tid == 256) {
       if (sh.q_issued) mbar_wait(&sh.q_full, 0);
       for (int s = 0; s < PF_STAGES; ++s) {
         const int kl = sh.k_issued - 1 - ((sh.k_issued - 1 - s) % PF_STAGES + PF_STAGES) % PF_STAGES;
