@@ -545,7 +545,7 @@ int launch_mma(const WinArgs& a, int n_chunks2, int max_len, cudaStream_t st) {
     t.qw = a.qw; t.consider_len = a.consider_len; t.part = a.part;
     t.tplane = a.stats + stats_floats(a.B, a.H); t.tplane_stride = (int64_t)plane_stride_of(max_len);
     t.score_out = a.score_out; t.planes_out = a.planes_out; t.score_stride = a.score_stride;
-    t.B = a.B; t.H = a.H; t.KVH = a.KVH; t.G = G; t.W = a.W; t.S = window_tc_splits(a.B, a.KVH, n_sms);
+    t.B = a.B; t.H = a.H; t.KVH = a.KVH; t.G = G; t.W = a.W; t.S = window_tc_splits(a.B, a.KVH, n_sms, max_len);
     t.selector = a.selector; t.n_sms = n_sms; t.scale = a.scale; t.status = a.status;
     return window_tc_launch(is_bf16 ? OMNIKV_BF16 : OMNIKV_F16, t, tm_k, max_len, st);
   }

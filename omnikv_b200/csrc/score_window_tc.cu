@@ -258,7 +258,11 @@ __global__ void __launch_bounds__(P1Shape<G>::THREADS, 2) window_tc_pass1(const 
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n = a.consider_len[b];
-  const int chunk = ceil_div(ceil_div(n, a.S), TC_TILE) * TC_TILE;
+  // chunks are sized by the LONGEST sequence of the batch: every CTA then has the same amount of work, a short
+  // sequence uses fewer of its S splits (the others hand in empty partials)
+  int n_max = n;
+  for (int bb = 0; bb < a.B; ++bb) n_max = max(n_max, a.consider_len[bb]);
+  const int chunk = ceil_div(ceil_div(n_max, a.S), TC_TILE) * TC_TILE;
   const int r0 = min(n, split * chunk), r1 = min(n, r0 + chunk);
   const int n_sub = r1 > r0 ? ceil_div(r1 - r0, TC_TILE) : 0;
   float* part = a.part + ((((size_t)b * a.H + kvh * G) * TC_WPAD) * a.S + split) * 2;  // + (hl*16 + w) * S * 2
@@ -370,11 +374,34 @@ __global__ void __launch_bounds__(TC_THREADS, 1) window_tc_pass2(const WinTcArgs
   unsigned char* ring = smem;
   unsigned char* q_s = smem + P2_STAGES * TC_KTILE_BYTES;                 // [n_kvh][N rows x 256 bytes]
   float* c2_s = reinterpret_cast<float*>(q_s + (size_t)n_kvh * N * 256);  // [n_kvh * N]
-  const int b = blockIdx.y;
+  // The CTAs of the (flat) grid are dealt to the sequences in proportion to their key tiles, every sequence at least
+  // one: b = this CTA's sequence, `loc` its number among the sequence's `cnt` CTAs (tiles loc, loc + cnt, ...).
+  int b = 0, loc = (int)blockIdx.x, cnt = (int)gridDim.x;
+  if (a.B > 1) {
+    long long total = 0;
+    for (int bb = 0; bb < a.B; ++bb) total += ceil_div(a.consider_len[bb], TC_TILE);
+    const int spare = (int)gridDim.x - a.B;
+    int used = 0;
+    for (int bb = 0; bb < a.B; ++bb)
+      used += total > 0 ? (int)((long long)spare * ceil_div(a.consider_len[bb], TC_TILE) / total) : 0;
+    const int left = spare - used;  // < B: one more each for the first sequences
+    int start = 0;
+    for (int bb = 0; bb < a.B; ++bb) {
+      const int c = 1 + (total > 0 ? (int)((long long)spare * ceil_div(a.consider_len[bb], TC_TILE) / total) : 0) +
+                    (bb < left ? 1 : 0);
+      if ((int)blockIdx.x < start + c) {
+        b = bb;
+        loc = (int)blockIdx.x - start;
+        cnt = c;
+        break;
+      }
+      start += c;
+    }
+  }
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n = a.consider_len[b];
   const int n_tiles = ceil_div(n, TC_TILE);
-  const int my_tiles = (int)blockIdx.x < n_tiles ? ceil_div(n_tiles - (int)blockIdx.x, (int)gridDim.x) : 0;
+  const int my_tiles = loc < n_tiles ? ceil_div(n_tiles - loc, cnt) : 0;
   if (my_tiles == 0) return;
   const int n_sub = my_tiles * n_kvh;
   const T* qb = static_cast<const T*>(a.qw) + (size_t)b * a.H * a.W * kHeadDim;
@@ -382,7 +409,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) window_tc_pass2(const WinTcArgs
     stage_q_block<T>(q_s + (size_t)kv * N * 256, qb, (kvh0 + kv) * G, G, a.W, tid, TC_THREADS);
   tc_setup<P2_STAGES>(sh, tmem_cols(N), warp, 128);
   auto sub = [&](int j, int& row0, int& kv) {
-    row0 = ((int)blockIdx.x + (j / n_kvh) * (int)gridDim.x) * TC_TILE;
+    row0 = (loc + (j / n_kvh) * cnt) * TC_TILE;
     kv = j % n_kvh;
   };
   if (warp == 4) {
@@ -428,7 +455,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) window_tc_pass2(const WinTcArgs
       float x[N];
       if (!take_accumulator<N>(sh, j, x, warp, (j % kAccBufs) * N, a.status)) break;
       const int kv = j % n_kvh;
-      const int p = ((int)blockIdx.x + (j / n_kvh) * (int)gridDim.x) * TC_TILE + tid;
+      const int p = (loc + (j / n_kvh) * cnt) * TC_TILE + tid;
       if (kv == 0) {
 #pragma unroll
         for (int w = 0; w < TC_WPAD; ++w) t[w] = (first || p >= n) ? -INFINITY : tplane[(size_t)w * a.tplane_stride + p];
@@ -472,11 +499,12 @@ int launch_tc(const WinTcArgs& a, const CUtensorMap& tm_k, int max_len, cudaStre
   window_tc_pass1<T, G><<<dim3(a.S, a.KVH, a.B), P1Shape<G>::THREADS, smem1, st>>>(a, tm_k);
   OMNIKV_CUDA_OK(cudaGetLastError());
   const int max_tiles = ceil_div(max_len, TC_TILE);
-  int per_seq = ceil_div(a.n_sms, a.B);
-  if (per_seq > max_tiles) per_seq = max_tiles;
+  // one CTA per SM (the query blocks and the ring fill its shared memory), never fewer than one per sequence
+  int n_ctas = a.n_sms < a.B * max_tiles ? a.n_sms : a.B * max_tiles;
+  if (n_ctas < a.B) n_ctas = a.B;
   for (int kvh0 = 0; kvh0 < a.KVH; kvh0 += group) {
     const int n_kvh = a.KVH - kvh0 < group ? a.KVH - kvh0 : group;
-    window_tc_pass2<T, G><<<dim3(per_seq, a.B), TC_THREADS, smem2, st>>>(a, tm_k, kvh0, n_kvh, kvh0 == 0 ? 1 : 0,
+    window_tc_pass2<T, G><<<dim3(n_ctas), TC_THREADS, smem2, st>>>(a, tm_k, kvh0, n_kvh, kvh0 == 0 ? 1 : 0,
                                                                         kvh0 + n_kvh >= a.KVH ? 1 : 0);
     OMNIKV_CUDA_OK(cudaGetLastError());
   }
@@ -490,8 +518,11 @@ bool window_tc_supported(int G, int KVH) {
   return G == 1 || G == 2 || G == 4;  // 16 G accumulator columns and as many running sums per key
 }
 
-int window_tc_splits(int B, int KVH, int n_sms) {
+int window_tc_splits(int B, int KVH, int n_sms, int max_len) {
   int s = 2 * (n_sms / (B * KVH > 0 ? B * KVH : 1));  // one wave of two CTAs per SM
+  // a batch has more (sequence, KV head) pairs than that: chunks of about 4096 keys, dealt out as CTAs retire, even
+  // out sequences of different lengths
+  if (B > 1 && s < ceil_div(max_len, 4096)) s = ceil_div(max_len, 4096);
   return s < 1 ? 1 : (s > kWindowTcMaxSplits ? kWindowTcMaxSplits : s);
 }
 

@@ -25,7 +25,7 @@ struct WinTcArgs {
 // Whether the tensor-memory path covers this head grouping (the query blocks of all KV heads must fit in shared
 // memory beside the K ring; a thread holds one accumulator row of 16 G columns in registers).
 bool window_tc_supported(int G, int KVH);
-int window_tc_splits(int B, int KVH, int n_sms);
+int window_tc_splits(int B, int KVH, int n_sms, int max_len);
 int window_tc_launches(int G, int KVH);  // kernels one call launches
 // tm_k: tensor map over the K cache [B, KVH, rows, 128] with boxes of 64 elements x 128 rows, 128-byte swizzle.
 int window_tc_launch(int dtype, const WinTcArgs& a, const CUtensorMap& tm_k, int max_len, cudaStream_t st);
