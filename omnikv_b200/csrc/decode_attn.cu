@@ -86,9 +86,9 @@ inline bool g_attn_tma_enabled() {
   return on;
 }
 
-template <bool WITH_V>
+template <bool WITH_V, int ST = STAGES>
 constexpr int mma_smem_bytes() {
-  return STAGES * (WITH_V ? 2 : 1) * TILE_BYTES + Q_BYTES;
+  return ST * (WITH_V ? 2 : 1) * TILE_BYTES + Q_BYTES;
 }
 
 // Row range [r0, r1) of split `split` out of S for a list of n rows (chunks are TILE-aligned).  The chunk
@@ -203,28 +203,34 @@ __device__ __forceinline__ void finish_group(const AttnArgs& a, int b, int kvh, 
 // map [B, KVH, rows, d]; the map's 128-byte swizzle (16-byte chunk c of row r lands at chunk c ^ (r & 7)) makes
 // the unpadded rows conflict-free for ldmatrix.  Rows past the sequence but inside the capacity arrive as they
 // are in memory: their scores are masked and their V rows are zeroed in shared memory before use.
-constexpr int kCopyCpAsync = 0, kCopyBulkRows = 1, kCopyTma = 2;
+constexpr int kCopyCpAsync = 0, kCopyBulkRows = 1, kCopyTma = 2, kCopyBulkPairs = 3;
+constexpr int PAIR_PITCH = 528;  // K row | V row of one cache position (512 bytes) + 16 pad: conflict-free for ldmatrix
 constexpr int TMA_BOX_BYTES = kTmaBoxBytes;
 
-template <typename T, bool WITH_V, bool WITH_SCORE, int MODE>
-__global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const AttnArgs a,
+template <typename T, bool WITH_V, bool WITH_SCORE, int MODE, int ST = STAGES>
+__global__ void __launch_bounds__(NTHREADS, ST > STAGES ? 1 : 2) decode_attn_mma_kernel(const AttnArgs a,
                                                                       const __grid_constant__ CUtensorMap tm_k,
                                                                       const __grid_constant__ CUtensorMap tm_v) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ int last_flag;
-  constexpr bool BULK = MODE == kCopyBulkRows;
+  // kCopyBulkPairs: the cache stores the V row of a position right behind its K row (the token-major layout of a
+  // sparse layer), so ONE 512-byte bulk copy brings both: half as many copies -- the copy engine takes about 25
+  // cycles per copy whatever its size, which bounds a CTA that streams scattered rows
+  constexpr bool PAIR = MODE == kCopyBulkPairs;
+  constexpr bool BULK = MODE == kCopyBulkRows || PAIR;
+  constexpr int RP = PAIR ? PAIR_PITCH : PITCH;  // byte pitch of a staged row
   constexpr bool TMA = MODE == kCopyTma;
   constexpr int STAGE_BYTES = TMA ? (WITH_V ? 4 : 2) * TMA_BOX_BYTES : (WITH_V ? 2 : 1) * TILE_BYTES;
   // the swizzled boxes want 1024-byte alignment
   unsigned char* smem = TMA ? reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023)
                             : smem_raw;
-  unsigned char* q_s = smem + STAGES * STAGE_BYTES;
+  unsigned char* q_s = smem + ST * STAGE_BYTES;
   // byte address of the 16-byte piece at (row, byte column) of a staged K or V tile
   auto staged = [&](const unsigned char* tile_base, int row, int colb) -> const unsigned char* {
     if constexpr (TMA)
       return swz128(tile_base, row, colb);
     else
-      return tile_base + row * PITCH + colb;
+      return tile_base + row * RP + colb;
   };
 
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -250,7 +256,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
   int r0, r1;
   split_range(n, a.B > 1 ? batch_max_rows(a, n) : n, a.S, split, r0, r1);
   const int ntiles = r1 > r0 ? ceil_div(r1 - r0, TILE) : 0;
-  const bool early = ntiles > 0 && (r1 < n || ntiles > STAGES - 1);
+  const bool early = ntiles > 0 && (r1 < n || ntiles > ST - 1);
   if (!early) {
     pdl_wait();
     if (a.pdl_trigger) pdl_trigger();
@@ -293,18 +299,29 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
     return ((long long)(startB + (R - nA)) * a.b_sr) | (1ll << 62);  // bit 62: segment B
   };
   // ---- BULK: thread t owns row t & 63 of every tile, K for t < 64 and V for t >= 64 ----
-  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t full_bar[ST];
   const int my_row = tid & (TILE - 1);
   const bool my_v = tid >= TILE;
   constexpr unsigned ROW_BYTES = kHeadDim * sizeof(T);
   auto issue_bulk = [&](int tile, long long off) {
-    const int slot = tile % STAGES;
-    unsigned char* dst = smem + slot * STAGE_BYTES + (my_v ? TILE_BYTES : 0) + my_row * PITCH;
+    const int slot = tile % ST;
+    unsigned char* dst = smem + slot * STAGE_BYTES + (PAIR ? my_row * PAIR_PITCH : (my_v ? TILE_BYTES : 0) + my_row * PITCH);
     if (tid == 0) {  // bytes this stage will receive: its valid rows, K and V
       const int nvalid = min(TILE, r1 - (r0 + tile * TILE));
       mbar_expect_tx(&full_bar[slot], (unsigned)nvalid * ROW_BYTES * (WITH_V ? 2u : 1u));
     }
-    if (my_v && !WITH_V) return;
+    if (my_v && (!WITH_V || PAIR)) return;
+    if constexpr (PAIR) {
+      if (off >= 0) {
+        const bool segB = (off >> 62) != 0;
+        const long long o = off & ~(1ll << 62);
+        tma_bulk_g2s(dst, (segB ? kB : kA) + o, 2 * ROW_BYTES, &full_bar[slot]);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 2 * (int)ROW_BYTES / 16; ++c) *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(0, 0, 0, 0);
+      }
+      return;
+    }
     if (off >= 0) {
       const bool segB = (off >> 62) != 0;
       const long long o = off & ~(1ll << 62);
@@ -341,7 +358,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
   };
 
   auto issue_tma = [&](int tile) {  // one thread: the tile's boxes
-    const int slot = tile % STAGES;
+    const int slot = tile % ST;
     unsigned char* dst = smem + slot * STAGE_BYTES;
     mbar_expect_tx(&full_bar[slot], STAGE_BYTES);
     const int row0 = r0 + tile * TILE;
@@ -353,40 +370,40 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
     }
   };
 
-  // the index lookups of the first STAGES tiles go out together, then the copies of the first STAGES-1 tiles
+  // the index lookups of the first ST tiles go out together, then the copies of the first ST-1 tiles
   long long offb_next = -1;
   long long offc_next[RPT];
   if constexpr (TMA) {
     if (tid == 0) {
 #pragma unroll
-      for (int s = 0; s < STAGES; ++s) mbar_init(&full_bar[s], 1);
+      for (int s = 0; s < ST; ++s) mbar_init(&full_bar[s], 1);
       asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
 #pragma unroll
-      for (int s = 0; s < STAGES - 1; ++s)
+      for (int s = 0; s < ST - 1; ++s)
         if (s < ntiles) issue_tma(s);
     }
     __syncthreads();
   } else if constexpr (BULK) {
     if (tid == 0) {
 #pragma unroll
-      for (int s = 0; s < STAGES; ++s) mbar_init(&full_bar[s], 1);
+      for (int s = 0; s < ST; ++s) mbar_init(&full_bar[s], 1);
       asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
-    long long first[STAGES - 1];
+    long long first[ST - 1];
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) first[s] = row_offset(s, my_row);
-    offb_next = row_offset(STAGES - 1, my_row);
+    for (int s = 0; s < ST - 1; ++s) first[s] = row_offset(s, my_row);
+    offb_next = row_offset(ST - 1, my_row);
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s)
+    for (int s = 0; s < ST - 1; ++s)
       if (s < ntiles) issue_bulk(s, first[s]);
   } else {
-    long long first[STAGES - 1][RPT];
+    long long first[ST - 1][RPT];
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) resolve_cp(s, first[s]);
-    resolve_cp(STAGES - 1, offc_next);
+    for (int s = 0; s < ST - 1; ++s) resolve_cp(s, first[s]);
+    resolve_cp(ST - 1, offc_next);
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
+    for (int s = 0; s < ST - 1; ++s) {
       if (s < ntiles) issue_cp(s, first[s]);
       cp_async_commit();
     }
@@ -436,14 +453,14 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
   float* score_row = WITH_SCORE ? a.score_out + ((size_t)kvh * a.B + b) * a.score_stride : nullptr;
 
   for (int tile = 0; tile < ntiles; ++tile) {
-    const int nt = tile + STAGES - 1;
+    const int nt = tile + ST - 1;
     if constexpr (TMA) {
       __syncthreads();  // every thread is done with tile - 1: its slot may be refilled
       if (tid == 0 && nt < ntiles) issue_tma(nt);
-      if (!mbar_wait(&full_bar[tile % STAGES], (tile / STAGES) & 1) && a.status) atomicExch(a.status, 5);
+      if (!mbar_wait(&full_bar[tile % ST], (tile / ST) & 1) && a.status) atomicExch(a.status, 5);
       if (WITH_V && tile == ntiles - 1 && r0 + ntiles * TILE > r1) {
         // the last tile reaches past the sequence: those rows hold whatever the cache holds; clear their V
-        unsigned char* vt = smem + (tile % STAGES) * STAGE_BYTES + 2 * TMA_BOX_BYTES;
+        unsigned char* vt = smem + (tile % ST) * STAGE_BYTES + 2 * TMA_BOX_BYTES;
         const int first_bad = r1 - (r0 + tile * TILE);
         for (int i = tid; i < (TILE - first_bad) * 16; i += NTHREADS) {
           const int row = first_bad + (i >> 4), piece = i & 15;  // 16 pieces of 16 bytes per 256-byte row
@@ -456,16 +473,16 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
       __syncthreads();
       if (nt < ntiles) issue_bulk(nt, offb_next);
       offb_next = row_offset(nt + 1, my_row);
-      if (!mbar_wait(&full_bar[tile % STAGES], (tile / STAGES) & 1) && a.status) atomicExch(a.status, 5);
+      if (!mbar_wait(&full_bar[tile % ST], (tile / ST) & 1) && a.status) atomicExch(a.status, 5);
     } else {
-      cp_async_wait<STAGES - 2>();
+      cp_async_wait<ST - 2>();
       __syncthreads();
-      if (nt < ntiles) issue_cp(nt % STAGES, offc_next);
+      if (nt < ntiles) issue_cp(nt % ST, offc_next);
       cp_async_commit();
       resolve_cp(nt + 1, offc_next);
     }
-    const unsigned char* ks = smem + (tile % STAGES) * STAGE_BYTES;
-    const unsigned char* vs = ks + (TMA ? 2 * TMA_BOX_BYTES : TILE_BYTES);
+    const unsigned char* ks = smem + (tile % ST) * STAGE_BYTES;
+    const unsigned char* vs = ks + (TMA ? 2 * TMA_BOX_BYTES : (PAIR ? (int)(kHeadDim * sizeof(T)) : TILE_BYTES));
 
     // S = Q K^T for this warp's 16 rows: two n-tiles of 8 rows
     float s[2][4];
@@ -582,6 +599,11 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
       acc += o_s[((size_t)w * 16 + r) * kHeadDim + tid] * wgt;
       l += ml_s[(w * 16 + r) * 2 + 1] * wgt;
     }
+    if (a.S == 1) {  // one split: this is the result, no partials and no arrival count
+      static_cast<T*>(a.out)[(size_t)b * a.q_sb + (size_t)(kvh * G + r) * a.q_sh + tid] =
+          from_float<T>(l > 0.f ? acc / l : 0.f);
+      continue;
+    }
     const size_t base = ((size_t)(b * a.H + kvh * G + r) * a.S + split);
     ws_o[base * kHeadDim + tid] = acc;
     if (tid == 0) {
@@ -589,6 +611,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) decode_attn_mma_kernel(const Attn
       ws_ml[base * 2 + 1] = l;
     }
   }
+  if (a.S == 1) return;
   ATTN_STAMP(4);  // partials written
   // the shared scratch of finish_group starts behind the cross-warp merge area used above
   finish_group<T>(a, b, kvh, ml_s + NWARPS * 16 * 2, &last_flag);
@@ -769,7 +792,13 @@ int launch_mma(AttnArgs a, bool with_v, bool with_score, int64_t a_rows, cudaStr
   (mode == kCopyTma        ? go(decode_attn_mma_kernel<T, V, SC, kCopyTma>, V ? tma_v : tma_k)        \
    : mode == kCopyBulkRows ? go(decode_attn_mma_kernel<T, V, SC, kCopyBulkRows>, V ? smem_v : smem_k) \
                            : go(decode_attn_mma_kernel<T, V, SC, kCopyCpAsync>, V ? smem_v : smem_k))
-  if (with_v && with_score) rc = OMNIKV_ATTN_GO(true, true);
+  // scattered rows of a cache whose V row lies right behind the K row of the same position: one copy per position
+  const size_t row_b = kHeadDim * sizeof(T);
+  const bool pairs = mode == kCopyBulkRows && with_v && !with_score && sizeof(T) == 2 &&
+                     static_cast<const unsigned char*>(a.vA) == static_cast<const unsigned char*>(a.kA) + row_b &&
+                     (!a.kB || static_cast<const unsigned char*>(a.vB) == static_cast<const unsigned char*>(a.kB) + row_b);
+  if (pairs) rc = go(decode_attn_mma_kernel<T, true, false, kCopyBulkPairs>, smem_v);
+  else if (with_v && with_score) rc = OMNIKV_ATTN_GO(true, true);
   else if (with_v) rc = OMNIKV_ATTN_GO(true, false);
   else rc = OMNIKV_ATTN_GO(false, true);
 #undef OMNIKV_ATTN_GO

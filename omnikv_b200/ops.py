@@ -83,8 +83,7 @@ def default_splits(B: int, KVH: int, max_rows: int, device) -> int:
     if B > 1 and max_rows <= 8192:
         # short lists of a batch (the selected rows of sparse layers): a CTA costs about seven 64-row tiles of fixed
         # time (prologue, split merge) whatever it streams, and two CTAs fit on an SM, so the count that minimises
-        # waves x (tiles per CTA + 7) wins -- 2 instead of 5 for 16 sequences x 8 KV heads x 2112 rows (measured:
-        # 7.31 vs 7.52 ms per step of the batch-16 workload; 1 -> 8.05, 3 -> 7.57)
+        # waves x (tiles per CTA + 7) wins -- 2 instead of 5 for 16 sequences x 8 KV heads x 2112 rows
         slots, tiles = 2 * sm_count(device), -(-max_rows // 64)
         s = min(range(1, 9), key=lambda c: (-(-ctas * c // slots)) * (-(-tiles // c) + 7))
     elif B > 1:  # ragged batches: chunks are sized by the longest sequence, so aim at two waves of equal CTAs

@@ -95,19 +95,30 @@ def test_score_only_mode_matches_fused(dtype):
 @pytest.mark.parametrize("B,P,ks,tails,splits", [
     (1, 5000, [335], [1], 4), (1, 5000, [1], [0], 1), (2, 3000, [200, 64], [7, 130], 3), (1, 70000, [4690], [128], 37),
     (3, 1000, [1000, 0, 999], [3, 5, 0], 5),
+    # long lists with one split (direct output, no merge) and with two; ragged: a short and an empty list beside a long one
+    (2, 6000, [3000, 2100], [5, 64], 1), (3, 6000, [3000, 70, 0], [5, 1, 0], 2), (1, 4000, [2112], [0], 1),
 ])
-def test_sparse_attention(dtype, B, P, ks, tails, splits):
+@pytest.mark.parametrize("layout", ["planes", "pairs"])
+def test_sparse_attention(dtype, B, P, ks, tails, splits, layout):
     H, KVH, d = 32, 8, 128
     cap = P + 256
     k, v = make_kv(B, KVH, cap, d, dtype, 5)
+    if layout == "pairs":  # the token-major layout of a sparse layer: the V row of a position right behind its K row
+        kv = torch.stack([k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3)], dim=3).contiguous()  # [B, rows, KVH, K|V, d]
+        k, v = kv[:, :, :, 0].permute(0, 2, 1, 3), kv[:, :, :, 1].permute(0, 2, 1, 3)
     q = make_q(B, H, d, dtype, 6, 1.5)
     g = torch.Generator().manual_seed(7)
     kmax = max(max(ks), 1)
     idx = torch.zeros(B, kmax, dtype=torch.int64)
     for b in range(B):
         idx[b, :ks[b]] = torch.sort(torch.randperm(P, generator=g)[:ks[b]]).values
-    out = ops().decode_attn(q.cuda(), k.cuda(), v.cuda(), dev_i32(ks), idx=idx.to(torch.int32).cuda(),
-                            k_tail=k.cuda(), v_tail=v.cuda(), tail_start=dev_i32([P] * B), tail_len=dev_i32(tails),
+    if layout == "pairs":
+        kvc = kv.cuda()
+        kc, vc = kvc[:, :, :, 0].permute(0, 2, 1, 3), kvc[:, :, :, 1].permute(0, 2, 1, 3)
+    else:
+        kc, vc = k.cuda(), v.cuda()
+    out = ops().decode_attn(q.cuda(), kc, vc, dev_i32(ks), idx=idx.to(torch.int32).cuda(),
+                            k_tail=kc, v_tail=vc, tail_start=dev_i32([P] * B), tail_len=dev_i32(tails),
                             n_splits=splits)
     torch.cuda.synchronize()
     for b in range(B):
