@@ -300,6 +300,7 @@ def main():
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--ctx", type=int, default=131072)
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=1, help="sparse_attn: sequences (2048 selected rows + 64 tail rows each)")
     ap.add_argument("--library", action="store_true", help="prefill_attn: also time PyTorch's fused attention")
     ap.add_argument("--kv-layout", default="interleaved", choices=["interleaved", "planes"],
                     help="dense_attn / score_window: K|V rows of a head interleaved, or in two separate runs of rows")
@@ -351,6 +352,8 @@ def main():
         else:                            # K and V rows of a head interleaved (every other dense layer)
             kv = rnd(B, KVH, L + 64, 2, d)
             kc, vc, q = kv[:, :, :, 0, :], kv[:, :, :, 1, :], rnd(B, H, d)
+    if args.case == "sparse_attn" and args.batch > 1:  # the sparse layers of the batch-16 workload: 2048 rows + tail each
+        B, L, k_sel = args.batch, 32768, 2048
     if args.case == "sparse_attn":
         kv = rnd(B, L + 64, KVH, 2, d)
         kc, vc, q = kv[:, :, :, 0, :].permute(0, 2, 1, 3), kv[:, :, :, 1, :].permute(0, 2, 1, 3), rnd(B, H, d)
@@ -362,11 +365,12 @@ def main():
         fn = lambda: ops.decode_attn(q, kc, vc, n_all, score_out=planes, score_len=n_p, n_splits=args.splits or None)  # noqa: E731
         nbytes = 2 * KVH * d * 2 * (L + 1)
     elif args.case == "sparse_attn":
-        idx = torch.sort(torch.randperm(L, generator=g, device=dev)[:k_sel]).values.to(torch.int32)[None].contiguous()
-        cnt, n_p, one = i32([k_sel]), i32([L]), i32([1])
+        idx = torch.stack([torch.sort(torch.randperm(L, generator=g, device=dev)[:k_sel]).values.to(torch.int32)
+                           for _ in range(B)]).contiguous()
+        cnt, n_p, one = i32([k_sel] * B), i32([L] * B), i32([64 if B > 1 else 1] * B)
         fn = lambda: ops.decode_attn(q, kc, vc, cnt, idx=idx, k_tail=kc, v_tail=vc, tail_start=n_p, tail_len=one,  # noqa: E731
                                      max_rows=k_sel + 64, n_splits=args.splits or None)
-        nbytes = 2 * KVH * d * 2 * (k_sel + 1)
+        nbytes = 2 * KVH * d * 2 * (k_sel + (64 if B > 1 else 1)) * B
     elif args.case == "topk":
         planes = torch.randn(KVH, B, L, generator=g, device=dev)
         n_p, kk = i32([L]), i32([k_sel])
