@@ -475,6 +475,8 @@ def main():
             tp.enable_peer_reduce(8 * 8192 * 2, dev)  # a batch-8 hidden state of the 70B shape in bf16
         else:
             tp.enable_peer_exchange(4096, dev)
+            # the filter layers' score planes (MAX) and the sharded logits (gather) through peer memory as well
+            tp.enable_peer_reduce(max(8 // world * args.ctx * 4, 128256 // world * 4), dev)
 
     warmup = max(3, args.warmup)
     cfg, make_cfg, lm, B, lens = build_workload(args, world, rank, dev, tp)

@@ -428,6 +428,13 @@ size_t omnikv_tp_exchange_bytes(int hidden);
  * the peers' flags gives up after two seconds (status 4). */
 int omnikv_tp_allreduce_sum(int dtype, void* x, int64_t n, const omnikv_tp_exchange* t, int32_t* status,
                             void* stream);
+/* The same exchange as element-wise MAX of fp32 vectors (the filter layers' score planes before the top-k: a step
+ * the reference's fork does not have, it selects per rank, lightllm/models/llama_omnikv/triton_kernel/
+ * flash_decoding.py:76) and as an all-gather: out[r * n + i] = rank r's x[i] (the vocabulary-sharded logits,
+ * lightllm/models/llama_omnikv/layer_infer/post_layer_infer.py:140-148).  Same buffer, size and call-order rules. */
+int omnikv_tp_allreduce_max(void* x, int64_t n, const omnikv_tp_exchange* t, int32_t* status, void* stream);
+int omnikv_tp_allgather(int dtype, const void* x, int64_t n, void* out, const omnikv_tp_exchange* t, int32_t* status,
+                        void* stream);
 int omnikv_decode_qkv(int dtype, const void* h, const void* norm_w, float eps, const void* w_qkv, int hidden,
                       int H, int KVH, int head_dim, const float* inv_freq, const int32_t* rope_pos,
                       void* q_out, void* k_cache_seq, void* v_cache_seq, int64_t kv_stride_h,

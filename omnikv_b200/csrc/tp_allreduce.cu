@@ -1,4 +1,6 @@
-// Small SUM all-reduce over peer-mapped memory (NVLink), for the hidden state of a batched decode step.
+// Small collectives over peer-mapped memory (NVLink): SUM all-reduce (the hidden state of a batched decode step), MAX
+// all-reduce (the filter layers' fp32 score planes: order independent, so every rank ends with bit-identical planes
+// and runs the same top-k) and all-gather (the vocabulary-sharded logits).  Below, for the SUM:
 //
 // At 8 ranks the hidden state of a decode step is tens to hundreds of KB: an all-reduce of that size is
 // latency, and a ring or tree pays several hops.  Here every rank stores its vector straight into a slot of
@@ -33,7 +35,9 @@ struct ArArgs {
   const unsigned* my_flags;  // local [2 slots][8]
   unsigned* done;          // local: [0] counter of finished CTAs (self-resetting), [1] calls made so far
   int* status;
+  void* out;               // gather: [world][n_vec] vectors
 };
+enum { OP_SUM = 0, OP_MAX = 1, OP_GATHER = 2 };
 
 template <typename T>
 __device__ __forceinline__ void add8(const uint4& v, float (&acc)[8]);
@@ -70,7 +74,7 @@ __device__ __forceinline__ uint4 pack8<float>(const float (&acc)[8]) {
   return make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3]));
 }
 
-template <typename T>
+template <typename T, int OP>
 __global__ void __launch_bounds__(AR_THREADS) tp_allreduce_kernel(const ArArgs a) {
   __shared__ int fail;
   __shared__ unsigned call_s;
@@ -115,22 +119,46 @@ __global__ void __launch_bounds__(AR_THREADS) tp_allreduce_kernel(const ArArgs a
   }
   __syncthreads();
   if (fail) return;
-  // 3. sum in rank order, fp32, rounded once
   const uint4* mine = a.my_slots + (size_t)slot * 8 * a.slot_stride_vec;
-  for (int v = blockIdx.x * AR_THREADS + tid; v < a.n_vec; v += stride) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int r = 0; r < a.world; ++r) add8<T>(__ldcg(mine + (size_t)r * a.slot_stride_vec + v), acc);
-    x[v] = pack8<T>(acc);
+  if constexpr (OP == OP_GATHER) {
+    // 3. the ranks' vectors one behind the other
+    uint4* out = static_cast<uint4*>(a.out);
+    for (int r = 0; r < a.world; ++r)
+      for (int v = blockIdx.x * AR_THREADS + tid; v < a.n_vec; v += stride)
+        out[(size_t)r * a.n_vec + v] = __ldcg(mine + (size_t)r * a.slot_stride_vec + v);
+  } else if constexpr (OP == OP_MAX) {
+    // 3. element-wise maximum of fp32 vectors (any order gives the same bits)
+    for (int v = blockIdx.x * AR_THREADS + tid; v < a.n_vec; v += stride) {
+      uint4 m = __ldcg(mine + v);
+      for (int r = 1; r < a.world; ++r) {
+        const uint4 o = __ldcg(mine + (size_t)r * a.slot_stride_vec + v);
+        m.x = __float_as_uint(fmaxf(__uint_as_float(m.x), __uint_as_float(o.x)));
+        m.y = __float_as_uint(fmaxf(__uint_as_float(m.y), __uint_as_float(o.y)));
+        m.z = __float_as_uint(fmaxf(__uint_as_float(m.z), __uint_as_float(o.z)));
+        m.w = __float_as_uint(fmaxf(__uint_as_float(m.w), __uint_as_float(o.w)));
+      }
+      x[v] = m;
+    }
+  } else {
+    // 3. sum in rank order, fp32, rounded once
+    for (int v = blockIdx.x * AR_THREADS + tid; v < a.n_vec; v += stride) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int r = 0; r < a.world; ++r) add8<T>(__ldcg(mine + (size_t)r * a.slot_stride_vec + v), acc);
+      x[v] = pack8<T>(acc);
+    }
   }
 }
 
 }  // namespace
 }  // namespace omnikv
 
-extern "C" int omnikv_tp_allreduce_sum(int dtype, void* x, int64_t n, const omnikv_tp_exchange* t, int32_t* status,
-                                       void* stream) {
-  using namespace omnikv;
+namespace omnikv {
+namespace {
+int tp_collective(int op, int dtype, void* x, int64_t n, void* out, const omnikv_tp_exchange* t, int32_t* status,
+                  void* stream) {
   if (!x || n <= 0 || !t || !status) return OMNIKV_E_BADARG;
+  if (op == OP_GATHER && !out) return OMNIKV_E_BADARG;
+  if (op == OP_MAX && dtype != OMNIKV_F32) return OMNIKV_E_UNSUPPORTED;
   if (t->world <= 1) return OMNIKV_OK;
   if (t->world > 8 || t->rank < 0 || t->rank >= t->world || !t->done_counter || t->hidden <= 0)
     return OMNIKV_E_BADARG;
@@ -153,15 +181,35 @@ extern "C" int omnikv_tp_allreduce_sum(int dtype, void* x, int64_t n, const omni
   a.my_slots = reinterpret_cast<const uint4*>(mine);
   a.slot_stride_vec = slot_bytes / 16;
   a.my_flags = reinterpret_cast<const unsigned*>(mine + flags_off);
-  a.done = t->done_counter; a.status = status;
+  a.done = t->done_counter; a.status = status; a.out = out;
   int grid = ceil_div(a.n_vec, AR_THREADS);
   if (grid > AR_MAX_CTAS) grid = AR_MAX_CTAS;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  switch (dtype) {
-    case OMNIKV_BF16: tp_allreduce_kernel<__nv_bfloat16><<<grid, AR_THREADS, 0, st>>>(a); break;
-    case OMNIKV_F16: tp_allreduce_kernel<__half><<<grid, AR_THREADS, 0, st>>>(a); break;
-    default: tp_allreduce_kernel<float><<<grid, AR_THREADS, 0, st>>>(a); break;
+  if (op == OP_GATHER) {
+    tp_allreduce_kernel<float, OP_GATHER><<<grid, AR_THREADS, 0, st>>>(a);  // moves 16-byte vectors: any element type
+  } else if (op == OP_MAX) {
+    tp_allreduce_kernel<float, OP_MAX><<<grid, AR_THREADS, 0, st>>>(a);
+  } else {
+    switch (dtype) {
+      case OMNIKV_BF16: tp_allreduce_kernel<__nv_bfloat16, OP_SUM><<<grid, AR_THREADS, 0, st>>>(a); break;
+      case OMNIKV_F16: tp_allreduce_kernel<__half, OP_SUM><<<grid, AR_THREADS, 0, st>>>(a); break;
+      default: tp_allreduce_kernel<float, OP_SUM><<<grid, AR_THREADS, 0, st>>>(a); break;
+    }
   }
   OMNIKV_CUDA_OK(cudaGetLastError());
   return OMNIKV_OK;
+}
+}  // namespace
+}  // namespace omnikv
+
+extern "C" int omnikv_tp_allreduce_sum(int dtype, void* x, int64_t n, const omnikv_tp_exchange* t, int32_t* status,
+                                       void* stream) {
+  return omnikv::tp_collective(omnikv::OP_SUM, dtype, x, n, nullptr, t, status, stream);
+}
+extern "C" int omnikv_tp_allreduce_max(void* x, int64_t n, const omnikv_tp_exchange* t, int32_t* status, void* stream) {
+  return omnikv::tp_collective(omnikv::OP_MAX, OMNIKV_F32, x, n, nullptr, t, status, stream);
+}
+extern "C" int omnikv_tp_allgather(int dtype, const void* x, int64_t n, void* out, const omnikv_tp_exchange* t,
+                                   int32_t* status, void* stream) {
+  return omnikv::tp_collective(omnikv::OP_GATHER, dtype, const_cast<void*>(x), n, out, t, status, stream);
 }

@@ -364,6 +364,28 @@ def tp_allreduce_sum(x: torch.Tensor, exchange) -> None:
     _count(1)
 
 
+def tp_allreduce_max(x: torch.Tensor, exchange) -> None:
+    """``omnikv_tp_allreduce_max``: in-place element-wise MAX of the contiguous fp32 tensor ``x`` over the ranks."""
+    _need_cuda(x)
+    if not x.is_contiguous() or x.dtype != torch.float32:
+        raise abi.OmniKVError("tp_allreduce_max: contiguous fp32 tensor expected")
+    abi.check(abi.lib().omnikv_tp_allreduce_max(x.data_ptr(), x.numel(), _xref(exchange),
+                                                status_word(x.device).data_ptr(), _stream()), "omnikv_tp_allreduce_max")
+    _count(1)
+
+
+def tp_allgather(x: torch.Tensor, exchange, world: int) -> torch.Tensor:
+    """``omnikv_tp_allgather``: the ranks' contiguous tensors ``x`` one behind the other, ``[world, x.numel()]``."""
+    _need_cuda(x)
+    if not x.is_contiguous():
+        raise abi.OmniKVError("tp_allgather: contiguous tensor expected")
+    out = torch.empty(world, x.numel(), dtype=x.dtype, device=x.device)
+    abi.check(abi.lib().omnikv_tp_allgather(_DT[x.dtype], x.data_ptr(), x.numel(), out.data_ptr(), _xref(exchange),
+                                            status_word(x.device).data_ptr(), _stream()), "omnikv_tp_allgather")
+    _count(1)
+    return out
+
+
 def rope_append(qkv: torch.Tensor, H: int, KVH: int, inv_freq: torch.Tensor, rope_pos: torch.Tensor,
                 q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cache_pos: torch.Tensor) -> None:
     """``omnikv_rope_append``.  qkv ``[B, (H+2KVH)*128]`` (rows contiguous); q_out ``[B, H, 128]``; caches

@@ -19,7 +19,8 @@ At batch 1 the two SUM all-reduces per layer are latency, not bandwidth (8 KB of
 ``PeerExchange`` they are fused into the weight-streaming kernels on both sides -- the projection kernel
 stores its partial sums straight into every rank's peer-mapped buffer over NVLink and raises a flag, the next
 kernel waits for the flags (bounded) and adds the partials while it loads its activations
-(``omnikv_tp_exchange`` in the C header).  NCCL remains the transport for the score planes and the logits.
+(``omnikv_tp_exchange`` in the C header).  With ``enable_peer_reduce`` the score planes (MAX) and the logits
+(all-gather) travel through one-hop peer-memory kernels as well; NCCL is the fallback for anything that does not fit.
 """
 from __future__ import annotations
 
@@ -139,15 +140,33 @@ class TPGroup:
         dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
         return t
 
+    def _peer_fits(self, t: torch.Tensor) -> bool:
+        """Whether ``t`` goes through the peer-memory kernels (depends on shapes only: all ranks agree)."""
+        r = self.reducer
+        nbytes = t.numel() * t.element_size()
+        return (r is not None and t.is_cuda and t.is_contiguous() and nbytes % 16 == 0 and 0 < nbytes <= r.hidden * 4
+                and t.dtype in (torch.bfloat16, torch.float16, torch.float32))
+
     def all_reduce_max(self, t: torch.Tensor) -> torch.Tensor:
-        if self.world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        if self.world <= 1:
+            return t
+        if t.dtype == torch.float32 and self._peer_fits(t):
+            from . import ops
+            ops.tp_allreduce_max(t, self.reducer.at(0))
+            self.peer_reduce_calls += 1
+            return t
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
         return t
 
     def all_gather_last(self, t: torch.Tensor) -> torch.Tensor:
         """Concatenate the ranks' tensors along the last dimension."""
         if self.world == 1:
             return t
+        if t.numel() == t.shape[-1] and self._peer_fits(t.contiguous()):  # one row: the ranks' rows back to back
+            from . import ops
+            out = ops.tp_allgather(t.contiguous(), self.reducer.at(0), self.world)
+            self.peer_reduce_calls += 1
+            return out.view(*t.shape[:-1], self.world * t.shape[-1])
         parts = [torch.empty_like(t) for _ in range(self.world)]
         dist.all_gather(parts, t.contiguous(), group=self.group)
         return torch.cat(parts, dim=-1)

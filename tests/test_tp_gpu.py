@@ -148,6 +148,21 @@ def _worker_reduce(rank, world, port, ret):
                 tp.all_reduce_sum(x)
                 used += tp.peer_reduce_calls - seq0
                 exact = exact and torch.equal(x, want.to(dtype))
+                # the same exchange as an all-gather of one row, and (fp32) as an element-wise MAX
+                z = torch.randn(1, n, generator=g, device=dev).to(dtype)
+                parts = [torch.empty_like(z) for _ in range(world)]
+                dist.all_gather(parts, z)
+                seq0 = tp.peer_reduce_calls
+                exact = exact and torch.equal(tp.all_gather_last(z), torch.cat(parts, dim=-1))
+                exact = exact and tp.peer_reduce_calls == seq0 + 1
+                if dtype == torch.float32:
+                    y = torch.randn(3, n, generator=g, device=dev)
+                    parts = [torch.empty_like(y) for _ in range(world)]
+                    dist.all_gather(parts, y)
+                    seq0 = tp.peer_reduce_calls
+                    tp.all_reduce_max(y)
+                    exact = exact and torch.equal(y, torch.stack(parts).max(dim=0).values)
+                    exact = exact and tp.peer_reduce_calls == seq0 + 1
         # a tensor above the buffer's capacity goes through NCCL (same numbers up to summation order)
         tp.begin_step()
         big = torch.ones(1 << 20, device=dev)
@@ -221,8 +236,8 @@ def _worker_reduce(rank, world, port, ret):
 
 
 def test_tp2_peer_allreduce():
-    """omnikv_tp_allreduce_sum on 2 GPUs: bit-exact rank-ordered fp32 sums for all dtypes and sizes over several
-    steps (slot reuse), NCCL fallback above the capacity, CUDA-graph replays of an odd number of calls on changing
+    """omnikv_tp_allreduce_sum / _max / omnikv_tp_allgather on 2 GPUs: bit-exact rank-ordered fp32 sums for all dtypes
+    and sizes over several steps (slot reuse), exact maxima and gathers on the same exchange, NCCL fallback above the capacity, CUDA-graph replays of an odd number of calls on changing
     data, and a batch-3 decode
     of a sharded model equal to the single-GPU model."""
     if torch.cuda.device_count() < 2:
@@ -235,7 +250,9 @@ def test_tp2_peer_allreduce():
         assert has, "symmetric memory / peer access unavailable"
         assert exact and used == 36 and fell_back and graph_ok
         assert err <= 1e-4, err
-        assert last_seq == 8  # two all-reduces per layer of the last decode forward went through the kernel
+        # the last decode forward: two SUM all-reduces per layer and the filter layer's MAX of the score planes went
+        # through the kernel (the logits of a batch of three are gathered by NCCL: only single rows take the peer path)
+        assert last_seq == 9
 
 
 def _worker_fused_vs_unsharded(rank, world, port, ret):
