@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define OMNIKV_ABI_VERSION 4
+#define OMNIKV_ABI_VERSION 5
 
 typedef enum {
   OMNIKV_OK = 0,

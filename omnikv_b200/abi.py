@@ -12,7 +12,7 @@ from pathlib import Path
 _LIB_PATH = Path(os.environ.get("OMNIKV_B200_LIB") or Path(__file__).resolve().parent / "_lib" / "libomnikv_b200.so")
 _lib = None
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 F32, BF16, F16 = 0, 1, 2
 SEL_SOFTMAX_LAST, SEL_UNIFORM, SEL_EXP = 0, 1, 2
 NO_ALLOC_SCRATCH_BYTES = 4 * 1024 * 1024
