@@ -270,7 +270,7 @@ int omnikv_kv_append(int dtype, const void* k_new, const void* v_new, void* k_ca
  * q [B, H, Sq, d], k and v [B, KVH, Skv, d] (Skv >= q_pos0 + Sq; a chunk of queries against a longer cache passes its
  * first position as q_pos0), out [B, Sq, H, d]; all 16-bit of one dtype, element strides given (multiples of 8,
  * rows of d contiguous elements, bases 16-byte aligned), so k and v may be views of a cache or of a fused
- * projection.  tcgen05 kernel: 128 queries of a head per CTA, tiles by TMA, accumulators in tensor memory.
+ * projection.  tcgen05 kernels: 128 or 2 x 128 queries of a head per CTA, tiles by TMA, accumulators in tensor memory.
  * status (optional device word) is set to 6 if a bounded wait ran out.
  * ------------------------------------------------------------------------------------------ */
 typedef struct {
@@ -287,6 +287,8 @@ typedef struct {
   void* out;
   int64_t o_stride_b, o_stride_row, o_stride_h;
   int32_t* status;
+  int32_t variant; /* 0: two query tiles per CTA, P and O in tensor memory (default); 1: one query tile per CTA, P
+                      through shared memory and O in registers (the first version, kept for fault isolation) */
 } omnikv_prefill_params;
 
 int omnikv_prefill_attn(const omnikv_prefill_params* p, void* stream);

@@ -66,7 +66,7 @@ class PrefillParams(C.Structure):
         ("k", C.c_void_p), ("k_stride_b", C.c_int64), ("k_stride_h", C.c_int64), ("k_stride_row", C.c_int64),
         ("v", C.c_void_p), ("v_stride_b", C.c_int64), ("v_stride_h", C.c_int64), ("v_stride_row", C.c_int64),
         ("out", C.c_void_p), ("o_stride_b", C.c_int64), ("o_stride_row", C.c_int64), ("o_stride_h", C.c_int64),
-        ("status", C.c_void_p),
+        ("status", C.c_void_p), ("variant", C.c_int32),
     ]
 
 

@@ -379,6 +379,9 @@ int launch_prefill(const omnikv_prefill_params* p, cudaStream_t stream) {
 }
 
 }  // namespace
+
+template <typename T>
+int launch_prefill2(const omnikv_prefill_params* p, cudaStream_t stream);  // prefill_attn2.cu
 }  // namespace omnikv
 
 extern "C" int omnikv_prefill_attn(const omnikv_prefill_params* p, void* stream) {
@@ -393,5 +396,7 @@ extern "C" int omnikv_prefill_attn(const omnikv_prefill_params* p, void* stream)
   if (p->o_stride_row % 8 || p->o_stride_h % 8 || p->o_stride_b % 8 || (reinterpret_cast<uintptr_t>(p->out) & 15))
     return OMNIKV_E_BADARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return p->dtype == OMNIKV_BF16 ? launch_prefill<__nv_bfloat16>(p, s) : launch_prefill<__half>(p, s);
+  if (p->variant == 1) return p->dtype == OMNIKV_BF16 ? launch_prefill<__nv_bfloat16>(p, s) : launch_prefill<__half>(p, s);
+  if (p->variant != 0) return OMNIKV_E_BADARG;
+  return p->dtype == OMNIKV_BF16 ? launch_prefill2<__nv_bfloat16>(p, s) : launch_prefill2<__half>(p, s);
 }

@@ -267,7 +267,7 @@ def score_window(qw: torch.Tensor, k: torch.Tensor, consider_len: torch.Tensor, 
 
 
 def prefill_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, q_pos0: int = 0,
-                 scale: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 scale: Optional[float] = None, out: Optional[torch.Tensor] = None, variant: int = 0) -> torch.Tensor:
     """``omnikv_prefill_attn``: causal attention of a block of prompt queries.  q ``[B,H,Sq,d]``, k and v
     ``[B,KVH,Skv,d]`` with ``Skv >= q_pos0 + Sq`` (any strides that are multiples of 8 elements, rows contiguous),
     16-bit.  Query ``i`` sees keys ``j <= q_pos0 + i``.  Returns ``[B, Sq, H, d]``."""
@@ -289,6 +289,7 @@ def prefill_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, q_pos0: i
     p.v_stride_b, p.v_stride_h, p.v_stride_row = v.stride(0), v.stride(1), v.stride(2)
     p.o_stride_b, p.o_stride_row, p.o_stride_h = out.stride(0), out.stride(1), out.stride(2)
     p.status = status_word(q.device).data_ptr()
+    p.variant = int(variant)  # 0: two query tiles per CTA (default), 1: the one-tile kernel
     abi.check(abi.lib().omnikv_prefill_attn(C.byref(p), _stream()), "omnikv_prefill_attn")
     _count(1)
     return out

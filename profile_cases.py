@@ -271,7 +271,8 @@ def prefill_case(ctx: int, reps: int, library: bool):
     rnd = lambda *s: torch.randn(*s, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)  # noqa: E731
     q, k, v = rnd(1, H, ctx, d), rnd(1, KVH, ctx, d), rnd(1, KVH, ctx, d)
     flops = 4.0 * H * d * ctx * (ctx + 1) / 2  # two products over the causal triangle
-    legs = [("tcgen05 kernel", lambda: ops.prefill_attn(q, k, v))]
+    legs = [("tcgen05 kernel", lambda: ops.prefill_attn(q, k, v)),
+            ("tcgen05 kernel, one query tile per CTA", lambda: ops.prefill_attn(q, k, v, variant=1))]
     if library:
         legs.append(("torch sdpa", lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)))
     outs = {}

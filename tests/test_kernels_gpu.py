@@ -682,8 +682,11 @@ def _causal_reference(q, k, v, q_pos0, scale):
     (2, 4, 1, 1000, 1000, 0),    # batch, eight key tiles, one KV head for four query heads
     (1, 4, 4, 200, 520, 320),    # a chunk of queries behind 320 cached keys
     (1, 32, 8, 2048, 2048, 0),   # Llama-3-8B head counts
+    (1, 2, 1, 130, 130, 0),      # a second query tile of two rows
+    (1, 2, 2, 600, 4000, 3400),  # a chunk deep inside a long cache: many key tiles before the diagonal
 ])
-def test_prefill_attention_matches_definition(dtype, B, H, KVH, Sq, Skv, q_pos0):
+@pytest.mark.parametrize("variant", [0, 1])
+def test_prefill_attention_matches_definition(dtype, B, H, KVH, Sq, Skv, q_pos0, variant):
     """tcgen05 prefill attention through the C ABI against the fp32 definition (2e-2 absolute for 16-bit inputs:
     P is rounded to 16 bits before the second product, as in flash attention)."""
     g = torch.Generator().manual_seed(Sq * 7 + H)
@@ -691,7 +694,7 @@ def test_prefill_attention_matches_definition(dtype, B, H, KVH, Sq, Skv, q_pos0)
     k = torch.randn(B, KVH, Skv, 128, generator=g).to(dtype).cuda()
     v = torch.randn(B, KVH, Skv, 128, generator=g).to(dtype).cuda()
     scale = 1.0 / math.sqrt(128)
-    out = ops().prefill_attn(q, k, v, q_pos0=q_pos0)
+    out = ops().prefill_attn(q, k, v, q_pos0=q_pos0, variant=variant)
     ops().check_status(q.device)
     ref = _causal_reference(q, k, v, q_pos0, scale)
     assert out.shape == (B, Sq, H, 128)
