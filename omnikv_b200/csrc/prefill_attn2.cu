@@ -226,21 +226,21 @@ prefill_attn2_kernel(const Pf2Args a, const __grid_constant__ CUtensorMap tm_q, 
       tc_fence_after();
       const int key0 = j * P2_TILE;
       const bool masked = key0 + P2_TILE - 1 > a.q_pos0 + q0 + q * P2_TILE;  // some query of this tile sees only part
-      // pass A: the row's maximum (raw logits; the scale is positive)
+      // pass A: the row's maximum (raw logits; the scale is positive); 64 columns per round trip to tensor memory
       float mraw = -INFINITY;
 #pragma unroll
-      for (int cb = 0; cb < P2_TILE; cb += 32) {
-        float v[32];
-        tmem_ld16(s_addr + cb, *reinterpret_cast<float(*)[16]>(&v[0]));
-        tmem_ld16(s_addr + cb + 16, *reinterpret_cast<float(*)[16]>(&v[16]));
+      for (int cb = 0; cb < P2_TILE; cb += 64) {
+        float v[64];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) tmem_ld16(s_addr + cb + 16 * u, *reinterpret_cast<float(*)[16]>(&v[16 * u]));
         tmem_ld_wait();
         if (masked) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
+          for (int i = 0; i < 64; ++i)
             if (key0 + cb + i <= pos) mraw = fmaxf(mraw, v[i]);
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mraw = fmaxf(mraw, v[i]);
+          for (int i = 0; i < 64; ++i) mraw = fmaxf(mraw, v[i]);
         }
       }
       // The reference maximum m moves only when the row's maximum has outgrown it by more than the gap (and on the
@@ -266,12 +266,18 @@ prefill_attn2_kernel(const Pf2Args a, const __grid_constant__ CUtensorMap tm_q, 
       // pass B: P = 2^(S c - m) as 16-bit pairs into the columns the logits came from, row sum
       const float mref = (m == -INFINITY) ? 0.f : m;
       float sum = 0.f;
+      float vb[2][32];
+      tmem_ld16(s_addr, *reinterpret_cast<float(*)[16]>(&vb[0][0]));
+      tmem_ld16(s_addr + 16, *reinterpret_cast<float(*)[16]>(&vb[0][16]));
+      tmem_ld_wait();
 #pragma unroll
-      for (int cb = 0; cb < P2_TILE; cb += 32) {
-        float v[32];
-        tmem_ld16(s_addr + cb, *reinterpret_cast<float(*)[16]>(&v[0]));
-        tmem_ld16(s_addr + cb + 16, *reinterpret_cast<float(*)[16]>(&v[16]));
-        tmem_ld_wait();
+      for (int ci = 0; ci < P2_TILE / 32; ++ci) {
+        const int cb = ci * 32;
+        float(&v)[32] = vb[ci & 1];
+        if (ci + 1 < P2_TILE / 32) {  // the next chunk travels while this one is exponentiated
+          tmem_ld16(s_addr + cb + 32, *reinterpret_cast<float(*)[16]>(&vb[(ci + 1) & 1][0]));
+          tmem_ld16(s_addr + cb + 48, *reinterpret_cast<float(*)[16]>(&vb[(ci + 1) & 1][16]));
+        }
         unsigned r[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -284,7 +290,9 @@ prefill_attn2_kernel(const Pf2Args a, const __grid_constant__ CUtensorMap tm_q, 
           sum += p0 + p1;
           r[i >> 1] = pk2<T>(p0, p1);
         }
-        tmem_st16(s_addr + (cb >> 1), r);  // columns [cb / 2, cb / 2 + 16): logits this thread has already read
+        // columns [cb / 2, cb / 2 + 16): logits this thread has already read (the chunk in flight starts at cb + 32)
+        tmem_st16(s_addr + (cb >> 1), r);
+        if (ci + 1 < P2_TILE / 32) tmem_ld_wait();
       }
       l += sum;
       tmem_st_wait();
