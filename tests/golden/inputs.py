@@ -172,3 +172,33 @@ ROPE_DYNAMIC_SEQ = dict(head_dim=128, rope_theta=500000.0, max_position_embeddin
                         rope_scaling={"type": "dynamic", "factor": 4.0},
                         forwards=[(0, 600), (600, 1), (0, 1500), (1500, 1), (1501, 1), (1502, 1), (0, 1200), (1200, 1),
                                   (0, 300), (300, 1), (0, 2000), (2000, 1)])
+
+
+# The decode attention of the reference's LightLLM fork over a paged pool: one request of 3000 tokens for the
+# selecting call (the fork asserts batch 1 there) and three ragged requests for the plain call.
+LIGHTLLM = dict(seed=515, H=8, KVH=2, d=128, pool_tokens=6144, n_requests=5, max_seq=3200, k=2048,
+                select=dict(req=3, L=3000), dense=dict(reqs=[1, 4, 0], lens=[700, 256, 1033]))
+
+
+def lightllm_inputs():
+    """pool / pool2 ``[tokens, 2*KVH, d]`` (two layers' KV with the same paging), the request table, queries."""
+    c = LIGHTLLM
+    rng = np.random.default_rng(c["seed"])
+    H, KVH, d = c["H"], c["KVH"], c["d"]
+    pool = rng.standard_normal((c["pool_tokens"], 2 * KVH, d)).astype(np.float32)
+    pool2 = rng.standard_normal((c["pool_tokens"], 2 * KVH, d)).astype(np.float32)
+    perm = rng.permutation(c["pool_tokens"]).astype(np.int32)
+    table = np.zeros((c["n_requests"], c["max_seq"]), dtype=np.int32)
+    used = 0
+    for req, n in [(c["select"]["req"], c["select"]["L"])] + list(zip(c["dense"]["reqs"], c["dense"]["lens"])):
+        table[req, :n] = perm[used:used + n]
+        used += n
+    q_sel = rng.standard_normal((1, H, d)).astype(np.float32)
+    q_sparse = rng.standard_normal((1, H, d)).astype(np.float32)
+    q_dense = rng.standard_normal((len(c["dense"]["reqs"]), H, d)).astype(np.float32)
+    # a few keys stand out, so that membership in the top 2048 of 3000 is not decided by the last bits
+    L = c["select"]["L"]
+    hot = rng.permutation(L)[: L // 40]
+    qm = q_sel[0].mean(axis=0)
+    pool[table[c["select"]["req"], hot], :KVH] += (3.0 * qm / np.linalg.norm(qm)).astype(np.float32)
+    return dict(pool=pool, pool2=pool2, table=table, q_sel=q_sel, q_sparse=q_sparse, q_dense=q_dense)

@@ -37,6 +37,7 @@ HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE))
 from inputs import (CACHE_FLOW, OPERATOR, cache_flow_inputs, checksum, operator_inputs,  # noqa: E402
                     selector_case_list, selector_inputs)
+import inputs as gi  # noqa: E402
 
 
 sys.path.insert(0, str(HERE.parent.parent))
@@ -397,10 +398,68 @@ def make_rope_fixture(ref_root):
     print("rope arrays:", len(arrays))
 
 
+def make_lightllm_fixture(ref_root):
+    """The fork's own Triton kernels (omnikv-lightllm/lightllm/models/llama_omnikv/triton_kernel/
+    flash_decoding_stage1.py, flash_decoding_stage2.py), loaded by path and run on CPU tensors by Triton's
+    interpreter (TRITON_INTERPRET=1, set in main() before triton is imported), called as
+    token_decode_attention_flash_decoding calls them (flash_decoding.py:57-93 for the selecting call, :176-214 for
+    the plain one): outputs, the per-position score (max over heads of what the kernel writes to Attn_Score), the
+    top-2048 choice and the attention over the chosen rows of another layer's pool."""
+    import importlib.util
+    base = os.path.join(ref_root, "omnikv-lightllm", "lightllm", "models", "llama_omnikv", "triton_kernel")
+    mods = {}
+    for name in ("flash_decoding_stage1", "flash_decoding_stage2"):
+        spec = importlib.util.spec_from_file_location("ref_" + name, os.path.join(base, name + ".py"))
+        mods[name] = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mods[name])
+    s1, s2 = mods["flash_decoding_stage1"], mods["flash_decoding_stage2"]
+    c, x = gi.LIGHTLLM, gi.lightllm_inputs()
+    H, KVH, d, BS = c["H"], c["KVH"], c["d"], 256  # BLOCK_SEQ of flash_decoding.py:24
+    t = {k: torch.from_numpy(v) for k, v in x.items()}
+    table = t["table"]
+
+    def run(q, pool, tab, reqs, lens, with_score):
+        B, max_len = q.shape[0], int(max(lens))
+        b_req, b_len = torch.tensor(reqs, dtype=torch.int32), torch.tensor(lens, dtype=torch.int32)
+        mid_o = torch.zeros(B, H, max_len // BS + 1, d)
+        mid_l = torch.zeros(B, H, max_len // BS + 1)
+        o = torch.zeros(B, H, d)
+        k, v = pool[:, :KVH], pool[:, KVH:]
+        score = None
+        if with_score:
+            score = torch.zeros(B, H, max_len)
+            s1.flash_decode_stage1_with_score(q, k, v, tab, b_req, b_len, max_len, mid_o, mid_l, score, BS)
+        else:
+            s1.flash_decode_stage1(q, k, v, tab, b_req, b_len, max_len, mid_o, mid_l, BS)
+        s2.flash_decode_stage2(mid_o, mid_l, b_len, o, BS)
+        return o, score
+
+    req, L = c["select"]["req"], c["select"]["L"]
+    sel_out, score = run(t["q_sel"], t["pool"], table, [req], [L], True)
+    score_max = score.max(dim=1).values[0]                      # flash_decoding.py:75
+    n_imp = min(c["k"], L)                                       # :79
+    _, topk_idx = torch.topk(score_max[:L], dim=-1, k=n_imp)     # :80-82
+    imp = torch.zeros(c["n_requests"], c["k"], dtype=torch.int32)
+    imp[req, :n_imp] = torch.index_select(table[req, :L], dim=-1, index=topk_idx)  # :85-93
+    sparse_out, _ = run(t["q_sparse"], t["pool2"], imp, [req], [n_imp], False)    # a later layer over the chosen rows
+    dense_out, _ = run(t["q_dense"], t["pool"], table, c["dense"]["reqs"], c["dense"]["lens"], False)
+    np.savez_compressed(HERE / "lightllm.npz", sel_out=sel_out.numpy(), score_max=score_max.numpy(),
+                        topk_idx=topk_idx.numpy().astype(np.int32),
+                        sel_pos_sorted=np.sort(topk_idx.numpy()).astype(np.int32), sparse_out=sparse_out.numpy(),
+                        dense_out=dense_out.numpy())
+    (HERE / "lightllm.json").write_text(json.dumps(dict(cfg=c, inputs_checksum=gi.checksum(list(x.values())),
+                                                        block_seq=BS, triton="interpreter mode on CPU tensors")))
+    print("lightllm: selected", n_imp, "of", L)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the OmniKV checkout")
+    ap.add_argument("--only", default="", help="generate one fixture only (e.g. lightllm)")
     args = ap.parse_args()
+    os.environ["TRITON_INTERPRET"] = "1"  # the fork's Triton kernels run on CPU tensors (before triton is imported)
+    if args.only == "lightllm":
+        return make_lightllm_fixture(os.path.abspath(args.reference))
     ref_omnikv, ref_cache = import_reference(os.path.abspath(args.reference))
     torch.set_num_threads(8)
     make_selector_fixture(ref_omnikv)
@@ -411,6 +470,7 @@ def main():
     make_lazy_rule_fixture(ref_cache)
     make_layer_hook_fixture(ref_omnikv, ref_cache)
     make_rope_fixture(os.path.abspath(args.reference))
+    make_lightllm_fixture(os.path.abspath(args.reference))
 
 
 if __name__ == "__main__":

@@ -109,3 +109,52 @@ def test_refuses_prefill_and_bad_types():
     st.b_seq_len = st.b_seq_len.long()
     with pytest.raises(TypeError):
         attn(q.cuda(), st, H, d, pool_d[:, :KVH], pool_d[:, KVH:])
+
+
+def test_adapter_matches_the_forks_triton_kernels():
+    """The adapter (fp32 pool, through the C ABI) on the inputs of tests/golden/lightllm.npz, whose outputs come from
+    the fork's own Triton kernels: the selecting call's output, the recorded rows (the fork's top-2048 set, up to a
+    band at the threshold), a later layer's attention over those rows, and the plain ragged call."""
+    import json
+    from pathlib import Path
+
+    import numpy as np
+
+    import inputs as gi
+    from omnikv_b200.lightllm_adapter import token_decode_attention_flash_decoding as attn
+    from parity import band_check
+    G = Path(__file__).resolve().parent / "golden"
+    gold = np.load(G / "lightllm.npz")
+    c, x = gi.LIGHTLLM, gi.lightllm_inputs()
+    meta = json.loads((G / "lightllm.json").read_text())
+    assert abs(meta["inputs_checksum"] - gi.checksum(list(x.values()))) < 1e-6 * abs(meta["inputs_checksum"])
+    H, KVH, d, k = c["H"], c["KVH"], c["d"], c["k"]
+    t = {n: torch.from_numpy(v).cuda() for n, v in x.items()}
+    req, L = c["select"]["req"], c["select"]["L"]
+
+    def state(reqs, lens):
+        imp = torch.zeros(2, c["n_requests"], k + 64, dtype=torch.int32, device="cuda")
+        rm = SimpleNamespace(req_to_token_indexs=t["table"], req_to_imp_token_indexs=imp)
+        return SimpleNamespace(batch_size=len(reqs), max_len_in_batch=max(lens),
+                               b_seq_len=torch.tensor(lens, dtype=torch.int32, device="cuda"),
+                               b_req_idx=torch.tensor(reqs, dtype=torch.int32, device="cuda"), req_manager=rm,
+                               is_prefill=False, imp_seq_len=None, max_imp_len_batch=0)
+
+    pool, pool2 = t["pool"], t["pool2"]
+    st = state([req], [L])
+    o = attn(t["q_sel"].reshape(1, H * d), st, H, d, pool[:, :KVH], pool[:, KVH:], do_select=True, tp_rank=0)
+    assert np.abs(o.float().cpu().numpy().reshape(1, H, d) - gold["sel_out"]).max() <= 1e-4
+    n_imp = int(st.imp_seq_len[0].item())
+    assert n_imp == k == st.max_imp_len_batch
+    rows = st.req_manager.req_to_imp_token_indexs[0, req, :n_imp].cpu()
+    inv = {int(r): p for p, r in enumerate(x["table"][req, :L].tolist())}
+    got = torch.tensor(sorted(inv[int(r)] for r in rows.tolist()))
+    # the fixture's scores are raw logits (magnitude up to 40): 1e-3 there is the 1e-4 band of the scaled scores
+    band_check(torch.from_numpy(gold["score_max"]), k, got.tolist(), gold["sel_pos_sorted"].tolist(), 1e-3,
+               "rows recorded by the selecting call")
+    o2 = attn(t["q_sparse"].reshape(1, H * d), st, H, d, pool2[:, :KVH], pool2[:, KVH:], tp_rank=0)
+    if torch.equal(got, torch.from_numpy(gold["sel_pos_sorted"]).long()):  # same rows: same attention
+        assert np.abs(o2.float().cpu().numpy().reshape(1, H, d) - gold["sparse_out"]).max() <= 1e-4
+    st3 = state(c["dense"]["reqs"], c["dense"]["lens"])
+    o3 = attn(t["q_dense"].reshape(-1, H * d), st3, H, d, pool[:, :KVH], pool[:, KVH:])
+    assert np.abs(o3.float().cpu().numpy().reshape(-1, H, d) - gold["dense_out"]).max() <= 1e-4

@@ -633,3 +633,23 @@ def test_batched_decode_tcgen05_linear_and_fused_adds_match_library_path(dtype):
     # other summation order inside every projection and SiLU(gate) * up taken from the unrounded sums: measured 0.024
     # on logits of magnitude 1 (a few 16-bit steps after six layers)
     assert (logits[0] - logits[2]).abs().max().item() <= 4e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_prefill_kernel_matches_library_attention_in_the_model(dtype):
+    """The prompt pass of a 16-bit model through this package's tcgen05 attention kernel against the same pass
+    through PyTorch's fused attention: the logits and the K rows the pass leaves in the cache (the kernel sees batch 2,
+    grouped heads and a prompt that does not fill its last tile)."""
+    outs = {}
+    for kern in ("tcgen05", "sdpa"):
+        cfg = small_config(selector_cls="last", num_of_selected_tokens=0.25, prefill_kernel=kern)
+        lm, _ = build(cfg, dtype)
+        g = torch.Generator().manual_seed(3)
+        ids = torch.randint(0, 1000, (2, 333), generator=g).cuda()
+        out = lm(input_ids=ids)
+        cache = out.past_key_values
+        outs[kern] = (out.logits.float(), [cache._k[i][:, :, :333].float().clone() for i in range(cfg.num_hidden_layers)])
+    a, b = outs["tcgen05"], outs["sdpa"]
+    assert (a[0] - b[0]).abs().max().item() <= 2e-2
+    for ka, kb in zip(a[1], b[1]):  # keys of deeper layers depend on the attention output of the layers before
+        assert (ka - kb).abs().max().item() <= 2e-2 * max(1.0, kb.abs().max().item())

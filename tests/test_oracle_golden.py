@@ -199,3 +199,31 @@ def test_cache_flow_d128_matches_reference(cls_name):
             kk, vv = cache.update(t(x["k_new"][s][i]), t(x["v_new"][s][i]), i)
             assert [gi.signature(kk.numpy()), gi.signature(vv.numpy())] == c["returns"][f"{cls_name}/{s}/{i}"]
     assert cache._seen_tokens == c["returns"][f"{cls_name}/seen"]
+
+
+def test_lightllm_oracle_matches_the_forks_triton_kernels():
+    """oracle/lightllm_oracle.py against what the fork's own Triton kernels produced (run by Triton's interpreter
+    when the fixture was made): outputs of the selecting call and of the plain ragged call, the raw-logit scores,
+    the top-2048 positions, and the attention of a later layer over exactly those rows."""
+    from oracle import lightllm_oracle as lo
+    meta = json.loads((G / "lightllm.json").read_text())
+    gold = np.load(G / "lightllm.npz")
+    c, x = gi.LIGHTLLM, gi.lightllm_inputs()
+    assert meta["cfg"] == json.loads(json.dumps(c))
+    assert abs(meta["inputs_checksum"] - gi.checksum(list(x.values()))) < 1e-6 * abs(meta["inputs_checksum"])
+    t = {k: torch.from_numpy(v) for k, v in x.items()}
+    KVH = c["KVH"]
+    pk, pv, table = t["pool"][:, :KVH], t["pool"][:, KVH:], t["table"]
+    req, L = c["select"]["req"], c["select"]["L"]
+    out = lo.paged_decode_attention(t["q_sel"], pk, pv, table, [req], [L])
+    assert np.abs(out.numpy() - gold["sel_out"]).max() <= 1e-5
+    score = lo.fork_scores(t["q_sel"], pk, table, [req], [L])[0]
+    assert np.abs(score.numpy() - gold["score_max"]).max() <= 1e-4  # raw logits of magnitude up to 40
+    pos = lo.select_positions(t["q_sel"], pk, table, [req], [L], c["k"])[0]
+    assert np.array_equal(pos.numpy().astype(np.int32), gold["sel_pos_sorted"])
+    assert set(gold["topk_idx"].tolist()) == set(gold["sel_pos_sorted"].tolist())
+    p2k, p2v = t["pool2"][:, :KVH], t["pool2"][:, KVH:]
+    sparse = lo.selected_decode_attention(t["q_sparse"], p2k, p2v, table, [req], [pos])
+    assert np.abs(sparse.numpy() - gold["sparse_out"]).max() <= 1e-5
+    dense = lo.paged_decode_attention(t["q_dense"], pk, pv, table, c["dense"]["reqs"], c["dense"]["lens"])
+    assert np.abs(dense.numpy() - gold["dense_out"]).max() <= 1e-5
