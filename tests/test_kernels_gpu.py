@@ -792,3 +792,31 @@ def test_add_rms_norm(dtype, tol, n, hidden, with_delta):
     out = ops().add_rms_norm(h, delta, w, 1e-5)
     assert torch.equal(h, want_h)  # the residual stream is updated in place, rounded once
     assert ((out.float() - want).abs() / want.abs().clamp(min=1.0)).max().item() <= tol
+
+
+def test_prefill_attention_random_shapes():
+    """Forty seeded random shapes (batch, grouped heads, chunk lengths that leave partial tiles, chunks at an offset
+    inside a longer cache, K/V as strided views) through both prompt-attention kernels against the fp32 definition."""
+    rng = np.random.default_rng(77)
+    for it in range(40):
+        B = int(rng.integers(1, 3))
+        KVH = int(rng.choice([1, 2, 4]))
+        H = KVH * int(rng.choice([1, 2, 4]))
+        Sq = int(rng.integers(1, 700))
+        q_pos0 = int(rng.choice([0, 0, int(rng.integers(0, 900))]))
+        Skv = q_pos0 + Sq + int(rng.choice([0, 0, int(rng.integers(0, 300))]))
+        dtype = torch.bfloat16 if it % 2 == 0 else torch.float16
+        g = torch.Generator().manual_seed(1000 + it)
+        q = (torch.randn(B, H, Sq, 128, generator=g) * 1.5).to(dtype).cuda()
+        if it % 3 == 0:  # K and V side by side in one buffer (row stride of two rows)
+            kv = torch.randn(B, KVH, Skv, 2, 128, generator=g).to(dtype).cuda()
+            k, v = kv[:, :, :, 0], kv[:, :, :, 1]
+        else:
+            k = torch.randn(B, KVH, Skv, 128, generator=g).to(dtype).cuda()
+            v = torch.randn(B, KVH, Skv, 128, generator=g).to(dtype).cuda()
+        ref = _causal_reference(q, k, v, q_pos0, 1.0 / math.sqrt(128))
+        for variant in (0, 1):
+            out = ops().prefill_attn(q, k, v, q_pos0=q_pos0, variant=variant)
+            err = (out.float() - ref).abs().max().item()
+            assert err <= 2e-2, (it, variant, B, H, KVH, Sq, Skv, q_pos0, err)
+    ops().check_status("cuda")
