@@ -22,7 +22,9 @@
  *     dependent launch; OMNIKV_ATTN_TMA=0 keeps dense decode attention on its cp.async variant;
  *     OMNIKV_WINDOW_TMA=0 does the same for the window selector's mma.sync kernels; OMNIKV_WINDOW_TC=0 keeps the
  *     window selector off its tcgen05 kernels; OMNIKV_TOPK_CLUSTER=8 limits omnikv_topk to the portable cluster size.
- *     They exist for measurements and fault isolation; results are the same.
+ *     OMNIKV_ATTN_COOP=0 has every split merge of decode attention done by the last CTA of its group (by default a dense
+ *     layer with 64 splits or more on a grid that is resident as a whole merges them across all of its CTAs).
+ *     They exist for measurements and fault isolation; results are the same up to the order of fp32 sums.
  */
 #ifndef OMNIKV_B200_H_
 #define OMNIKV_B200_H_

@@ -42,6 +42,7 @@ struct AttnArgs {
   float* ws_ml;
   unsigned* ws_cnt;   // [B*KVH] arrival counters of the splits, zero between launches
   int pdl_trigger;    // 1: the grid is fully resident, the next kernel may be scheduled early
+  int coop_merge;     // 1: the splits of a (sequence, KV head) merge together (see coop_merge); needs a resident grid
   int trace_slot;     // profiling build: slot of the stamp array this launch writes
   int* status;        // device word for bounded-wait failures, or nullptr
   int B, H, KVH, G, S;
@@ -81,6 +82,14 @@ constexpr int Q_BYTES = 16 * PITCH;
 inline bool g_attn_tma_enabled() {
   static const bool on = [] {
     const char* e = getenv("OMNIKV_ATTN_TMA");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+bool g_attn_coop_enabled() {  // OMNIKV_ATTN_COOP=0: every merge by the last CTA of its group
+  static const bool on = [] {
+    const char* e = getenv("OMNIKV_ATTN_COOP");
     return !(e && e[0] == '0');
   }();
   return on;
@@ -192,6 +201,97 @@ __device__ __forceinline__ void finish_group(const AttnArgs& a, int b, int kvh, 
   if (tid == 0) a.ws_cnt[b * a.KVH + kvh] = 0u;
 }
 
+// The merge of MANY splits (a dense layer under tensor parallelism: 148 per KV head) by one last CTA is a chain of ten
+// L2 round trips (10.8 us measured at four GPUs).  When the whole grid is resident (the host checks the occupancy),
+// the splits of a (sequence, KV head) instead wait for one another -- thread 0 of every CTA counts itself in and
+// polls the count, bounded by time -- and then EVERY CTA merges a slice of the group's G x 128 outputs: four output
+// values per CTA, the S partials of them read by one warp in a single round trip (lane = split, up to eight per
+// lane), combined with shuffles in a fixed order.  The CTA that leaves last clears both counters.
+template <typename T>
+__device__ __forceinline__ void coop_merge(const AttnArgs& a, int b, int kvh, int split, int* flag_s) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int S = a.S, G = a.G;
+  unsigned* arrive = a.ws_cnt + b * a.KVH + kvh;
+  unsigned* depart = a.ws_cnt + 2048 + b * a.KVH + kvh;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    atomicAdd(arrive, 1u);
+    bool ok = ld_volatile_u32(arrive) >= (unsigned)S;
+    if (!ok) {
+      const unsigned long long t0 = globaltimer_ns();
+      for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 16 && !ok; ++i) ok = ld_volatile_u32(arrive) >= (unsigned)S;
+        if (ok || globaltimer_ns() - t0 > kWaitNs) break;
+      }
+    }
+    if (!ok && a.status) atomicExch(a.status, 5);
+    *flag_s = ok ? 1 : 0;
+  }
+  __syncthreads();
+  if (!*flag_s) return;
+  __threadfence();
+  const int total = G * kHeadDim;
+  const int chunk = ceil_div(ceil_div(total, S), 4) * 4;  // output values of this CTA
+  if (warp == 0) {
+    for (int e = split * chunk; e < min(total, split * chunk + chunk); e += 4) {
+      const int r = e / kHeadDim, d0 = e % kHeadDim, h = kvh * G + r;
+      const size_t base = (size_t)(b * a.H + h) * S;
+      float2 ml[8];
+      float4 ov[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int sidx = lane + 32 * u;
+        ml[u] = make_float2(-INFINITY, 0.f);
+        ov[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (sidx < S) {
+          ml[u] = __ldcg(reinterpret_cast<const float2*>(a.ws_ml + (base + sidx) * 2));
+          ov[u] = __ldcg(reinterpret_cast<const float4*>(a.ws_o + (base + sidx) * kHeadDim + d0));
+        }
+      }
+      float M = -INFINITY;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) M = fmaxf(M, ml[u].x);
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+      const float Mu = (M == -INFINITY) ? 0.f : M;
+      float l = 0.f;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float wt = (ml[u].x == -INFINITY) ? 0.f : exp2f((ml[u].x - Mu) * kLog2e);
+        l = fmaf(ml[u].y, wt, l);
+        acc.x = fmaf(ov[u].x, wt, acc.x);
+        acc.y = fmaf(ov[u].y, wt, acc.y);
+        acc.z = fmaf(ov[u].z, wt, acc.z);
+        acc.w = fmaf(ov[u].w, wt, acc.w);
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        l += __shfl_xor_sync(0xffffffffu, l, off);
+        acc.x += __shfl_xor_sync(0xffffffffu, acc.x, off);
+        acc.y += __shfl_xor_sync(0xffffffffu, acc.y, off);
+        acc.z += __shfl_xor_sync(0xffffffffu, acc.z, off);
+        acc.w += __shfl_xor_sync(0xffffffffu, acc.w, off);
+      }
+      if (lane == 0) {
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        T* dst = static_cast<T*>(a.out) + (size_t)b * a.q_sb + (size_t)h * a.q_sh + d0;
+        dst[0] = from_float<T>(acc.x * inv);
+        dst[1] = from_float<T>(acc.y * inv);
+        dst[2] = from_float<T>(acc.z * inv);
+        dst[3] = from_float<T>(acc.w * inv);
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0 && atomicAdd(depart, 1u) == (unsigned)(S - 1)) {  // every CTA of the group is past its wait
+    atomicExch(arrive, 0u);
+    atomicExch(depart, 0u);
+  }
+}
+
 // BULK: how a tile's rows travel to shared memory.  true: one 256-byte bulk copy per row (the copy engine moves
 // it and signals the stage's mbarrier) -- sixteen times fewer instructions and request slots than cp.async, which
 // is what a sparse layer's scattered rows need (22.5 instead of 28.7 us per layer).  false: sixteen 16-byte
@@ -274,7 +374,8 @@ __global__ void __launch_bounds__(NTHREADS, ST > STAGES ? 1 : 2) decode_attn_mma
           ws_ml[base * 2 + 1] = 0.f;
         }
       }
-      finish_group<T>(a, b, kvh, reinterpret_cast<float*>(smem), &last_flag);
+      if (a.coop_merge) coop_merge<T>(a, b, kvh, split, &last_flag);
+      else finish_group<T>(a, b, kvh, reinterpret_cast<float*>(smem), &last_flag);
     }
     return;
   }
@@ -614,7 +715,8 @@ __global__ void __launch_bounds__(NTHREADS, ST > STAGES ? 1 : 2) decode_attn_mma
   if (a.S == 1) return;
   ATTN_STAMP(4);  // partials written
   // the shared scratch of finish_group starts behind the cross-warp merge area used above
-  finish_group<T>(a, b, kvh, ml_s + NWARPS * 16 * 2, &last_flag);
+  if (a.coop_merge) coop_merge<T>(a, b, kvh, split, &last_flag);
+  else finish_group<T>(a, b, kvh, ml_s + NWARPS * 16 * 2, &last_flag);
   ATTN_STAMP(5);  // counted in (and, for the last CTA of the group, merged)
 }
 
@@ -772,6 +874,13 @@ int launch_mma(AttnArgs a, bool with_v, bool with_score, int64_t a_rows, cudaStr
     mode = kCopyTma;
   auto go = [&](auto kern, int smem) -> int {
     OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    // many splits of a dense layer, and a grid that is resident as a whole: the splits merge together
+    a.coop_merge = 0;
+    if (mode == kCopyTma && with_v && a.S >= 64 && a.S <= 256 && a.B * a.KVH <= 2048 && g_attn_coop_enabled()) {
+      int per_sm = 0;
+      OMNIKV_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NTHREADS, smem));
+      if ((long long)a.S * a.KVH * a.B <= (long long)per_sm * n_sms) a.coop_merge = 1;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;

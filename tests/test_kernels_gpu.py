@@ -663,6 +663,31 @@ def test_dense_attn_tensor_map_tiles_equal_cp_async(dtype, B, L, cap):
     assert (outs[0][0][:1].float().cpu() - ref).abs().max().item() < 2e-2
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("L,splits,with_score", [(20000, 148, False), (20000, 64, True), (300, 64, False), (9000, 100, False)])
+def test_dense_attention_with_many_splits_merged_together(dtype, L, splits, with_score):
+    """A dense layer whose splits fit on the GPU at once (one or two KV heads per rank, as under tensor parallelism):
+    the splits wait for one another and every CTA merges a slice of the output.  Same result as the merge by the last
+    CTA (a few splits) up to the order of fp32 sums, right against the oracle, the same on a second call (the
+    counters are left at zero), also when most splits are empty."""
+    g = torch.Generator(device="cuda").manual_seed(41)
+    B, H, KVH, d = 1, 8, 2, 128
+    kv = torch.randn(B, KVH, L + 64, 2, d, generator=g, device="cuda").to(dtype)
+    kc, vc = kv[:, :, :, 0, :], kv[:, :, :, 1, :]
+    q = (torch.randn(B, H, d, generator=g, device="cuda") * 1.5).to(dtype)
+    n = dev_i32([L])
+    planes = torch.zeros(KVH, B, L + 64, dtype=torch.float32, device="cuda") if with_score else None
+    kw = dict(score_out=planes, score_len=n) if with_score else {}
+    many = ops().decode_attn(q, kc, vc, n, state_capacity=True, n_splits=splits, **kw)
+    again = ops().decode_attn(q, kc, vc, n, state_capacity=True, n_splits=splits, **kw)
+    few = ops().decode_attn(q, kc, vc, n, state_capacity=True, n_splits=4, **kw)
+    ops().check_status("cuda")
+    assert torch.equal(many, again)
+    assert (many.float() - few.float()).abs().max().item() <= 4e-3
+    ref = oracle.dense_attention(q.cpu(), kc[:, :, :L].cpu(), vc[:, :, :L].cpu())
+    assert (many.float().cpu() - ref).abs().max().item() < 2e-2
+
+
 def _causal_reference(q, k, v, q_pos0, scale):
     """fp32 definition: query i sees keys j <= q_pos0 + i.  q [B,H,Sq,d], k/v [B,KVH,Skv,d] -> [B,Sq,H,d]."""
     B, H, Sq, d = q.shape
