@@ -201,7 +201,7 @@ __device__ __forceinline__ void finish_group(const AttnArgs& a, int b, int kvh, 
   if (tid == 0) a.ws_cnt[b * a.KVH + kvh] = 0u;
 }
 
-// The merge of MANY splits (a dense layer under tensor parallelism: 148 per KV head) by one last CTA is a chain of ten
+// The merge of MANY splits (a layer under tensor parallelism: 148 per KV head of a dense layer, 69 of a sparse one) by one last CTA is a chain of ten
 // L2 round trips (10.8 us measured at four GPUs).  When the whole grid is resident (the host checks the occupancy),
 // the splits of a (sequence, KV head) instead wait for one another -- thread 0 of every CTA counts itself in and
 // polls the count, bounded by time -- and then EVERY CTA merges a slice of the group's G x 128 outputs: four output
@@ -874,9 +874,11 @@ int launch_mma(AttnArgs a, bool with_v, bool with_score, int64_t a_rows, cudaStr
     mode = kCopyTma;
   auto go = [&](auto kern, int smem) -> int {
     OMNIKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    // many splits of a dense layer, and a grid that is resident as a whole: the splits merge together
+    // many splits (64 or more: one or two local KV heads under tensor parallelism) and a grid that is resident as a
+    // whole: the splits merge together.  With fewer splits the CTAs that wait hold their SMs longer than the merge by
+    // the last CTA costs (measured at 37 splits x 8 KV heads: 3.57 against 3.53 ms per step).
     a.coop_merge = 0;
-    if (mode == kCopyTma && with_v && a.S >= 64 && a.S <= 256 && a.B * a.KVH <= 2048 && g_attn_coop_enabled()) {
+    if (mode != kCopyCpAsync && with_v && a.S >= 64 && a.S <= 256 && a.B * a.KVH <= 2048 && g_attn_coop_enabled()) {
       int per_sm = 0;
       OMNIKV_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NTHREADS, smem));
       if ((long long)a.S * a.KVH * a.B <= (long long)per_sm * n_sms) a.coop_merge = 1;
