@@ -380,7 +380,12 @@ def build_workload(args, world, rank, dev, tp):
     wl = args.workload
 
     def make_cfg():
-        if wl == "tp70b":
+        if wl == "tp70b" and args.rank_shape_of > 1:  # one rank's share of the 70B shape on one GPU, no exchange
+            n = args.rank_shape_of
+            cfg = LlamaCompressorConfig(num_hidden_layers=args.layers, hidden_size=8192, intermediate_size=28672 // n,
+                                        num_attention_heads=64 // n, num_key_value_heads=8 // n,
+                                        vocab_size=128256 // n, head_dim=128)
+        elif wl == "tp70b":
             cfg = LlamaCompressorConfig(num_hidden_layers=args.layers, hidden_size=8192, intermediate_size=28672,
                                         num_attention_heads=64, num_key_value_heads=8)
         elif args.rank_shape_of > 1:

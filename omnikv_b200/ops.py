@@ -85,7 +85,9 @@ def default_splits(B: int, KVH: int, max_rows: int, device) -> int:
         # time (prologue, split merge) whatever it streams, and two CTAs fit on an SM, so the count that minimises
         # waves x (tiles per CTA + 7) wins -- 2 instead of 5 for 16 sequences x 8 KV heads x 2112 rows
         slots, tiles = 2 * sm_count(device), -(-max_rows // 64)
-        s = min(range(1, 9), key=lambda c: (-(-ctas * c // slots)) * (-(-tiles // c) + 7))
+        # (few sequences, e.g. eight with one local KV head each, want many splits: the merge of c partials costs
+        # about c / 16 further tile times)
+        s = min(range(1, 65), key=lambda c: (-(-ctas * c // slots)) * (-(-tiles // c) + 7 + c / 16))
     elif B > 1:  # ragged batches: chunks are sized by the longest sequence, so aim at two waves of equal CTAs
         s = -(-4 * sm_count(device) // ctas)
     else:
