@@ -352,6 +352,12 @@ int omnikv_rope_append(int dtype, const void* qkv, int64_t qkv_stride_b, int B, 
                        const float* inv_freq, const int32_t* rope_pos, void* q_out, int64_t q_stride_b,
                        void* k_cache, void* v_cache, int64_t cache_stride_b, int64_t cache_stride_h,
                        int64_t cache_stride_row, const int32_t* cache_pos, void* stream);
+/* The observation window's queries of a window selector straight from the q projection: qlin[b][w] = H heads x
+ * head_dim (element strides given), every query rotated at rope_pos[b] (the reference rotates all window queries at
+ * the current position, modeling/omnikv.py:52-57, :66-71), written as out [B, H, W, head_dim] contiguous: the qw
+ * argument of omnikv_score_window.  One launch instead of the transpose and the element-wise rotary kernels. */
+int omnikv_rope_window(int dtype, const void* qlin, int64_t stride_b, int64_t stride_w, int B, int W, int H,
+                       int head_dim, const float* inv_freq, const int32_t* rope_pos, void* out, void* stream);
 /* The residual add and the RMSNorm behind it as one launch (batched decode): h[b] += delta[b] when delta is given
  * (rounded to the residual stream's type), out[b] = RMSNorm(h[b], eps) * norm_w.  Replaces the separate add and norm
  * kernels between the third-party decoder modules (modeling/omnikv.py:229-232 and the next layer's :156). */

@@ -112,6 +112,9 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const T* __restrict__ 
                                                           const int* __restrict__ rope_pos, T* __restrict__ q_out,
                                                           int64_t q_sb, T* k_cache, T* v_cache, int64_t c_sb,
                                                           int64_t c_sh, int64_t c_sr, const int* __restrict__ cache_pos) {
+  // the attention kernel that follows may be scheduled at once: before its own wait for this grid it only reads
+  // lengths, index lists and cache rows OTHER than the ones written here
+  pdl_trigger();
   const int b = blockIdx.y;
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   const int heads = H + 2 * KVH;
@@ -138,6 +141,26 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const T* __restrict__ 
   }
   dst[i] = from_float<T>(x0);
   dst[i + 64] = from_float<T>(x1);
+}
+
+// The observation window's queries straight from the q projection: qlin[b][w] = H heads x head_dim, every one rotated
+// at the CURRENT position of its sequence (as the reference's window selectors do, modeling/omnikv.py:52-57, :66-71),
+// written as [B, H, W, head_dim] for omnikv_score_window.  fp32 arithmetic, rounded once.
+template <typename T>
+__global__ void __launch_bounds__(256) rope_window_kernel(const T* __restrict__ qlin, int64_t sb, int64_t sw, int H, int W,
+                                                          const float* __restrict__ inv_freq,
+                                                          const int* __restrict__ rope_pos, T* __restrict__ out) {
+  const int b = blockIdx.z, w = blockIdx.y;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= H * 64) return;
+  const int hh = t >> 6, i = t & 63;
+  const T* src = qlin + (size_t)b * sb + (size_t)w * sw + (size_t)hh * kHeadDim;
+  const float x0 = to_float(src[i]), x1 = to_float(src[i + 64]);
+  float sn, cs;
+  sincosf((float)rope_pos[b] * inv_freq[i], &sn, &cs);
+  T* dst = out + (((size_t)b * H + hh) * W + w) * kHeadDim;
+  dst[i] = from_float<T>(x0 * cs - x1 * sn);
+  dst[i + 64] = from_float<T>(x1 * cs + x0 * sn);
 }
 
 // act[b][j] = silu(gu[b][j]) * gu[b][inter + j]: the SwiGLU product of a fused gate/up projection.
@@ -425,6 +448,32 @@ extern "C" int omnikv_rope_append(int dtype, const void* qkv, int64_t qkv_stride
     default: return OMNIKV_E_UNSUPPORTED;
   }
 #undef OMNIKV_ROPE_LAUNCH
+  OMNIKV_CUDA_OK(cudaGetLastError());
+  return OMNIKV_OK;
+}
+
+extern "C" int omnikv_rope_window(int dtype, const void* qlin, int64_t stride_b, int64_t stride_w, int B, int W, int H,
+                                  int head_dim, const float* inv_freq, const int32_t* rope_pos, void* out, void* stream) {
+  using namespace omnikv;
+  if (!qlin || !inv_freq || !rope_pos || !out || B <= 0 || W <= 0 || H <= 0 || B > 65535 || W > 65535) return OMNIKV_E_BADARG;
+  if (head_dim != kHeadDim) return OMNIKV_E_UNSUPPORTED;
+  dim3 grid(ceil_div(H * 64, 256), W, B);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case OMNIKV_BF16:
+      rope_window_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(qlin), stride_b, stride_w, H,
+                                                              W, inv_freq, rope_pos, static_cast<__nv_bfloat16*>(out));
+      break;
+    case OMNIKV_F16:
+      rope_window_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(qlin), stride_b, stride_w, H, W, inv_freq,
+                                                       rope_pos, static_cast<__half*>(out));
+      break;
+    case OMNIKV_F32:
+      rope_window_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(qlin), stride_b, stride_w, H, W, inv_freq,
+                                                      rope_pos, static_cast<float*>(out));
+      break;
+    default: return OMNIKV_E_UNSUPPORTED;
+  }
   OMNIKV_CUDA_OK(cudaGetLastError());
   return OMNIKV_OK;
 }

@@ -443,9 +443,16 @@ class OmniKVMulLayer(nn.Module):
                 self.hidden_state_window = win.contiguous()
             window_hs = self.hidden_state_window
         W = window_hs.shape[1]
-        cos, sin = position_embeddings
-        q = F.linear(window_hs, attn.q_proj.weight).view(B, W, attn.num_heads, attn.head_dim).transpose(1, 2)
-        q = apply_rotary(q, cos, sin).contiguous()
+        q = F.linear(window_hs, attn.q_proj.weight)
+        rope_pos = getattr(cache, "rope_pos_dev", None)
+        if (rope_pos is not None and q.is_cuda and attn.head_dim == 128 and attn.rotary_emb.attention_scaling == 1.0
+                and self.config.get("fused_small_ops", True)):
+            q = ops.rope_window(q, attn.num_heads, attn.rotary_emb.inv_freq, rope_pos)  # one launch, no rotary table
+        else:
+            if position_embeddings is None:
+                position_embeddings = attn.rotary_emb(window_hs, cache.pos_dev[:, None])
+            cos, sin = position_embeddings
+            q = apply_rotary(q.view(B, W, attn.num_heads, attn.head_dim).transpose(1, 2), cos, sin).contiguous()
         torch.sub(cache.prefill_len_dev, st.nptw, out=st.consider)
         torch.clamp(st.k0 - st.nptw, min=1, out=st.k)
         if st.planes is None:
@@ -518,8 +525,6 @@ class OmniKVMulLayer(nn.Module):
                 st.planes = torch.zeros(self.self_attn.num_key_value_heads, hidden_states.shape[0], st.max_len,
                                         dtype=torch.float32, device=dev)
             return st.planes, cache.prefill_len_dev
-        if position_embeddings is None:
-            position_embeddings = self.self_attn.rotary_emb(hidden_states, cache.pos_dev[:, None])
         self._select(self.input_layernorm(hidden_states) if normed is None else normed, position_embeddings, cache)
         return None, None
 

@@ -431,6 +431,21 @@ def add_rms_norm(h: torch.Tensor, delta: Optional[torch.Tensor], norm_w: torch.T
     return out
 
 
+def rope_window(qlin: torch.Tensor, H: int, inv_freq: torch.Tensor, rope_pos: torch.Tensor) -> torch.Tensor:
+    """``omnikv_rope_window``.  qlin ``[B, W, H*128]`` (rows contiguous) -> rotated queries ``[B, H, W, 128]``, every
+    window slot rotated at ``rope_pos[b]`` (int32, device)."""
+    _need_cuda(qlin, inv_freq, rope_pos)
+    B, W, n = qlin.shape
+    if qlin.stride(2) != 1 or n != H * 128:
+        raise abi.OmniKVError("rope_window: qlin must be [B, W, H*128] with contiguous rows")
+    out = torch.empty(B, H, W, 128, dtype=qlin.dtype, device=qlin.device)
+    abi.check(abi.lib().omnikv_rope_window(_DT[qlin.dtype], qlin.data_ptr(), qlin.stride(0), qlin.stride(1), B, W, H, 128,
+                                           inv_freq.data_ptr(), rope_pos.data_ptr(), out.data_ptr(), _stream()),
+              "omnikv_rope_window")
+    _count(1)
+    return out
+
+
 def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``omnikv_silu_mul``.  gate_up ``[B, 2*inter]`` (rows contiguous) -> ``silu(gate) * up`` ``[B, inter]``."""
     _need_cuda(gate_up, out)

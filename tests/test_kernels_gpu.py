@@ -845,3 +845,23 @@ def test_prefill_attention_random_shapes():
             err = (out.float() - ref).abs().max().item()
             assert err <= 2e-2, (it, variant, B, H, KVH, Sq, Skv, q_pos0, err)
     ops().check_status("cuda")
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 2e-2), (torch.float16, 4e-3), (torch.float32, 2e-6)])
+def test_rope_window(dtype, tol):
+    """Window queries from the q projection: every slot rotated at its sequence's current position, laid out
+    [B, H, W, d]; against the rotate_half formula in fp32."""
+    B, W, H, d = 3, 16, 8, 128
+    g = torch.Generator().manual_seed(12)
+    qlin = torch.randn(B, W, H * d, generator=g).to(dtype).cuda()
+    inv_freq = (1.0 / (500000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).cuda()
+    pos = dev_i32([5, 4099, 131071])
+    out = ops().rope_window(qlin, H, inv_freq, pos)
+    x = qlin.float().view(B, W, H, d).transpose(1, 2)  # [B, H, W, d]
+    ang = pos.float()[:, None] * inv_freq[None, :]     # [B, 64]
+    cos = torch.cat([ang.cos(), ang.cos()], -1)[:, None, None, :]
+    sin = torch.cat([ang.sin(), ang.sin()], -1)[:, None, None, :]
+    rot = torch.cat([-x[..., 64:], x[..., :64]], -1)
+    want = x * cos + rot * sin
+    assert out.shape == (B, H, W, d)
+    assert (out.float() - want).abs().max().item() <= tol * max(1.0, want.abs().max().item())
