@@ -301,6 +301,7 @@ def main():
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--ctx", type=int, default=131072)
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--contiguous-idx", action="store_true", help="sparse_attn: select rows 0..k-1 instead of random ones")
     ap.add_argument("--batch", type=int, default=1, help="sparse_attn: sequences (2048 selected rows + 64 tail rows each)")
     ap.add_argument("--library", action="store_true", help="prefill_attn: also time PyTorch's fused attention")
     ap.add_argument("--kv-layout", default="interleaved", choices=["interleaved", "planes"],
@@ -366,8 +367,11 @@ def main():
         fn = lambda: ops.decode_attn(q, kc, vc, n_all, score_out=planes, score_len=n_p, n_splits=args.splits or None)  # noqa: E731
         nbytes = 2 * KVH * d * 2 * (L + 1)
     elif args.case == "sparse_attn":
-        idx = torch.stack([torch.sort(torch.randperm(L, generator=g, device=dev)[:k_sel]).values.to(torch.int32)
-                           for _ in range(B)]).contiguous()
+        if args.contiguous_idx:  # the same number of rows, but neighbours in memory: separates the cost of scattered DRAM
+            idx = torch.arange(k_sel, device=dev, dtype=torch.int32)[None].repeat(B, 1).contiguous()  # reads from the copies
+        else:
+            idx = torch.stack([torch.sort(torch.randperm(L, generator=g, device=dev)[:k_sel]).values.to(torch.int32)
+                               for _ in range(B)]).contiguous()
         cnt, n_p, one = i32([k_sel] * B), i32([L] * B), i32([64 if B > 1 else 1] * B)
         fn = lambda: ops.decode_attn(q, kc, vc, cnt, idx=idx, k_tail=kc, v_tail=vc, tail_start=n_p, tail_len=one,  # noqa: E731
                                      max_rows=k_sel + 64, n_splits=args.splits or None)
