@@ -158,8 +158,9 @@ __device__ __forceinline__ bool take_accumulator(TcShared& sh, int j, float (&v)
   return true;
 }
 
+// Setup in two halves: the first touches no global memory, the second publishes the staged query blocks.
 template <int STAGES>
-__device__ __forceinline__ void tc_setup(TcShared& sh, unsigned ncols, int warp, int n_epilogue_threads) {
+__device__ __forceinline__ void tc_setup_begin(TcShared& sh, unsigned ncols, int warp, int n_epilogue_threads) {
   if (threadIdx.x == 0) {
     sh.fail = 0;
     sh.issued = 0;
@@ -179,6 +180,9 @@ __device__ __forceinline__ void tc_setup(TcShared& sh, unsigned ncols, int warp,
     tmem_alloc(&sh.tmem_base, ncols);
     tmem_relinquish();
   }
+}
+
+__device__ __forceinline__ void tc_setup_end() {
   // the query block was written with ordinary stores; the tensor core reads it through the async proxy
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   tc_fence_before();
@@ -257,6 +261,11 @@ __global__ void __launch_bounds__(P1Shape<G>::THREADS, 2) window_tc_pass1(const 
   unsigned char* q_s = smem + P1_STAGES * TC_KTILE_BYTES;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // Launched as a programmatic dependent: the CTAs are scheduled while the previous kernel of the stream drains, and
+  // touch no global memory before it has completed.  The trigger comes AFTER the wait, so a pass-2 CTA that starts
+  // early knows that everything older than this launch (lengths, window queries, K) is complete and visible.
+  pdl_wait();
+  pdl_trigger();
   const int n = a.consider_len[b];
   // chunks are sized by the LONGEST sequence of the batch: every CTA then has the same amount of work, a short
   // sequence uses fewer of its S splits (the others hand in empty partials)
@@ -274,7 +283,8 @@ __global__ void __launch_bounds__(P1Shape<G>::THREADS, 2) window_tc_pass1(const 
     return;
   }
   stage_q_block<T>(q_s, static_cast<const T*>(a.qw) + (size_t)b * a.H * a.W * kHeadDim, kvh * G, G, a.W, tid, THREADS);
-  tc_setup<P1_STAGES>(sh, tmem_cols(N), warp, EPI);
+  tc_setup_begin<P1_STAGES>(sh, tmem_cols(N), warp, EPI);
+  tc_setup_end();
   if (warp == EPI / 32) {
     if (lane == 0) {
       auto psub = [&](int j, int& row0, int& kv) { row0 = r0 + j * TC_TILE; kv = kvh; };
@@ -402,12 +412,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1) window_tc_pass2(const WinTcArgs
   const int n = a.consider_len[b];
   const int n_tiles = ceil_div(n, TC_TILE);
   const int my_tiles = loc < n_tiles ? ceil_div(n_tiles - loc, cnt) : 0;
-  if (my_tiles == 0) return;
+  // Launched as a programmatic dependent of pass 1 (or of the previous pass-2 launch): a CTA takes its SM as soon as
+  // that launch's CTAs leave it, stages its query blocks, fills its K ring and runs its first MMAs.  Only the epilogue
+  // warps read what the previous launch wrote (the partial normalisers, the plane of running maxima), and they wait
+  // for it first.  The window queries and K are older than pass 1, which triggers only after its own wait.
+  pdl_trigger();
+  if (my_tiles == 0) {
+    pdl_wait();  // a launch is complete only after its predecessor: later kernels rely on that order
+    return;
+  }
   const int n_sub = my_tiles * n_kvh;
   const T* qb = static_cast<const T*>(a.qw) + (size_t)b * a.H * a.W * kHeadDim;
   for (int kv = 0; kv < n_kvh; ++kv)
     stage_q_block<T>(q_s + (size_t)kv * N * 256, qb, (kvh0 + kv) * G, G, a.W, tid, TC_THREADS);
-  tc_setup<P2_STAGES>(sh, tmem_cols(N), warp, 128);
+  tc_setup_begin<P2_STAGES>(sh, tmem_cols(N), warp, 128);
+  tc_setup_end();
   auto sub = [&](int j, int& row0, int& kv) {
     row0 = (loc + (j / n_kvh) * cnt) * TC_TILE;
     kv = j % n_kvh;
@@ -422,6 +441,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) window_tc_pass2(const WinTcArgs
   } else {
     // log2 of the softmax normaliser of this launch's (head, slot) rows, from the splits of pass 1 (what a separate
     // merge kernel would do; here it runs while the first K tiles are on their way)
+    pdl_wait();
     for (int i = tid; i < n_kvh * N; i += 128) {
       const float2* pr = reinterpret_cast<const float2*>(a.part) + (((size_t)b * a.H + kvh0 * G) * TC_WPAD + i) * a.S;
       float M = -INFINITY, L = 0.f;
@@ -496,17 +516,15 @@ int launch_tc(const WinTcArgs& a, const CUtensorMap& tm_k, int max_len, cudaStre
   const int smem2 = P2_STAGES * TC_KTILE_BYTES + group * N * 256 + group * N * (int)sizeof(float) + 1024;
   OMNIKV_CUDA_OK(cudaFuncSetAttribute(window_tc_pass1<T, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1));
   OMNIKV_CUDA_OK(cudaFuncSetAttribute(window_tc_pass2<T, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
-  window_tc_pass1<T, G><<<dim3(a.S, a.KVH, a.B), P1Shape<G>::THREADS, smem1, st>>>(a, tm_k);
-  OMNIKV_CUDA_OK(cudaGetLastError());
+  OMNIKV_CUDA_OK(launch_pdl_smem_args(window_tc_pass1<T, G>, dim3(a.S, a.KVH, a.B), dim3(P1Shape<G>::THREADS), smem1, st, a, tm_k));
   const int max_tiles = ceil_div(max_len, TC_TILE);
   // one CTA per SM (the query blocks and the ring fill its shared memory), never fewer than one per sequence
   int n_ctas = a.n_sms < a.B * max_tiles ? a.n_sms : a.B * max_tiles;
   if (n_ctas < a.B) n_ctas = a.B;
   for (int kvh0 = 0; kvh0 < a.KVH; kvh0 += group) {
     const int n_kvh = a.KVH - kvh0 < group ? a.KVH - kvh0 : group;
-    window_tc_pass2<T, G><<<dim3(n_ctas), TC_THREADS, smem2, st>>>(a, tm_k, kvh0, n_kvh, kvh0 == 0 ? 1 : 0,
-                                                                        kvh0 + n_kvh >= a.KVH ? 1 : 0);
-    OMNIKV_CUDA_OK(cudaGetLastError());
+    OMNIKV_CUDA_OK(launch_pdl_smem_args(window_tc_pass2<T, G>, dim3(n_ctas), dim3(TC_THREADS), smem2, st, a, tm_k, kvh0, n_kvh,
+                                        kvh0 == 0 ? 1 : 0, kvh0 + n_kvh >= a.KVH ? 1 : 0));
   }
   return OMNIKV_OK;
 }
