@@ -69,7 +69,6 @@ struct GemvArgs {
   void* tp_h_out;                   // local [K]: CTA 0 stores the summed residual stream here
   const unsigned* tp_epoch;         // device word bumped once per decode step
   unsigned tp_seq;                  // tag = epoch * 256 + seq + 1
-  int tp_batch;                     // (vector, rank) pairs a consumer thread fetches per round trip, 1..4
   int trace_slot;                   // profiling build: which slot of the stamp array this launch writes
   int tail_pool;                    // chunks at the end of the matrix handed out dynamically (0: all static)
   int* tail_next;                   // [2] device: next index of the pool, finished producers (self-resetting)
@@ -275,7 +274,7 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
   consumer_bar();  // the previous phase no longer reads the staging area
   if (threadIdx.x == 0) GEMV_STAMP(a, 6);
   // Partial sums of other ranks are consumed by the stand-alone kernel only, and for at most 8192 activations
-  // (four vectors per thread: their sums and a batch of entries fit the register file; the host checks the size).
+  // (four vectors per thread, whose sums stay in registers; the host checks the size).
   constexpr bool TP_OK = !COHERENT && K <= kTpMaxHidden;
   const bool tp_consume = TP_OK && a.tp_world > 1 && a.tp_my_ll != nullptr;
   constexpr int NT_ = GV_CONSUMER_WARPS * 32;
@@ -291,81 +290,35 @@ __device__ __forceinline__ bool consume_phase(const GemvArgs& a, const Ring& rin
     // needs from that kernel -- the local rank's partials -- comes through the tagged entries, and whatever else
     // it reads was written by kernels that had completed before the predecessor computed a single row.
     const unsigned want = __ldcg(a.tp_epoch) * 256u + a.tp_seq + 1u;
-    // A (vector, rank) pair is four 16-byte loads = eight entries.  The thread first polls ONE 16-byte load per rank
-    // (the head of its first vector: the polling of a whole grid stays light on L2); once every rank's head has
-    // arrived the rest almost always has too, and the pairs are fetched up to TP_BATCH at a time with all loads of a
-    // batch in flight together -- one round trip to L2 per batch instead of one per pair (with eight ranks the
-    // pairs of a thread used to cost sixteen round trips in a row).  A pair of a batch that does not carry the tag
-    // yet is asked for again, together with the other late ones.
-    constexpr int TP_BATCH = 4;
-    const auto tags_ok = [want](const uint4 (&e)[4]) {
-      return e[0].y == want && e[0].w == want && e[1].y == want && e[1].w == want && e[2].y == want &&
-             e[2].w == want && e[3].y == want && e[3].w == want;
-    };
-    unsigned long long t0 = 0ull;
-    bool gave_up = false;
-    const auto out_of_time = [&](unsigned spin) {  // bounded by time: an absent rank costs kWaitNs, then the kernel reports and returns
-      if ((spin & 63u) != 63u) return false;
-      const unsigned long long now = globaltimer_ns();
-      if (t0 == 0ull) t0 = now;
-      if (now - t0 > kWaitNs || cs.fail) {
-        cs.fail = 1;
-        atomicExch(a.status, 4);
-        return true;
-      }
-      return false;
-    };
-    if (tid < K / 8 && a.tp_batch > 1) {
-      unsigned okm = 0u;
-      const unsigned all = (1u << a.tp_world) - 1u;
-      for (unsigned spin = 0;; ++spin) {
-        uint4 s0[8];
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-          if (r < a.tp_world && !((okm >> r) & 1u))
-            s0[r] = __ldcv(reinterpret_cast<const uint4*>(a.tp_my_ll + (size_t)r * K + (size_t)tid * 8));
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-          if (r < a.tp_world && !((okm >> r) & 1u) && s0[r].y == want && s0[r].w == want) okm |= 1u << r;
-        if (okm == all) break;
-        if (out_of_time(spin)) { gave_up = true; break; }
-      }
-    }
 #pragma unroll
     for (int i = 0; i < NV_; ++i) {
 #pragma unroll
       for (int e = 0; e < 8; ++e) psum[i][e] = 0.f;
       const int v = tid + i * NT_;
-      if (v >= K / 8 || gave_up) continue;
-      for (int r0 = 0; r0 < a.tp_world; r0 += a.tp_batch) {
-        uint4 e[TP_BATCH][4];
-        unsigned ok = 0u;
-        const int nb = min(a.tp_batch, a.tp_world - r0);
-        const unsigned all = (1u << nb) - 1u;
+      if (v >= K / 8) continue;
+      for (int r = 0; r < a.tp_world; ++r) {
+        const uint4* src = reinterpret_cast<const uint4*>(a.tp_my_ll + (size_t)r * K + (size_t)v * 8);
+        uint4 e0, e1, e2, e3;
+        unsigned long long t0 = 0ull;
         for (unsigned spin = 0;; ++spin) {
-#pragma unroll
-          for (int u = 0; u < TP_BATCH; ++u) {
-            if (u < nb && !((ok >> u) & 1u)) {
-              const uint4* src = reinterpret_cast<const uint4*>(a.tp_my_ll + (size_t)(r0 + u) * K + (size_t)v * 8);
-              e[u][0] = __ldcv(src); e[u][1] = __ldcv(src + 1); e[u][2] = __ldcv(src + 2); e[u][3] = __ldcv(src + 3);
+          e0 = __ldcv(src); e1 = __ldcv(src + 1); e2 = __ldcv(src + 2); e3 = __ldcv(src + 3);
+          const bool ok = e0.y == want && e0.w == want && e1.y == want && e1.w == want && e2.y == want &&
+                          e2.w == want && e3.y == want && e3.w == want;
+          if (ok) break;
+          if ((spin & 63u) == 63u) {  // bounded by time: an absent rank costs kWaitNs, then the kernel reports and returns
+            const unsigned long long now = globaltimer_ns();
+            if (t0 == 0ull) t0 = now;
+            if (now - t0 > kWaitNs || cs.fail) {
+              cs.fail = 1;
+              atomicExch(a.status, 4);
+              break;
             }
           }
-#pragma unroll
-          for (int u = 0; u < TP_BATCH; ++u)
-            if (u < nb && !((ok >> u) & 1u) && tags_ok(e[u])) ok |= 1u << u;
-          if (ok == all) break;
-          if (out_of_time(spin)) { gave_up = true; break; }
         }
-        if (gave_up) break;
-#pragma unroll
-        for (int u = 0; u < TP_BATCH; ++u) {  // in rank order: the same sums on every rank
-          if (u < nb) {
-            psum[i][0] += __uint_as_float(e[u][0].x); psum[i][1] += __uint_as_float(e[u][0].z);
-            psum[i][2] += __uint_as_float(e[u][1].x); psum[i][3] += __uint_as_float(e[u][1].z);
-            psum[i][4] += __uint_as_float(e[u][2].x); psum[i][5] += __uint_as_float(e[u][2].z);
-            psum[i][6] += __uint_as_float(e[u][3].x); psum[i][7] += __uint_as_float(e[u][3].z);
-          }
-        }
+        psum[i][0] += __uint_as_float(e0.x); psum[i][1] += __uint_as_float(e0.z);
+        psum[i][2] += __uint_as_float(e1.x); psum[i][3] += __uint_as_float(e1.z);
+        psum[i][4] += __uint_as_float(e2.x); psum[i][5] += __uint_as_float(e2.z);
+        psum[i][6] += __uint_as_float(e3.x); psum[i][7] += __uint_as_float(e3.z);
       }
     }
     consumer_bar();
@@ -886,12 +839,6 @@ int tp_fill_consumer(GemvArgs& a, const omnikv_tp_exchange* t, int k, void* h_ou
   a.tp_h_out = h_out;
   a.tp_epoch = t->epoch;
   a.tp_seq = (unsigned)t->seq;
-  static const int batch = [] {  // OMNIKV_TP_BATCH=1: one pair per round trip
-    const char* e = getenv("OMNIKV_TP_BATCH");
-    const int v = e ? atoi(e) : 4;
-    return v >= 1 && v <= 4 ? v : 4;
-  }();
-  a.tp_batch = batch;
   return OMNIKV_OK;
 }
 
