@@ -411,8 +411,9 @@ int omnikv_silu_mul(int dtype, const void* gate_up, int64_t gate_up_stride_b, vo
  * step must hold an EVEN number of them (a decoder layer has two), so that the last exchange of a step and the
  * first of the next never share a slot; *epoch is a local device word that every rank bumps once per decode
  * step (it must never repeat: tags identify an exchange for good).  All ranks must issue the same sequence of
- * calls.  world <= 8.  NULL or world <= 1: no exchange.  The wait for the peers' entries gives up after two
- * seconds (status 4). */
+ * calls.  world <= 8.  NULL or world <= 1: no exchange.  A consumer takes a residual stream of at most 8192
+ * values (OMNIKV_E_UNSUPPORTED above that).  The wait for the peers' entries gives up after two seconds
+ * (status 4). */
 typedef struct {
   int32_t world, rank;
   void* peer_base[8];
