@@ -5,6 +5,11 @@
 // the keys resident in shared memory (the scores are read from L2/HBM exactly once); the four
 // 8-bit digit histograms are built with warp-aggregated shared-memory atomics and summed across
 // the cluster through distributed shared memory.  Integer atomics only: the result is deterministic.
+//
+// This kernel never lets its successor be scheduled early (no griddepcontrol.launch_dependents, although most SMs
+// are idle while one cluster selects): the decode attention kernels read the index list and its count BEFORE their
+// own dependent-launch wait, which is only sound because the kernel right behind the selector cannot start -- and
+// so cannot let its own successors start -- before the selector has completed.
 #include <cooperative_groups.h>
 
 #include <stdlib.h>
