@@ -277,7 +277,7 @@ extern "C" int omnikv_topk(const float* scores, int n_planes, int64_t plane_stri
             (n_planes == 1 || plane_stride % 4 == 0) && (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15) == 0) &&
             max_len % 4 == 0) ? 1 : 0;
 
-  // Slices of at most 8192 keys per CTA; a cluster of 16 (above the portable limit of 8) when the device can
+  // Slices of at most 8192 keys per CTA (1024 for a single sequence); a cluster of 16 (above the portable limit of 8) when the device can
   // co-schedule one, since the load of the score planes and every histogram pass scale with the CTA count.
   static const int max_cluster = [] {
     const char* e = getenv("OMNIKV_TOPK_CLUSTER");
@@ -290,7 +290,10 @@ extern "C" int omnikv_topk(const float* scores, int n_planes, int64_t plane_stri
   int csize = 1;
   for (int limit = max_cluster;; limit = 8) {
     csize = 1;
-    while (csize < limit && ceil_div(max_len, csize) > 8192) csize *= 2;
+    // a single sequence leaves the other SMs idle anyway: slices down to 1024 keys (every phase is a latency chain
+    // whose length goes with the slice); a batch keeps 8192 keys per CTA so that its clusters fit the device together
+    const int slice_keys = B == 1 ? 1024 : 8192;
+    while (csize < limit && ceil_div(max_len, csize) > slice_keys) csize *= 2;
     const int slice = ceil_div(ceil_div(max_len, csize), 4) * 4;
     const bool resident = slice <= TK_RESIDENT_KEYS;
     if (!resident && (!workspace || workspace_bytes < omnikv_topk_workspace_bytes(B, max_len))) return OMNIKV_E_WORKSPACE;
