@@ -194,3 +194,23 @@ def test_rope_parameters_match_reference():
         np.testing.assert_allclose(emb.inv_freq.numpy(), gold[f"dynamic_seq/{i}/inv_freq"], rtol=2e-6, atol=0, err_msg=str(i))
         cos, _ = emb(torch.zeros(1, dtype=torch.float32), pos)
         np.testing.assert_allclose(cos[0, -1].numpy(), gold[f"dynamic_seq/{i}/cos_last"], atol=2e-4, rtol=0)
+
+
+def test_attention_split_counts_on_a_148_sm_device(monkeypatch):
+    """The split-count model of decode attention (host logic): bounds and the cases it was tuned on."""
+    from omnikv_b200 import ops
+    monkeypatch.setattr(ops, "sm_count", lambda device: 148)
+    dev = torch.device("cpu")
+    # one sequence: two CTAs per SM, never more splits than SMs
+    assert ops.default_splits(1, 8, 131073, dev) == 37
+    assert ops.default_splits(1, 2, 131073, dev) == 148
+    assert ops.default_splits(1, 1, 131073, dev) == 148
+    # the selected rows of a batch's sparse layers: few splits (fixed cost per CTA), more when the batch is small
+    assert ops.default_splits(16, 8, 2112, dev) == 2
+    assert ops.default_splits(8, 1, 4391, dev) > ops.default_splits(16, 8, 2112, dev)
+    # ragged long batches: two waves of equal CTAs
+    assert ops.default_splits(16, 8, 32832, dev) == 5
+    # never below one, never less than 128 rows per split
+    for B, KVH, rows in [(1, 8, 1), (1, 8, 100), (1, 8, 300), (4, 8, 200), (64, 8, 129), (3, 1, 7000)]:
+        s = ops.default_splits(B, KVH, rows, dev)
+        assert 1 <= s <= max(1, (rows + 127) // 128), (B, KVH, rows, s)
