@@ -177,6 +177,19 @@ def test_topk_ties_planes_append_and_specials():
     assert torch.equal(idx[2, :100].cpu().long(), torch.arange(100))
 
 
+@pytest.mark.parametrize("L", [1000, 1025, 2500, 5000, 9000, 16384, 16385, 60000])
+def test_topk_single_sequence_cluster_sizes(L):
+    """One sequence gets slices of 1024 keys: clusters of 1, 2, 4, 8 and 16 CTAs, with heavy ties across the slices."""
+    g = torch.Generator().manual_seed(100 + L)
+    planes = (torch.randn(2, 1, L, generator=g) * 2).round() / 2
+    s = planes.max(dim=0).values
+    for n, k, app in ([L, max(1, int(0.067 * L)), 0], [L - 1, L - 1, 2], [L, 1, 0], [max(1, L - 517), 700, 5]):
+        idx = torch.full((1, L + 16), -1, dtype=torch.int32, device="cuda")
+        idx, cnt = ops().topk(planes.cuda(), dev_i32([n]), dev_i32([k]), append_n=dev_i32([app]), idx_out=idx, max_len=L)
+        torch.cuda.synchronize()
+        _check_topk(s, [n], [k], idx, cnt, [app])
+
+
 def test_topk_nan_ranks_first():
     s = torch.randn(1, 1000)
     s[0, 123] = float("nan")
